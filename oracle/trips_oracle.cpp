@@ -1,0 +1,675 @@
+// CPU oracle for the TRIPS trilinear point-splatting hot path.  TEST INFRASTRUCTURE ONLY -- see trips_oracle.h.
+// PARITY UNPINNED: no reference fixture exists for this path; pinned by known-answer and finite-difference tests.
+//
+// Build: g++ -O3 -fopenmp -ffp-contract=off -shared -fPIC (see oracle/Makefile).  -ffp-contract=off is required:
+// together with nvcc -fmad=false it makes every fp32 expression below round exactly like the CUDA kernels.
+#include "trips_oracle.h"
+
+#include <algorithm>
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <vector>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+#include "../trips_b200/csrc/trips_math.h"  // reproducible exp / log shared with the kernels
+
+namespace
+{
+constexpr int kMaxLayers   = 8;   // RenderConstants.h:38
+constexpr int kMaxKeep     = 16;  // PointRenderer.h:178
+constexpr float kAlphaCut  = 0.001f;  // ALPHA_DEST_CUTOFF, RenderForward.cu:907
+
+struct Pose
+{
+    float qx, qy, qz, qw, tx, ty, tz;
+    float R[9];  // row-major rotation matrix of the quaternion
+};
+
+// DeviceRenderParams::Pose casts the stored SE3d to float (RenderConstants.h:85-88).
+Pose make_pose(const double* p)
+{
+    Pose o;
+    o.qx = (float)p[0];
+    o.qy = (float)p[1];
+    o.qz = (float)p[2];
+    o.qw = (float)p[3];
+    o.tx = (float)p[4];
+    o.ty = (float)p[5];
+    o.tz = (float)p[6];
+    // Eigen::Quaternion::toRotationMatrix
+    float tx = 2.f * o.qx, ty = 2.f * o.qy, tz = 2.f * o.qz;
+    float twx = tx * o.qw, twy = ty * o.qw, twz = tz * o.qw;
+    float txx = tx * o.qx, txy = ty * o.qx, txz = tz * o.qx;
+    float tyy = ty * o.qy, tyz = tz * o.qy, tzz = tz * o.qz;
+    o.R[0] = 1.f - (tyy + tzz);
+    o.R[1] = txy - twz;
+    o.R[2] = txz + twy;
+    o.R[3] = txy + twz;
+    o.R[4] = 1.f - (txx + tzz);
+    o.R[5] = tyz - twx;
+    o.R[6] = txz - twy;
+    o.R[7] = tyz + twx;
+    o.R[8] = 1.f - (txx + tyy);
+    return o;
+}
+
+// Sophus SE3f * point = quaternion rotation (Eigen _transformVector) + translation.
+inline void transform_point(const Pose& V, const float* p, float* out)
+{
+    float ux = V.qy * p[2] - V.qz * p[1];
+    float uy = V.qz * p[0] - V.qx * p[2];
+    float uz = V.qx * p[1] - V.qy * p[0];
+    ux += ux;
+    uy += uy;
+    uz += uz;
+    float cx = V.qy * uz - V.qz * uy;
+    float cy = V.qz * ux - V.qx * uz;
+    float cz = V.qx * uy - V.qy * ux;
+    out[0]   = ((p[0] + V.qw * ux) + cx) + V.tx;
+    out[1]   = ((p[1] + V.qw * uy) + cy) + V.ty;
+    out[2]   = ((p[2] + V.qw * uz) + cz) + V.tz;
+}
+
+struct Cam
+{
+    Pose V;
+    float fx, fy, cx, cy, s;         // K
+    float cfx, cfy, ccx, ccy, cs;    // crop transform
+    float r00, r01, r10, r11;        // crop rotation
+    float cenx, ceny;                // (w/2, h/2) with integer division, RenderForward.cu:303
+    int w, h;
+};
+
+Cam make_cam(const OrView* v)
+{
+    Cam c;
+    c.V   = make_pose(v->pose);
+    c.fx  = v->intrinsics[0];
+    c.fy  = v->intrinsics[1];
+    c.cx  = v->intrinsics[2];
+    c.cy  = v->intrinsics[3];
+    c.s   = v->intrinsics[4];
+    c.cfx = v->crop_transform[0];
+    c.cfy = v->crop_transform[1];
+    c.ccx = v->crop_transform[2];
+    c.ccy = v->crop_transform[3];
+    c.cs  = v->crop_transform[4];
+    c.r00 = v->crop_rotation[0];
+    c.r01 = v->crop_rotation[1];
+    c.r10 = v->crop_rotation[2];
+    c.r11 = v->crop_rotation[3];
+    c.w   = v->w;
+    c.h   = v->h;
+    c.cenx = (float)(v->w / 2);
+    c.ceny = (float)(v->h / 2);
+    return c;
+}
+
+// ProjectPointPinholeWoNormal (PointRendererHelper.h:232-253) with zero distortion, followed by the crop
+// transform and crop rotation of CountAndCollectTiled (RenderForward.cu:302-303, 69-76).
+inline void project(const Cam& c, const float* p, float& u, float& v, float& z)
+{
+    float pv[3];
+    transform_point(c.V, p, pv);
+    z        = std::fmax(pv[2], 0.f);
+    float iz = 1.f / pv[2];
+    float nx = pv[0] * iz;
+    float ny = pv[1] * iz;
+    // K.normalizedToImage
+    float ix = (c.fx * nx + c.s * ny) + c.cx;
+    float iy = c.fy * ny + c.cy;
+    // crop_transform.normalizedToImage
+    float jx = (c.cfx * ix + c.cs * iy) + c.ccx;
+    float jy = c.cfy * iy + c.ccy;
+    // rotateCropAroundCenter
+    float dx = jx - c.cenx;
+    float dy = jy - c.ceny;
+    float rx = c.r00 * dx + c.r01 * dy;
+    float ry = c.r10 * dx + c.r11 * dy;
+    u        = rx + c.cenx;
+    v        = ry + c.ceny;
+}
+
+// compute_point_size_fac (PointBlending.h:81-149).  floor/ceil of log2 are taken exactly from the float's bits.
+inline float layer_factor(float ps, int layer, int L, float* grad)
+{
+    int lo = 0, hi = 0;
+    if (ps > 1.f)
+    {
+        lo = std::min(std::max(0, tm_floor_log2(ps)), L - 1);
+        hi = std::min(std::max(0, tm_ceil_log2(ps)), L - 1);
+    }
+    if (layer < lo)
+    {
+        if (grad) *grad = 0.f;
+        return 1.f;
+    }
+    float f = 1.f;
+    if (hi == 0)
+    {
+        f = 0.75f * tm_expf(ps - 1.f) + 0.25f;
+        if (grad) *grad = 0.27591f * ps;
+    }
+    else if (lo == hi)
+    {
+        if (grad) *grad = 1.f;
+    }
+    else
+    {
+        float l_l = (float)(1 << lo);
+        float l_h = (float)(1 << hi);
+        f         = (ps - l_l) / (l_h - l_l);
+        if (layer == lo) f = 1.f - f;
+        if (grad)
+        {
+            float J = 1.f / (l_h - l_l);
+            if (layer == lo) J = -J;
+            *grad = J;
+        }
+    }
+    return f;
+}
+}  // namespace
+
+struct OrFrame
+{
+    int N = 0, C = 0, L = 0, K = 0, train = 0;
+    int W[kMaxLayers], H[kMaxLayers];
+    int64_t base[kMaxLayers + 1];
+    int64_t P = 0, F = 0, Kf = 0, V = 0;
+    std::vector<float> depth;
+    std::vector<int32_t> nlayers;
+    std::vector<float> rec;  // [N,4]
+    std::vector<int32_t> counts;
+    std::vector<int64_t> offsets;
+    std::vector<uint64_t> frags;
+    std::vector<float> pyramid;
+    std::vector<int32_t> nrec;
+    std::vector<int32_t> rec_pid;
+    std::vector<float> rec_alpha;
+};
+
+extern "C" {
+
+int or_max_threads(void)
+{
+#ifdef _OPENMP
+    return omp_get_max_threads();
+#else
+    return 1;
+#endif
+}
+
+float or_layer_factor(float ps, int layer, int num_layers, float* grad) { return layer_factor(ps, layer, num_layers, grad); }
+float or_softplus(float x) { return tm_softplus(x); }
+float or_expf(float x) { return tm_expf(x); }
+float or_logf(float x) { return tm_logf(x); }
+void or_project(const OrView* view, const float* p3, float* u, float* v, float* z)
+{
+    Cam c = make_cam(view);
+    project(c, p3, *u, *v, *z);
+}
+
+OrFrame* or_forward(const OrScene* sc, const OrView* view, const OrParams* pr)
+{
+    OrFrame* f = new OrFrame();
+    const int N = sc->n_points, C = sc->channels, L = pr->num_layers, K = pr->k_keep;
+    if (L < 1 || L > kMaxLayers || K < 1 || K > kMaxKeep)
+    {
+        delete f;
+        return nullptr;
+    }
+    f->N = N;
+    f->C = C;
+    f->L = L;
+    f->K = K;
+    f->train = pr->train;
+    // layer sizes: ceil halving (PointRenderer.cu:385-389)
+    {
+        int w = view->w, h = view->h;
+        int64_t b = 0;
+        for (int l = 0; l < L; ++l)
+        {
+            f->W[l]    = w;
+            f->H[l]    = h;
+            f->base[l] = b;
+            b += (int64_t)w * h;
+            h = (int)std::ceil((float)h / 2.f);
+            w = (int)std::ceil((float)w / 2.f);
+        }
+        f->base[L] = b;
+        f->P       = b;
+    }
+    const Cam cam = make_cam(view);
+    f->depth.assign(N, -1.f);
+    f->nlayers.assign(N, 0);
+    f->rec.assign((size_t)N * 4, 0.f);
+    f->counts.assign(f->P, 0);
+
+    const float fxc = cam.fx * cam.cfx;
+    int32_t* counts = f->counts.data();
+
+    // ---- A1: project, cull, select layers, count (CountAndCollectTiled, RenderForward.cu:168-366) ----
+    int64_t visible = 0;
+#pragma omp parallel for schedule(static) reduction(+ : visible)
+    for (int i = 0; i < N; ++i)
+    {
+        int tex = sc->index ? sc->index[i] : i;
+        if (pr->viewer_only)
+        {
+            if (sc->confidence[tex] < pr->stability_cutoff_value) continue;  // discard_point_for_confidence
+        }
+        else if (pr->train && sc->dropout)
+        {
+            if (sc->dropout[i] == 1.f) continue;
+        }
+        float s = tm_softplus(sc->point_size[i]);
+        float u, v, z;
+        project(cam, sc->position + (size_t)i * 4, u, v, z);
+        float radius_px = fxc * sc->position[(size_t)i * 4 + 3] / z;
+        float ps        = fxc * s / z;
+        auto dropped    = [&](float rad) {
+            return pr->drop_out_points_by_radius && (float)(int)rad < pr->drop_out_radius_threshold;
+        };
+        if (z <= 0.f || u < 0.f || u >= (float)(f->W[0] - 1) || v < 0.f || v >= (float)(f->H[0] - 1)) continue;
+        if (dropped(radius_px)) continue;
+        f->depth[i]               = z;
+        f->rec[(size_t)i * 4 + 0] = u;
+        f->rec[(size_t)i * 4 + 1] = v;
+        f->rec[(size_t)i * 4 + 2] = ps;
+        f->rec[(size_t)i * 4 + 3] = tm_bits_to_float((uint32_t)tex);
+        int hi = 0;
+        if (ps > 1.f) hi = std::min(tm_ceil_log2(ps), L - 1);
+        int layer = 0;
+        float x = u, y = v, rad = radius_px;
+        for (; layer < hi + 1; ++layer, x *= 0.5f, y *= 0.5f, rad *= 0.5f)
+        {
+            int px = (int)std::floor(x), py = (int)std::floor(y);
+            if (px < 0 || px >= f->W[layer] - 1 || py < 0 || py >= f->H[layer] - 1 || dropped(rad)) break;
+            for (int k = 0; k < 4; ++k)
+            {
+                int64_t pix = f->base[layer] + (int64_t)(py + k / 2) * f->W[layer] + (px + k % 2);
+#pragma omp atomic
+                counts[pix]++;
+            }
+        }
+        f->nlayers[i] = layer;
+        visible++;
+    }
+    f->V = visible;
+
+    // ---- A2: exclusive scan over the whole pyramid (RenderForward.cu:1155-1232) ----
+    f->offsets.resize(f->P);
+    {
+        int64_t run = 0;
+        for (int64_t p = 0; p < f->P; ++p)
+        {
+            f->offsets[p] = run;
+            run += counts[p];
+        }
+        f->F = run;
+    }
+    f->frags.resize(f->F);
+    // ---- collect (SplattingPass, RenderForward.cu:368-436) ----
+    {
+        std::vector<int32_t> cursor(f->P, 0);
+        int32_t* cur = cursor.data();
+#pragma omp parallel for schedule(static)
+        for (int i = 0; i < N; ++i)
+        {
+            float z = f->depth[i];
+            if (!(z > 0.f)) continue;
+            uint64_t key = ((uint64_t)tm_float_to_bits(z) << 32) | (uint32_t)i;
+            float x = f->rec[(size_t)i * 4 + 0], y = f->rec[(size_t)i * 4 + 1];
+            for (int layer = 0; layer < f->nlayers[i]; ++layer, x *= 0.5f, y *= 0.5f)
+            {
+                int px = (int)std::floor(x), py = (int)std::floor(y);
+                for (int k = 0; k < 4; ++k)
+                {
+                    int64_t pix = f->base[layer] + (int64_t)(py + k / 2) * f->W[layer] + (px + k % 2);
+                    int32_t slot;
+#pragma omp atomic capture
+                    slot = cur[pix]++;
+                    f->frags[f->offsets[pix] + slot] = key;
+                }
+            }
+        }
+    }
+    // list order is unspecified in the reference (slot = atomicAdd result); the oracle stores every list
+    // sorted by the 64-bit key (depth bits, then point id).
+#pragma omp parallel for schedule(dynamic, 4096)
+    for (int64_t p = 0; p < f->P; ++p)
+    {
+        if (counts[p] > 1) std::sort(f->frags.begin() + f->offsets[p], f->frags.begin() + f->offsets[p] + counts[p]);
+    }
+
+    // ---- A3: top-K + front-to-back blend (FastSortFusedNew, RenderForward.cu:474-1059) ----
+    f->pyramid.assign((size_t)C * f->P, 0.f);
+    f->nrec.assign(f->P, 0);
+    if (pr->train)
+    {
+        f->rec_pid.assign((size_t)f->P * kMaxKeep, -1);
+        f->rec_alpha.assign((size_t)f->P * kMaxKeep, -1.f);
+    }
+    int64_t kept = 0;
+#pragma omp parallel for schedule(dynamic, 1024) reduction(+ : kept)
+    for (int64_t p = 0; p < f->P; ++p)
+    {
+        int layer = 0;
+        while (p >= f->base[layer + 1]) ++layer;
+        int64_t t = p - f->base[layer];
+        int gx = (int)(t % f->W[layer]), gy = (int)(t / f->W[layer]);
+        int n = std::min(counts[p], K);
+        kept += n;
+        float alpha[kMaxKeep], T[kMaxKeep];
+        float contrib[kMaxKeep][16];
+        int tex[kMaxKeep], pid[kMaxKeep];
+        const float fac = 1.f / (float)(1 << layer);
+        for (int j = 0; j < n; ++j)
+        {
+            uint64_t key = f->frags[f->offsets[p] + j];
+            int i        = (int)(uint32_t)(key & 0xffffffffu);
+            pid[j]       = i;
+            float u = f->rec[(size_t)i * 4 + 0], v = f->rec[(size_t)i * 4 + 1], ps = f->rec[(size_t)i * 4 + 2];
+            tex[j]   = (int)tm_float_to_bits(f->rec[(size_t)i * 4 + 3]);
+            float ux = u * fac, uy = v * fac;
+            float b  = (1.f - std::fabs(ux - (float)gx)) * (1.f - std::fabs(uy - (float)gy));
+            if (std::fabs(ux - (float)gx) > 1.f || std::fabs(uy - (float)gy) > 1.f) b = 0.f;
+            float a = b * sc->confidence[tex[j]];
+            a *= layer_factor(ps, layer, L, nullptr);
+            alpha[j] = a;
+        }
+        // transmittance chain: T_j = T_{j-1} * (1 - alpha_{j-1}); reported as 0 below the cut-off
+        float run = 1.f;
+        for (int j = 0; j < n; ++j)
+        {
+            if (j > 0) run = run * (1.f - alpha[j - 1]);
+            T[j] = (j == 0 || run >= kAlphaCut) ? run : 0.f;
+        }
+        for (int j = 0; j < kMaxKeep; ++j)
+            for (int c = 0; c < C; ++c) contrib[j][c] = (j < n) ? T[j] * alpha[j] * sc->texture[(size_t)c * sc->n_tex + tex[j]] : 0.f;
+        // butterfly sum over 16 lanes (xor shuffle with offsets 1,2,4,8, RenderForward.cu:983-994)
+        for (int off = 1; off < kMaxKeep; off *= 2)
+            for (int j = 0; j < kMaxKeep; j += 2 * off)
+                for (int c = 0; c < C; ++c) contrib[j][c] = contrib[j][c] + contrib[j + off][c];
+        float wb;
+        if (n == 0)
+            wb = 1.f;  // the reference reads a neighbouring lane here; defined as pure background
+        else if (pr->bg_uses_Tn)
+        {
+            float tn = run * (1.f - alpha[n - 1]);
+            wb       = (T[n - 1] >= kAlphaCut && tn >= kAlphaCut) ? tn : 0.f;
+        }
+        else
+            wb = T[n - 1];
+        for (int c = 0; c < C; ++c)
+        {
+            float o = contrib[0][c];
+            if (wb >= kAlphaCut) o += sc->background[c] * (wb * 1.f);
+            f->pyramid[(size_t)C * f->base[layer] + ((size_t)c * f->H[layer] + gy) * f->W[layer] + gx] = o;
+        }
+        if (pr->train)
+        {
+            int m = 0;
+            for (int j = 0; j < n; ++j)
+            {
+                if (T[j] >= kAlphaCut)
+                {
+                    f->rec_pid[(size_t)p * kMaxKeep + j]   = pid[j];
+                    f->rec_alpha[(size_t)p * kMaxKeep + j] = alpha[j];
+                    m = j + 1;
+                }
+            }
+            f->nrec[p] = m;
+        }
+    }
+    f->Kf = kept;
+    return f;
+}
+
+void or_frame_free(OrFrame* f) { delete f; }
+int64_t or_num_pixels(const OrFrame* f) { return f->P; }
+int64_t or_num_fragments(const OrFrame* f) { return f->F; }
+int64_t or_num_kept(const OrFrame* f) { return f->Kf; }
+int64_t or_num_visible(const OrFrame* f) { return f->V; }
+void or_layer_size(const OrFrame* f, int layer, int* w, int* h, int64_t* base)
+{
+    if (w) *w = f->W[layer];
+    if (h) *h = f->H[layer];
+    if (base) *base = f->base[layer];
+}
+
+void or_get_points(const OrFrame* f, float* depth, int32_t* nlayers, float* rec)
+{
+    if (depth) memcpy(depth, f->depth.data(), sizeof(float) * f->N);
+    if (nlayers) memcpy(nlayers, f->nlayers.data(), sizeof(int32_t) * f->N);
+    if (rec) memcpy(rec, f->rec.data(), sizeof(float) * 4 * f->N);
+}
+void or_get_lists(const OrFrame* f, int32_t* counts, int64_t* offsets, uint64_t* frags)
+{
+    if (counts) memcpy(counts, f->counts.data(), sizeof(int32_t) * f->P);
+    if (offsets) memcpy(offsets, f->offsets.data(), sizeof(int64_t) * f->P);
+    if (frags) memcpy(frags, f->frags.data(), sizeof(uint64_t) * f->F);
+}
+void or_get_pyramid(const OrFrame* f, float* out) { memcpy(out, f->pyramid.data(), sizeof(float) * f->pyramid.size()); }
+void or_get_records(const OrFrame* f, int32_t* nrec, int32_t* rec_pid, float* rec_alpha)
+{
+    if (nrec) memcpy(nrec, f->nrec.data(), sizeof(int32_t) * f->P);
+    if (rec_pid && !f->rec_pid.empty()) memcpy(rec_pid, f->rec_pid.data(), sizeof(int32_t) * f->rec_pid.size());
+    if (rec_alpha && !f->rec_alpha.empty()) memcpy(rec_alpha, f->rec_alpha.data(), sizeof(float) * f->rec_alpha.size());
+}
+
+// ---- A4: backward (BlendBackwardsBilinearTiled, RenderBackward.cu:90-618) ----
+// Ticket -> pixel uses the ceil-halved layer sizes of the forward pass (the reference halves with floor here,
+// RenderBackward.cu:112-130, which skips rows of odd-sized layers; that is treated as a defect, not followed).
+void or_backward(const OrFrame* f, const OrScene* sc, const OrView* view, const OrParams* pr, const float* grad_pyramid,
+                 double* g_texture, double* g_confidence, double* g_position, double* g_point_size,
+                 double* g_background, double* g_pose, double* g_intrinsics)
+{
+    const int C = f->C, L = f->L, K = f->K;
+    const Cam cam   = make_cam(view);
+    const float fxc = cam.fx * cam.cfx;
+    std::vector<double> bg_acc(C, 0.0);
+    double pose_acc[6] = {0, 0, 0, 0, 0, 0};
+    double k_acc[5]    = {0, 0, 0, 0, 0};
+#pragma omp parallel
+    {
+        std::vector<double> bg_local(C, 0.0);
+        double pose_local[6] = {0, 0, 0, 0, 0, 0};
+        double k_local[5]    = {0, 0, 0, 0, 0};
+#pragma omp for schedule(dynamic, 1024)
+        for (int64_t p = 0; p < f->P; ++p)
+        {
+            int layer = 0;
+            while (p >= f->base[layer + 1]) ++layer;
+            int64_t t = p - f->base[layer];
+            int gx = (int)(t % f->W[layer]), gy = (int)(t / f->W[layer]);
+            float g_in[16];
+            for (int c = 0; c < C; ++c)
+                g_in[c] = grad_pyramid[(size_t)C * f->base[layer] + ((size_t)c * f->H[layer] + gy) * f->W[layer] + gx];
+            const int32_t* rpid  = &f->rec_pid[(size_t)p * kMaxKeep];
+            const float* ralpha  = &f->rec_alpha[(size_t)p * kMaxKeep];
+            float conf_grad[kMaxKeep];
+            int texs[kMaxKeep];
+            for (int j = 0; j < kMaxKeep; ++j) conf_grad[j] = 0.f;
+            int idx          = 0;
+            float alpha_dest = 1.f;
+            do
+            {
+                bool fg         = true;
+                float alpha_val = (idx >= K) ? -1.f : ralpha[idx];
+                if (alpha_val == -1.f)
+                {
+                    fg        = false;
+                    alpha_val = 1.f;
+                }
+                int tex = 0;
+                if (fg)
+                {
+                    int pid   = rpid[idx];
+                    tex       = sc->index ? sc->index[pid] : pid;
+                    texs[idx] = tex;
+                }
+                float colors[16];
+                for (int c = 0; c < C; ++c) colors[c] = fg ? sc->texture[(size_t)c * sc->n_tex + tex] : sc->background[c];
+                float g_alpha = 0.f;
+                for (int c = 0; c < C; ++c)
+                {
+                    float g = alpha_dest * alpha_val * g_in[c];
+                    if (fg)
+                    {
+#pragma omp atomic
+                        g_texture[(size_t)c * sc->n_tex + tex] += (double)g;
+                    }
+                    else
+                        bg_local[c] += (double)g;
+                    g_alpha += colors[c] * g_in[c];
+                }
+                g_alpha *= alpha_dest;
+                if (fg) conf_grad[idx] += g_alpha;
+                for (int j = 0; j < idx; ++j)
+                {
+                    float a_j    = ralpha[j];
+                    float g_iter = 0.f;
+                    for (int c = 0; c < C; ++c)
+                    {
+                        const float epsilon = 1e-9f;
+                        float dem           = 1.f / (1.f - a_j + epsilon);
+                        float g_a           = (g_in[c] * colors[c] * alpha_dest * alpha_val * dem);
+                        g_iter -= g_a;
+                    }
+                    conf_grad[j] += g_iter;
+                }
+                alpha_dest = (1.f - alpha_val) * alpha_dest;
+                if (!fg) break;
+                ++idx;
+            } while (idx < K + 1 && alpha_dest >= kAlphaCut);
+
+            for (int i = 0; i < idx; ++i)
+            {
+                int pid = rpid[i];
+                int tex = texs[i];
+                // the forward pass stored uv = ip * 2^-layer, the corner index and ps (RenderForward.cu:957-979);
+                // they are recomputed here from the per-point record with the same arithmetic.
+                const float fac = 1.f / (float)(1 << layer);
+                float ux = f->rec[(size_t)pid * 4 + 0] * fac, uy = f->rec[(size_t)pid * 4 + 1] * fac;
+                float ps = f->rec[(size_t)pid * 4 + 2];
+                int q    = ((float)gx < ux ? 0 : 1) + ((float)gy < uy ? 0 : 2);  // blend_fac_index
+                float ga = conf_grad[i];
+                // compute_blending_fac (PointBlending.h:216-257)
+                float sx = ux - std::floor(ux), sy = uy - std::floor(uy);
+                float bf[4]   = {(1.f - sx) * (1.f - sy), sx * (1.f - sy), (1.f - sx) * sy, sx * sy};
+                float J[4][2] = {{sy - 1.f, sx - 1.f}, {1.f - sy, -sx}, {-sy, 1.f - sx}, {sy, sx}};
+                if (std::fabs(ux - (float)gx) > 1.f || std::fabs(uy - (float)gy) > 1.f)
+                    for (int k = 0; k < 4; ++k) bf[k] *= 0.f;
+                float conf = sc->confidence[tex];
+                float lf_grad = 0.f;
+                float lf      = layer_factor(ps, layer, L, &lf_grad);
+                float g_conf  = bf[q] * lf * ga;
+#pragma omp atomic
+                g_confidence[tex] += (double)g_conf;
+                float gbs   = conf * lf * ga;
+                float grad0 = J[q][0] * gbs, grad1 = J[q][1] * gbs;  // dR_dp = J_uv^T * e_q * gbs
+
+                // ProjectPointPinholeBackward (PointRendererHelper.h:434-494), zero distortion
+                const float* pos = sc->position + (size_t)pid * 4;
+                float pv[3];
+                transform_point(cam.V, pos, pv);
+                float z = pv[2];
+                if (z <= 0.f) continue;
+                float g_layer_proj = fxc / z;
+                float iz = 1.f / z;
+                float nx = pv[0] * iz, ny = pv[1] * iz;
+                // crop rotation^T, crop transform^T, K^T
+                float gr0 = cam.r00 * grad0 + cam.r10 * grad1;
+                float gr1 = cam.r01 * grad0 + cam.r11 * grad1;
+                float gk0 = cam.cfx * gr0;               // J_p_K2^T = [[cfx,0],[cs,cfy]]
+                float gk1 = cam.cs * gr0 + cam.cfy * gr1;
+                float gn0 = cam.fx * gk0;                // J_p_K1^T = [[fx,0],[s,fy]]
+                float gn1 = cam.s * gk0 + cam.fy * gk1;
+                // DivideByZ^T
+                float gv0 = iz * gn0;
+                float gv1 = iz * gn1;
+                float gv2 = (-pv[0] * iz * iz) * gn0 + (-pv[1] * iz * iz) * gn1;
+                // J_point^T = R^T
+                const float* R = cam.V.R;
+                float gp0 = R[0] * gv0 + R[3] * gv1 + R[6] * gv2;
+                float gp1 = R[1] * gv0 + R[4] * gv1 + R[7] * gv2;
+                float gp2 = R[2] * gv0 + R[5] * gv1 + R[8] * gv2;
+                if (g_point_size)
+                {
+                    float J_sp = tm_softplus_grad(sc->point_size[pid]);
+                    float glp  = J_sp * g_layer_proj * lf_grad * ga;
+                    float gl   = bf[q] * conf * glp;
+#pragma omp atomic
+                    g_point_size[pid] += (double)gl;
+                }
+                if (g_position)
+                {
+#pragma omp atomic
+                    g_position[(size_t)pid * 4 + 0] += (double)gp0;
+#pragma omp atomic
+                    g_position[(size_t)pid * 4 + 1] += (double)gp1;
+#pragma omp atomic
+                    g_position[(size_t)pid * 4 + 2] += (double)gp2;
+                }
+                // pose tangent: J_pose = [I | -skew(pv)]  ->  g = (gv, pv x gv)
+                pose_local[0] += gv0;
+                pose_local[1] += gv1;
+                pose_local[2] += gv2;
+                pose_local[3] += (double)(pv[1] * gv2 - pv[2] * gv1);
+                pose_local[4] += (double)(pv[2] * gv0 - pv[0] * gv2);
+                pose_local[5] += (double)(pv[0] * gv1 - pv[1] * gv0);
+                // K: d(ix,iy)/d(fx,fy,cx,cy,s) = [[nx,0,1,0,ny],[0,ny,0,1,0]]
+                k_local[0] += (double)(nx * gk0);
+                k_local[1] += (double)(ny * gk1);
+                k_local[2] += (double)gk0;
+                k_local[3] += (double)gk1;
+                k_local[4] += (double)(ny * gk0);
+            }
+        }
+#pragma omp critical
+        {
+            for (int c = 0; c < C; ++c) bg_acc[c] += bg_local[c];
+            for (int k = 0; k < 6; ++k) pose_acc[k] += pose_local[k];
+            for (int k = 0; k < 5; ++k) k_acc[k] += k_local[k];
+        }
+    }
+    if (g_background)
+        for (int c = 0; c < C; ++c) g_background[c] += bg_acc[c];
+    if (g_pose)
+        for (int k = 0; k < 6; ++k) g_pose[k] += pose_acc[k];
+    if (g_intrinsics)
+        for (int k = 0; k < 5; ++k) g_intrinsics[k] += k_acc[k];
+    (void)pr;
+}
+
+// ---- A5: Adam (adam_step, MyAdam.cu:41-88) ----
+void or_adam(int64_t n, float* w, const float* g, float* m, float* v, int64_t* steps, float lr, float beta1, float beta2,
+             float eps, float rel_decay, float abs_decay, float clip, float lower_lr, float upper_lr)
+{
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < n; ++i)
+    {
+        float gradient = g[i] / 1.f;
+        float weight   = w[i];
+        if (gradient == 0.f) continue;
+        float gsq = gradient * gradient;
+        float fm = m[i] = beta1 * m[i] + (1.f - beta1) * gradient;
+        float sm = v[i] = beta2 * v[i] + (1.f - beta2) * gsq;
+        steps[i]        = steps[i] + 1;
+        uint32_t step   = (uint32_t)steps[i];
+        float lr_t      = lr * (std::sqrt(1.f - std::pow(beta2, (float)step)) / (1.f - std::pow(beta1, (float)step)));
+        float eff       = std::fmin(std::fmax(lr_t / (std::sqrt(sm) + eps), lower_lr), upper_lr);
+        float decayed   = (1.f - rel_decay * lr_t) * weight - std::copysign(abs_decay * lr_t, weight);
+        float nw        = decayed - eff * fm;
+        if (clip != 0.f) nw = nw < -clip ? -clip : (clip < nw ? clip : nw);
+        w[i] = nw;
+    }
+}
+
+}  // extern "C"

@@ -1,0 +1,92 @@
+/* CPU oracle for the TRIPS trilinear point-splatting hot path.  TEST INFRASTRUCTURE ONLY.
+ *
+ * This is a plain C++17 / OpenMP restatement of the reference's CUDA kernels (lfranke/TRIPS,
+ * src/lib/rendering/RenderForward.cu, RenderBackward.cu, PointBlending.h, PointRendererHelper.h and
+ * src/lib/models/MyAdam.cu).  It exists to check the CUDA library and to be timed as the CPU baseline;
+ * nothing in the shipped package may call it.
+ *
+ * PARITY UNPINNED: the reference has no tests, fixtures or golden vectors for this path and cannot be
+ * compiled without its un-vendored `saiga` submodule, so this restatement is pinned only by hand-derived
+ * known-answer cases and finite-difference checks, not by reference outputs.
+ */
+#pragma once
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct
+{
+    int n_points;            /* N */
+    int n_tex;               /* columns of texture / confidence */
+    int channels;            /* C */
+    const float* position;   /* [N,4] xyz + drop-out radius */
+    const float* point_size; /* [N] raw, softplus-parametrised */
+    const int32_t* index;    /* [N] point -> texture column, or NULL for identity */
+    const float* texture;    /* [C, n_tex] */
+    const float* confidence; /* [n_tex], already sigmoid-activated */
+    const float* background; /* [C] */
+    const float* dropout;    /* [N] per-view mask (1 = dropped) or NULL */
+} OrScene;
+
+typedef struct
+{
+    int w, h;
+    double pose[8];         /* world->view: quaternion x,y,z,w then translation x,y,z, one pad */
+    float intrinsics[13];   /* fx fy cx cy s + 8 distortion coefficients (must be zero) */
+    float crop_transform[5]; /* fx fy cx cy s */
+    float crop_rotation[4]; /* row-major 2x2 */
+} OrView;
+
+typedef struct
+{
+    int num_layers;
+    int k_keep; /* fragments kept per pixel, <= 16 */
+    int train;
+    int drop_out_points_by_radius;
+    float drop_out_radius_threshold;
+    int viewer_only;
+    float stability_cutoff_value;
+    int bg_uses_Tn; /* 0 = reference behaviour (weight before the last kept fragment) */
+} OrParams;
+
+typedef struct OrFrame OrFrame; /* all intermediates of one rendered view */
+
+int or_max_threads(void);
+
+OrFrame* or_forward(const OrScene* scene, const OrView* view, const OrParams* params);
+void or_frame_free(OrFrame* f);
+
+int64_t or_num_pixels(const OrFrame* f);    /* P */
+int64_t or_num_fragments(const OrFrame* f); /* F */
+int64_t or_num_kept(const OrFrame* f);      /* Kf = sum min(len, K) */
+int64_t or_num_visible(const OrFrame* f);   /* V */
+void or_layer_size(const OrFrame* f, int layer, int* w, int* h, int64_t* base);
+
+/* copy-outs; every pointer may be NULL */
+void or_get_points(const OrFrame* f, float* depth /*[N]*/, int32_t* nlayers /*[N]*/, float* rec /*[N,4] u v ps texidx-bits*/);
+void or_get_lists(const OrFrame* f, int32_t* counts /*[P]*/, int64_t* offsets /*[P]*/, uint64_t* frags /*[F]*/);
+void or_get_pyramid(const OrFrame* f, float* out /*[sum_l C*H_l*W_l], layer-major, channel-planar*/);
+void or_get_records(const OrFrame* f, int32_t* nrec /*[P]*/, int32_t* rec_pid /*[P,16]*/, float* rec_alpha /*[P,16]*/);
+
+/* Backward of one view.  grad_pyramid has the layout of or_get_pyramid.  Outputs are ACCUMULATED in double. */
+void or_backward(const OrFrame* f, const OrScene* scene, const OrView* view, const OrParams* params,
+                 const float* grad_pyramid, double* g_texture /*[C,n_tex]*/, double* g_confidence /*[n_tex]*/,
+                 double* g_position /*[N,4], w untouched*/, double* g_point_size /*[N]*/,
+                 double* g_background /*[C]*/, double* g_pose /*[6] or NULL*/, double* g_intrinsics /*[5] or NULL*/);
+
+/* Reference Adam (MyAdam.cu:41-88) over n elements; steps is int64 per element. */
+void or_adam(int64_t n, float* w, const float* g, float* m, float* v, int64_t* steps, float lr, float beta1,
+             float beta2, float eps, float rel_decay, float abs_decay, float clip, float lower_lr, float upper_lr);
+
+/* primitives exposed for known-answer tests */
+float or_layer_factor(float ps, int layer, int num_layers, float* grad);
+float or_softplus(float x);
+float or_expf(float x);
+float or_logf(float x);
+void or_project(const OrView* view, const float* p3, float* u, float* v, float* z);
+
+#ifdef __cplusplus
+}
+#endif
