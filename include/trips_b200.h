@@ -1,0 +1,170 @@
+/* trips_b200 -- C ABI of the B200 (sm_100a) point-splatting rasterizer, its backward pass and the fused Adam.
+ *
+ * This is the boundary a TRIPS build binds instead of its own CUDA kernels.  Every entry point replaces one
+ * piece of the reference (paths relative to the lfranke/TRIPS source tree); all data pointers are DEVICE
+ * pointers owned by the caller unless stated otherwise, layouts are the reference's own tensor layouts, and
+ * work is enqueued on the given stream.  Functions return TRIPS_OK (0) or a negative TripsStatus; no entry
+ * point aborts the process or traps the device (the reference uses SAIGA_ASSERT / CUDA_KERNEL_ASSERT).
+ */
+#ifndef TRIPS_B200_H
+#define TRIPS_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TRIPS_MAX_LAYERS 8  /* src/lib/rendering/RenderConstants.h:38 */
+#define TRIPS_MAX_KEEP 16   /* src/lib/rendering/PointRenderer.h:178 (max_pixels_per_list) */
+#define TRIPS_MAX_CHANNELS 16
+
+typedef enum
+{
+    TRIPS_OK                  = 0,
+    TRIPS_ERR_INVALID_ARG     = -1,
+    TRIPS_ERR_CUDA            = -2,
+    TRIPS_ERR_OUT_OF_MEMORY   = -3,
+    TRIPS_ERR_UNSUPPORTED     = -4, /* camera model / flag outside the implemented live path */
+    TRIPS_ERR_NO_FORWARD      = -5, /* backward without a matching training forward */
+    TRIPS_ERR_TOO_LARGE       = -6  /* size beyond a stated maximum */
+} TripsStatus;
+
+/* Bits of the device status word (trips_last_status): conditions the reference would assert on. */
+#define TRIPS_DEV_BAD_TEXTURE_INDEX 1u /* RenderBackward.cu:217-218 */
+#define TRIPS_DEV_NONZERO_DISTORTION 2u /* distortion model not implemented: coefficients were ignored */
+#define TRIPS_DEV_FRAGMENT_OVERFLOW 4u /* a view's fragment count exceeded the list buffer */
+
+typedef struct TripsContext TripsContext;
+
+/* The scene as the reference's modules hold it.
+ * position, point_size, index: NeuralPointCloudCuda (src/lib/rendering/NeuralPointCloudCuda.h:78-96);
+ * texture, confidence, background: NeuralPointTexture after PrepareTexture / PrepareConfidence
+ * (src/lib/models/NeuralTexture.h:40-57); poses: PoseModule::poses_se3, intrinsics: IntrinsicsModule::intrinsics
+ * (src/lib/data/NeuralStructure.cpp:20-33,104-117), both read through DeviceRenderParams (RenderConstants.h:85-100). */
+typedef struct
+{
+    int n_points;             /* N */
+    int n_tex;                /* columns of texture / confidence */
+    int channels;             /* C: 3, 4, 6, 8 or 16 */
+    const float* position;    /* [N,4] xyz + drop-out radius */
+    const float* point_size;  /* [N] softplus-parametrised world-space size */
+    const int32_t* index;     /* [N] point -> texture column; NULL = identity */
+    const float* texture;     /* [C,n_tex] */
+    const float* confidence;  /* [n_tex] activated confidence */
+    const float* background;  /* [C] */
+    const float* dropout;     /* [B,N] 1 = point dropped in that view (training only); NULL = none */
+    const double* poses;      /* [n_images,8] world->view: quaternion x,y,z,w, translation x,y,z, pad */
+    int n_images;
+    const float* intrinsics;  /* [n_cameras,13] fx fy cx cy s + 8 distortion coefficients (must be 0) */
+    int n_cameras;
+} TripsScene;
+
+/* One view = ReducedImageInfo (src/lib/data/SceneData.h:40-61).  crop_rotation is row-major. */
+typedef struct
+{
+    int w, h;
+    int image_index;
+    int camera_index;
+    int camera_model_type; /* 0 = PINHOLE_DISTORTION, the only model implemented */
+    float crop_transform[5]; /* fx fy cx cy s */
+    float crop_rotation[4];
+} TripsView;
+
+/* The RenderParams fields the live path reads (src/lib/data/Settings.h:19-108, RenderConstants.h:115-140). */
+typedef struct
+{
+    int num_layers;                  /* 1..8 */
+    int k_keep;                      /* fragments kept per pixel, 1..16 (reference: 16) */
+    int train;                       /* 1: keep backward records, honour dropout */
+    int drop_out_points_by_radius;
+    float drop_out_radius_threshold;
+    int viewer_only;                 /* 1: discard points with confidence < stability_cutoff_value */
+    float stability_cutoff_value;
+    int bg_uses_Tn;                  /* 0 = reference behaviour for the background weight */
+} TripsRenderParams;
+
+/* Gradient outputs of BlendPointCloudBackward (src/lib/rendering/PointRenderer.cu:1423-1426).
+ * Any pointer may be NULL (that gradient is not produced).  Buffers are overwritten, not accumulated. */
+typedef struct
+{
+    float* texture;      /* [C,n_tex] */
+    float* background;   /* [C] */
+    float* points;       /* [N,4], w = 0 */
+    double* pose_tangent; /* [n_images,6] */
+    float* intrinsics;   /* [n_cameras,13]; only the 5 pinhole coefficients receive gradients */
+    float* confidence;   /* [n_tex] */
+    float* point_size;   /* [N] ("g_layer") */
+} TripsGrads;
+
+/* Counters of the last forward call, summed over its views. */
+typedef struct
+{
+    int64_t visible_points; /* V */
+    int64_t fragments;      /* F */
+    int64_t kept_fragments; /* Kf = sum over pixels of min(list length, k_keep) */
+    int64_t pixels;         /* B * P */
+    int64_t max_list_length;
+} TripsStats;
+
+/* Context = PointRendererCache (src/lib/rendering/PointRenderer.h:120-232): owns all scratch memory and the
+ * records saved for backward.  One context per device and per concurrent stream. */
+int trips_context_create(TripsContext** out, int device);
+void trips_context_destroy(TripsContext* ctx);
+const char* trips_status_string(int status);
+const char* trips_last_error(const TripsContext* ctx);
+
+/* Replaces BlendPointCloudForward / PointRendererCache::RenderFast16
+ * (src/lib/rendering/PointRenderer.cu:676-1191, RenderForward.cu:1065-1394).
+ * out_layers: HOST array of num_layers device pointers; layer l is [B,C,H_l,W_l] float32 contiguous with
+ * ceil-halved sizes (PointRenderer.cu:385-389).  All views must share (w, h). */
+int trips_forward(TripsContext* ctx, const TripsScene* scene, const TripsView* views, int n_views,
+                  const TripsRenderParams* params, float* const* out_layers, void* stream);
+
+/* Replaces BlendPointCloudBackward / BlendBackwardsBilinearFast
+ * (src/lib/rendering/PointRenderer.cu:1232-1427, RenderBackward.cu:90-691).  Uses the records of the last
+ * trips_forward on this context.  grad_layers: HOST array of num_layers device pointers, same shapes as out_layers. */
+int trips_backward(TripsContext* ctx, const TripsScene* scene, const float* const* grad_layers, const TripsGrads* grads,
+                   void* stream);
+
+/* Blocks until the stream is idle and returns the OR of device status bits raised since the last call. */
+uint32_t trips_last_status(TripsContext* ctx, void* stream);
+int trips_get_stats(TripsContext* ctx, TripsStats* out, void* stream);
+
+/* One parameter tensor of MyAdam (src/lib/models/MyAdam.cu:164-345): weights, gradient and optimizer state. */
+typedef struct
+{
+    float* weights;
+    const float* gradients;
+    float* first_moments;
+    float* second_moments;
+    int32_t* steps; /* per-element step counter (the reference keeps int64) */
+    int64_t n;
+    float lr;
+    float beta1, beta2, eps;
+    float relative_weight_decay, absolute_weight_decay, weight_clipping_magnitude;
+    float lower_lr_bound, upper_lr_bound; /* AdaBound bounds; 0 and FLT_MAX when off */
+} TripsAdamTensor;
+
+/* Replaces MyAdam::step's per-tensor adam_step launches (src/lib/models/MyAdam.cu:41-88,226-280) with one
+ * launch over all tensors.  `tensors` is a HOST array. */
+int trips_adam_step(TripsContext* ctx, const TripsAdamTensor* tensors, int n_tensors, void* stream);
+
+/* ---- inspection of the intermediates of the last forward call (used by the parity tests) ---- */
+/* Per-point results of view `view`: depth [N] (-1 = culled), nlayers [N] int32, record [N,4] (u, v, size_px, texture index bits).
+ * HOST output pointers, any may be NULL.  RenderForward.cu:311-363. */
+int trips_debug_points(TripsContext* ctx, int view, float* depth, int32_t* nlayers, float* record, void* stream);
+/* Per-pixel list lengths [P] int32, start offsets [P] int64 (relative to the view's first fragment) and the
+ * view's fragments (64-bit keys: depth bits << 32 | point id) in list order.  HOST pointers; pass frags = NULL
+ * and read *n_frags first to size the buffer.  RenderForward.cu:387-413. */
+int trips_debug_lists(TripsContext* ctx, int view, int32_t* counts, int64_t* offsets, uint64_t* frags, int64_t* n_frags,
+                      void* stream);
+/* Backward records of view `view`: nrec [P] int32, point ids [P,16] int32 (-1 = absent), alphas [P,16] (-1 = absent).
+ * RenderForward.cu:957-979. */
+int trips_debug_records(TripsContext* ctx, int view, int32_t* nrec, int32_t* rec_pid, float* rec_alpha, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TRIPS_B200_H */

@@ -414,15 +414,14 @@ OrFrame* or_forward(const OrScene* sc, const OrView* view, const OrParams* pr)
         }
         if (pr->train)
         {
+            // Records exist for the leading fragments whose transmittance is above the cut-off; the backward
+            // pass stops at the first absent record (RenderBackward.cu:205-210), so later ones are never read.
             int m = 0;
-            for (int j = 0; j < n; ++j)
+            while (m < n && T[m] >= kAlphaCut)
             {
-                if (T[j] >= kAlphaCut)
-                {
-                    f->rec_pid[(size_t)p * kMaxKeep + j]   = pid[j];
-                    f->rec_alpha[(size_t)p * kMaxKeep + j] = alpha[j];
-                    m = j + 1;
-                }
+                f->rec_pid[(size_t)p * kMaxKeep + m]   = pid[m];
+                f->rec_alpha[(size_t)p * kMaxKeep + m] = alpha[m];
+                ++m;
             }
             f->nrec[p] = m;
         }

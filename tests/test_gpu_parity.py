@@ -1,0 +1,222 @@
+"""GPU parity: the CUDA library (called through the C ABI) against the CPU oracle on identical seeded inputs.
+
+Bars: per-point projection results, list lengths, offsets, fragment lists (as sorted sets), kept point ids and the
+number of backward records are BIT-EXACT; alphas and pyramid values within 1e-5 relative; gradients within 1e-4
+relative (relative to max(|reference|, 1 % of the largest reference magnitude of that tensor))."""
+import numpy as np
+import pytest
+
+from trips_b200 import scenes
+from util import gpu_render, oracle_frames, rel_err, sort_lists
+
+pytestmark = pytest.mark.gpu
+
+TOL_PYRAMID = 1e-5
+TOL_GRAD = 1e-4
+
+
+def _variants():
+    v = {}
+    v["base_L4_K16"] = (scenes.tiny(), {}, None)
+    v["K8"] = (scenes.tiny(k_keep=8, seed=11), {}, None)
+    v["L1"] = (scenes.tiny(num_layers=1, seed=12), {}, None)
+    v["L8_odd_97x65"] = (scenes.tiny(num_layers=8, width=97, height=65, seed=13, size_range=(5e-3, 1.5)), {}, None)
+    v["C3"] = (scenes.tiny(channels=3, seed=14), {}, None)
+    v["C6"] = (scenes.tiny(channels=6, seed=15, n_points=1500), {}, None)
+    v["C8"] = (scenes.tiny(channels=8, seed=16, n_points=1500), {}, None)
+    v["C16"] = (scenes.tiny(channels=16, seed=17, n_points=1500), {}, None)
+    s = scenes.tiny(seed=18, n_points=6000, size_range=(0.05, 0.6))
+    s.confidence[:] = 1.0  # opaque points: transmittance falls below the cut-off, records end early
+    v["saturating"] = (s, {}, None)
+    v["drop_radius"] = (scenes.tiny(seed=19), dict(drop_out_points_by_radius=True, drop_out_radius_threshold=2.0), None)
+    v["bg_Tn"] = (scenes.tiny(seed=20), dict(bg_uses_Tn=True), None)
+    s = scenes.tiny(seed=21)
+    rng = np.random.default_rng(5)
+    v["index_permuted"] = (s, {}, rng.permutation(s.n_points).astype(np.int32))
+    s = scenes.tiny(seed=22, n_points=3000)
+    s.position[:, 2] += 100.0  # everything behind / outside every camera
+    v["all_culled"] = (s, {}, None)
+    v["three_views_long_lists"] = (scenes.tiny(seed=23, n_points=20000, width=64, height=48, n_views=3), {}, None)
+    return v
+
+
+VARIANTS = _variants()
+
+
+@pytest.mark.parametrize("name", list(VARIANTS))
+def test_forward_backward_parity(name, oracle_lib, cuda_lib):
+    import torch
+    s, kw, index = VARIANTS[name]
+    okw = dict(kw)
+    sa, op, frames = oracle_frames(s, train=True, index=index, **okw)
+    ns, info, blend = gpu_render(s, train=True, index=index, **kw)
+    for t in (ns.texture.texture_raw, ns.texture.confidence_raw, ns.texture.background_color_raw,
+              ns.point_cloud_cuda.t_position, ns.point_cloud_cuda.t_point_size):
+        t.requires_grad_(True)
+    ns.poses.tangent_poses.requires_grad_(True)
+    ns.intrinsics.intrinsics.requires_grad_(True)
+    outs = blend(info)
+    torch.cuda.synchronize()
+    assert info.cache.last_status() == 0
+    C = s.channels
+    st = info.cache.stats()
+    assert st["fragments"] == sum(f.F for f in frames)
+    assert st["kept_fragments"] == sum(f.Kf for f in frames)
+    assert st["visible_points"] == sum(f.V for f in frames)
+
+    grad_flat = []
+    for b, f in enumerate(frames):
+        # ---- per point ----
+        depth, nl, rec = info.cache.debug_points(b, s.n_points)
+        odepth, onl, orec = f.points()
+        assert np.array_equal(depth.view(np.uint32), odepth.view(np.uint32)), "depth differs"
+        assert np.array_equal(nl, onl), "layer counts differ"
+        vis = odepth > 0
+        assert np.array_equal(rec.view(np.uint32)[vis], orec.view(np.uint32)[vis]), "point records differ"
+        # ---- lists ----
+        counts, offsets, frags = info.cache.debug_lists(b, f.P)
+        ocounts, ooffsets, ofrags = f.lists()
+        assert np.array_equal(counts, ocounts), "list lengths differ"
+        assert np.array_equal(offsets, ooffsets), "list offsets differ"
+        assert frags.size == ofrags.size
+        assert np.array_equal(sort_lists(counts, offsets, frags), ofrags), "fragment lists differ"
+        # ---- kept fragments (sorted top-K) and records ----
+        nrec, pid, alpha = info.cache.debug_records(b, f.P)
+        onrec, opid, oalpha = f.records()
+        assert np.array_equal(nrec, onrec), "record counts differ"
+        assert np.array_equal(pid, opid), "sorted kept indices differ"
+        assert rel_err(alpha, oalpha, floor=1e-6) <= TOL_PYRAMID
+        # ---- pyramid ----
+        opyr = f.pyramid()
+        for l, o in enumerate(outs):
+            got = o[b].detach().cpu().numpy()
+            assert got.shape == opyr[l].shape
+            err = np.max(np.abs(got - opyr[l]) / np.maximum(np.abs(opyr[l]), 1e-3))
+            assert err <= TOL_PYRAMID, f"layer {l}: {err}"
+        grad_flat.append(scenes.target_gradient(s, b))
+
+    # ---- backward: loss = sum_b <g_b, out_b> ----
+    loss = 0
+    for b, f in enumerate(frames):
+        for l, (w, h, base) in enumerate(f.layers):
+            g = torch.from_numpy(grad_flat[b][C * base:C * (base + w * h)].reshape(C, h, w)).cuda()
+            loss = loss + (outs[l][b] * g).sum()
+    loss.backward()
+    torch.cuda.synchronize()
+    ref = None
+    for b, f in enumerate(frames):
+        r = f.backward(grad_flat[b])
+        if ref is None:
+            ref = {k: v.copy() for k, v in r.items() if k not in ("pose", "intrinsics")}
+            ref["pose"] = [r["pose"]]
+            ref["intrinsics"] = [r["intrinsics"]]
+        else:
+            for k in ("texture", "confidence", "position", "point_size", "background"):
+                ref[k] += r[k]
+            ref["pose"].append(r["pose"])
+            ref["intrinsics"].append(r["intrinsics"])
+    got = dict(texture=ns.texture.texture_raw.grad, confidence=ns.texture.confidence_raw.grad.reshape(-1),
+               position=ns.point_cloud_cuda.t_position.grad, point_size=ns.point_cloud_cuda.t_point_size.grad.reshape(-1),
+               background=ns.texture.background_color_raw.grad)
+    for k, g in got.items():
+        e = rel_err(g.cpu().numpy(), ref[k])
+        assert e <= TOL_GRAD, f"grad {k}: rel err {e}"
+    assert np.all(ns.point_cloud_cuda.t_position.grad[:, 3].cpu().numpy() == 0)
+    gpose = ns.poses.tangent_poses.grad.cpu().numpy()
+    gintr = ns.intrinsics.intrinsics.grad.cpu().numpy()
+    for b in range(len(frames)):
+        assert rel_err(gpose[b], ref["pose"][b]) <= TOL_GRAD, "pose gradient"
+        assert rel_err(gintr[b, :5], ref["intrinsics"][b]) <= TOL_GRAD, "intrinsics gradient"
+        assert np.all(gintr[b, 5:] == 0)
+
+
+def test_forward_inference_matches_training_output(oracle_lib, cuda_lib):
+    """train = false renders the same pyramid and keeps no records (RenderForward.cu:865-880 vs 957-979)."""
+    import torch
+    s = scenes.tiny(seed=31)
+    _, _, frames = oracle_frames(s, train=False)
+    ns, info, blend = gpu_render(s, train=False)
+    with torch.no_grad():
+        outs = blend(info)
+    for b, f in enumerate(frames):
+        for l, o in enumerate(f.pyramid()):
+            got = outs[l][b].cpu().numpy()
+            assert np.max(np.abs(got - o) / np.maximum(np.abs(o), 1e-3)) <= TOL_PYRAMID
+
+
+def test_config1_forward(oracle_lib, cuda_lib):
+    """The CPU-runnable benchmark case in full: 200 k points, 640x480, 4 layers, K = 8, forward only."""
+    import torch
+    s = scenes.config1()
+    _, _, frames = oracle_frames(s, train=False)
+    ns, info, blend = gpu_render(s, train=False)
+    with torch.no_grad():
+        outs = blend(info)
+    f = frames[0]
+    counts, offsets, frags = info.cache.debug_lists(0, f.P)
+    ocounts, ooffsets, ofrags = f.lists()
+    assert np.array_equal(counts, ocounts)
+    assert np.array_equal(offsets, ooffsets)
+    assert np.array_equal(sort_lists(counts, offsets, frags), ofrags)
+    for l, o in enumerate(f.pyramid()):
+        got = outs[l][0].cpu().numpy()
+        assert np.max(np.abs(got - o) / np.maximum(np.abs(o), 1e-3)) <= TOL_PYRAMID
+
+
+def test_adam_matches_reference_update(oracle_lib, cuda_lib):
+    """Three consecutive steps with zero-gradient holes against the scalar restatement of adam_step."""
+    import torch
+    from trips_b200.optim import MyAdam
+    import oracle
+    rng = np.random.default_rng(0)
+    sizes = [(4, 1003), (1, 1003), (1003, 4), (5,)]
+    ws = [rng.normal(size=sz).astype(np.float32) for sz in sizes]
+    params = [torch.nn.Parameter(torch.from_numpy(w.copy()).cuda()) for w in ws]
+    opt = MyAdam([dict(params=params[:2], lr=1e-3), dict(params=params[2:], lr=5e-3, relative_weight_decay=0.01,
+                                                         absolute_weight_decay=0.001, weight_clipping_magnitude=2.5)])
+    ref_w = [w.copy().reshape(-1) for w in ws]
+    ref_m = [np.zeros_like(w) for w in ref_w]
+    ref_v = [np.zeros_like(w) for w in ref_w]
+    ref_s = [np.zeros(w.size, np.int64) for w in ref_w]
+    for step in range(3):
+        for i, p in enumerate(params):
+            g = rng.normal(size=sizes[i]).astype(np.float32)
+            g[rng.random(size=sizes[i]) < 0.3] = 0.0  # unseen elements
+            p.grad = torch.from_numpy(g).cuda()
+            kw = dict(lr=1e-3) if i < 2 else dict(lr=5e-3, rel_decay=0.01, abs_decay=0.001, clip=2.5)
+            oracle.adam(ref_w[i], g.reshape(-1).copy(), ref_m[i], ref_v[i], ref_s[i], **kw)
+        opt.step()
+    torch.cuda.synchronize()
+    for i, p in enumerate(params):
+        assert rel_err(p.detach().cpu().numpy().reshape(-1), ref_w[i], floor=1e-6) <= 1e-5
+        st = opt.state[p]
+        assert np.array_equal(st["param_steps"].cpu().numpy().reshape(-1), ref_s[i])
+        assert rel_err(st["first_moments"].cpu().numpy().reshape(-1), ref_m[i], floor=1e-9) <= 1e-5
+        assert rel_err(st["second_moments"].cpu().numpy().reshape(-1), ref_v[i], floor=1e-12) <= 1e-5
+
+
+def test_error_paths(cuda_lib):
+    """Argument errors come back as status codes, not aborts (the reference asserts)."""
+    import torch
+    from trips_b200 import TripsError
+    from trips_b200.renderer import BlendPointCloudBackward
+    s = scenes.tiny(n_points=100)
+    ns, info, blend = gpu_render(s, train=False)
+    info.images[1].w += 2
+    with pytest.raises(TripsError):
+        blend(info)
+    info.images[1].w -= 2
+    info.images[0].camera_model_type = 1  # OCAM: not implemented
+    with pytest.raises(TripsError) as e:
+        blend(info)
+    assert e.value.status == -4
+    info.images[0].camera_model_type = 0
+    info.num_layers = 9
+    with pytest.raises(TripsError):
+        blend(info)
+    info.num_layers = 4
+    with torch.no_grad():
+        outs = blend(info)
+    with pytest.raises(TripsError) as e:  # backward after an inference forward
+        BlendPointCloudBackward(None, info, [torch.zeros_like(o) for o in outs])
+    assert e.value.status == -5

@@ -1,0 +1,479 @@
+// C ABI of libtrips_b200: context (scratch owner), forward, backward, fused Adam and the inspection calls.
+// The host logic here replaces PointRendererCache (src/lib/rendering/PointRenderer.cu:197-528) and the host
+// parts of RenderFast16 / BlendBackwardsBilinearFast / MyAdam::step.
+#include <cfloat>
+#include <cstdio>
+#include <cstring>
+#include <new>
+#include <string>
+#include <vector>
+
+#include "common.cuh"
+
+using namespace trips;
+
+namespace
+{
+struct DevBuf
+{
+    void* p      = nullptr;
+    size_t bytes = 0;
+};
+
+inline cudaError_t ensure(DevBuf& b, size_t bytes, double growth = 1.0)
+{
+    if (bytes <= b.bytes) return cudaSuccess;
+    if (b.p) cudaFree(b.p);
+    b.p          = nullptr;
+    b.bytes      = 0;
+    size_t want  = (size_t)((double)bytes * growth);
+    want         = (want + 255) & ~(size_t)255;
+    cudaError_t e = cudaMalloc(&b.p, want);
+    if (e != cudaSuccess && want > bytes)
+    {
+        (void)cudaGetLastError();
+        want = (bytes + 255) & ~(size_t)255;
+        e    = cudaMalloc(&b.p, want);
+    }
+    if (e == cudaSuccess) b.bytes = want;
+    return e;
+}
+}  // namespace
+
+struct TripsContext
+{
+    int device   = 0;
+    int sm_count = 148;
+    std::string error;
+    // forward scratch
+    DevBuf views, cams, rec, depth, nlay, counts, offsets, partial, view_base, frags, tex_packed, rec_n, records, stats, ticket;
+    // backward scratch
+    DevBuf g_tex, g_conf, g_pos, g_small;
+    // adam
+    DevBuf adam_tab;
+    // pinned host mirror: view_base[B+1] then DevStats
+    void* h_pinned      = nullptr;
+    size_t h_pinned_bytes = 0;
+    // state of the last forward call
+    bool have_forward = false;
+    Geom geom{};
+    TripsRenderParams params{};
+    int B = 0, N = 0, n_tex = 0, C = 0;
+    int nchunks = 0;
+    unsigned long long total_frags = 0;
+    TripsStats host_stats{};
+};
+
+#define CU_CHECK(ctx, expr)                                                                      \
+    do                                                                                           \
+    {                                                                                            \
+        cudaError_t _e = (expr);                                                                 \
+        if (_e != cudaSuccess)                                                                   \
+        {                                                                                        \
+            (ctx)->error = std::string(#expr) + ": " + cudaGetErrorString(_e);                   \
+            (void)cudaGetLastError();                                                            \
+            return _e == cudaErrorMemoryAllocation ? TRIPS_ERR_OUT_OF_MEMORY : TRIPS_ERR_CUDA;   \
+        }                                                                                        \
+    } while (0)
+
+static int fail(TripsContext* ctx, int code, const char* msg)
+{
+    if (ctx) ctx->error = msg;
+    return code;
+}
+
+static void free_buf(DevBuf& b)
+{
+    if (b.p) cudaFree(b.p);
+    b.p     = nullptr;
+    b.bytes = 0;
+}
+
+static ScenePtrs scene_ptrs(const TripsScene* s)
+{
+    ScenePtrs sp;
+    sp.N          = s->n_points;
+    sp.n_tex      = s->n_tex;
+    sp.C          = s->channels;
+    sp.position   = reinterpret_cast<const float4*>(s->position);
+    sp.point_size = s->point_size;
+    sp.index      = s->index;
+    sp.texture    = s->texture;
+    sp.confidence = s->confidence;
+    sp.background = s->background;
+    sp.dropout    = s->dropout;
+    return sp;
+}
+
+static FwdBuffers fwd_buffers(TripsContext* c)
+{
+    FwdBuffers fb;
+    fb.rec        = (float4*)c->rec.p;
+    fb.depth      = (float*)c->depth.p;
+    fb.nlay       = (uint8_t*)c->nlay.p;
+    fb.counts     = (uint32_t*)c->counts.p;
+    fb.offsets    = (uint32_t*)c->offsets.p;
+    fb.partial    = (uint32_t*)c->partial.p;
+    fb.view_base  = (unsigned long long*)c->view_base.p;
+    fb.frags      = (unsigned long long*)c->frags.p;
+    fb.frag_cap   = c->frags.bytes / 8;
+    fb.tex_packed = (float*)c->tex_packed.p;
+    fb.rec_n      = (uint8_t*)c->rec_n.p;
+    fb.records    = (uint2*)c->records.p;
+    fb.stats      = (DevStats*)c->stats.p;
+    fb.ticket     = (unsigned int*)c->ticket.p;
+    return fb;
+}
+
+static bool valid_channels(int c) { return c == 3 || c == 4 || c == 6 || c == 8 || c == 16; }
+
+extern "C" {
+
+const char* trips_status_string(int status)
+{
+    switch (status)
+    {
+        case TRIPS_OK: return "ok";
+        case TRIPS_ERR_INVALID_ARG: return "invalid argument";
+        case TRIPS_ERR_CUDA: return "CUDA error";
+        case TRIPS_ERR_OUT_OF_MEMORY: return "out of device memory";
+        case TRIPS_ERR_UNSUPPORTED: return "unsupported camera model or flag";
+        case TRIPS_ERR_NO_FORWARD: return "backward without a training forward pass";
+        case TRIPS_ERR_TOO_LARGE: return "size beyond the supported maximum";
+        default: return "unknown status";
+    }
+}
+
+const char* trips_last_error(const TripsContext* ctx) { return ctx ? ctx->error.c_str() : "null context"; }
+
+int trips_context_create(TripsContext** out, int device)
+{
+    if (!out) return TRIPS_ERR_INVALID_ARG;
+    *out = nullptr;
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || device < 0 || device >= count)
+    {
+        (void)cudaGetLastError();
+        return TRIPS_ERR_CUDA;
+    }
+    TripsContext* c = new (std::nothrow) TripsContext();
+    if (!c) return TRIPS_ERR_OUT_OF_MEMORY;
+    c->device = device;
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, device) == cudaSuccess) c->sm_count = prop.multiProcessorCount;
+    *out = c;
+    return TRIPS_OK;
+}
+
+void trips_context_destroy(TripsContext* c)
+{
+    if (!c) return;
+    DevBuf* all[] = {&c->views, &c->cams, &c->rec, &c->depth, &c->nlay, &c->counts, &c->offsets, &c->partial, &c->view_base,
+                     &c->frags, &c->tex_packed, &c->rec_n, &c->records, &c->stats, &c->ticket, &c->g_tex, &c->g_conf,
+                     &c->g_pos, &c->g_small, &c->adam_tab};
+    for (DevBuf* b : all) free_buf(*b);
+    if (c->h_pinned) cudaFreeHost(c->h_pinned);
+    delete c;
+}
+
+int trips_forward(TripsContext* ctx, const TripsScene* scene, const TripsView* views, int n_views,
+                  const TripsRenderParams* params, float* const* out_layers, void* stream)
+{
+    if (!ctx) return TRIPS_ERR_INVALID_ARG;
+    if (!scene || !views || !params || !out_layers || n_views < 1) return fail(ctx, TRIPS_ERR_INVALID_ARG, "null argument");
+    if (params->num_layers < 1 || params->num_layers > TRIPS_MAX_LAYERS) return fail(ctx, TRIPS_ERR_INVALID_ARG, "num_layers must be 1..8");
+    if (params->k_keep < 1 || params->k_keep > TRIPS_MAX_KEEP) return fail(ctx, TRIPS_ERR_INVALID_ARG, "k_keep must be 1..16");
+    if (!valid_channels(scene->channels)) return fail(ctx, TRIPS_ERR_INVALID_ARG, "channels must be 3, 4, 6, 8 or 16");
+    if (scene->n_points < 0 || scene->n_tex < 1 || scene->n_images < 1 || scene->n_cameras < 1)
+        return fail(ctx, TRIPS_ERR_INVALID_ARG, "bad scene sizes");
+    if (scene->n_points > 0 && (!scene->position || !scene->point_size)) return fail(ctx, TRIPS_ERR_INVALID_ARG, "null point arrays");
+    if (!scene->texture || !scene->confidence || !scene->background || !scene->poses || !scene->intrinsics)
+        return fail(ctx, TRIPS_ERR_INVALID_ARG, "null scene arrays");
+    if (!scene->index && scene->n_tex < scene->n_points) return fail(ctx, TRIPS_ERR_INVALID_ARG, "identity index needs n_tex >= n_points");
+    const int w = views[0].w, h = views[0].h;
+    if (w < 2 || h < 2) return fail(ctx, TRIPS_ERR_INVALID_ARG, "image must be at least 2x2");
+    for (int b = 0; b < n_views; ++b)
+    {
+        if (views[b].w != w || views[b].h != h) return fail(ctx, TRIPS_ERR_INVALID_ARG, "all views of a call must share (w, h)");
+        if (views[b].camera_model_type != 0) return fail(ctx, TRIPS_ERR_UNSUPPORTED, "only the pinhole camera model is implemented");
+        if (views[b].image_index < 0 || views[b].image_index >= scene->n_images || views[b].camera_index < 0 ||
+            views[b].camera_index >= scene->n_cameras)
+            return fail(ctx, TRIPS_ERR_INVALID_ARG, "view index out of range");
+    }
+    for (int l = 0; l < params->num_layers; ++l)
+        if (!out_layers[l]) return fail(ctx, TRIPS_ERR_INVALID_ARG, "null output layer");
+    cudaStream_t st = (cudaStream_t)stream;
+    ctx->have_forward = false;
+
+    Geom g{};
+    g.L = params->num_layers;
+    {
+        long long base = 0;
+        int lw = w, lh = h;
+        for (int l = 0; l < g.L; ++l)
+        {
+            g.W[l]    = lw;
+            g.H[l]    = lh;
+            g.base[l] = (int)base;
+            base += (long long)lw * lh;
+            lw = (lw + 1) / 2;  // ceil halving, PointRenderer.cu:385-389
+            lh = (lh + 1) / 2;
+        }
+        for (int l = g.L; l <= TRIPS_MAX_LAYERS; ++l) g.base[l] = (int)base;
+        if (base > (1ll << 30)) return fail(ctx, TRIPS_ERR_TOO_LARGE, "pyramid has more than 2^30 pixels");
+        g.P = (int)base;
+    }
+    const int B       = n_views;
+    const size_t N    = (size_t)scene->n_points;
+    const size_t P    = (size_t)g.P;
+    const int C       = scene->channels;
+    const int nchunks = (int)((P + kScanChunk - 1) / kScanChunk);
+    if (N * 4ull * g.L >= (1ull << 32)) return fail(ctx, TRIPS_ERR_TOO_LARGE, "a view could hold more than 2^32 fragments");
+    if ((unsigned long long)B * ((P + 31) / 32) >= (1ull << 32)) return fail(ctx, TRIPS_ERR_TOO_LARGE, "too many pixel tiles");
+
+    CU_CHECK(ctx, ensure(ctx->views, sizeof(TripsView) * B));
+    CU_CHECK(ctx, ensure(ctx->cams, sizeof(CamConst) * B));
+    CU_CHECK(ctx, ensure(ctx->rec, sizeof(float4) * N * B + 16));
+    CU_CHECK(ctx, ensure(ctx->depth, sizeof(float) * N * B + 16));
+    CU_CHECK(ctx, ensure(ctx->nlay, N * B + 16));
+    CU_CHECK(ctx, ensure(ctx->counts, sizeof(uint32_t) * P * B));
+    CU_CHECK(ctx, ensure(ctx->offsets, sizeof(uint32_t) * P * B));
+    CU_CHECK(ctx, ensure(ctx->partial, sizeof(uint32_t) * (size_t)nchunks * B));
+    CU_CHECK(ctx, ensure(ctx->view_base, sizeof(unsigned long long) * (B + 1)));
+    CU_CHECK(ctx, ensure(ctx->tex_packed, sizeof(float) * (size_t)scene->n_tex * C));
+    CU_CHECK(ctx, ensure(ctx->stats, sizeof(DevStats)));
+    CU_CHECK(ctx, ensure(ctx->ticket, sizeof(unsigned) * (size_t)(B > 64 ? B : 64)));
+    if (params->train)
+    {
+        CU_CHECK(ctx, ensure(ctx->rec_n, P * B));
+        CU_CHECK(ctx, ensure(ctx->records, sizeof(uint2) * 16 * P * B));
+    }
+    if (ctx->frags.bytes == 0) CU_CHECK(ctx, ensure(ctx->frags, 8 * 1024 * 1024));
+    size_t pinned_need = sizeof(unsigned long long) * (B + 1) + sizeof(DevStats);
+    if (ctx->h_pinned_bytes < pinned_need)
+    {
+        if (ctx->h_pinned) cudaFreeHost(ctx->h_pinned);
+        ctx->h_pinned = nullptr;
+        CU_CHECK(ctx, cudaMallocHost(&ctx->h_pinned, pinned_need * 2));
+        ctx->h_pinned_bytes = pinned_need * 2;
+    }
+
+    ScenePtrs sp  = scene_ptrs(scene);
+    FwdBuffers fb = fwd_buffers(ctx);
+    CU_CHECK(ctx, cudaMemsetAsync(ctx->stats.p, 0, sizeof(DevStats), st));
+    CU_CHECK(ctx, cudaMemsetAsync(ctx->counts.p, 0, sizeof(uint32_t) * P * B, st));
+    // the view table comes from pageable host memory: the copy is staged before the call returns
+    CU_CHECK(ctx, cudaMemcpyAsync(ctx->views.p, views, sizeof(TripsView) * B, cudaMemcpyHostToDevice, st));
+    CU_CHECK(ctx, launch_setup_cams((const TripsView*)ctx->views.p, B, scene->poses, scene->n_images, scene->intrinsics,
+                                    scene->n_cameras, (CamConst*)ctx->cams.p, fb.stats, st));
+    CU_CHECK(ctx, launch_pack_texture(sp, fb.tex_packed, st));
+    if (N > 0) CU_CHECK(ctx, launch_project_count(sp, (const CamConst*)ctx->cams.p, g, *params, B, fb, st));
+    {
+        FwdBuffers fscan = fb;
+        fscan.frag_cap   = ~0ull;  // sizing pass: the list buffer is grown below, nothing can overflow yet
+        CU_CHECK(ctx, launch_scan(g, B, params->k_keep, fscan, nchunks, st));
+    }
+    // The only host synchronisation of the forward pass: fragment totals of all views, to size the list buffer.
+    // (The reference synchronises 2 * num_layers times per view for the same purpose, RenderForward.cu:1201-1208.)
+    unsigned long long* h_base = (unsigned long long*)ctx->h_pinned;
+    DevStats* h_stats          = (DevStats*)(h_base + (B + 1));
+    CU_CHECK(ctx, cudaMemcpyAsync(h_base, ctx->view_base.p, sizeof(unsigned long long) * (B + 1), cudaMemcpyDeviceToHost, st));
+    CU_CHECK(ctx, cudaMemcpyAsync(h_stats, ctx->stats.p, sizeof(DevStats), cudaMemcpyDeviceToHost, st));
+    CU_CHECK(ctx, cudaStreamSynchronize(st));
+    const unsigned long long total = h_base[B];
+    if (total * 8 > ctx->frags.bytes)
+    {
+        CU_CHECK(ctx, ensure(ctx->frags, (size_t)total * 8, 1.25));
+        fb = fwd_buffers(ctx);
+    }
+    ctx->total_frags = total;
+    if (N > 0) CU_CHECK(ctx, launch_collect(sp, g, B, fb, st));
+    LayerPtrs out{};
+    for (int l = 0; l < g.L; ++l) out.p[l] = out_layers[l];
+    CU_CHECK(ctx, launch_sort_blend(sp, g, *params, B, fb, out, ctx->sm_count, st));
+
+    ctx->geom    = g;
+    ctx->params  = *params;
+    ctx->B       = B;
+    ctx->N       = (int)N;
+    ctx->n_tex   = scene->n_tex;
+    ctx->C       = C;
+    ctx->nchunks = nchunks;
+    ctx->host_stats.visible_points  = (int64_t)h_stats->visible;
+    ctx->host_stats.fragments       = (int64_t)total;
+    ctx->host_stats.kept_fragments  = (int64_t)h_stats->kept;
+    ctx->host_stats.pixels          = (int64_t)P * B;
+    ctx->host_stats.max_list_length = (int64_t)h_stats->max_len;
+    ctx->have_forward          = true;
+    return TRIPS_OK;
+}
+
+int trips_backward(TripsContext* ctx, const TripsScene* scene, const float* const* grad_layers, const TripsGrads* grads,
+                   void* stream)
+{
+    if (!ctx) return TRIPS_ERR_INVALID_ARG;
+    if (!scene || !grad_layers || !grads) return fail(ctx, TRIPS_ERR_INVALID_ARG, "null argument");
+    if (!ctx->have_forward || !ctx->params.train) return fail(ctx, TRIPS_ERR_NO_FORWARD, "no training forward pass to differentiate");
+    if (scene->n_points != ctx->N || scene->n_tex != ctx->n_tex || scene->channels != ctx->C)
+        return fail(ctx, TRIPS_ERR_INVALID_ARG, "scene sizes differ from the forward pass");
+    const Geom& g = ctx->geom;
+    for (int l = 0; l < g.L; ++l)
+        if (!grad_layers[l]) return fail(ctx, TRIPS_ERR_INVALID_ARG, "null gradient layer");
+    cudaStream_t st = (cudaStream_t)stream;
+    const int B = ctx->B, C = ctx->C;
+    const size_t N = (size_t)ctx->N, n_tex = (size_t)ctx->n_tex;
+
+    CU_CHECK(ctx, ensure(ctx->g_tex, sizeof(float) * n_tex * C));
+    CU_CHECK(ctx, ensure(ctx->g_conf, sizeof(float) * n_tex));
+    CU_CHECK(ctx, ensure(ctx->g_pos, sizeof(float4) * N + 16));
+    const size_t small_bytes = sizeof(double) * (TRIPS_MAX_CHANNELS + (size_t)B * 11);
+    CU_CHECK(ctx, ensure(ctx->g_small, small_bytes));
+    BwdBuffers bb;
+    bb.g_tex_packed = (float*)ctx->g_tex.p;
+    bb.g_conf       = (float*)ctx->g_conf.p;
+    bb.g_pos_size   = (float4*)ctx->g_pos.p;
+    bb.g_bg         = (double*)ctx->g_small.p;
+    bb.g_pose       = bb.g_bg + TRIPS_MAX_CHANNELS;
+    bb.g_k          = bb.g_pose + (size_t)B * 6;
+    CU_CHECK(ctx, cudaMemsetAsync(ctx->g_tex.p, 0, sizeof(float) * n_tex * C, st));
+    CU_CHECK(ctx, cudaMemsetAsync(ctx->g_conf.p, 0, sizeof(float) * n_tex, st));
+    if (N > 0) CU_CHECK(ctx, cudaMemsetAsync(ctx->g_pos.p, 0, sizeof(float4) * N, st));
+    CU_CHECK(ctx, cudaMemsetAsync(ctx->g_small.p, 0, small_bytes, st));
+    if (grads->pose_tangent) CU_CHECK(ctx, cudaMemsetAsync(grads->pose_tangent, 0, sizeof(double) * 6 * scene->n_images, st));
+    if (grads->intrinsics) CU_CHECK(ctx, cudaMemsetAsync(grads->intrinsics, 0, sizeof(float) * 13 * scene->n_cameras, st));
+
+    ScenePtrs sp  = scene_ptrs(scene);
+    FwdBuffers fb = fwd_buffers(ctx);
+    ConstLayerPtrs gin{};
+    for (int l = 0; l < g.L; ++l) gin.p[l] = grad_layers[l];
+    const bool cam_grads = grads->pose_tangent || grads->intrinsics;
+    CU_CHECK(ctx, launch_blend_backward(sp, (const CamConst*)ctx->cams.p, g, ctx->params, B, fb, bb, gin, cam_grads,
+                                        ctx->sm_count, st));
+    CU_CHECK(ctx, launch_unpack_grads(sp, (const CamConst*)ctx->cams.p, B, bb, *grads, st));
+    return TRIPS_OK;
+}
+
+uint32_t trips_last_status(TripsContext* ctx, void* stream)
+{
+    if (!ctx || !ctx->stats.p) return 0;
+    DevStats s{};
+    cudaStream_t st = (cudaStream_t)stream;
+    if (cudaMemcpyAsync(&s, ctx->stats.p, sizeof(s), cudaMemcpyDeviceToHost, st) != cudaSuccess) return 0;
+    if (cudaStreamSynchronize(st) != cudaSuccess) return 0;
+    unsigned zero = 0;
+    cudaMemcpyAsync((char*)ctx->stats.p + offsetof(DevStats, status), &zero, sizeof(unsigned), cudaMemcpyHostToDevice, st);
+    cudaStreamSynchronize(st);
+    return s.status;
+}
+
+int trips_get_stats(TripsContext* ctx, TripsStats* out, void* stream)
+{
+    (void)stream;
+    if (!ctx || !out) return TRIPS_ERR_INVALID_ARG;
+    if (!ctx->have_forward) return fail(ctx, TRIPS_ERR_NO_FORWARD, "no forward pass");
+    *out = ctx->host_stats;
+    return TRIPS_OK;
+}
+
+int trips_adam_step(TripsContext* ctx, const TripsAdamTensor* tensors, int n_tensors, void* stream)
+{
+    if (!ctx) return TRIPS_ERR_INVALID_ARG;
+    if (!tensors || n_tensors < 1) return fail(ctx, TRIPS_ERR_INVALID_ARG, "no tensors");
+    cudaStream_t st = (cudaStream_t)stream;
+    std::vector<int64_t> start(n_tensors + 1, 0);
+    for (int i = 0; i < n_tensors; ++i)
+    {
+        const TripsAdamTensor& t = tensors[i];
+        if (t.n < 0 || (t.n > 0 && (!t.weights || !t.gradients || !t.first_moments || !t.second_moments || !t.steps)))
+            return fail(ctx, TRIPS_ERR_INVALID_ARG, "null tensor in Adam group");
+        start[i + 1] = start[i] + (t.n + kAdamPerBlock - 1) / kAdamPerBlock;
+    }
+    if (start[n_tensors] >= (1ll << 31)) return fail(ctx, TRIPS_ERR_TOO_LARGE, "too many elements for one Adam launch");
+    const size_t tab_bytes   = sizeof(TripsAdamTensor) * n_tensors;
+    const size_t tab_aligned = (tab_bytes + 15) & ~(size_t)15;
+    CU_CHECK(ctx, ensure(ctx->adam_tab, tab_aligned + sizeof(int64_t) * (n_tensors + 1)));
+    CU_CHECK(ctx, cudaMemcpyAsync(ctx->adam_tab.p, tensors, tab_bytes, cudaMemcpyHostToDevice, st));
+    CU_CHECK(ctx, cudaMemcpyAsync((char*)ctx->adam_tab.p + tab_aligned, start.data(), sizeof(int64_t) * (n_tensors + 1),
+                                  cudaMemcpyHostToDevice, st));
+    CU_CHECK(ctx, launch_adam((const TripsAdamTensor*)ctx->adam_tab.p, (const int64_t*)((char*)ctx->adam_tab.p + tab_aligned),
+                              n_tensors, start[n_tensors], st));
+    return TRIPS_OK;
+}
+
+int trips_debug_points(TripsContext* ctx, int view, float* depth, int32_t* nlayers, float* record, void* stream)
+{
+    if (!ctx) return TRIPS_ERR_INVALID_ARG;
+    if (!ctx->have_forward) return fail(ctx, TRIPS_ERR_NO_FORWARD, "no forward pass");
+    if (view < 0 || view >= ctx->B) return fail(ctx, TRIPS_ERR_INVALID_ARG, "view out of range");
+    cudaStream_t st = (cudaStream_t)stream;
+    const size_t N = (size_t)ctx->N, off = (size_t)view * N;
+    std::vector<uint8_t> nl(N);
+    if (depth) CU_CHECK(ctx, cudaMemcpyAsync(depth, (float*)ctx->depth.p + off, sizeof(float) * N, cudaMemcpyDeviceToHost, st));
+    if (record) CU_CHECK(ctx, cudaMemcpyAsync(record, (float4*)ctx->rec.p + off, sizeof(float4) * N, cudaMemcpyDeviceToHost, st));
+    if (nlayers && N) CU_CHECK(ctx, cudaMemcpyAsync(nl.data(), (uint8_t*)ctx->nlay.p + off, N, cudaMemcpyDeviceToHost, st));
+    CU_CHECK(ctx, cudaStreamSynchronize(st));
+    if (nlayers)
+        for (size_t i = 0; i < N; ++i) nlayers[i] = nl[i];
+    return TRIPS_OK;
+}
+
+int trips_debug_lists(TripsContext* ctx, int view, int32_t* counts, int64_t* offsets, uint64_t* frags, int64_t* n_frags,
+                      void* stream)
+{
+    if (!ctx) return TRIPS_ERR_INVALID_ARG;
+    if (!ctx->have_forward) return fail(ctx, TRIPS_ERR_NO_FORWARD, "no forward pass");
+    if (view < 0 || view >= ctx->B) return fail(ctx, TRIPS_ERR_INVALID_ARG, "view out of range");
+    cudaStream_t st = (cudaStream_t)stream;
+    const size_t P = (size_t)ctx->geom.P, off = (size_t)view * P;
+    unsigned long long vb[2];
+    CU_CHECK(ctx, cudaMemcpyAsync(vb, (unsigned long long*)ctx->view_base.p + view, sizeof(vb), cudaMemcpyDeviceToHost, st));
+    std::vector<uint32_t> c(P), e(P);
+    CU_CHECK(ctx, cudaMemcpyAsync(c.data(), (uint32_t*)ctx->counts.p + off, sizeof(uint32_t) * P, cudaMemcpyDeviceToHost, st));
+    CU_CHECK(ctx, cudaMemcpyAsync(e.data(), (uint32_t*)ctx->offsets.p + off, sizeof(uint32_t) * P, cudaMemcpyDeviceToHost, st));
+    CU_CHECK(ctx, cudaStreamSynchronize(st));
+    const unsigned long long nf = vb[1] - vb[0];
+    if (n_frags) *n_frags = (int64_t)nf;
+    for (size_t i = 0; i < P; ++i)
+    {
+        if (counts) counts[i] = (int32_t)c[i];
+        if (offsets) offsets[i] = (int64_t)e[i] - (int64_t)c[i];  // the collect pass advanced the offsets to the list ends
+    }
+    if (frags && nf)
+    {
+        CU_CHECK(ctx, cudaMemcpyAsync(frags, (unsigned long long*)ctx->frags.p + vb[0], sizeof(uint64_t) * nf, cudaMemcpyDeviceToHost, st));
+        CU_CHECK(ctx, cudaStreamSynchronize(st));
+    }
+    return TRIPS_OK;
+}
+
+int trips_debug_records(TripsContext* ctx, int view, int32_t* nrec, int32_t* rec_pid, float* rec_alpha, void* stream)
+{
+    if (!ctx) return TRIPS_ERR_INVALID_ARG;
+    if (!ctx->have_forward || !ctx->params.train) return fail(ctx, TRIPS_ERR_NO_FORWARD, "no training forward pass");
+    if (view < 0 || view >= ctx->B) return fail(ctx, TRIPS_ERR_INVALID_ARG, "view out of range");
+    cudaStream_t st = (cudaStream_t)stream;
+    const size_t P = (size_t)ctx->geom.P, off = (size_t)view * P;
+    std::vector<uint8_t> n(P);
+    std::vector<uint2> r(P * 16);
+    CU_CHECK(ctx, cudaMemcpyAsync(n.data(), (uint8_t*)ctx->rec_n.p + off, P, cudaMemcpyDeviceToHost, st));
+    CU_CHECK(ctx, cudaMemcpyAsync(r.data(), (uint2*)ctx->records.p + off * 16, sizeof(uint2) * 16 * P, cudaMemcpyDeviceToHost, st));
+    CU_CHECK(ctx, cudaStreamSynchronize(st));
+    for (size_t p = 0; p < P; ++p)
+    {
+        if (nrec) nrec[p] = n[p];
+        for (int j = 0; j < 16; ++j)
+        {
+            const bool present = j < n[p];
+            if (rec_pid) rec_pid[p * 16 + j] = present ? (int32_t)r[p * 16 + j].x : -1;
+            if (rec_alpha)
+            {
+                float a;
+                memcpy(&a, &r[p * 16 + j].y, 4);
+                rec_alpha[p * 16 + j] = present ? a : -1.f;
+            }
+        }
+    }
+    return TRIPS_OK;
+}
+
+}  // extern "C"

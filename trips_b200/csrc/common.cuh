@@ -1,0 +1,208 @@
+// Internal declarations shared by the kernels and the C ABI of libtrips_b200.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/trips_b200.h"
+#include "trips_math.h"
+
+namespace trips
+{
+constexpr float kAlphaCut = 0.001f;  // ALPHA_DEST_CUTOFF, RenderForward.cu:907
+constexpr unsigned kFull  = 0xffffffffu;
+
+// Pyramid geometry shared by all views of a call: ceil-halved layer sizes and their pixel offsets.
+struct Geom
+{
+    int L;
+    int W[TRIPS_MAX_LAYERS];
+    int H[TRIPS_MAX_LAYERS];
+    int base[TRIPS_MAX_LAYERS + 1];
+    int P;
+};
+
+// Per-view constants built on the device from the pose / intrinsics tensors (setup_cams_kernel).
+struct CamConst
+{
+    float qx, qy, qz, qw, tx, ty, tz;
+    float R[9];
+    float fx, fy, cx, cy, s;
+    float cfx, cfy, ccx, ccy, cs;
+    float r00, r01, r10, r11;
+    float cenx, ceny;
+    int image_index, camera_index;
+};
+
+struct LayerPtrs
+{
+    float* p[TRIPS_MAX_LAYERS];
+};
+struct ConstLayerPtrs
+{
+    const float* p[TRIPS_MAX_LAYERS];
+};
+
+// Device-side counters of one forward call.
+struct DevStats
+{
+    unsigned long long visible;
+    unsigned long long kept;
+    unsigned int max_len;
+    unsigned int status;
+};
+
+// Everything the forward kernels need besides the scene (all device pointers into context scratch).
+struct FwdBuffers
+{
+    float4* rec;            // [B,N] u, v, size_px, texture index bits
+    float* depth;           // [B,N] view-space z, -1 = culled
+    uint8_t* nlay;          // [B,N] number of layers written
+    uint32_t* counts;       // [B,P] list lengths
+    uint32_t* offsets;      // [B,P] list start within the view (list end after the collect pass)
+    uint32_t* partial;      // [B,nchunks] scan partials
+    unsigned long long* view_base;   // [B+1] first fragment of each view in `frags`
+    unsigned long long* frags;       // [frag_cap] 64-bit keys: depth bits << 32 | point id
+    unsigned long long frag_cap;
+    float* tex_packed;      // [n_tex,C] descriptors, one row per point
+    uint8_t* rec_n;         // [B,P] records kept for backward
+    uint2* records;         // [B,P,16] (point id, alpha bits)
+    DevStats* stats;
+    unsigned int* ticket;
+};
+
+struct ScenePtrs
+{
+    int N, n_tex, C;
+    const float4* position;
+    const float* point_size;
+    const int32_t* index;
+    const float* texture;
+    const float* confidence;
+    const float* background;
+    const float* dropout;
+};
+
+struct BwdBuffers
+{
+    float* g_tex_packed;  // [n_tex,C]
+    float* g_conf;        // [n_tex]
+    float4* g_pos_size;   // [N] xyz gradient + raw point-size gradient
+    double* g_bg;         // [C]
+    double* g_pose;       // [B,6]
+    double* g_k;          // [B,5]
+};
+
+// ---- device helpers (op order mirrors the CPU oracle; compiled with -fmad=false) ----
+
+__device__ __forceinline__ void transform_point(const CamConst& V, float px, float py, float pz, float& ox, float& oy,
+                                                float& oz)
+{
+    // Sophus SE3f * p: Eigen quaternion _transformVector, then translation (PointRendererHelper.h:238)
+    float ux = V.qy * pz - V.qz * py;
+    float uy = V.qz * px - V.qx * pz;
+    float uz = V.qx * py - V.qy * px;
+    ux += ux;
+    uy += uy;
+    uz += uz;
+    float cx = V.qy * uz - V.qz * uy;
+    float cy = V.qz * ux - V.qx * uz;
+    float cz = V.qx * uy - V.qy * ux;
+    ox       = ((px + V.qw * ux) + cx) + V.tx;
+    oy       = ((py + V.qw * uy) + cy) + V.ty;
+    oz       = ((pz + V.qw * uz) + cz) + V.tz;
+}
+
+// ProjectPointPinholeWoNormal with zero distortion + crop transform + crop rotation
+// (PointRendererHelper.h:232-253, RenderForward.cu:302-303,69-76).
+__device__ __forceinline__ void project_point(const CamConst& c, float px, float py, float pz, float& u, float& v, float& z)
+{
+    float vx, vy, vz;
+    transform_point(c, px, py, pz, vx, vy, vz);
+    z        = fmaxf(vz, 0.f);
+    float iz = 1.f / vz;
+    float nx = vx * iz;
+    float ny = vy * iz;
+    float ix = (c.fx * nx + c.s * ny) + c.cx;
+    float iy = c.fy * ny + c.cy;
+    float jx = (c.cfx * ix + c.cs * iy) + c.ccx;
+    float jy = c.cfy * iy + c.ccy;
+    float dx = jx - c.cenx;
+    float dy = jy - c.ceny;
+    float rx = c.r00 * dx + c.r01 * dy;
+    float ry = c.r10 * dx + c.r11 * dy;
+    u        = rx + c.cenx;
+    v        = ry + c.ceny;
+}
+
+// compute_point_size_fac (PointBlending.h:81-149); floor / ceil of log2 taken from the float's bits.
+__device__ __forceinline__ float layer_factor(float ps, int layer, int L, float* grad)
+{
+    int lo = 0, hi = 0;
+    if (ps > 1.f)
+    {
+        lo = min(max(0, tm_floor_log2(ps)), L - 1);
+        hi = min(max(0, tm_ceil_log2(ps)), L - 1);
+    }
+    if (layer < lo)
+    {
+        if (grad) *grad = 0.f;
+        return 1.f;
+    }
+    float f = 1.f;
+    if (hi == 0)
+    {
+        f = 0.75f * tm_expf(ps - 1.f) + 0.25f;
+        if (grad) *grad = 0.27591f * ps;
+    }
+    else if (lo == hi)
+    {
+        if (grad) *grad = 1.f;
+    }
+    else
+    {
+        float l_l = (float)(1 << lo);
+        float l_h = (float)(1 << hi);
+        f         = (ps - l_l) / (l_h - l_l);
+        if (layer == lo) f = 1.f - f;
+        if (grad)
+        {
+            float J = 1.f / (l_h - l_l);
+            if (layer == lo) J = -J;
+            *grad = J;
+        }
+    }
+    return f;
+}
+
+__device__ __forceinline__ void pixel_to_layer(const Geom& g, int p, int& layer, int& gx, int& gy)
+{
+    int l = 0;
+#pragma unroll
+    for (int i = 1; i < TRIPS_MAX_LAYERS; ++i)
+        if (i < g.L && p >= g.base[i]) l = i;
+    int t = p - g.base[l];
+    layer = l;
+    gy    = t / g.W[l];
+    gx    = t - gy * g.W[l];
+}
+
+// ---- launchers (forward.cu / backward.cu / adam.cu) ----
+cudaError_t launch_setup_cams(const TripsView* d_views, int B, const double* poses, int n_images, const float* intrinsics,
+                              int n_cameras, CamConst* cams, DevStats* stats, cudaStream_t st);
+cudaError_t launch_pack_texture(const ScenePtrs& sc, float* tex_packed, cudaStream_t st);
+cudaError_t launch_project_count(const ScenePtrs& sc, const CamConst* cams, const Geom& g, const TripsRenderParams& pr,
+                                 int B, const FwdBuffers& fb, cudaStream_t st);
+cudaError_t launch_scan(const Geom& g, int B, int k_keep, const FwdBuffers& fb, int nchunks, cudaStream_t st);
+cudaError_t launch_collect(const ScenePtrs& sc, const Geom& g, int B, const FwdBuffers& fb, cudaStream_t st);
+cudaError_t launch_sort_blend(const ScenePtrs& sc, const Geom& g, const TripsRenderParams& pr, int B, const FwdBuffers& fb,
+                              const LayerPtrs& out, int sm_count, cudaStream_t st);
+cudaError_t launch_blend_backward(const ScenePtrs& sc, const CamConst* cams, const Geom& g, const TripsRenderParams& pr,
+                                  int B, const FwdBuffers& fb, const BwdBuffers& bb, const ConstLayerPtrs& grad_in,
+                                  bool want_cam_grads, int sm_count, cudaStream_t st);
+cudaError_t launch_unpack_grads(const ScenePtrs& sc, const CamConst* cams, int B, const BwdBuffers& bb,
+                                const TripsGrads& out, cudaStream_t st);
+cudaError_t launch_adam(const TripsAdamTensor* d_tensors, const int64_t* d_block_start, int n_tensors, int64_t total_blocks,
+                        cudaStream_t st);
+constexpr int kScanChunk   = 2048;
+constexpr int kAdamPerBlock = 1024 * 4;  // elements handled by one Adam block
+}  // namespace trips
