@@ -1,0 +1,424 @@
+#!/usr/bin/env python
+"""Benchmark of the point-splatting training step (forward + backward + gradient all-reduce + fused Adam).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c3|c2|c1|tiny]
+
+One step = every rank renders its 8 views of the 6 M-point / 1920x1080 / 8-layer / K=16 scene, back-propagates
+a gradient pyramid, the point gradients are summed over ranks (NCCL) and the fused Adam updates the point
+parameters.  Rank 0 prints ONE JSON line.  `value` is views/s with all inputs resident in HBM; `e2e` is the same
+step fed from pinned host memory (target pyramids H2D, L1 loss on the device, loss scalar D2H every step).
+`--impl reference` times the CPU restatement of the reference's kernels (oracle/, OpenMP on the host cores): the
+reference ships CUDA kernels only and cannot be built without its saiga submodule.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+
+METRIC = "fwd+bwd views/s (6M pts, 1920x1080, 8 layers, K=16, training step incl. grad all-reduce + fused Adam)"
+RECORD_BYTES = 8  # bytes per kept fragment saved for backward (point id + alpha)
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c3", choices=["c3", "c2", "c1", "tiny"])
+    ap.add_argument("--points", type=int, default=0, help="override the number of points (debugging)")
+    ap.add_argument("--views-per-gpu", type=int, default=0)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--cpu-views", type=int, default=1, help="views of the workload the CPU baseline renders")
+    return ap.parse_args()
+
+
+def make_workload(name, world, rank, points, views_per_gpu):
+    from trips_b200 import scenes
+    if name == "c3":
+        vpg = views_per_gpu or 8
+        s = scenes.config3(n_points=points or 6_000_000, n_views=vpg * world)
+    elif name == "c2":
+        vpg = views_per_gpu or 4
+        s = scenes.config2(n_points=points or 2_000_000, n_views=vpg * world)
+    elif name == "c1":
+        vpg = 1
+        s = scenes.config1(n_points=points or 200_000)
+        s.train = True
+    else:
+        vpg = views_per_gpu or 2
+        s = scenes.tiny(n_points=points or 4000, n_views=vpg * world)
+    my_views = list(range(rank * vpg, rank * vpg + vpg)) if s.n_views >= (rank + 1) * vpg else list(range(vpg))
+    return s, my_views, vpg
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.lines = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                                          "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for ln in self.proc.stdout:
+            self.lines.append(ln.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            pass
+        sm, mx, reasons, power = [], [], set(), []
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx.append(float(f[1]))
+                power.append(float(f[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def measured_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+def stage_bytes(stage, N, P, C, B, F, Kf):
+    """Algorithmic bytes of one launch of a stage over B views (F, Kf are totals over those views)."""
+    if stage == "project_count":
+        return 24 * N * B
+    if stage == "scan":
+        return 12 * P * B
+    if stage == "collect":
+        return 8 * F
+    if stage == "sort_blend":
+        return 8 * F + (4 * C + 16) * Kf + 4 * C * P * B + RECORD_BYTES * Kf
+    if stage == "blend_backward":
+        return RECORD_BYTES * Kf + 4 * C * P * B + 8 * (C + 5) * Kf
+    if stage == "adam":
+        return 36 * (N * (C + 1 + 4 + 1))
+    return 0
+
+
+# ----------------------------------------------------------------------------------------------------------------
+# CPU arm: the oracle (restatement of the reference kernels) on the host cores
+# ----------------------------------------------------------------------------------------------------------------
+def cpu_views_per_second(s, views, repeats=1, with_adam=True):
+    """Forward + backward of `views` with the oracle; returns (views/s, seconds, fragments)."""
+    import oracle
+    from trips_b200 import scenes
+    sa = oracle.SceneArrays.from_scene(s)
+    p = oracle.make_params(s.num_layers, s.k_keep, True)
+    g = scenes.target_gradient(s, views[0])
+    t0 = time.perf_counter()
+    frags = 0
+    n = 0
+    for _ in range(repeats):
+        for v in views:
+            f = oracle.forward(sa, oracle.make_view(s.width, s.height, s.poses[v], s.intrinsics[v]), p)
+            f.backward(g)
+            frags += f.F
+            n += 1
+            del f
+    dt = time.perf_counter() - t0
+    return n / dt, dt, frags
+
+
+def run_reference(args, rank):
+    """`--impl reference`: the CPU restatement timed on the host cores, one view of the workload per step."""
+    if rank != 0:
+        return
+    import oracle
+    from trips_b200 import scenes
+    oracle.build()
+    s, my_views, vpg = make_workload(args.workload, 1, 0, args.points, args.views_per_gpu)
+    sa = oracle.SceneArrays.from_scene(s)
+    p = oracle.make_params(s.num_layers, s.k_keep, True)
+    g = scenes.target_gradient(s, 0)
+    times = []
+    for it in range(args.warmup + args.steps):
+        v = my_views[it % len(my_views)]
+        t0 = time.perf_counter()
+        f = oracle.forward(sa, oracle.make_view(s.width, s.height, s.poses[v], s.intrinsics[v]), p)
+        f.backward(g)
+        dt = time.perf_counter() - t0
+        del f
+        if it >= args.warmup:
+            times.append(dt)
+    ms = 1000.0 * float(np.mean(times))
+    value = 1000.0 / ms
+    cores = oracle.max_threads()
+    sample = f"1 view of {s.name} per step (forward + backward, no Adam), {args.steps} steps"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "views/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic", "config": {"workload": s.name, "views_per_step": 1, "points": s.n_points},
+        "cpu_baseline": {"value": value, "unit": "views/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "views/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }))
+
+
+# ----------------------------------------------------------------------------------------------------------------
+# GPU arm
+# ----------------------------------------------------------------------------------------------------------------
+def run_ours(args, rank, world, local_rank):
+    import torch
+    import torch.distributed as dist
+    from trips_b200 import build as tb
+    from trips_b200.modules import NeuralScene, images_for
+    from trips_b200.optim import MyAdam
+    from trips_b200.renderer import NeuralRenderInfo, PointRendererCache, RenderParams
+    from trips_b200.scenes import layer_sizes, num_pyramid_pixels
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (no CPU fallback for the GPU arm)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if rank == 0:
+        tb.build()
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+        dist.barrier()
+
+    s, my_views, vpg = make_workload(args.workload, world, rank, args.points, args.views_per_gpu)
+    N, C, L = s.n_points, s.channels, s.num_layers
+    P = num_pyramid_pixels(s.width, s.height, L)
+    B = len(my_views)
+    ns = NeuralScene.from_synthetic(s, device=dev)
+    pc, tex = ns.point_cloud_cuda, ns.texture
+    cache = PointRendererCache(dev)
+    info = NeuralRenderInfo(scene=ns, images=images_for(s, my_views), params=RenderParams(num_texture_channels=C, k_keep=s.k_keep),
+                            num_layers=L, train=True, cache=cache)
+    # all point gradients live in one flat buffer so that one collective sums them over ranks
+    n_flat = C * N + N + 4 * N + N + C
+    flat = torch.zeros(n_flat, device=dev)
+    o = 0
+    gout = {}
+    for key, shape in (("texture", (C, N)), ("confidence", (1, N)), ("points", (N, 4)), ("point_size", (N, 1)), ("background", (C,))):
+        n = int(np.prod(shape))
+        gout[key] = flat[o:o + n].view(shape)
+        o += n
+    params = [tex.texture_raw, tex.confidence_raw, pc.t_position, pc.t_point_size, tex.background_color_raw]
+    for p_, k in zip(params, ("texture", "confidence", "points", "point_size", "background")):
+        p_.grad = gout[k]
+    opt = MyAdam(params, lr=1e-3, betas=(0.9, 0.999), cache=cache)
+    sizes = layer_sizes(s.width, s.height, L)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(1234 + rank)
+    numel = C * P
+    grads_in = [((torch.randint(0, 2, (B, C, h, w), device=dev, generator=gen).float() * 2 - 1) / numel) for (w, h) in sizes]
+    scene_args = lambda: (tex.texture, tex.background_color, pc.t_position, ns.intrinsics.intrinsics,  # noqa: E731
+                          tex.confidence_value_of_point, pc.t_point_size, pc.t_index, ns.poses.poses_se3)
+
+    def step_resident():
+        outs = cache.forward(info, *scene_args())
+        cache.backward(grads_in, *scene_args(), out=gout)
+        if world > 1:
+            dist.all_reduce(flat)
+        opt.step()
+        return outs
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step_resident()
+    barrier()
+    stats = cache.stats()
+    assert cache.last_status() == 0, "device status word raised"
+
+    # ---- timed region: K steps, inputs resident in HBM.  Working set per step (>2 GB) is far larger than L2. ----
+    cache.enable_stage_timers(True)
+    cache.stage_times(reset=True)
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        step_resident()
+    e1.record()
+    barrier()
+    ms_total = e0.elapsed_time(e1)
+    clocks = sampler.stop() if sampler else None
+    st = cache.stage_times(reset=True)
+    cache.enable_stage_timers(False)
+    t = torch.tensor([ms_total], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step = float(t.item()) / args.steps
+    value = world * B / (ms_step / 1000.0)
+
+    # ---- end to end: targets come from pinned host memory, loss goes back to the host, every step ----
+    e2e = None
+    if not args.no_e2e:
+        rng = np.random.Generator(np.random.Philox(4242 + rank))
+        host_t = [torch.from_numpy(rng.random((B, C, h, w), dtype=np.float32)).pin_memory() for (w, h) in sizes]
+        dev_t = [[torch.empty_like(x, device=dev) for x in host_t] for _ in range(2)]
+        grads_e = [torch.empty((B, C, h, w), device=dev) for (w, h) in sizes]
+        loss_dev = torch.zeros((), device=dev, dtype=torch.float64)
+        loss_host = torch.zeros((), dtype=torch.float64).pin_memory()
+        copy_stream = torch.cuda.Stream(dev)
+        ready = [torch.cuda.Event(), torch.cuda.Event()]
+        consumed = [torch.cuda.Event(), torch.cuda.Event()]
+        h2d = sum(x.numel() * 4 for x in host_t)
+
+        def upload(slot):
+            with torch.cuda.stream(copy_stream):
+                copy_stream.wait_event(consumed[slot])
+                for d, h_ in zip(dev_t[slot], host_t):
+                    d.copy_(h_, non_blocking=True)
+                ready[slot].record(copy_stream)
+
+        def step_e2e(i, last):
+            slot = i & 1
+            if not last:
+                upload(slot ^ 1)  # next step's targets travel while this step computes
+            cur = torch.cuda.current_stream(dev)
+            cur.wait_event(ready[slot])
+            outs = cache.forward(info, *scene_args())
+            cache.l1_loss_backward(outs, dev_t[slot], grads_e, loss_dev)
+            consumed[slot].record(cur)
+            cache.backward(grads_e, *scene_args(), out=gout)
+            if world > 1:
+                dist.all_reduce(flat)
+            opt.step()
+            loss_host.copy_(loss_dev, non_blocking=True)
+            cur.synchronize()  # the caller reads the loss every step
+            return float(loss_host)
+
+        for slot in (0, 1):
+            consumed[slot].record(torch.cuda.current_stream(dev))
+        upload(0)
+        for i in range(2):
+            step_e2e(i, False)
+        barrier()
+        t0 = time.perf_counter()
+        e0.record()
+        for i in range(args.steps):
+            step_e2e(i, i == args.steps - 1)
+        e1.record()
+        barrier()
+        wall = (time.perf_counter() - t0) * 1000.0
+        ms_e = max(e0.elapsed_time(e1), 0.0)
+        te = torch.tensor([ms_e], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(te, op=dist.ReduceOp.MAX)
+        ms_e_step = float(te.item()) / args.steps
+        e2e = {"value": world * B / (ms_e_step / 1000.0), "unit": "views/s", "h2d_bytes_per_step": int(h2d),
+               "d2h_bytes_per_step": 8, "ms_per_step": ms_e_step, "wall_ms_per_step": wall / args.steps}
+
+    if rank != 0:
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
+
+    # ---- roofline of the dominant kernel, from the stage timers of the timed region ----
+    peak, peak_kind = measured_peak()
+    F, Kf = stats["fragments"], stats["kept_fragments"]
+    per_stage = {}
+    launches_total = 0
+    for name, (ms, calls, launches) in st.items():
+        launches_total += launches
+        if calls:
+            per_stage[name] = {"ms_per_launch": ms / calls, "launches": int(launches)}
+    dom = max((k for k in per_stage if k in ("project_count", "scan", "collect", "sort_blend", "blend_backward", "adam")),
+              key=lambda k: per_stage[k]["ms_per_launch"])
+    dom_bytes = stage_bytes(dom, N, P, C, B, F, Kf)
+    achieved = dom_bytes / (per_stage[dom]["ms_per_launch"] * 1e-3) / 1e9
+    for k, v in per_stage.items():
+        b_ = stage_bytes(k, N, P, C, B, F, Kf)
+        v["alg_gb"] = b_ / 1e9
+        v["gbs"] = (b_ / (v["ms_per_launch"] * 1e-3) / 1e9) if b_ else None
+    total_alg = sum(stage_bytes(k, N, P, C, B, F, Kf) for k in ("project_count", "scan", "collect", "sort_blend", "blend_backward", "adam"))
+    roofline = {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                "peak_kind": peak_kind, "traffic": None, "alg_bytes_per_launch": dom_bytes,
+                "step_alg_bytes": total_alg, "step_gbs": total_alg / (ms_step * 1e-3) / 1e9, "stages": per_stage}
+
+    cpu = None
+    if world == 1 and not args.no_cpu_baseline:
+        import oracle
+        oracle.build()
+        vps, secs, cfr = cpu_views_per_second(s, my_views[:args.cpu_views])
+        cpu = {"value": vps, "unit": "views/s", "cores": oracle.max_threads(), "kind": "port",
+               "sample": f"{args.cpu_views} view(s) of {s.name}, forward + backward with the OpenMP oracle ({secs:.1f} s)"}
+
+    out = {
+        "metric": METRIC, "value": value, "unit": "views/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": ms_step, "ms_per_view": ms_step / B, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": s.name, "points": N, "views_per_gpu": B, "global_views_per_step": B * world, "width": s.width,
+                   "height": s.height, "layers": L, "k_keep": s.k_keep, "channels": C, "parallelism": f"view-dp{world}",
+                   "l2_policy": "inputs (>2 GB touched per step) larger than the 126 MB L2; no explicit flush",
+                   "fragments_per_step": int(F), "kept_fragments_per_step": int(Kf), "visible_points_per_step": int(stats["visible_points"]),
+                   "max_list_length": int(stats["max_list_length"]), "fragments_per_s": F * world / (ms_step * 1e-3)},
+        "e2e": e2e, "gpu_launches": int(launches_total), "roofline": roofline, "cpu_baseline": cpu, "clocks": clocks,
+    }
+    print(json.dumps(out))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    if world != args.gpus and world == 1 and args.gpus > 1:
+        raise SystemExit("launch with torch.distributed.run --nproc-per-node N for --gpus N")
+    run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

@@ -151,6 +151,38 @@ typedef struct
  * launch over all tensors.  `tensors` is a HOST array. */
 int trips_adam_step(TripsContext* ctx, const TripsAdamTensor* tensors, int n_tensors, void* stream);
 
+/* Stage timers: CUDA-event pairs around every kernel stage, the counterpart of the reference's
+ * SAIGA_OPTIONAL_TIME_MEASURE scopes (src/lib/rendering/RenderForward.cu:1090,1166,1238,1271,
+ * PointRenderer.cu:1338) carried in NeuralRenderInfo::timer_system.  Off by default. */
+enum
+{
+    TRIPS_STAGE_SETUP = 0,
+    TRIPS_STAGE_PACK,
+    TRIPS_STAGE_PROJECT_COUNT,
+    TRIPS_STAGE_SCAN,
+    TRIPS_STAGE_COLLECT,
+    TRIPS_STAGE_SORT_BLEND,
+    TRIPS_STAGE_BACKWARD,
+    TRIPS_STAGE_UNPACK,
+    TRIPS_STAGE_ADAM,
+    TRIPS_STAGE_LOSS,
+    TRIPS_NUM_STAGES
+};
+int trips_enable_stage_timers(TripsContext* ctx, int enable);
+/* Waits for the recorded events.  ms, timed_calls, kernel_launches: HOST arrays of TRIPS_NUM_STAGES entries (any
+ * may be NULL): accumulated milliseconds, number of timed spans and number of kernels launched per stage since
+ * the last reset (launches are counted whether or not the timers are on). */
+int trips_get_stage_times(TripsContext* ctx, double* ms, int64_t* timed_calls, int64_t* kernel_launches, int reset);
+const char* trips_stage_name(int stage);
+
+/* Benchmark helper with no counterpart on the reference's renderer path (its losses live in
+ * src/lib/models/Pipeline.cpp:703): for every pyramid layer grad = sign(out - target) / total_numel and
+ * *loss_out (device double) = mean |out - target| over all layers.  The three pointer arrays and layer_numel
+ * are HOST arrays of num_layers entries. */
+int trips_l1_loss_backward(TripsContext* ctx, const float* const* out_layers, const float* const* target_layers,
+                           float* const* grad_layers, const int64_t* layer_numel, int num_layers, double* loss_out,
+                           void* stream);
+
 /* ---- inspection of the intermediates of the last forward call (used by the parity tests) ---- */
 /* Per-point results of view `view`: depth [N] (-1 = culled), nlayers [N] int32, record [N,4] (u, v, size_px, texture index bits).
  * HOST output pointers, any may be NULL.  RenderForward.cu:311-363. */

@@ -13,6 +13,7 @@ LIB_PATH = os.path.join(HERE, "libtrips_b200.so")
 
 MAX_LAYERS = 8
 MAX_KEEP = 16
+NUM_STAGES = 10
 
 OK = 0
 ERR_INVALID_ARG = -1
@@ -75,6 +76,11 @@ SYMBOLS = {
     "trips_last_status": (C.c_uint32, [C.c_void_p, C.c_void_p]),
     "trips_get_stats": (C.c_int, [C.c_void_p, C.POINTER(TripsStats), C.c_void_p]),
     "trips_adam_step": (C.c_int, [C.c_void_p, C.POINTER(TripsAdamTensor), C.c_int, C.c_void_p]),
+    "trips_enable_stage_timers": (C.c_int, [C.c_void_p, C.c_int]),
+    "trips_get_stage_times": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int]),
+    "trips_stage_name": (C.c_char_p, [C.c_int]),
+    "trips_l1_loss_backward": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.POINTER(C.c_void_p),
+                                         C.POINTER(C.c_int64), C.c_int, C.c_void_p, C.c_void_p]),
     "trips_debug_points": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "trips_debug_lists": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(C.c_int64), C.c_void_p]),
     "trips_debug_records": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),

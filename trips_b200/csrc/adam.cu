@@ -94,4 +94,40 @@ cudaError_t launch_adam(const TripsAdamTensor* d_tensors, const int64_t* d_block
     adam_kernel<<<(unsigned)total_blocks, 256, 0, st>>>(d_tensors, d_block_start, n_tensors);
     return cudaGetLastError();
 }
+
+// L1 loss against a target pyramid and its gradient, all layers in one launch (benchmark helper).
+__global__ __launch_bounds__(256) void l1_loss_kernel(const __grid_constant__ L1Args a, int64_t total, float inv_total,
+                                                      double* __restrict__ loss_out)
+{
+    double acc = 0.0;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x)
+    {
+        int l = 0;
+#pragma unroll
+        for (int k = 1; k < TRIPS_MAX_LAYERS; ++k)
+            if (k < a.L && i >= a.start[k]) l = k;
+        const int64_t j = i - a.start[l];
+        const float d   = a.out[l][j] - a.target[l][j];
+        a.grad[l][j]    = d > 0.f ? inv_total : (d < 0.f ? -inv_total : 0.f);
+        acc += (double)fabsf(d);
+    }
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(kFull, acc, o);
+    __shared__ double s[8];
+    if ((threadIdx.x & 31) == 0) s[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0)
+    {
+        double t = 0.0;
+        for (int w = 0; w < 8; ++w) t += s[w];
+        atomicAdd(loss_out, t * (double)inv_total);
+    }
+}
+
+cudaError_t launch_l1_loss(const L1Args& a, int64_t total, double* loss_out, int sm_count, cudaStream_t st)
+{
+    if (total <= 0) return cudaSuccess;
+    int blocks = (int)min((int64_t)sm_count * 8, (total + 255) / 256);
+    l1_loss_kernel<<<blocks, 256, 0, st>>>(a, total, 1.0f / (float)total, loss_out);
+    return cudaGetLastError();
+}
 }  // namespace trips

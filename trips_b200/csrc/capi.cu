@@ -38,10 +38,73 @@ inline cudaError_t ensure(DevBuf& b, size_t bytes, double growth = 1.0)
     if (e == cudaSuccess) b.bytes = want;
     return e;
 }
+// Optional CUDA-event timers around every stage (the reference's SAIGA_OPTIONAL_TIME_MEASURE scopes,
+// RenderForward.cu:1090,1166,1238,1271, PointRenderer.cu:1338) and a launch counter per stage.
+struct StageTimers
+{
+    bool enabled = false;
+    struct Span
+    {
+        int stage;
+        cudaEvent_t a, b;
+    };
+    std::vector<Span> open;                            // recorded, not yet read back
+    std::vector<std::pair<cudaEvent_t, cudaEvent_t>> pool;  // reusable event pairs
+    double ms[TRIPS_NUM_STAGES]        = {};
+    int64_t launches[TRIPS_NUM_STAGES] = {};
+    int64_t timed[TRIPS_NUM_STAGES]    = {};
+
+    bool begin(int stage, cudaStream_t st, Span& sp)
+    {
+        if (!enabled) return false;
+        if (pool.empty())
+        {
+            cudaEvent_t a, b;
+            if (cudaEventCreate(&a) != cudaSuccess || cudaEventCreate(&b) != cudaSuccess) return false;
+            pool.emplace_back(a, b);
+        }
+        sp.stage = stage;
+        sp.a     = pool.back().first;
+        sp.b     = pool.back().second;
+        pool.pop_back();
+        cudaEventRecord(sp.a, st);
+        return true;
+    }
+    void end(const Span& sp, cudaStream_t st)
+    {
+        cudaEventRecord(sp.b, st);
+        open.push_back(sp);
+    }
+    void collect()
+    {
+        for (const Span& sp : open)
+        {
+            float t = 0.f;
+            if (cudaEventSynchronize(sp.b) == cudaSuccess && cudaEventElapsedTime(&t, sp.a, sp.b) == cudaSuccess)
+            {
+                ms[sp.stage] += t;
+                timed[sp.stage] += 1;
+            }
+            pool.emplace_back(sp.a, sp.b);
+        }
+        open.clear();
+    }
+    void destroy()
+    {
+        collect();
+        for (auto& pr : pool)
+        {
+            cudaEventDestroy(pr.first);
+            cudaEventDestroy(pr.second);
+        }
+        pool.clear();
+    }
+};
 }  // namespace
 
 struct TripsContext
 {
+    StageTimers timers;
     int device   = 0;
     int sm_count = 148;
     std::string error;
@@ -74,6 +137,18 @@ struct TripsContext
             (void)cudaGetLastError();                                                            \
             return _e == cudaErrorMemoryAllocation ? TRIPS_ERR_OUT_OF_MEMORY : TRIPS_ERR_CUDA;   \
         }                                                                                        \
+    } while (0)
+
+// Runs `expr` (which launches `n` kernels of `stage`) between two events when the stage timers are on.
+#define STAGE(ctx, stage, n, st, expr)                      \
+    do                                                      \
+    {                                                       \
+        StageTimers::Span _sp;                              \
+        bool _t = (ctx)->timers.begin((stage), (st), _sp);  \
+        cudaError_t _se = (expr);                           \
+        if (_t) (ctx)->timers.end(_sp, (st));               \
+        (ctx)->timers.launches[(stage)] += (n);             \
+        CU_CHECK(ctx, _se);                                 \
     } while (0)
 
 static int fail(TripsContext* ctx, int code, const char* msg)
@@ -172,6 +247,7 @@ void trips_context_destroy(TripsContext* c)
                      &c->frags, &c->tex_packed, &c->rec_n, &c->records, &c->stats, &c->ticket, &c->g_tex, &c->g_conf,
                      &c->g_pos, &c->g_small, &c->adam_tab};
     for (DevBuf* b : all) free_buf(*b);
+    c->timers.destroy();
     if (c->h_pinned) cudaFreeHost(c->h_pinned);
     delete c;
 }
@@ -264,14 +340,15 @@ int trips_forward(TripsContext* ctx, const TripsScene* scene, const TripsView* v
     CU_CHECK(ctx, cudaMemsetAsync(ctx->counts.p, 0, sizeof(uint32_t) * P * B, st));
     // the view table comes from pageable host memory: the copy is staged before the call returns
     CU_CHECK(ctx, cudaMemcpyAsync(ctx->views.p, views, sizeof(TripsView) * B, cudaMemcpyHostToDevice, st));
-    CU_CHECK(ctx, launch_setup_cams((const TripsView*)ctx->views.p, B, scene->poses, scene->n_images, scene->intrinsics,
-                                    scene->n_cameras, (CamConst*)ctx->cams.p, fb.stats, st));
-    CU_CHECK(ctx, launch_pack_texture(sp, fb.tex_packed, st));
-    if (N > 0) CU_CHECK(ctx, launch_project_count(sp, (const CamConst*)ctx->cams.p, g, *params, B, fb, st));
+    STAGE(ctx, TRIPS_STAGE_SETUP, 1, st,
+          launch_setup_cams((const TripsView*)ctx->views.p, B, scene->poses, scene->n_images, scene->intrinsics,
+                            scene->n_cameras, (CamConst*)ctx->cams.p, fb.stats, st));
+    STAGE(ctx, TRIPS_STAGE_PACK, 1, st, launch_pack_texture(sp, fb.tex_packed, st));
+    if (N > 0) STAGE(ctx, TRIPS_STAGE_PROJECT_COUNT, 1, st, launch_project_count(sp, (const CamConst*)ctx->cams.p, g, *params, B, fb, st));
     {
         FwdBuffers fscan = fb;
         fscan.frag_cap   = ~0ull;  // sizing pass: the list buffer is grown below, nothing can overflow yet
-        CU_CHECK(ctx, launch_scan(g, B, params->k_keep, fscan, nchunks, st));
+        STAGE(ctx, TRIPS_STAGE_SCAN, 3, st, launch_scan(g, B, params->k_keep, fscan, nchunks, st));
     }
     // The only host synchronisation of the forward pass: fragment totals of all views, to size the list buffer.
     // (The reference synchronises 2 * num_layers times per view for the same purpose, RenderForward.cu:1201-1208.)
@@ -287,10 +364,10 @@ int trips_forward(TripsContext* ctx, const TripsScene* scene, const TripsView* v
         fb = fwd_buffers(ctx);
     }
     ctx->total_frags = total;
-    if (N > 0) CU_CHECK(ctx, launch_collect(sp, g, B, fb, st));
+    if (N > 0) STAGE(ctx, TRIPS_STAGE_COLLECT, 1, st, launch_collect(sp, g, B, fb, st));
     LayerPtrs out{};
     for (int l = 0; l < g.L; ++l) out.p[l] = out_layers[l];
-    CU_CHECK(ctx, launch_sort_blend(sp, g, *params, B, fb, out, ctx->sm_count, st));
+    STAGE(ctx, TRIPS_STAGE_SORT_BLEND, 1, st, launch_sort_blend(sp, g, *params, B, fb, out, ctx->sm_count, st));
 
     ctx->geom    = g;
     ctx->params  = *params;
@@ -347,9 +424,10 @@ int trips_backward(TripsContext* ctx, const TripsScene* scene, const float* cons
     ConstLayerPtrs gin{};
     for (int l = 0; l < g.L; ++l) gin.p[l] = grad_layers[l];
     const bool cam_grads = grads->pose_tangent || grads->intrinsics;
-    CU_CHECK(ctx, launch_blend_backward(sp, (const CamConst*)ctx->cams.p, g, ctx->params, B, fb, bb, gin, cam_grads,
-                                        ctx->sm_count, st));
-    CU_CHECK(ctx, launch_unpack_grads(sp, (const CamConst*)ctx->cams.p, B, bb, *grads, st));
+    STAGE(ctx, TRIPS_STAGE_BACKWARD, 1, st,
+          launch_blend_backward(sp, (const CamConst*)ctx->cams.p, g, ctx->params, B, fb, bb, gin, cam_grads, ctx->sm_count, st));
+    const int n_unpack = (grads->texture ? 1 : 0) + ((grads->points || grads->point_size) ? 1 : 0) + 1;
+    STAGE(ctx, TRIPS_STAGE_UNPACK, n_unpack, st, launch_unpack_grads(sp, (const CamConst*)ctx->cams.p, B, bb, *grads, st));
     return TRIPS_OK;
 }
 
@@ -395,8 +473,70 @@ int trips_adam_step(TripsContext* ctx, const TripsAdamTensor* tensors, int n_ten
     CU_CHECK(ctx, cudaMemcpyAsync(ctx->adam_tab.p, tensors, tab_bytes, cudaMemcpyHostToDevice, st));
     CU_CHECK(ctx, cudaMemcpyAsync((char*)ctx->adam_tab.p + tab_aligned, start.data(), sizeof(int64_t) * (n_tensors + 1),
                                   cudaMemcpyHostToDevice, st));
-    CU_CHECK(ctx, launch_adam((const TripsAdamTensor*)ctx->adam_tab.p, (const int64_t*)((char*)ctx->adam_tab.p + tab_aligned),
-                              n_tensors, start[n_tensors], st));
+    STAGE(ctx, TRIPS_STAGE_ADAM, 1, st,
+          launch_adam((const TripsAdamTensor*)ctx->adam_tab.p, (const int64_t*)((char*)ctx->adam_tab.p + tab_aligned), n_tensors,
+                      start[n_tensors], st));
+    return TRIPS_OK;
+}
+
+int trips_enable_stage_timers(TripsContext* ctx, int enable)
+{
+    if (!ctx) return TRIPS_ERR_INVALID_ARG;
+    ctx->timers.enabled = enable != 0;
+    return TRIPS_OK;
+}
+
+int trips_get_stage_times(TripsContext* ctx, double* ms, int64_t* timed_calls, int64_t* kernel_launches, int reset)
+{
+    if (!ctx) return TRIPS_ERR_INVALID_ARG;
+    ctx->timers.collect();
+    for (int i = 0; i < TRIPS_NUM_STAGES; ++i)
+    {
+        if (ms) ms[i] = ctx->timers.ms[i];
+        if (timed_calls) timed_calls[i] = ctx->timers.timed[i];
+        if (kernel_launches) kernel_launches[i] = ctx->timers.launches[i];
+        if (reset)
+        {
+            ctx->timers.ms[i]       = 0.0;
+            ctx->timers.timed[i]    = 0;
+            ctx->timers.launches[i] = 0;
+        }
+    }
+    return TRIPS_OK;
+}
+
+const char* trips_stage_name(int stage)
+{
+    static const char* names[TRIPS_NUM_STAGES] = {"setup_cams", "pack_texture", "project_count", "scan", "collect",
+                                                  "sort_blend", "blend_backward", "unpack_grads", "adam", "l1_loss"};
+    return (stage >= 0 && stage < TRIPS_NUM_STAGES) ? names[stage] : "?";
+}
+
+int trips_l1_loss_backward(TripsContext* ctx, const float* const* out_layers, const float* const* target_layers,
+                           float* const* grad_layers, const int64_t* layer_numel, int num_layers, double* loss_out,
+                           void* stream)
+{
+    if (!ctx) return TRIPS_ERR_INVALID_ARG;
+    if (!out_layers || !target_layers || !grad_layers || !layer_numel || !loss_out || num_layers < 1 ||
+        num_layers > TRIPS_MAX_LAYERS)
+        return fail(ctx, TRIPS_ERR_INVALID_ARG, "bad l1 loss arguments");
+    cudaStream_t st = (cudaStream_t)stream;
+    L1Args a{};
+    int64_t total = 0;
+    for (int l = 0; l < num_layers; ++l)
+    {
+        if (!out_layers[l] || !target_layers[l] || !grad_layers[l] || layer_numel[l] < 0)
+            return fail(ctx, TRIPS_ERR_INVALID_ARG, "null layer in l1 loss");
+        a.out[l]    = out_layers[l];
+        a.target[l] = target_layers[l];
+        a.grad[l]   = grad_layers[l];
+        a.start[l]  = total;
+        total += layer_numel[l];
+    }
+    for (int l = num_layers; l <= TRIPS_MAX_LAYERS; ++l) a.start[l] = total;
+    a.L = num_layers;
+    CU_CHECK(ctx, cudaMemsetAsync(loss_out, 0, sizeof(double), st));
+    STAGE(ctx, TRIPS_STAGE_LOSS, 1, st, launch_l1_loss(a, total, loss_out, ctx->sm_count, st));
     return TRIPS_OK;
 }
 

@@ -203,6 +203,15 @@ cudaError_t launch_unpack_grads(const ScenePtrs& sc, const CamConst* cams, int B
                                 const TripsGrads& out, cudaStream_t st);
 cudaError_t launch_adam(const TripsAdamTensor* d_tensors, const int64_t* d_block_start, int n_tensors, int64_t total_blocks,
                         cudaStream_t st);
+struct L1Args
+{
+    const float* out[TRIPS_MAX_LAYERS];
+    const float* target[TRIPS_MAX_LAYERS];
+    float* grad[TRIPS_MAX_LAYERS];
+    int64_t start[TRIPS_MAX_LAYERS + 1];
+    int L;
+};
+cudaError_t launch_l1_loss(const L1Args& a, int64_t total, double* loss_out, int sm_count, cudaStream_t st);
 constexpr int kScanChunk   = 2048;
 constexpr int kAdamPerBlock = 1024 * 4;  // elements handled by one Adam block
 }  // namespace trips

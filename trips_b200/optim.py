@@ -21,7 +21,7 @@ _FLT_MAX = 3.4028234663852886e38
 class MyAdam(torch.optim.Optimizer):
     def __init__(self, params: Iterable, lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8,
                  relative_weight_decay: float = 0.0, absolute_weight_decay: float = 0.0,
-                 weight_clipping_magnitude: float = 0.0, adabound: bool = False):
+                 weight_clipping_magnitude: float = 0.0, adabound: bool = False, cache=None):
         if lr < 0:
             raise ValueError(f"Invalid learning rate: {lr}")
         if eps < 0:
@@ -36,9 +36,13 @@ class MyAdam(torch.optim.Optimizer):
                         absolute_weight_decay=absolute_weight_decay, weight_clipping_magnitude=weight_clipping_magnitude,
                         adabound=adabound)
         super().__init__(params, defaults)
+        # `cache`: a PointRendererCache whose library context (stream-ordered scratch, stage timers) is shared
         self._ctx = None
+        self._shared = cache
 
     def _context(self, device):
+        if self._shared is not None:
+            return self._shared._h
         if self._ctx is None:
             h = C.c_void_p()
             _lib.check(_lib.lib().trips_context_create(C.byref(h), device.index or 0))

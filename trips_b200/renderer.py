@@ -168,8 +168,12 @@ class PointRendererCache:
         return outs
 
     def backward(self, grad_layers: Sequence[torch.Tensor], texture, background_color, points, intrinsics, confidence,
-                 point_size, index, poses, want_pose=False, want_intrinsics=False, want_points=True, want_size=True):
+                 point_size, index, poses, want_pose=False, want_intrinsics=False, want_points=True, want_size=True,
+                 out: Optional[dict] = None):
+        """`out` may hold preallocated gradient tensors (keys texture, background, points, confidence, point_size),
+        e.g. views into one flat buffer that is then all-reduced in a single call."""
         dev = points.device
+        out = out or {}
         sc = self._scene_struct(texture, background_color, points, intrinsics, confidence.reshape(-1), point_size.reshape(-1),
                                 None if index is None else index.reshape(-1), poses, self._dropout)
         grads_in = [g.contiguous() for g in grad_layers]
@@ -177,16 +181,41 @@ class PointRendererCache:
             if g.dtype != torch.float32:
                 raise ValueError("image gradients must be float32")  # PointRenderer.cu:1236-1239
         gp = (C.c_void_p * len(grads_in))(*[g.data_ptr() for g in grads_in])
-        g_tex = torch.empty_like(texture)
-        g_bg = torch.empty_like(background_color)
-        g_conf = torch.empty_like(confidence)
-        g_points = torch.empty_like(points) if want_points else None
-        g_size = torch.empty_like(point_size) if want_size else None
+        g_tex = out.get("texture") if out.get("texture") is not None else torch.empty_like(texture)
+        g_bg = out.get("background") if out.get("background") is not None else torch.empty_like(background_color)
+        g_conf = out.get("confidence") if out.get("confidence") is not None else torch.empty_like(confidence)
+        g_points = (out.get("points") if out.get("points") is not None else torch.empty_like(points)) if want_points else None
+        g_size = (out.get("point_size") if out.get("point_size") is not None else torch.empty_like(point_size)) if want_size else None
         g_pose = torch.empty((poses.shape[0], 6), device=dev, dtype=torch.float64) if want_pose else None
         g_intr = torch.empty_like(intrinsics) if want_intrinsics else None
         gs = _lib.TripsGrads(_ptr(g_tex), _ptr(g_bg), _ptr(g_points), _ptr(g_pose), _ptr(g_intr), _ptr(g_conf), _ptr(g_size))
         _lib.check(_lib.lib().trips_backward(self._h, C.byref(sc), gp, C.byref(gs), _stream_ptr(dev)), self._h)
         return g_tex, g_bg, g_points, g_pose, g_intr, g_conf, g_size
+
+    # -- stage timers (the reference's timer_system scopes) and the L1 benchmark loss ------------------------------------
+    def enable_stage_timers(self, on: bool = True):
+        _lib.check(_lib.lib().trips_enable_stage_timers(self._h, int(on)), self._h)
+
+    def stage_times(self, reset: bool = True) -> dict:
+        """{stage name: (accumulated ms, timed spans, kernels launched)} since the last reset."""
+        n = _lib.NUM_STAGES
+        ms = (C.c_double * n)()
+        calls = (C.c_int64 * n)()
+        launches = (C.c_int64 * n)()
+        _lib.check(_lib.lib().trips_get_stage_times(self._h, ms, calls, launches, int(reset)), self._h)
+        return {_lib.lib().trips_stage_name(i).decode(): (ms[i], calls[i], launches[i]) for i in range(n)}
+
+    def l1_loss_backward(self, outs: Sequence[torch.Tensor], targets: Sequence[torch.Tensor], grads: Sequence[torch.Tensor],
+                         loss_out: torch.Tensor):
+        """grads[l] = sign(outs[l] - targets[l]) / total numel, loss_out (float64 scalar on the device) = mean |diff|."""
+        n = len(outs)
+        assert loss_out.dtype == torch.float64 and loss_out.is_cuda
+        op = (C.c_void_p * n)(*[t.data_ptr() for t in outs])
+        tp = (C.c_void_p * n)(*[t.data_ptr() for t in targets])
+        gp = (C.c_void_p * n)(*[t.data_ptr() for t in grads])
+        numel = (C.c_int64 * n)(*[t.numel() for t in outs])
+        _lib.check(_lib.lib().trips_l1_loss_backward(self._h, op, tp, gp, numel, n, _ptr(loss_out), _stream_ptr(outs[0].device)),
+                   self._h)
 
     # -- inspection -----------------------------------------------------------------------------------------------
     def stats(self) -> dict:
