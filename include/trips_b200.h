@@ -157,8 +157,7 @@ int trips_adam_step(TripsContext* ctx, const TripsAdamTensor* tensors, int n_ten
 enum
 {
     TRIPS_STAGE_SETUP = 0,
-    TRIPS_STAGE_PACK,
-    TRIPS_STAGE_PROJECT_COUNT,
+    TRIPS_STAGE_BIN_POINTS,
     TRIPS_STAGE_SCAN,
     TRIPS_STAGE_COLLECT,
     TRIPS_STAGE_SORT_BLEND,

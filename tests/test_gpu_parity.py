@@ -37,6 +37,8 @@ def _variants():
     s.position[:, 2] += 100.0  # everything behind / outside every camera
     v["all_culled"] = (s, {}, None)
     v["three_views_long_lists"] = (scenes.tiny(seed=23, n_points=20000, width=64, height=48, n_views=3), {}, None)
+    # lists of several hundred fragments: exercises the streaming top-K path used for lists longer than 192
+    v["very_long_lists"] = (scenes.tiny(seed=24, n_points=60000, width=40, height=30, n_views=1, num_layers=3), {}, None)
     return v
 
 

@@ -13,7 +13,7 @@ LIB_PATH = os.path.join(HERE, "libtrips_b200.so")
 
 MAX_LAYERS = 8
 MAX_KEEP = 16
-NUM_STAGES = 10
+NUM_STAGES = 9
 
 OK = 0
 ERR_INVALID_ARG = -1

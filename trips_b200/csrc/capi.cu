@@ -109,9 +109,9 @@ struct TripsContext
     int sm_count = 148;
     std::string error;
     // forward scratch
-    DevBuf views, cams, rec, depth, nlay, counts, offsets, partial, view_base, frags, tex_packed, rec_n, records, stats, ticket;
+    DevBuf views, cams, bin_count, bin_cursor, entry_base, entries, counts, offsets, partial, view_base, frags, rec_n, records, stats, ticket;
     // backward scratch
-    DevBuf g_tex, g_conf, g_pos, g_small;
+    DevBuf egrad, g_tex, g_conf, g_pos, g_small;
     // adam
     DevBuf adam_tab;
     // pinned host mirror: view_base[B+1] then DevStats
@@ -124,6 +124,7 @@ struct TripsContext
     int B = 0, N = 0, n_tex = 0, C = 0;
     int nchunks = 0;
     unsigned long long total_frags = 0;
+    unsigned long long total_entries = 0;  // visible points summed over the views of the last forward call
     TripsStats host_stats{};
 };
 
@@ -183,16 +184,16 @@ static ScenePtrs scene_ptrs(const TripsScene* s)
 static FwdBuffers fwd_buffers(TripsContext* c)
 {
     FwdBuffers fb;
-    fb.rec        = (float4*)c->rec.p;
-    fb.depth      = (float*)c->depth.p;
-    fb.nlay       = (uint8_t*)c->nlay.p;
+    fb.bin_count  = (uint32_t*)c->bin_count.p;
+    fb.bin_cursor = (uint32_t*)c->bin_cursor.p;
+    fb.entry_base = (unsigned long long*)c->entry_base.p;
+    fb.entries    = (float*)c->entries.p;
     fb.counts     = (uint32_t*)c->counts.p;
     fb.offsets    = (uint32_t*)c->offsets.p;
     fb.partial    = (uint32_t*)c->partial.p;
     fb.view_base  = (unsigned long long*)c->view_base.p;
-    fb.frags      = (unsigned long long*)c->frags.p;
-    fb.frag_cap   = c->frags.bytes / 8;
-    fb.tex_packed = (float*)c->tex_packed.p;
+    fb.frags      = (uint4*)c->frags.p;
+    fb.frag_cap   = c->frags.bytes / sizeof(uint4);
     fb.rec_n      = (uint8_t*)c->rec_n.p;
     fb.records    = (uint2*)c->records.p;
     fb.stats      = (DevStats*)c->stats.p;
@@ -243,9 +244,9 @@ int trips_context_create(TripsContext** out, int device)
 void trips_context_destroy(TripsContext* c)
 {
     if (!c) return;
-    DevBuf* all[] = {&c->views, &c->cams, &c->rec, &c->depth, &c->nlay, &c->counts, &c->offsets, &c->partial, &c->view_base,
-                     &c->frags, &c->tex_packed, &c->rec_n, &c->records, &c->stats, &c->ticket, &c->g_tex, &c->g_conf,
-                     &c->g_pos, &c->g_small, &c->adam_tab};
+    DevBuf* all[] = {&c->views, &c->cams, &c->bin_count, &c->bin_cursor, &c->entry_base, &c->entries, &c->counts, &c->offsets,
+                     &c->partial, &c->view_base, &c->frags, &c->rec_n, &c->records, &c->stats, &c->ticket, &c->egrad, &c->g_tex,
+                     &c->g_conf, &c->g_pos, &c->g_small, &c->adam_tab};
     for (DevBuf* b : all) free_buf(*b);
     c->timers.destroy();
     if (c->h_pinned) cudaFreeHost(c->h_pinned);
@@ -298,6 +299,22 @@ int trips_forward(TripsContext* ctx, const TripsScene* scene, const TripsView* v
         for (int l = g.L; l <= TRIPS_MAX_LAYERS; ++l) g.base[l] = (int)base;
         if (base > (1ll << 30)) return fail(ctx, TRIPS_ERR_TOO_LARGE, "pyramid has more than 2^30 pixels");
         g.P = (int)base;
+        int tb = 0;
+        for (int l = 0; l < TRIPS_MAX_LAYERS; ++l)
+        {
+            g.tile_base[l] = tb;
+            g.tiles_x[l]   = 1;
+            if (l < g.L)
+            {
+                g.tiles_x[l] = (g.W[l] + kTileW - 1) / kTileW;
+                tb += g.tiles_x[l] * ((g.H[l] + kTileH - 1) / kTileH);
+            }
+        }
+        g.tile_base[TRIPS_MAX_LAYERS] = tb;
+        g.n_tiles = tb;
+        g.bins_x  = ((w - 1) >> kBinShift) + 1;
+        g.bins_y  = ((h - 1) >> kBinShift) + 1;
+        g.n_bins  = g.bins_x * g.bins_y;
     }
     const int B       = n_views;
     const size_t N    = (size_t)scene->n_points;
@@ -305,18 +322,20 @@ int trips_forward(TripsContext* ctx, const TripsScene* scene, const TripsView* v
     const int C       = scene->channels;
     const int nchunks = (int)((P + kScanChunk - 1) / kScanChunk);
     if (N * 4ull * g.L >= (1ull << 32)) return fail(ctx, TRIPS_ERR_TOO_LARGE, "a view could hold more than 2^32 fragments");
-    if ((unsigned long long)B * ((P + 31) / 32) >= (1ull << 32)) return fail(ctx, TRIPS_ERR_TOO_LARGE, "too many pixel tiles");
+    if ((unsigned long long)B * (unsigned long long)g.n_tiles >= (1ull << 32)) return fail(ctx, TRIPS_ERR_TOO_LARGE, "too many pixel tiles");
+    const size_t ES = (size_t)entry_stride(C);
 
     CU_CHECK(ctx, ensure(ctx->views, sizeof(TripsView) * B));
     CU_CHECK(ctx, ensure(ctx->cams, sizeof(CamConst) * B));
-    CU_CHECK(ctx, ensure(ctx->rec, sizeof(float4) * N * B + 16));
-    CU_CHECK(ctx, ensure(ctx->depth, sizeof(float) * N * B + 16));
-    CU_CHECK(ctx, ensure(ctx->nlay, N * B + 16));
+    CU_CHECK(ctx, ensure(ctx->bin_count, sizeof(uint32_t) * (size_t)g.n_bins * B));
+    CU_CHECK(ctx, ensure(ctx->bin_cursor, sizeof(uint32_t) * (size_t)g.n_bins * B));
+    CU_CHECK(ctx, ensure(ctx->entry_base, sizeof(unsigned long long) * (B + 1)));
+    // entries are sized for the worst case (every point visible in every view): no host round trip is needed to size them
+    CU_CHECK(ctx, ensure(ctx->entries, sizeof(float) * ES * N * B + 16));
     CU_CHECK(ctx, ensure(ctx->counts, sizeof(uint32_t) * P * B));
     CU_CHECK(ctx, ensure(ctx->offsets, sizeof(uint32_t) * P * B));
     CU_CHECK(ctx, ensure(ctx->partial, sizeof(uint32_t) * (size_t)nchunks * B));
     CU_CHECK(ctx, ensure(ctx->view_base, sizeof(unsigned long long) * (B + 1)));
-    CU_CHECK(ctx, ensure(ctx->tex_packed, sizeof(float) * (size_t)scene->n_tex * C));
     CU_CHECK(ctx, ensure(ctx->stats, sizeof(DevStats)));
     CU_CHECK(ctx, ensure(ctx->ticket, sizeof(unsigned) * (size_t)(B > 64 ? B : 64)));
     if (params->train)
@@ -324,7 +343,7 @@ int trips_forward(TripsContext* ctx, const TripsScene* scene, const TripsView* v
         CU_CHECK(ctx, ensure(ctx->rec_n, P * B));
         CU_CHECK(ctx, ensure(ctx->records, sizeof(uint2) * 16 * P * B));
     }
-    if (ctx->frags.bytes == 0) CU_CHECK(ctx, ensure(ctx->frags, 8 * 1024 * 1024));
+    if (ctx->frags.bytes == 0) CU_CHECK(ctx, ensure(ctx->frags, 16 * 1024 * 1024));
     size_t pinned_need = sizeof(unsigned long long) * (B + 1) + sizeof(DevStats);
     if (ctx->h_pinned_bytes < pinned_need)
     {
@@ -343,8 +362,7 @@ int trips_forward(TripsContext* ctx, const TripsScene* scene, const TripsView* v
     STAGE(ctx, TRIPS_STAGE_SETUP, 1, st,
           launch_setup_cams((const TripsView*)ctx->views.p, B, scene->poses, scene->n_images, scene->intrinsics,
                             scene->n_cameras, (CamConst*)ctx->cams.p, fb.stats, st));
-    STAGE(ctx, TRIPS_STAGE_PACK, 1, st, launch_pack_texture(sp, fb.tex_packed, st));
-    if (N > 0) STAGE(ctx, TRIPS_STAGE_PROJECT_COUNT, 1, st, launch_project_count(sp, (const CamConst*)ctx->cams.p, g, *params, B, fb, st));
+    STAGE(ctx, TRIPS_STAGE_BIN_POINTS, N > 0 ? 3 : 1, st, launch_bin_points(sp, (const CamConst*)ctx->cams.p, g, *params, B, fb, st));
     {
         FwdBuffers fscan = fb;
         fscan.frag_cap   = ~0ull;  // sizing pass: the list buffer is grown below, nothing can overflow yet
@@ -358,13 +376,14 @@ int trips_forward(TripsContext* ctx, const TripsScene* scene, const TripsView* v
     CU_CHECK(ctx, cudaMemcpyAsync(h_stats, ctx->stats.p, sizeof(DevStats), cudaMemcpyDeviceToHost, st));
     CU_CHECK(ctx, cudaStreamSynchronize(st));
     const unsigned long long total = h_base[B];
-    if (total * 8 > ctx->frags.bytes)
+    if (total * sizeof(uint4) > ctx->frags.bytes)
     {
-        CU_CHECK(ctx, ensure(ctx->frags, (size_t)total * 8, 1.25));
+        CU_CHECK(ctx, ensure(ctx->frags, (size_t)total * sizeof(uint4), 1.25));
         fb = fwd_buffers(ctx);
     }
-    ctx->total_frags = total;
-    if (N > 0) STAGE(ctx, TRIPS_STAGE_COLLECT, 1, st, launch_collect(sp, g, B, fb, st));
+    ctx->total_frags   = total;
+    ctx->total_entries = h_stats->visible;
+    if (N > 0) STAGE(ctx, TRIPS_STAGE_COLLECT, 1, st, launch_collect(sp, g, B, fb, ctx->sm_count, st));
     LayerPtrs out{};
     for (int l = 0; l < g.L; ++l) out.p[l] = out_layers[l];
     STAGE(ctx, TRIPS_STAGE_SORT_BLEND, 1, st, launch_sort_blend(sp, g, *params, B, fb, out, ctx->sm_count, st));
@@ -400,18 +419,22 @@ int trips_backward(TripsContext* ctx, const TripsScene* scene, const float* cons
     const int B = ctx->B, C = ctx->C;
     const size_t N = (size_t)ctx->N, n_tex = (size_t)ctx->n_tex;
 
+    const size_t GS = (size_t)egrad_stride(C);
+    CU_CHECK(ctx, ensure(ctx->egrad, sizeof(float) * GS * (size_t)ctx->total_entries + 16, 1.25));
     CU_CHECK(ctx, ensure(ctx->g_tex, sizeof(float) * n_tex * C));
     CU_CHECK(ctx, ensure(ctx->g_conf, sizeof(float) * n_tex));
     CU_CHECK(ctx, ensure(ctx->g_pos, sizeof(float4) * N + 16));
     const size_t small_bytes = sizeof(double) * (TRIPS_MAX_CHANNELS + (size_t)B * 11);
     CU_CHECK(ctx, ensure(ctx->g_small, small_bytes));
     BwdBuffers bb;
+    bb.egrad        = (float*)ctx->egrad.p;
     bb.g_tex_packed = (float*)ctx->g_tex.p;
     bb.g_conf       = (float*)ctx->g_conf.p;
     bb.g_pos_size   = (float4*)ctx->g_pos.p;
     bb.g_bg         = (double*)ctx->g_small.p;
     bb.g_pose       = bb.g_bg + TRIPS_MAX_CHANNELS;
     bb.g_k          = bb.g_pose + (size_t)B * 6;
+    if (ctx->total_entries) CU_CHECK(ctx, cudaMemsetAsync(ctx->egrad.p, 0, sizeof(float) * GS * (size_t)ctx->total_entries, st));
     CU_CHECK(ctx, cudaMemsetAsync(ctx->g_tex.p, 0, sizeof(float) * n_tex * C, st));
     CU_CHECK(ctx, cudaMemsetAsync(ctx->g_conf.p, 0, sizeof(float) * n_tex, st));
     if (N > 0) CU_CHECK(ctx, cudaMemsetAsync(ctx->g_pos.p, 0, sizeof(float4) * N, st));
@@ -426,8 +449,9 @@ int trips_backward(TripsContext* ctx, const TripsScene* scene, const float* cons
     const bool cam_grads = grads->pose_tangent || grads->intrinsics;
     STAGE(ctx, TRIPS_STAGE_BACKWARD, 1, st,
           launch_blend_backward(sp, (const CamConst*)ctx->cams.p, g, ctx->params, B, fb, bb, gin, cam_grads, ctx->sm_count, st));
-    const int n_unpack = (grads->texture ? 1 : 0) + ((grads->points || grads->point_size) ? 1 : 0) + 1;
-    STAGE(ctx, TRIPS_STAGE_UNPACK, n_unpack, st, launch_unpack_grads(sp, (const CamConst*)ctx->cams.p, B, bb, *grads, st));
+    const int n_unpack = (N > 0 ? 1 : 0) + (grads->texture ? 1 : 0) + ((grads->points || grads->point_size) ? 1 : 0) + 1;
+    STAGE(ctx, TRIPS_STAGE_UNPACK, n_unpack, st,
+          launch_unpack_grads(sp, (const CamConst*)ctx->cams.p, B, fb, bb, *grads, ctx->sm_count, st));
     return TRIPS_OK;
 }
 
@@ -507,8 +531,8 @@ int trips_get_stage_times(TripsContext* ctx, double* ms, int64_t* timed_calls, i
 
 const char* trips_stage_name(int stage)
 {
-    static const char* names[TRIPS_NUM_STAGES] = {"setup_cams", "pack_texture", "project_count", "scan", "collect",
-                                                  "sort_blend", "blend_backward", "unpack_grads", "adam", "l1_loss"};
+    static const char* names[TRIPS_NUM_STAGES] = {"setup_cams", "bin_points", "scan", "collect", "sort_blend",
+                                                  "blend_backward", "unpack_grads", "adam", "l1_loss"};
     return (stage >= 0 && stage < TRIPS_NUM_STAGES) ? names[stage] : "?";
 }
 
@@ -546,14 +570,38 @@ int trips_debug_points(TripsContext* ctx, int view, float* depth, int32_t* nlaye
     if (!ctx->have_forward) return fail(ctx, TRIPS_ERR_NO_FORWARD, "no forward pass");
     if (view < 0 || view >= ctx->B) return fail(ctx, TRIPS_ERR_INVALID_ARG, "view out of range");
     cudaStream_t st = (cudaStream_t)stream;
-    const size_t N = (size_t)ctx->N, off = (size_t)view * N;
-    std::vector<uint8_t> nl(N);
-    if (depth) CU_CHECK(ctx, cudaMemcpyAsync(depth, (float*)ctx->depth.p + off, sizeof(float) * N, cudaMemcpyDeviceToHost, st));
-    if (record) CU_CHECK(ctx, cudaMemcpyAsync(record, (float4*)ctx->rec.p + off, sizeof(float4) * N, cudaMemcpyDeviceToHost, st));
-    if (nlayers && N) CU_CHECK(ctx, cudaMemcpyAsync(nl.data(), (uint8_t*)ctx->nlay.p + off, N, cudaMemcpyDeviceToHost, st));
+    const size_t N = (size_t)ctx->N, ES = (size_t)entry_stride(ctx->C);
+    unsigned long long eb[2];
+    CU_CHECK(ctx, cudaMemcpyAsync(eb, (unsigned long long*)ctx->entry_base.p + view, sizeof(eb), cudaMemcpyDeviceToHost, st));
     CU_CHECK(ctx, cudaStreamSynchronize(st));
-    if (nlayers)
-        for (size_t i = 0; i < N; ++i) nlayers[i] = nl[i];
+    const size_t n = (size_t)(eb[1] - eb[0]);
+    std::vector<float> e(n * ES);
+    if (n) CU_CHECK(ctx, cudaMemcpyAsync(e.data(), (float*)ctx->entries.p + eb[0] * ES, sizeof(float) * n * ES, cudaMemcpyDeviceToHost, st));
+    CU_CHECK(ctx, cudaStreamSynchronize(st));
+    // the per-point arrays of the reference (depth = -1 for culled points) are rebuilt from the view's entries
+    for (size_t i = 0; i < N; ++i)
+    {
+        if (depth) depth[i] = -1.f;
+        if (nlayers) nlayers[i] = 0;
+        if (record) record[4 * i] = record[4 * i + 1] = record[4 * i + 2] = record[4 * i + 3] = 0.f;
+    }
+    for (size_t k = 0; k < n; ++k)
+    {
+        const float* en = e.data() + k * ES;
+        int32_t pid, nl;
+        memcpy(&pid, en + 4, 4);
+        memcpy(&nl, en + 7, 4);
+        if (pid < 0 || (size_t)pid >= N) continue;
+        if (depth) depth[pid] = en[3];
+        if (nlayers) nlayers[pid] = nl;
+        if (record)
+        {
+            record[4 * (size_t)pid + 0] = en[0];
+            record[4 * (size_t)pid + 1] = en[1];
+            record[4 * (size_t)pid + 2] = en[2];
+            record[4 * (size_t)pid + 3] = en[11];
+        }
+    }
     return TRIPS_OK;
 }
 
@@ -580,8 +628,10 @@ int trips_debug_lists(TripsContext* ctx, int view, int32_t* counts, int64_t* off
     }
     if (frags && nf)
     {
-        CU_CHECK(ctx, cudaMemcpyAsync(frags, (unsigned long long*)ctx->frags.p + vb[0], sizeof(uint64_t) * nf, cudaMemcpyDeviceToHost, st));
+        std::vector<uint4> f(nf);
+        CU_CHECK(ctx, cudaMemcpyAsync(f.data(), (uint4*)ctx->frags.p + vb[0], sizeof(uint4) * nf, cudaMemcpyDeviceToHost, st));
         CU_CHECK(ctx, cudaStreamSynchronize(st));
+        for (unsigned long long i = 0; i < nf; ++i) frags[i] = ((uint64_t)f[i].y << 32) | f[i].x;
     }
     return TRIPS_OK;
 }
@@ -595,9 +645,25 @@ int trips_debug_records(TripsContext* ctx, int view, int32_t* nrec, int32_t* rec
     const size_t P = (size_t)ctx->geom.P, off = (size_t)view * P;
     std::vector<uint8_t> n(P);
     std::vector<uint2> r(P * 16);
+    const size_t ES = (size_t)entry_stride(ctx->C);
+    unsigned long long eb[2];
+    CU_CHECK(ctx, cudaMemcpyAsync(eb, (unsigned long long*)ctx->entry_base.p + view, sizeof(eb), cudaMemcpyDeviceToHost, st));
     CU_CHECK(ctx, cudaMemcpyAsync(n.data(), (uint8_t*)ctx->rec_n.p + off, P, cudaMemcpyDeviceToHost, st));
     CU_CHECK(ctx, cudaMemcpyAsync(r.data(), (uint2*)ctx->records.p + off * 16, sizeof(uint2) * 16 * P, cudaMemcpyDeviceToHost, st));
     CU_CHECK(ctx, cudaStreamSynchronize(st));
+    const size_t n_e = (size_t)(eb[1] - eb[0]);
+    std::vector<float> e(n_e * ES);
+    if (n_e) CU_CHECK(ctx, cudaMemcpyAsync(e.data(), (float*)ctx->entries.p + eb[0] * ES, sizeof(float) * n_e * ES, cudaMemcpyDeviceToHost, st));
+    CU_CHECK(ctx, cudaStreamSynchronize(st));
+    // records hold the entry index of the fragment's point; report the point id
+    for (size_t p = 0; p < P; ++p)
+        for (int j = 0; j < n[p]; ++j)
+        {
+            const uint32_t ei = r[p * 16 + j].x;
+            uint32_t pid      = 0xffffffffu;
+            if (ei < n_e) memcpy(&pid, e.data() + (size_t)ei * ES + 4, 4);
+            r[p * 16 + j].x = pid;
+        }
     for (size_t p = 0; p < P; ++p)
     {
         if (nrec) nrec[p] = n[p];

@@ -10,15 +10,22 @@ namespace trips
 {
 constexpr float kAlphaCut = 0.001f;  // ALPHA_DEST_CUTOFF, RenderForward.cu:907
 constexpr unsigned kFull  = 0xffffffffu;
+constexpr int kBinShift   = 5;   // visible points are bucketed by 32x32-pixel screen bins of layer 0
+constexpr int kTileW      = 8;   // one warp renders / differentiates an 8x4 pixel tile
+constexpr int kTileH      = 4;
 
-// Pyramid geometry shared by all views of a call: ceil-halved layer sizes and their pixel offsets.
+// Pyramid geometry shared by all views of a call.
 struct Geom
 {
     int L;
-    int W[TRIPS_MAX_LAYERS];
+    int W[TRIPS_MAX_LAYERS];            // ceil-halved layer sizes (PointRenderer.cu:385-389)
     int H[TRIPS_MAX_LAYERS];
-    int base[TRIPS_MAX_LAYERS + 1];
-    int P;
+    int base[TRIPS_MAX_LAYERS + 1];     // first pixel of every layer in the per-view pixel arrays (row-major)
+    int P;                              // pixels per view
+    int tiles_x[TRIPS_MAX_LAYERS];      // 8x4 pixel tiles per layer row
+    int tile_base[TRIPS_MAX_LAYERS + 1];
+    int n_tiles;                        // tiles per view
+    int bins_x, bins_y, n_bins;         // 32x32 screen bins of layer 0
 };
 
 // Per-view constants built on the device from the pose / intrinsics tensors (setup_cams_kernel).
@@ -51,21 +58,31 @@ struct DevStats
     unsigned int status;
 };
 
+// A visible point of one view ("entry"): everything the later stages need, gathered once, 16-byte aligned, and
+// stored in screen-bin order so that fragments of neighbouring pixels read neighbouring entries.
+//   float  0..3   u, v (layer-0 image position), size in pixels, view-space depth
+//   float  4..7   point id (bits), confidence, raw point size, number of layers written (bits)
+//   float  8..11  world position x, y, z, texture index (bits)
+//   float 12..    descriptor row (C floats, padded to a multiple of 4)
+__host__ __device__ constexpr int entry_stride(int C) { return 12 + ((C + 3) & ~3); }
+// Gradient accumulator of an entry: xyz + raw size | confidence, 3 pad | descriptor row.
+__host__ __device__ constexpr int egrad_stride(int C) { return 8 + ((C + 3) & ~3); }
+
 // Everything the forward kernels need besides the scene (all device pointers into context scratch).
 struct FwdBuffers
 {
-    float4* rec;            // [B,N] u, v, size_px, texture index bits
-    float* depth;           // [B,N] view-space z, -1 = culled
-    uint8_t* nlay;          // [B,N] number of layers written
-    uint32_t* counts;       // [B,P] list lengths
-    uint32_t* offsets;      // [B,P] list start within the view (list end after the collect pass)
-    uint32_t* partial;      // [B,nchunks] scan partials
-    unsigned long long* view_base;   // [B+1] first fragment of each view in `frags`
-    unsigned long long* frags;       // [frag_cap] 64-bit keys: depth bits << 32 | point id
+    uint32_t* bin_count;              // [B,n_bins] visible points per screen bin
+    uint32_t* bin_cursor;             // [B,n_bins] first entry of the bin within the view, advanced while scattering
+    unsigned long long* entry_base;   // [B+1] first entry of each view
+    float* entries;                   // [sum V_b, entry_stride]
+    uint32_t* counts;                 // [B,P] list lengths
+    uint32_t* offsets;                // [B,P] list start within the view (list end after the collect pass)
+    uint32_t* partial;                // [B,nchunks] scan partials
+    unsigned long long* view_base;    // [B+1] first fragment of each view in `frags`
+    uint4* frags;                     // [frag_cap] x = point id, y = depth bits (y:x = 64-bit sort key), z = alpha bits, w = entry index within the view
     unsigned long long frag_cap;
-    float* tex_packed;      // [n_tex,C] descriptors, one row per point
-    uint8_t* rec_n;         // [B,P] records kept for backward
-    uint2* records;         // [B,P,16] (point id, alpha bits)
+    uint8_t* rec_n;                   // [B,P] records kept for backward
+    uint2* records;                   // [B,P,16] (entry index within the view, alpha bits)
     DevStats* stats;
     unsigned int* ticket;
 };
@@ -84,6 +101,7 @@ struct ScenePtrs
 
 struct BwdBuffers
 {
+    float* egrad;         // [sum V_b, egrad_stride] per-entry gradient accumulators
     float* g_tex_packed;  // [n_tex,C]
     float* g_conf;        // [n_tex]
     float4* g_pos_size;   // [N] xyz gradient + raw point-size gradient
@@ -174,33 +192,36 @@ __device__ __forceinline__ float layer_factor(float ps, int layer, int L, float*
     return f;
 }
 
-__device__ __forceinline__ void pixel_to_layer(const Geom& g, int p, int& layer, int& gx, int& gy)
+// Pixel handled by `lane` of the warp that owns 8x4 tile `tile` of a view; p = -1 outside the image.
+__device__ __forceinline__ void tile_pixel(const Geom& g, int tile, int lane, int& layer, int& gx, int& gy, int& p)
 {
     int l = 0;
 #pragma unroll
     for (int i = 1; i < TRIPS_MAX_LAYERS; ++i)
-        if (i < g.L && p >= g.base[i]) l = i;
-    int t = p - g.base[l];
-    layer = l;
-    gy    = t / g.W[l];
-    gx    = t - gy * g.W[l];
+        if (i < g.L && tile >= g.tile_base[i]) l = i;
+    const int t  = tile - g.tile_base[l];
+    const int ty = t / g.tiles_x[l];
+    const int tx = t - ty * g.tiles_x[l];
+    layer        = l;
+    gx           = tx * kTileW + (lane & (kTileW - 1));
+    gy           = ty * kTileH + (lane >> 3);
+    p            = (gx < g.W[l] && gy < g.H[l]) ? g.base[l] + gy * g.W[l] + gx : -1;
 }
 
 // ---- launchers (forward.cu / backward.cu / adam.cu) ----
 cudaError_t launch_setup_cams(const TripsView* d_views, int B, const double* poses, int n_images, const float* intrinsics,
                               int n_cameras, CamConst* cams, DevStats* stats, cudaStream_t st);
-cudaError_t launch_pack_texture(const ScenePtrs& sc, float* tex_packed, cudaStream_t st);
-cudaError_t launch_project_count(const ScenePtrs& sc, const CamConst* cams, const Geom& g, const TripsRenderParams& pr,
-                                 int B, const FwdBuffers& fb, cudaStream_t st);
+cudaError_t launch_bin_points(const ScenePtrs& sc, const CamConst* cams, const Geom& g, const TripsRenderParams& pr, int B,
+                              const FwdBuffers& fb, cudaStream_t st);
 cudaError_t launch_scan(const Geom& g, int B, int k_keep, const FwdBuffers& fb, int nchunks, cudaStream_t st);
-cudaError_t launch_collect(const ScenePtrs& sc, const Geom& g, int B, const FwdBuffers& fb, cudaStream_t st);
+cudaError_t launch_collect(const ScenePtrs& sc, const Geom& g, int B, const FwdBuffers& fb, int sm_count, cudaStream_t st);
 cudaError_t launch_sort_blend(const ScenePtrs& sc, const Geom& g, const TripsRenderParams& pr, int B, const FwdBuffers& fb,
                               const LayerPtrs& out, int sm_count, cudaStream_t st);
 cudaError_t launch_blend_backward(const ScenePtrs& sc, const CamConst* cams, const Geom& g, const TripsRenderParams& pr,
                                   int B, const FwdBuffers& fb, const BwdBuffers& bb, const ConstLayerPtrs& grad_in,
                                   bool want_cam_grads, int sm_count, cudaStream_t st);
-cudaError_t launch_unpack_grads(const ScenePtrs& sc, const CamConst* cams, int B, const BwdBuffers& bb,
-                                const TripsGrads& out, cudaStream_t st);
+cudaError_t launch_unpack_grads(const ScenePtrs& sc, const CamConst* cams, int B, const FwdBuffers& fb, const BwdBuffers& bb,
+                                const TripsGrads& out, int sm_count, cudaStream_t st);
 cudaError_t launch_adam(const TripsAdamTensor* d_tensors, const int64_t* d_block_start, int n_tensors, int64_t total_blocks,
                         cudaStream_t st);
 struct L1Args
@@ -212,6 +233,6 @@ struct L1Args
     int L;
 };
 cudaError_t launch_l1_loss(const L1Args& a, int64_t total, double* loss_out, int sm_count, cudaStream_t st);
-constexpr int kScanChunk   = 2048;
+constexpr int kScanChunk    = 2048;
 constexpr int kAdamPerBlock = 1024 * 4;  // elements handled by one Adam block
 }  // namespace trips

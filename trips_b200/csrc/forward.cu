@@ -1,7 +1,7 @@
 // Forward rasterizer: project + count, scan, collect, per-pixel top-K sort and front-to-back blend.
 //
 // Stage map to the reference (src/lib/rendering/RenderForward.cu):
-//   project_count_kernel  <- CountAndCollectTiled        (:168-366)
+//   bin_count / bin_scan / bin_scatter kernels <- CountAndCollectTiled (:168-366)
 //   scan_*_kernel         <- cub::DeviceScan + host glue (:1155-1232), here one device-side scan per view, no host sync
 //   collect_kernel        <- SplattingPass               (:368-436)
 //   sort_blend_kernel     <- FastSortFusedNew            (:474-1059)
@@ -77,119 +77,197 @@ cudaError_t launch_setup_cams(const TripsView* d_views, int B, const double* pos
 }
 
 // ------------------------------------------------------------------------------------------------------------
-// descriptor repack: texture [C,n_tex] -> rows [n_tex,C] so that one fragment gathers one 4C-byte row
+// project + cull + layer select, bucket the visible points of every view by 32x32 screen bin, count fragments
+//
+// Three kernels: (1) count visible points per (view, bin); (2) exclusive scan of the bin counts; (3) project again,
+// take a slot in the bin, write the point's 16-byte-aligned entry there and add 1 to the list length of every
+// pixel its 2x2 footprints touch, on each pyramid layer it is drawn into.  Replaces CountAndCollectTiled
+// (RenderForward.cu:168-366).  Projecting twice costs two coalesced reads of position + size per view and avoids
+// writing and re-reading a per-point record for all N points.
 // ------------------------------------------------------------------------------------------------------------
-template <int C>
-__global__ void pack_texture_kernel(const float* __restrict__ tex, int n_tex, float* __restrict__ out)
+struct Projected
 {
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < (size_t)n_tex; i += (size_t)gridDim.x * blockDim.x)
+    float u, v, z, ps, rad;
+    int tex;
+    bool ok;
+};
+
+__device__ __forceinline__ Projected project_visible(const ScenePtrs& sc, const CamConst& cam, const Geom& g,
+                                                     const TripsRenderParams& pr, size_t bN, int i, float fxc)
+{
+    Projected r;
+    r.ok  = false;
+    r.tex = sc.index ? __ldg(sc.index + i) : i;
+    if (pr.viewer_only)
     {
-        float v[C];
-#pragma unroll
-        for (int c = 0; c < C; ++c) v[c] = __ldg(tex + (size_t)c * n_tex + i);
-#pragma unroll
-        for (int c = 0; c < C; ++c) out[i * C + c] = v[c];
+        // discard_point_for_confidence, RenderForward.cu:122-130
+        if ((unsigned)r.tex < (unsigned)sc.n_tex && __ldg(sc.confidence + r.tex) < pr.stability_cutoff_value) return r;
     }
+    else if (pr.train && sc.dropout)
+    {
+        if (__ldg(sc.dropout + bN + i) == 1.f) return r;
+    }
+    const float4 p = __ldg(sc.position + i);
+    const float s  = tm_softplus(__ldg(sc.point_size + i));
+    project_point(cam, p.x, p.y, p.z, r.u, r.v, r.z);
+    r.rad = fxc * p.w / r.z;
+    r.ps  = fxc * s / r.z;
+    bool ok = !(r.z <= 0.f || r.u < 0.f || r.u >= (float)(g.W[0] - 1) || r.v < 0.f || r.v >= (float)(g.H[0] - 1));
+    if (ok && pr.drop_out_points_by_radius && (float)(int)r.rad < pr.drop_out_radius_threshold) ok = false;
+    r.ok = ok;
+    return r;
 }
 
-cudaError_t launch_pack_texture(const ScenePtrs& sc, float* tex_packed, cudaStream_t st)
-{
-    int blocks = (int)min((size_t)148 * 16, ((size_t)sc.n_tex + 255) / 256);
-    if (blocks < 1) blocks = 1;
-    switch (sc.C)
-    {
-        case 3: pack_texture_kernel<3><<<blocks, 256, 0, st>>>(sc.texture, sc.n_tex, tex_packed); break;
-        case 4: pack_texture_kernel<4><<<blocks, 256, 0, st>>>(sc.texture, sc.n_tex, tex_packed); break;
-        case 6: pack_texture_kernel<6><<<blocks, 256, 0, st>>>(sc.texture, sc.n_tex, tex_packed); break;
-        case 8: pack_texture_kernel<8><<<blocks, 256, 0, st>>>(sc.texture, sc.n_tex, tex_packed); break;
-        case 16: pack_texture_kernel<16><<<blocks, 256, 0, st>>>(sc.texture, sc.n_tex, tex_packed); break;
-        default: return cudaErrorInvalidValue;
-    }
-    return cudaGetLastError();
-}
-
-// ------------------------------------------------------------------------------------------------------------
-// project + cull + layer select + count
-// ------------------------------------------------------------------------------------------------------------
-__global__ __launch_bounds__(256) void project_count_kernel(ScenePtrs sc, const CamConst* __restrict__ cams,
-                                                            const __grid_constant__ Geom g,
-                                                            TripsRenderParams pr, FwdBuffers fb)
+__global__ __launch_bounds__(256) void bin_count_kernel(ScenePtrs sc, const CamConst* __restrict__ cams,
+                                                        const __grid_constant__ Geom g, TripsRenderParams pr, FwdBuffers fb)
 {
     __shared__ CamConst cam;
     const int b = blockIdx.y;
     if (threadIdx.x < sizeof(CamConst) / 4) ((int*)&cam)[threadIdx.x] = ((const int*)&cams[b])[threadIdx.x];
     __syncthreads();
-    const int N        = sc.N;
-    const size_t bN    = (size_t)b * N;
-    uint32_t* counts   = fb.counts + (size_t)b * g.P;
-    const float fxc    = cam.fx * cam.cfx;
-    const float w_hi   = (float)(g.W[0] - 1);
-    const float h_hi   = (float)(g.H[0] - 1);
-    unsigned n_visible = 0;
-    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < N; i += gridDim.x * blockDim.x)
+    const size_t bN = (size_t)b * sc.N;
+    const float fxc = cam.fx * cam.cfx;
+    uint32_t* bins  = fb.bin_count + (size_t)b * g.n_bins;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < sc.N; i += gridDim.x * blockDim.x)
     {
-        float depth_out = -1.f;
-        uint8_t nl_out  = 0;
-        float4 rec_out  = make_float4(0.f, 0.f, 0.f, 0.f);
-        bool skip       = false;
-        int tex         = sc.index ? __ldg(sc.index + i) : i;
-        if (pr.viewer_only)
-        {
-            // discard_point_for_confidence, RenderForward.cu:122-130
-            if ((unsigned)tex < (unsigned)sc.n_tex && __ldg(sc.confidence + tex) < pr.stability_cutoff_value) skip = true;
-        }
-        else if (pr.train && sc.dropout)
-        {
-            if (__ldg(sc.dropout + bN + i) == 1.f) skip = true;
-        }
-        if (!skip)
-        {
-            const float4 p = __ldg(sc.position + i);
-            const float s  = tm_softplus(__ldg(sc.point_size + i));
-            float u, v, z;
-            project_point(cam, p.x, p.y, p.z, u, v, z);
-            float rad      = fxc * p.w / z;
-            const float ps = fxc * s / z;
-            bool ok        = !(z <= 0.f || u < 0.f || u >= w_hi || v < 0.f || v >= h_hi);
-            if (ok && pr.drop_out_points_by_radius && (float)(int)rad < pr.drop_out_radius_threshold) ok = false;
-            if (ok)
-            {
-                depth_out = z;
-                rec_out   = make_float4(u, v, ps, __int_as_float(tex));
-                int hi    = 0;
-                if (ps > 1.f) hi = min(tm_ceil_log2(ps), g.L - 1);
-                int layer = 0;
-                float x = u, y = v;
-                for (; layer < hi + 1; ++layer, x *= 0.5f, y *= 0.5f, rad *= 0.5f)
-                {
-                    int px = __float2int_rd(x), py = __float2int_rd(y);
-                    if (px < 0 || px >= g.W[layer] - 1 || py < 0 || py >= g.H[layer] - 1) break;
-                    if (pr.drop_out_points_by_radius && (float)(int)rad < pr.drop_out_radius_threshold) break;
-                    uint32_t* c0 = counts + g.base[layer] + py * g.W[layer] + px;
-                    atomicAdd(c0, 1u);
-                    atomicAdd(c0 + 1, 1u);
-                    atomicAdd(c0 + g.W[layer], 1u);
-                    atomicAdd(c0 + g.W[layer] + 1, 1u);
-                }
-                nl_out = (uint8_t)layer;
-                n_visible++;
-            }
-        }
-        fb.depth[bN + i] = depth_out;
-        fb.nlay[bN + i]  = nl_out;
-        fb.rec[bN + i]   = rec_out;
+        const Projected r = project_visible(sc, cam, g, pr, bN, i, fxc);
+        if (r.ok) atomicAdd(bins + (__float2int_rd(r.v) >> kBinShift) * g.bins_x + (__float2int_rd(r.u) >> kBinShift), 1u);
     }
-    // one atomic per warp for the visible-point counter
-    for (int o = 16; o > 0; o >>= 1) n_visible += __shfl_xor_sync(kFull, n_visible, o);
-    if ((threadIdx.x & 31) == 0 && n_visible) atomicAdd(&fb.stats->visible, (unsigned long long)n_visible);
 }
 
-cudaError_t launch_project_count(const ScenePtrs& sc, const CamConst* cams, const Geom& g, const TripsRenderParams& pr,
-                                 int B, const FwdBuffers& fb, cudaStream_t st)
+// one block: per view, exclusive scan of the bin counts -> first entry of every bin; entry_base = running total
+__global__ __launch_bounds__(1024) void bin_scan_kernel(const uint32_t* __restrict__ bin_count, uint32_t* __restrict__ bin_cursor,
+                                                        int n_bins, int B, unsigned long long* __restrict__ entry_base,
+                                                        DevStats* stats)
 {
-    int bx = (sc.N + 255) / 256;
-    bx     = max(1, min(bx, 148 * 8));
-    project_count_kernel<<<dim3(bx, B), 256, 0, st>>>(sc, cams, g, pr, fb);
+    __shared__ uint32_t sm[32];
+    __shared__ uint32_t carry_s;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    unsigned long long base = 0;
+    for (int b = 0; b < B; ++b)
+    {
+        const uint32_t* c = bin_count + (size_t)b * n_bins;
+        uint32_t* o       = bin_cursor + (size_t)b * n_bins;
+        if (threadIdx.x == 0) carry_s = 0;
+        __syncthreads();
+        for (int s = 0; s < n_bins; s += 1024)
+        {
+            const int i  = s + threadIdx.x;
+            uint32_t v   = (i < n_bins) ? c[i] : 0u;
+            uint32_t inc = v;
+#pragma unroll
+            for (int k = 1; k < 32; k <<= 1)
+            {
+                uint32_t t = __shfl_up_sync(kFull, inc, k);
+                if (lane >= k) inc += t;
+            }
+            if (lane == 31) sm[warp] = inc;
+            __syncthreads();
+            uint32_t wsum = sm[lane];
+            uint32_t winc = wsum;
+#pragma unroll
+            for (int k = 1; k < 32; k <<= 1)
+            {
+                uint32_t t = __shfl_up_sync(kFull, winc, k);
+                if (lane >= k) winc += t;
+            }
+            const uint32_t tot   = __shfl_sync(kFull, winc, 31);
+            const uint32_t woff  = __shfl_sync(kFull, winc - wsum, warp);
+            const uint32_t carry = carry_s;
+            if (i < n_bins) o[i] = carry + woff + inc - v;
+            __syncthreads();
+            if (threadIdx.x == 0) carry_s = carry + tot;
+            __syncthreads();
+        }
+        if (threadIdx.x == 0)
+        {
+            entry_base[b] = base;
+            base += carry_s;
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0)
+    {
+        entry_base[B]  = base;
+        stats->visible = base;
+    }
+}
+
+template <int C>
+__global__ __launch_bounds__(256) void bin_scatter_kernel(ScenePtrs sc, const CamConst* __restrict__ cams,
+                                                          const __grid_constant__ Geom g, TripsRenderParams pr, FwdBuffers fb)
+{
+    constexpr int ES = entry_stride(C);
+    __shared__ CamConst cam;
+    const int b = blockIdx.y;
+    if (threadIdx.x < sizeof(CamConst) / 4) ((int*)&cam)[threadIdx.x] = ((const int*)&cams[b])[threadIdx.x];
+    __syncthreads();
+    const size_t bN  = (size_t)b * sc.N;
+    const float fxc  = cam.fx * cam.cfx;
+    uint32_t* cursor = fb.bin_cursor + (size_t)b * g.n_bins;
+    uint32_t* counts = fb.counts + (size_t)b * g.P;
+    float* entries   = fb.entries + fb.entry_base[b] * ES;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < sc.N; i += gridDim.x * blockDim.x)
+    {
+        const Projected r = project_visible(sc, cam, g, pr, bN, i, fxc);
+        if (!r.ok) continue;
+        const int bin       = (__float2int_rd(r.v) >> kBinShift) * g.bins_x + (__float2int_rd(r.u) >> kBinShift);
+        const uint32_t slot = atomicAdd(cursor + bin, 1u);
+        // layers 0..hi, stopping where the 2x2 footprint leaves the layer (RenderForward.cu:342-363)
+        int hi = 0;
+        if (r.ps > 1.f) hi = min(tm_ceil_log2(r.ps), g.L - 1);
+        int layer = 0;
+        float x = r.u, y = r.v, rad = r.rad;
+        for (; layer < hi + 1; ++layer, x *= 0.5f, y *= 0.5f, rad *= 0.5f)
+        {
+            const int px = __float2int_rd(x), py = __float2int_rd(y);
+            if (px < 0 || px >= g.W[layer] - 1 || py < 0 || py >= g.H[layer] - 1) break;
+            if (pr.drop_out_points_by_radius && (float)(int)rad < pr.drop_out_radius_threshold) break;
+            uint32_t* c0 = counts + g.base[layer] + py * g.W[layer] + px;
+            atomicAdd(c0, 1u);
+            atomicAdd(c0 + 1, 1u);
+            atomicAdd(c0 + g.W[layer], 1u);
+            atomicAdd(c0 + g.W[layer] + 1, 1u);
+        }
+        float conf = 0.f;
+        const bool tex_ok = (unsigned)r.tex < (unsigned)sc.n_tex;
+        if (tex_ok)
+            conf = __ldg(sc.confidence + r.tex);
+        else
+            atomicOr(&fb.stats->status, TRIPS_DEV_BAD_TEXTURE_INDEX);  // the point is drawn with alpha 0
+        const float4 p = __ldg(sc.position + i);
+        float4* e      = reinterpret_cast<float4*>(entries + (size_t)slot * ES);
+        e[0]           = make_float4(r.u, r.v, r.ps, r.z);
+        e[1]           = make_float4(__int_as_float(i), conf, __ldg(sc.point_size + i), __int_as_float(layer));
+        e[2]           = make_float4(p.x, p.y, p.z, __int_as_float(tex_ok ? r.tex : -1));
+        float row[(C + 3) & ~3];
+#pragma unroll
+        for (int c = 0; c < ((C + 3) & ~3); ++c) row[c] = (c < C && tex_ok) ? __ldg(sc.texture + (size_t)c * sc.n_tex + r.tex) : 0.f;
+#pragma unroll
+        for (int c = 0; c < ((C + 3) & ~3); c += 4) e[3 + c / 4] = make_float4(row[c], row[c + 1], row[c + 2], row[c + 3]);
+    }
+}
+
+cudaError_t launch_bin_points(const ScenePtrs& sc, const CamConst* cams, const Geom& g, const TripsRenderParams& pr, int B,
+                              const FwdBuffers& fb, cudaStream_t st)
+{
+    cudaError_t e = cudaMemsetAsync(fb.bin_count, 0, sizeof(uint32_t) * (size_t)B * g.n_bins, st);
+    if (e != cudaSuccess) return e;
+    int bx = max(1, min((sc.N + 255) / 256, 148 * 8));
+    if (sc.N > 0) bin_count_kernel<<<dim3(bx, B), 256, 0, st>>>(sc, cams, g, pr, fb);
+    bin_scan_kernel<<<1, 1024, 0, st>>>(fb.bin_count, fb.bin_cursor, g.n_bins, B, fb.entry_base, fb.stats);
+    if (sc.N > 0)
+    {
+        switch (sc.C)
+        {
+            case 3: bin_scatter_kernel<3><<<dim3(bx, B), 256, 0, st>>>(sc, cams, g, pr, fb); break;
+            case 4: bin_scatter_kernel<4><<<dim3(bx, B), 256, 0, st>>>(sc, cams, g, pr, fb); break;
+            case 6: bin_scatter_kernel<6><<<dim3(bx, B), 256, 0, st>>>(sc, cams, g, pr, fb); break;
+            case 8: bin_scatter_kernel<8><<<dim3(bx, B), 256, 0, st>>>(sc, cams, g, pr, fb); break;
+            case 16: bin_scatter_kernel<16><<<dim3(bx, B), 256, 0, st>>>(sc, cams, g, pr, fb); break;
+            default: return cudaErrorInvalidValue;
+        }
+    }
     return cudaGetLastError();
 }
 
@@ -331,59 +409,94 @@ cudaError_t launch_scan(const Geom& g, int B, int k_keep, const FwdBuffers& fb, 
 }
 
 // ------------------------------------------------------------------------------------------------------------
-// collect: four threads per point write the 64-bit fragment keys into the per-pixel lists
+// collect: four threads per visible point (entry) write one 16-byte fragment per (layer, footprint pixel) into the
+// per-pixel lists: the 64-bit sort key (depth bits << 32 | point id), the fragment's alpha and the entry index.
+// Computing alpha here, where every lane holds a fragment, keeps the per-fragment arithmetic (bilinear weight,
+// confidence, layer factor) out of the per-pixel blend.  alpha = bilinear * confidence * layer factor, in the
+// operation order of FastSortFusedNew (RenderForward.cu:882-899).  Replaces SplattingPass (RenderForward.cu:368-436).
+// Entries are in screen-bin order, so the list cursors and the fragment stores of a block stay within a small
+// window of the pixel arrays.
 // ------------------------------------------------------------------------------------------------------------
-__global__ __launch_bounds__(256) void collect_kernel(int N, const __grid_constant__ Geom g, FwdBuffers fb)
+__global__ __launch_bounds__(256) void collect_kernel(int ES, const __grid_constant__ Geom g, FwdBuffers fb)
 {
-    const int b        = blockIdx.y;
-    const size_t bN    = (size_t)b * N;
-    uint32_t* cursor   = fb.offsets + (size_t)b * g.P;
+    const int b      = blockIdx.y;
+    uint32_t* cursor = fb.offsets + (size_t)b * g.P;
     const unsigned long long vbase = fb.view_base[b];
     const unsigned long long vend  = fb.view_base[b + 1];
     if (vend > fb.frag_cap) return;  // list buffer too small: the overflow status bit is already raised
-    unsigned long long* frags = fb.frags + vbase;
-    const size_t total = (size_t)N * 4;
+    uint4* frags         = fb.frags + vbase;
+    const size_t n_entry = (size_t)(fb.entry_base[b + 1] - fb.entry_base[b]);
+    const float* entries = fb.entries + fb.entry_base[b] * ES;
+    const size_t total   = n_entry * 4;
     for (size_t t = (size_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (size_t)gridDim.x * blockDim.x)
     {
-        const int i   = (int)(t >> 2);
-        const int sub = (int)(t & 3);
-        const float z = fb.depth[bN + i];
-        if (!(z > 0.f)) continue;
-        const int nl      = fb.nlay[bN + i];
-        const float4 r    = fb.rec[bN + i];
-        const unsigned long long key = ((unsigned long long)__float_as_uint(z) << 32) | (unsigned)i;
-        float x = r.x, y = r.y;
+        const size_t ei = t >> 2;
+        const int sub   = (int)(t & 3);
+        const float4 e0 = *reinterpret_cast<const float4*>(entries + ei * ES);      // u v ps z
+        const float4 e1 = *reinterpret_cast<const float4*>(entries + ei * ES + 4);  // pid conf raw nl
+        const int nl     = __float_as_int(e1.w);
+        const float conf = e1.y;
+        float x = e0.x, y = e0.y;
         for (int layer = 0; layer < nl; ++layer, x *= 0.5f, y *= 0.5f)
         {
-            int px = __float2int_rd(x) + (sub & 1), py = __float2int_rd(y) + (sub >> 1);
-            uint32_t slot = atomicAdd(cursor + g.base[layer] + py * g.W[layer] + px, 1u);
-            frags[slot]   = key;
+            const int px = __float2int_rd(x) + (sub & 1), py = __float2int_rd(y) + (sub >> 1);
+            const uint32_t slot = atomicAdd(cursor + g.base[layer] + py * g.W[layer] + px, 1u);
+            // x, y equal (u, v) * 2^-layer exactly (power-of-two scaling)
+            const float dx = fabsf(x - (float)px), dy = fabsf(y - (float)py);
+            float bl = (1.f - dx) * (1.f - dy);
+            if (dx > 1.f || dy > 1.f) bl = 0.f;
+            float a = bl * conf;
+            a *= layer_factor(e0.z, layer, g.L, nullptr);
+            frags[slot] = make_uint4(__float_as_uint(e1.x), __float_as_uint(e0.w), __float_as_uint(a), (unsigned)ei);
         }
     }
 }
 
-cudaError_t launch_collect(const ScenePtrs& sc, const Geom& g, int B, const FwdBuffers& fb, cudaStream_t st)
+cudaError_t launch_collect(const ScenePtrs& sc, const Geom& g, int B, const FwdBuffers& fb, int sm_count, cudaStream_t st)
 {
-    size_t threads = (size_t)sc.N * 4;
-    int bx         = (int)min((size_t)148 * 32, (threads + 255) / 256);
-    collect_kernel<<<dim3(max(bx, 1), B), 256, 0, st>>>(sc.N, g, fb);
+    collect_kernel<<<dim3(sm_count * 8 / max(1, min(B, 8)) + 1, B), 256, 0, st>>>(entry_stride(sc.C), g, fb);
     return cudaGetLastError();
 }
 
 // ------------------------------------------------------------------------------------------------------------
-// per-pixel top-K sort in registers + front-to-back blend
+// per-pixel top-K selection + front-to-back blend
+//
+// One warp renders an 8x4 pixel tile of one view.
+//   phase A (lane = fragment, lanes densely packed over the tile's fragments): every fragment finds its pixel by a
+//     binary search over the tile's list lengths and its rank in the pixel's list by counting the smaller 64-bit
+//     keys; ranks below K go to shared memory in sorted order together with the descriptor row of their entry (and,
+//     when training, to the backward records).  Lists longer than kRankMax take the streaming path instead: a
+//     half-warp keeps the 16 nearest fragments in registers and merges the list in chunks of 16 with bitonic
+//     compare-exchange steps over warp shuffles.
+//   phase B (lane = pixel): the sequential transmittance recurrence and the colour sum over the kept fragments.
+// Replaces FastSortFusedNew (RenderForward.cu:474-1059).
 // ------------------------------------------------------------------------------------------------------------
 typedef unsigned long long u64;
-constexpr u64 kInfKey = 0xffffffffffffffffull;
+constexpr u64 kInfKey    = 0xffffffffffffffffull;
+constexpr int kRankMax   = 192;  // longest list ranked by counting; longer lists use the streaming path
+constexpr int kSortedPad = 17;   // row pitch (entries) of the per-pixel sorted lists in shared memory
+constexpr int kSbThreads = 128;
+constexpr int kSbWarps   = kSbThreads / 32;
 
-__device__ __forceinline__ u64 cmpx(u64 key, int j_mask, bool keep_min)
+struct KeyVal
 {
-    u64 other = __shfl_xor_sync(kFull, key, j_mask);
-    return keep_min ? min(key, other) : max(key, other);
+    u64 key;
+    uint32_t alpha;
+    uint32_t eidx;
+};
+
+__device__ __forceinline__ KeyVal cmpx(KeyVal v, int j_mask, bool keep_min)
+{
+    KeyVal o;
+    o.key         = __shfl_xor_sync(kFull, v.key, j_mask);
+    o.alpha       = __shfl_xor_sync(kFull, v.alpha, j_mask);
+    o.eidx        = __shfl_xor_sync(kFull, v.eidx, j_mask);
+    const bool lt = v.key < o.key;
+    return (lt == keep_min) ? v : o;
 }
 
-// ascending bitonic sort of 16 keys held one per lane by each half-warp (10 compare-exchange steps)
-__device__ __forceinline__ u64 bitonic_sort16(u64 key, int j)
+// ascending bitonic sort of 16 fragments held one per lane by each half-warp (10 compare-exchange steps)
+__device__ __forceinline__ KeyVal bitonic_sort16(KeyVal v, int j)
 {
 #pragma unroll
     for (int k = 2; k <= 16; k <<= 1)
@@ -391,179 +504,321 @@ __device__ __forceinline__ u64 bitonic_sort16(u64 key, int j)
 #pragma unroll
         for (int s = k >> 1; s > 0; s >>= 1)
         {
-            bool up       = ((j & k) == 0) || (k == 16);
-            bool lower    = (j & s) == 0;
-            key           = cmpx(key, s, lower == up);
+            const bool up    = ((j & k) == 0) || (k == 16);
+            const bool lower = (j & s) == 0;
+            v                = cmpx(v, s, lower == up);
         }
     }
-    return key;
+    return v;
 }
 
-// a bitonic sequence of 16 keys -> ascending (4 steps)
-__device__ __forceinline__ u64 bitonic_merge16(u64 key, int j)
+// a bitonic sequence of 16 fragments -> ascending (4 steps)
+__device__ __forceinline__ KeyVal bitonic_merge16(KeyVal v, int j)
 {
 #pragma unroll
-    for (int s = 8; s > 0; s >>= 1) key = cmpx(key, s, (j & s) == 0);
-    return key;
+    for (int s = 8; s > 0; s >>= 1) v = cmpx(v, s, (j & s) == 0);
+    return v;
 }
 
-// One warp renders a tile of 32 consecutive pixels of one view, two pixels (one per half-warp) at a time:
-// lane j of a half-warp holds the j-th nearest fragment of its pixel.
+// A sorted entry in shared memory is (alpha, descriptor row[C]) when the row fits the shared-memory budget (C <= 4:
+// the gather happens in phase A where lanes are densely packed); for wider descriptors it is (entry index, alpha)
+// and phase B gathers.
 template <int C>
-__global__ __launch_bounds__(256) void sort_blend_kernel(ScenePtrs sc, const __grid_constant__ Geom g, TripsRenderParams pr, int B, FwdBuffers fb,
-                                                         const __grid_constant__ LayerPtrs out, unsigned n_tiles,
-                                                         unsigned tiles_per_view)
+struct SbEntry
 {
-    __shared__ float s_out[8][C][32];
-    const int lane  = threadIdx.x & 31;
-    const int warp  = threadIdx.x >> 5;
-    const int j     = lane & 15;
-    const int hbase = lane & 16;
-    const int K     = pr.k_keep;
+    static constexpr bool kStaged = (C <= 4);
+    static constexpr int kFloats  = kStaged ? (1 + C) : 2;
+};
+
+template <int C>
+__device__ __forceinline__ void sb_store_entry(float* dst, const float* entries, unsigned eidx, unsigned alpha_bits)
+{
+    if constexpr (SbEntry<C>::kStaged)
+    {
+        const float4 v4 = *reinterpret_cast<const float4*>(entries + (size_t)eidx * entry_stride(C) + 12);
+        dst[0]          = __uint_as_float(alpha_bits);
+        dst[1]          = v4.x;
+        if (C > 1) dst[2] = v4.y;
+        if (C > 2) dst[3] = v4.z;
+        if (C > 3) dst[4] = v4.w;
+    }
+    else
+    {
+        dst[0] = __uint_as_float(eidx);
+        dst[1] = __uint_as_float(alpha_bits);
+    }
+}
+
+template <int C>
+__global__ __launch_bounds__(kSbThreads) void sort_blend_kernel(ScenePtrs sc, const __grid_constant__ Geom g, TripsRenderParams pr,
+                                                                int B, FwdBuffers fb, const __grid_constant__ LayerPtrs out,
+                                                                unsigned n_tiles_total)
+{
+    constexpr int E  = SbEntry<C>::kFloats;
+    constexpr int ES = entry_stride(C);
+    __shared__ float s_sorted[kSbWarps][32 * kSortedPad * E];  // per warp: 32 pixels x K entries, nearest first
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const int K    = pr.k_keep;
+    float* sorted  = s_sorted[warp];
     float bg[C];
 #pragma unroll
     for (int c = 0; c < C; ++c) bg[c] = __ldg(sc.background + c);
 
     for (;;)
     {
-        unsigned tile = 0;
-        if (lane == 0) tile = atomicAdd(fb.ticket, 1u);
-        tile = __shfl_sync(kFull, tile, 0);
-        if (tile >= n_tiles) break;
-        const int b     = tile / tiles_per_view;
-        const int p0    = (tile - b * tiles_per_view) * 32;
-        const size_t bP = (size_t)b * g.P;
-        const size_t bN = (size_t)b * sc.N;
-        const u64* frags = fb.frags + fb.view_base[b];
-        // lane i owns pixel p0 + i for the coalesced loads / stores
-        const int p_mine = p0 + lane;
-        uint32_t cnt_mine = 0, start_mine = 0;
-        int layer_mine = 0, gx_mine = 0, gy_mine = 0;
-        if (p_mine < g.P)
+        unsigned ticket = 0;
+        if (lane == 0) ticket = atomicAdd(fb.ticket, 1u);
+        ticket = __shfl_sync(kFull, ticket, 0);
+        if (ticket >= n_tiles_total) break;
+        const int b          = ticket / (unsigned)g.n_tiles;
+        const int tile       = ticket - b * (unsigned)g.n_tiles;
+        const size_t bP      = (size_t)b * g.P;
+        const uint4* frags   = fb.frags + fb.view_base[b];
+        const float* entries = fb.entries + fb.entry_base[b] * ES;
+        int layer, gx, gy, p;
+        tile_pixel(g, tile, lane, layer, gx, gy, p);  // lane i owns one pixel of the tile
+        uint32_t cnt = 0, start = 0;
+        if (p >= 0)
         {
-            cnt_mine   = fb.counts[bP + p_mine];
-            start_mine = fb.offsets[bP + p_mine] - cnt_mine;  // offsets hold list ends after the collect pass
-            pixel_to_layer(g, p_mine, layer_mine, gx_mine, gy_mine);
+            cnt   = fb.counts[bP + p];
+            start = fb.offsets[bP + p] - cnt;  // offsets hold list ends after the collect pass
         }
-        for (int it = 0; it < 16; ++it)
+        uint32_t incl = cnt;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1)
         {
-            const int src        = it * 2 + (hbase >> 4);
-            const uint32_t cnt   = __shfl_sync(kFull, cnt_mine, src);
-            const uint32_t start = __shfl_sync(kFull, start_mine, src);
-            const int layer      = __shfl_sync(kFull, layer_mine, src);
-            const int gx         = __shfl_sync(kFull, gx_mine, src);
-            const int gy         = __shfl_sync(kFull, gy_mine, src);
-            const int p          = p0 + src;
-            const uint32_t cnt_o = __shfl_xor_sync(kFull, cnt, 16);
-            if (p0 + it * 2 >= g.P) break;  // warp-uniform: both pixels of this step are past the view's end
+            uint32_t t = __shfl_up_sync(kFull, incl, o);
+            if (lane >= o) incl += t;
+        }
+        const uint32_t rel_start  = incl - cnt;
+        const uint32_t tile_total = __shfl_sync(kFull, incl, 31);
+        uint32_t max_cnt          = cnt;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) max_cnt = max(max_cnt, __shfl_xor_sync(kFull, max_cnt, o));
 
-            // ---- streaming top-16: sort the first 16 fragments, then merge further chunks of 16 ----
-            u64 key = (j < (int)cnt) ? frags[start + j] : kInfKey;
-            key     = bitonic_sort16(key, j);
-            const uint32_t cnt_max = max(cnt, cnt_o);
-            for (uint32_t ch = 16; ch < cnt_max; ch += 16)
+        if (max_cnt <= (uint32_t)kRankMax)
+        {
+            // ---- phase A, counting path: lane = fragment ----
+            for (uint32_t t0 = 0; t0 < tile_total; t0 += 32)
             {
-                u64 nk      = (ch + j < cnt) ? frags[start + ch + j] : kInfKey;
-                u64 cur_max = __shfl_sync(kFull, key, hbase | 15);
-                if (__ballot_sync(kFull, nk < cur_max) == 0) continue;  // nothing nearer in either half
-                nk       = bitonic_sort16(nk, j);
-                u64 rev  = __shfl_sync(kFull, nk, hbase | (15 - j));
-                key      = min(key, rev);
-                key      = bitonic_merge16(key, j);
-            }
-            const int n = min((int)cnt, K);
-            const bool active = j < n;
-
-            // ---- alpha of my fragment ----
-            float a = 0.f;
-            int pid = -1, tex = 0;
-            if (active)
-            {
-                pid            = (int)(unsigned)(key & 0xffffffffull);
-                const float4 r = fb.rec[bN + pid];
-                tex            = __float_as_int(r.w);
-                const float fac = __int_as_float((127 - layer) << 23);  // 2^-layer
-                const float ux = r.x * fac, uy = r.y * fac;
-                const float dx = fabsf(ux - (float)gx), dy = fabsf(uy - (float)gy);
-                float bl = (1.f - dx) * (1.f - dy);
-                if (dx > 1.f || dy > 1.f) bl = 0.f;
-                if ((unsigned)tex >= (unsigned)sc.n_tex)
+                const uint32_t t = t0 + lane;
+                const bool valid = t < tile_total;
+                // pixel of this fragment: the last lane whose list starts at or before t
+                int seg = 0;
+#pragma unroll
+                for (int step = 16; step > 0; step >>= 1)
                 {
-                    atomicOr(&fb.stats->status, TRIPS_DEV_BAD_TEXTURE_INDEX);
-                    tex = 0;
-                    bl  = 0.f;
+                    const int probe       = seg + step;
+                    const uint32_t pstart = __shfl_sync(kFull, rel_start, probe & 31);
+                    if (probe < 32 && pstart <= t) seg = probe;
                 }
-                a = bl * __ldg(sc.confidence + tex);
-                a *= layer_factor(r.z, layer, g.L, nullptr);
-            }
-            // ---- transmittance chain T_j = T_{j-1} * (1 - a_{j-1}) ----
-            const int n_o   = min((int)cnt_o, K);
-            const int n_max = max(n, n_o);
-            float run = 1.f, T = 1.f;
-            for (int s = 1; s < n_max; ++s)
-            {
-                float am = __shfl_sync(kFull, a, hbase | (s - 1));
-                run      = run * (1.f - am);
-                if (j == s) T = run;
-            }
-            const float T_out = (j == 0 || T >= kAlphaCut) ? T : 0.f;
-            // ---- colour: butterfly sum over the 16 lanes ----
-            float col[C];
-            {
-                const float w = T_out * a;
-                const float* row = fb.tex_packed + (size_t)tex * C;
-#pragma unroll
-                for (int c = 0; c < C; ++c) col[c] = active ? w * __ldg(row + c) : 0.f;
-            }
-#pragma unroll
-            for (int o = 1; o < 16; o <<= 1)
-            {
-#pragma unroll
-                for (int c = 0; c < C; ++c) col[c] += __shfl_xor_sync(kFull, col[c], o);
-            }
-            // ---- background weight ----
-            float wb;
-            {
-                const int last = hbase | max(n - 1, 0);
-                float t_last   = __shfl_sync(kFull, T_out, last);
-                float tn_last  = __shfl_sync(kFull, T * (1.f - a), last);
-                if (n == 0)
-                    wb = 1.f;
-                else if (pr.bg_uses_Tn)
-                    wb = (t_last >= kAlphaCut && tn_last >= kAlphaCut) ? tn_last : 0.f;
-                else
-                    wb = t_last;
-            }
-            if (j == 0 && p < g.P)
-            {
-#pragma unroll
-                for (int c = 0; c < C; ++c)
+                const uint32_t seg_rel   = __shfl_sync(kFull, rel_start, seg);
+                const uint32_t seg_start = __shfl_sync(kFull, start, seg);
+                const uint32_t seg_cnt   = __shfl_sync(kFull, cnt, seg);
+                const int seg_p          = __shfl_sync(kFull, p, seg);
+                if (valid)
                 {
-                    float o = col[c];
-                    if (wb >= kAlphaCut) o += bg[c] * (wb * 1.f);
-                    s_out[warp][c][src] = o;
+                    const uint4 f   = frags[seg_start + (t - seg_rel)];
+                    const u64 mine  = ((u64)f.y << 32) | f.x;
+                    const uint2* kp = reinterpret_cast<const uint2*>(frags + seg_start);
+                    int rank        = 0;
+                    for (uint32_t i = 0; i < seg_cnt; ++i)
+                    {
+                        const uint2 o = kp[(size_t)i * 2];
+                        rank += ((((u64)o.y << 32) | o.x) < mine) ? 1 : 0;
+                    }
+                    if (rank < K)
+                    {
+                        sb_store_entry<C>(sorted + (seg * kSortedPad + rank) * E, entries, f.w, f.z);
+                        if (pr.train) fb.records[(bP + seg_p) * 16 + rank] = make_uint2(f.w, f.z);
+                    }
                 }
             }
-            // ---- records for backward: the leading fragments whose transmittance is above the cut-off ----
-            if (pr.train)
+        }
+        else
+        {
+            // ---- phase A, streaming path: a half-warp per pixel keeps the 16 nearest fragments in registers ----
+            const int j     = lane & 15;
+            const int hbase = lane & 16;
+            for (int it = 0; it < 16; ++it)
             {
-                unsigned ok   = __ballot_sync(kFull, active && T_out >= kAlphaCut);
-                unsigned half = (ok >> hbase) & 0xffffu;
-                int m         = __ffs(~half) - 1;  // number of leading set bits (<= 16)
-                if (p < g.P)
+                const int src        = it * 2 + (hbase >> 4);
+                const uint32_t cnt_s = __shfl_sync(kFull, cnt, src);
+                const uint32_t beg_s = __shfl_sync(kFull, start, src);
+                const int p_s        = __shfl_sync(kFull, p, src);
+                const uint32_t cnt_o = __shfl_xor_sync(kFull, cnt_s, 16);
+                KeyVal v;
+                v.key   = kInfKey;
+                v.alpha = 0u;
+                v.eidx  = 0u;
+                if (j < (int)cnt_s)
                 {
-                    if (j < m) fb.records[(bP + p) * 16 + j] = make_uint2((unsigned)pid, __float_as_uint(a));
-                    if (j == 0) fb.rec_n[bP + p] = (uint8_t)m;
+                    const uint4 f = frags[beg_s + j];
+                    v.key         = ((u64)f.y << 32) | f.x;
+                    v.alpha       = f.z;
+                    v.eidx        = f.w;
+                }
+                v = bitonic_sort16(v, j);
+                const uint32_t cnt_max = max(cnt_s, cnt_o);
+                for (uint32_t ch = 16; ch < cnt_max; ch += 16)
+                {
+                    KeyVal nk;
+                    nk.key   = kInfKey;
+                    nk.alpha = 0u;
+                    nk.eidx  = 0u;
+                    if (ch + j < cnt_s)
+                    {
+                        const uint4 f = frags[beg_s + ch + j];
+                        nk.key        = ((u64)f.y << 32) | f.x;
+                        nk.alpha      = f.z;
+                        nk.eidx       = f.w;
+                    }
+                    const u64 cur_max = __shfl_sync(kFull, v.key, hbase | 15);
+                    if (__ballot_sync(kFull, nk.key < cur_max) == 0) continue;  // nothing nearer in either half
+                    nk = bitonic_sort16(nk, j);
+                    KeyVal rev;
+                    rev.key   = __shfl_sync(kFull, nk.key, hbase | (15 - j));
+                    rev.alpha = __shfl_sync(kFull, nk.alpha, hbase | (15 - j));
+                    rev.eidx  = __shfl_sync(kFull, nk.eidx, hbase | (15 - j));
+                    if (rev.key < v.key) v = rev;
+                    v = bitonic_merge16(v, j);
+                }
+                if (j < min((int)cnt_s, K))
+                {
+                    sb_store_entry<C>(sorted + (src * kSortedPad + j) * E, entries, v.eidx, v.alpha);
+                    if (pr.train && p_s >= 0) fb.records[(bP + p_s) * 16 + j] = make_uint2(v.eidx, v.alpha);
                 }
             }
         }
         __syncwarp();
-        if (p_mine < g.P)
-        {
-            const int Wl = g.W[layer_mine], Hl = g.H[layer_mine];
-            float* o = out.p[layer_mine] + ((size_t)b * C * Hl + gy_mine) * Wl + gx_mine;
+
+        // ---- phase B: lane = pixel.  T_j = T_{j-1} * (1 - a_{j-1}), colour summed in the order of a 16-leaf
+        //      butterfly (RenderForward.cu:940-994) so that results do not depend on how lanes are assigned ----
+        const int n = min((int)cnt, K);
+        int n_max   = n;
 #pragma unroll
-            for (int c = 0; c < C; ++c) o[(size_t)c * Hl * Wl] = s_out[warp][c][lane];
+        for (int o = 16; o > 0; o >>= 1) n_max = max(n_max, __shfl_xor_sync(kFull, n_max, o));
+        float run = 1.f, t_last = 1.f, tn_last = 1.f;
+        int m      = 0;
+        bool alive = true;
+        float s0[C], s1[C], s2[C], s3[C];
+#pragma unroll
+        for (int c = 0; c < C; ++c) s0[c] = s1[c] = s2[c] = s3[c] = 0.f;
+        const float* my_sorted = sorted + lane * kSortedPad * E;
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+        {
+            if (j >= n_max) break;
+            float leaf[C];
+#pragma unroll
+            for (int c = 0; c < C; ++c) leaf[c] = 0.f;
+            if (j < n)
+            {
+                const float* e = my_sorted + j * E;
+                float a;
+                float row[C];
+                if constexpr (SbEntry<C>::kStaged)
+                {
+                    a = e[0];
+#pragma unroll
+                    for (int c = 0; c < C; ++c) row[c] = e[1 + c];
+                }
+                else
+                {
+                    const unsigned eidx = __float_as_uint(e[0]);
+                    a                   = e[1];
+                    const float* rp     = entries + (size_t)eidx * ES + 12;
+#pragma unroll
+                    for (int c = 0; c < C; c += 4)
+                    {
+                        const float4 v4 = *reinterpret_cast<const float4*>(rp + c);
+                        row[c] = v4.x;
+                        if (c + 1 < C) row[c + 1] = v4.y;
+                        if (c + 2 < C) row[c + 2] = v4.z;
+                        if (c + 3 < C) row[c + 3] = v4.w;
+                    }
+                }
+                const float T_out = (j == 0 || run >= kAlphaCut) ? run : 0.f;
+                const float w     = T_out * a;
+#pragma unroll
+                for (int c = 0; c < C; ++c) leaf[c] = w * row[c];
+                if (alive && T_out >= kAlphaCut)
+                    m = j + 1;
+                else
+                    alive = false;
+                if (j == n - 1)
+                {
+                    t_last  = T_out;
+                    tn_last = run * (1.f - a);
+                }
+                run = run * (1.f - a);
+            }
+            // binary-counter accumulation = pairwise tree over leaves 0..15
+#pragma unroll
+            for (int c = 0; c < C; ++c)
+            {
+                if ((j & 1) == 0)
+                    s0[c] = leaf[c];
+                else
+                {
+                    float p1 = s0[c] + leaf[c];
+                    if ((j & 2) == 0)
+                        s1[c] = p1;
+                    else
+                    {
+                        float p2 = s1[c] + p1;
+                        if ((j & 4) == 0)
+                            s2[c] = p2;
+                        else
+                        {
+                            float p3 = s2[c] + p2;
+                            if ((j & 8) == 0)
+                                s3[c] = p3;
+                            else
+                                s3[c] = s3[c] + p3;  // j == 15: the root
+                        }
+                    }
+                }
+            }
+        }
+        if (p >= 0)
+        {
+            // pending partial sums of an incomplete tree: the missing leaves are zeros, which add exactly
+            float col[C];
+            const int jm = n_max;
+#pragma unroll
+            for (int c = 0; c < C; ++c)
+            {
+                float t = 0.f;
+                if (jm >= 16)
+                    t = s3[c];
+                else
+                {
+                    if (jm & 1) t = s0[c];
+                    if (jm & 2) t = s1[c] + t;
+                    if (jm & 4) t = s2[c] + t;
+                    if (jm & 8) t = s3[c] + t;
+                }
+                col[c] = t;
+            }
+            float wb;
+            if (n == 0)
+                wb = 1.f;  // the reference reads a neighbouring lane here (RenderForward.cu:1002-1003): defined as pure background
+            else if (pr.bg_uses_Tn)
+                wb = (t_last >= kAlphaCut && tn_last >= kAlphaCut) ? tn_last : 0.f;
+            else
+                wb = t_last;
+            const int Wl = g.W[layer], Hl = g.H[layer];
+            float* o = out.p[layer] + ((size_t)b * C * Hl + gy) * Wl + gx;
+#pragma unroll
+            for (int c = 0; c < C; ++c)
+            {
+                float v = col[c];
+                if (wb >= kAlphaCut) v += bg[c] * (wb * 1.f);
+                o[(size_t)c * Hl * Wl] = v;
+            }
+            if (pr.train) fb.rec_n[bP + p] = (uint8_t)m;
         }
         __syncwarp();
     }
@@ -572,19 +827,18 @@ __global__ __launch_bounds__(256) void sort_blend_kernel(ScenePtrs sc, const __g
 cudaError_t launch_sort_blend(const ScenePtrs& sc, const Geom& g, const TripsRenderParams& pr, int B, const FwdBuffers& fb,
                               const LayerPtrs& out, int sm_count, cudaStream_t st)
 {
-    unsigned tiles_per_view = (unsigned)((g.P + 31) / 32);
-    unsigned n_tiles        = tiles_per_view * (unsigned)B;
-    cudaError_t e           = cudaMemsetAsync(fb.ticket, 0, sizeof(unsigned), st);
+    const unsigned n_tiles = (unsigned)g.n_tiles * (unsigned)B;
+    cudaError_t e          = cudaMemsetAsync(fb.ticket, 0, sizeof(unsigned), st);
     if (e != cudaSuccess) return e;
-    int blocks = (int)min((unsigned)(sm_count * 8), (n_tiles + 7) / 8);
+    int blocks = (int)min((unsigned)(sm_count * 16), (n_tiles + kSbWarps - 1) / kSbWarps);
     blocks     = max(blocks, 1);
     switch (sc.C)
     {
-        case 3: sort_blend_kernel<3><<<blocks, 256, 0, st>>>(sc, g, pr, B, fb, out, n_tiles, tiles_per_view); break;
-        case 4: sort_blend_kernel<4><<<blocks, 256, 0, st>>>(sc, g, pr, B, fb, out, n_tiles, tiles_per_view); break;
-        case 6: sort_blend_kernel<6><<<blocks, 256, 0, st>>>(sc, g, pr, B, fb, out, n_tiles, tiles_per_view); break;
-        case 8: sort_blend_kernel<8><<<blocks, 256, 0, st>>>(sc, g, pr, B, fb, out, n_tiles, tiles_per_view); break;
-        case 16: sort_blend_kernel<16><<<blocks, 256, 0, st>>>(sc, g, pr, B, fb, out, n_tiles, tiles_per_view); break;
+        case 3: sort_blend_kernel<3><<<blocks, kSbThreads, 0, st>>>(sc, g, pr, B, fb, out, n_tiles); break;
+        case 4: sort_blend_kernel<4><<<blocks, kSbThreads, 0, st>>>(sc, g, pr, B, fb, out, n_tiles); break;
+        case 6: sort_blend_kernel<6><<<blocks, kSbThreads, 0, st>>>(sc, g, pr, B, fb, out, n_tiles); break;
+        case 8: sort_blend_kernel<8><<<blocks, kSbThreads, 0, st>>>(sc, g, pr, B, fb, out, n_tiles); break;
+        case 16: sort_blend_kernel<16><<<blocks, kSbThreads, 0, st>>>(sc, g, pr, B, fb, out, n_tiles); break;
         default: return cudaErrorInvalidValue;
     }
     return cudaGetLastError();
