@@ -9,7 +9,8 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libtrips_b200.so")
+# TRIPS_B200_LIB selects another build of the same library (e.g. one compiled with different tuning macros)
+LIB_PATH = os.environ.get("TRIPS_B200_LIB") or os.path.join(HERE, "libtrips_b200.so")
 
 MAX_LAYERS = 8
 MAX_KEEP = 16

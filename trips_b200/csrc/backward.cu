@@ -49,10 +49,10 @@ constexpr int kBwdWarps   = kBwdThreads / 32;
 //     transmittance T_j, w_j = T_j alpha_j, and d_j = dLoss/dalpha_j = T_j G_j - (W_bg + sum_{i>j} W_i) / (1 - alpha_j + 1e-9)
 //     with W_i = G_i T_i alpha_i (RenderBackward.cu:262-303; the reference's O(K^2) inner loop becomes a reverse
 //     running sum).
-//   phase 2 (lane = kept fragment): the per-fragment chain to descriptors, confidence, position and size
-//     (RenderBackward.cu:335-466), accumulated with vector atomics into the per-entry gradient rows, which are in
-//     screen-bin order like the entries and therefore stay hot in L2 while a region of the image is processed.
-template <int C, bool CAM_GRADS>
+//   phase 2 (lane = kept fragment): descriptor gradient and the image-space sums of the fragment's entry
+//     (RenderBackward.cu:335-393), accumulated with two vector atomics into the per-entry gradient rows, which are
+//     in screen-bin order like the entries and therefore stay hot in L2 while a region of the image is processed.
+template <int C>
 __global__ __launch_bounds__(kBwdThreads) void blend_backward_kernel(ScenePtrs sc, const CamConst* __restrict__ cams,
                                                                      const __grid_constant__ Geom g, TripsRenderParams pr, int B,
                                                                      FwdBuffers fb, BwdBuffers bb,
@@ -64,7 +64,6 @@ __global__ __launch_bounds__(kBwdThreads) void blend_backward_kernel(ScenePtrs s
     __shared__ float s_d[kBwdWarps][32 * kPad];   // G_j, then dA_j = G_j T_j, finally d_j
     __shared__ float s_W[kBwdWarps][32 * kPad];   // alpha_j
     __shared__ float s_w[kBwdWarps][32 * kPad];   // w_j = T_j * alpha_j
-    __shared__ CamConst s_cam;
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
     float bg[C];
@@ -72,10 +71,6 @@ __global__ __launch_bounds__(kBwdThreads) void blend_backward_kernel(ScenePtrs s
     for (int c = 0; c < C; ++c) bg[c] = __ldg(sc.background + c);
 
     const int b = blockIdx.y;
-    if (threadIdx.x < sizeof(CamConst) / 4) ((int*)&s_cam)[threadIdx.x] = ((const int*)&cams[b])[threadIdx.x];
-    __syncthreads();
-    const CamConst& cam  = s_cam;
-    const float fxc      = cam.fx * cam.cfx;
     const size_t bP      = (size_t)b * g.P;
     const float* entries = fb.entries + fb.entry_base[b] * ES;
     float* egrad         = bb.egrad + fb.entry_base[b] * GS;
@@ -86,9 +81,6 @@ __global__ __launch_bounds__(kBwdThreads) void blend_backward_kernel(ScenePtrs s
     double acc_bg[C];
 #pragma unroll
     for (int c = 0; c < C; ++c) acc_bg[c] = 0.0;
-    double acc_cam[CAM_GRADS ? 11 : 1];
-#pragma unroll
-    for (int k = 0; k < (CAM_GRADS ? 11 : 1); ++k) acc_cam[k] = 0.0;
 
     for (;;)
     {
@@ -223,17 +215,8 @@ __global__ __launch_bounds__(kBwdThreads) void blend_backward_kernel(ScenePtrs s
             const float ga  = s_d[warp][seg * kPad + j];
             const float w   = s_w[warp][seg * kPad + j];
             const float4 e0v = *reinterpret_cast<const float4*>(en);      // u v ps z
-            const float4 e1v = *reinterpret_cast<const float4*>(en + 4);  // pid conf raw nl
-            const float4 e2v = *reinterpret_cast<const float4*>(en + 8);  // x y z tex
-            if (__float_as_int(e2v.w) < 0) continue;  // invalid texture index: flagged in the forward pass, alpha was 0
-            // descriptor gradient: T_j alpha_j g
-            {
-                float gt[(C + 3) & ~3];
-#pragma unroll
-                for (int c = 0; c < ((C + 3) & ~3); ++c) gt[c] = (c < C) ? w * s_g[warp][c < C ? c : 0][seg] : 0.f;
-                atomic_add_row<((C + 3) & ~3)>(eg + 8, gt);
-            }
-            // bilinear weights and their Jacobian at uv (compute_blending_fac, PointBlending.h:216-257)
+            const float conf = en[5];
+            // bilinear weight of this pixel and its Jacobian at uv (compute_blending_fac, PointBlending.h:216-257)
             const float fac = __int_as_float((127 - layer_s) << 23);
             const float ux = e0v.x * fac, uy = e0v.y * fac;
             const float ps = e0v.z;
@@ -243,50 +226,17 @@ __global__ __launch_bounds__(kBwdThreads) void blend_backward_kernel(ScenePtrs s
             const float J0 = (q & 1) ? ((q & 2) ? sy : (1.f - sy)) : ((q & 2) ? -sy : (sy - 1.f));
             const float J1 = (q & 2) ? ((q & 1) ? sx : (1.f - sx)) : ((q & 1) ? -sx : (sx - 1.f));
             if (fabsf(ux - (float)gx_s) > 1.f || fabsf(uy - (float)gy_s) > 1.f) bf *= 0.f;
-            const float conf = e1v.y;
             float lf_grad    = 0.f;
             const float lf   = layer_factor(ps, layer_s, g.L, &lf_grad);
-            atomicAdd(eg + 4, bf * lf * ga);
-            const float gbs   = conf * lf * ga;
-            const float grad0 = J0 * gbs, grad1 = J1 * gbs;
-            // ProjectPointPinholeBackward (PointRendererHelper.h:434-494), zero distortion
-            float vx, vy, vz;
-            transform_point(cam, e2v.x, e2v.y, e2v.z, vx, vy, vz);
-            if (vz > 0.f)
+            const float gbs  = conf * lf * ga;  // dLoss / d(bilinear weight) (RenderBackward.cu:385)
+            // image-space sums of the entry: the chain to position / size / pose is linear in them and is applied
+            // once per entry by entry_grad_finish_kernel
+            atomicAdd(reinterpret_cast<float4*>(eg), make_float4(J0 * gbs, J1 * gbs, bf * conf * lf_grad * ga, bf * lf * ga));
             {
-                const float g_layer_proj = fxc / vz;
-                const float iz = 1.f / vz;
-                const float nx = vx * iz, ny = vy * iz;
-                const float gr0 = cam.r00 * grad0 + cam.r10 * grad1;
-                const float gr1 = cam.r01 * grad0 + cam.r11 * grad1;
-                const float gk0 = cam.cfx * gr0;
-                const float gk1 = cam.cs * gr0 + cam.cfy * gr1;
-                const float gn0 = cam.fx * gk0;
-                const float gn1 = cam.s * gk0 + cam.fy * gk1;
-                const float gv0 = iz * gn0;
-                const float gv1 = iz * gn1;
-                const float gv2 = (-vx * iz * iz) * gn0 + (-vy * iz * iz) * gn1;
-                const float gp0 = cam.R[0] * gv0 + cam.R[3] * gv1 + cam.R[6] * gv2;
-                const float gp1 = cam.R[1] * gv0 + cam.R[4] * gv1 + cam.R[7] * gv2;
-                const float gp2 = cam.R[2] * gv0 + cam.R[5] * gv1 + cam.R[8] * gv2;
-                const float J_sp = tm_softplus_grad(e1v.z);
-                const float glp  = J_sp * g_layer_proj * lf_grad * ga;
-                const float gl   = bf * conf * glp;
-                atomicAdd(reinterpret_cast<float4*>(eg), make_float4(gp0, gp1, gp2, gl));
-                if constexpr (CAM_GRADS)
-                {
-                    acc_cam[0] += (double)gv0;
-                    acc_cam[1] += (double)gv1;
-                    acc_cam[2] += (double)gv2;
-                    acc_cam[3] += (double)(vy * gv2 - vz * gv1);
-                    acc_cam[4] += (double)(vz * gv0 - vx * gv2);
-                    acc_cam[5] += (double)(vx * gv1 - vy * gv0);
-                    acc_cam[6] += (double)(nx * gk0);
-                    acc_cam[7] += (double)(ny * gk1);
-                    acc_cam[8] += (double)gk0;
-                    acc_cam[9] += (double)gk1;
-                    acc_cam[10] += (double)(ny * gk0);
-                }
+                float gt[(C + 3) & ~3];
+#pragma unroll
+                for (int c = 0; c < ((C + 3) & ~3); ++c) gt[c] = (c < C) ? w * s_g[warp][c < C ? c : 0][seg] : 0.f;
+                atomic_add_row<((C + 3) & ~3)>(eg + 4, gt);
             }
         }
         __syncwarp();
@@ -297,21 +247,6 @@ __global__ __launch_bounds__(kBwdThreads) void blend_backward_kernel(ScenePtrs s
     {
         double v = warp_sum_d(acc_bg[c]);
         if (lane == 0 && v != 0.0) atomicAdd(bb.g_bg + c, v);
-    }
-    if constexpr (CAM_GRADS)
-    {
-#pragma unroll
-        for (int k = 0; k < 11; ++k)
-        {
-            double v = warp_sum_d(acc_cam[k]);
-            if (lane == 0 && v != 0.0)
-            {
-                if (k < 6)
-                    atomicAdd(bb.g_pose + (size_t)b * 6 + k, v);
-                else
-                    atomicAdd(bb.g_k + (size_t)b * 5 + (k - 6), v);
-            }
-        }
     }
 }
 
@@ -325,10 +260,7 @@ cudaError_t launch_blend_backward(const ScenePtrs& sc, const CamConst* cams, con
     dim3 grid(bx, B);
 #define TRIPS_BWD_CASE(CC)                                                                                         \
     case CC:                                                                                                       \
-        if (want_cam_grads)                                                                                        \
-            blend_backward_kernel<CC, true><<<grid, kBwdThreads, 0, st>>>(sc, cams, g, pr, B, fb, bb, grad_in);    \
-        else                                                                                                       \
-            blend_backward_kernel<CC, false><<<grid, kBwdThreads, 0, st>>>(sc, cams, g, pr, B, fb, bb, grad_in);   \
+        blend_backward_kernel<CC><<<grid, kBwdThreads, 0, st>>>(sc, cams, g, pr, B, fb, bb, grad_in);             \
         break;
     switch (sc.C)
     {
@@ -347,30 +279,81 @@ cudaError_t launch_blend_backward(const ScenePtrs& sc, const CamConst* cams, con
 // per-entry gradient rows -> per-point sums (one set of atomics per visible point and view instead of one per
 // fragment), then the reference's output layouts (PointRenderer.cu:1423-1426)
 // ------------------------------------------------------------------------------------------------------------
-template <int C>
-__global__ __launch_bounds__(256) void entry_grad_scatter_indirect(FwdBuffers fb, BwdBuffers bb, int B)
+// Applies, once per entry, the chain from the accumulated image-space sums to the point: crop rotation, crop
+// transform, pinhole, division by z and the rotation (ProjectPointPinholeBackward, PointRendererHelper.h:434-494,
+// zero distortion), the softplus derivative for the size, and adds the entry's gradients to its point
+// (one set of atomics per visible point and view instead of one per fragment).  Pose and intrinsics gradients
+// are summed per view in double (RenderBackward.cu:453-466,587-611).
+template <int C, bool CAM_GRADS>
+__global__ __launch_bounds__(256) void entry_grad_finish_kernel(FwdBuffers fb, BwdBuffers bb, const CamConst* __restrict__ cams, int B)
 {
     constexpr int ES = entry_stride(C);
     constexpr int GS = egrad_stride(C);
-    const unsigned long long n_total = fb.entry_base[B];
-    for (unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; i < n_total;
+    __shared__ CamConst cam;
+    __shared__ double s_acc[8][11];
+    const int b = blockIdx.y;
+    if (threadIdx.x < sizeof(CamConst) / 4) ((int*)&cam)[threadIdx.x] = ((const int*)&cams[b])[threadIdx.x];
+    __syncthreads();
+    const float fxc = cam.fx * cam.cfx;
+    const unsigned long long first = fb.entry_base[b], n = fb.entry_base[b + 1] - first;
+    const float* entries = fb.entries + first * ES;
+    const float* egrad   = bb.egrad + first * GS;
+    double acc[CAM_GRADS ? 11 : 1];
+#pragma unroll
+    for (int k = 0; k < (CAM_GRADS ? 11 : 1); ++k) acc[k] = 0.0;
+    for (unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
          i += (unsigned long long)gridDim.x * blockDim.x)
     {
-        const float* en = fb.entries + i * ES;
-        const float* eg = bb.egrad + i * GS;
-        const int pid   = __float_as_int(en[4]);
-        const int tex   = __float_as_int(en[11]);
-        const float4 gp = *reinterpret_cast<const float4*>(eg);
-        if (gp.x != 0.f || gp.y != 0.f || gp.z != 0.f || gp.w != 0.f) atomicAdd(bb.g_pos_size + pid, gp);
+        const float* en = entries + i * ES;
+        const float* eg = egrad + i * GS;
+        const float4 s4 = *reinterpret_cast<const float4*>(eg);      // sum J0 gbs, sum J1 gbs, sum bf conf lf' ga, sum bf lf ga
+        const float4 e1 = *reinterpret_cast<const float4*>(en + 4);  // pid conf raw nl
+        const float4 e2 = *reinterpret_cast<const float4*>(en + 8);  // x y z tex
+        const int pid   = __float_as_int(e1.x);
+        const int tex   = __float_as_int(e2.w);
+        float vx, vy, vz;
+        transform_point(cam, e2.x, e2.y, e2.z, vx, vy, vz);
+        if (vz > 0.f && (s4.x != 0.f || s4.y != 0.f || s4.z != 0.f))
+        {
+            const float iz  = 1.f / vz;
+            const float gr0 = cam.r00 * s4.x + cam.r10 * s4.y;
+            const float gr1 = cam.r01 * s4.x + cam.r11 * s4.y;
+            const float gk0 = cam.cfx * gr0;
+            const float gk1 = cam.cs * gr0 + cam.cfy * gr1;
+            const float gn0 = cam.fx * gk0;
+            const float gn1 = cam.s * gk0 + cam.fy * gk1;
+            const float gv0 = iz * gn0;
+            const float gv1 = iz * gn1;
+            const float gv2 = (-vx * iz * iz) * gn0 + (-vy * iz * iz) * gn1;
+            const float gp0 = cam.R[0] * gv0 + cam.R[3] * gv1 + cam.R[6] * gv2;
+            const float gp1 = cam.R[1] * gv0 + cam.R[4] * gv1 + cam.R[7] * gv2;
+            const float gp2 = cam.R[2] * gv0 + cam.R[5] * gv1 + cam.R[8] * gv2;
+            const float gl  = tm_softplus_grad(e1.z) * (fxc / vz) * s4.z;
+            atomicAdd(bb.g_pos_size + pid, make_float4(gp0, gp1, gp2, gl));
+            if constexpr (CAM_GRADS)
+            {
+                const float nx = vx * iz, ny = vy * iz;
+                acc[0] += (double)gv0;
+                acc[1] += (double)gv1;
+                acc[2] += (double)gv2;
+                acc[3] += (double)(vy * gv2 - vz * gv1);
+                acc[4] += (double)(vz * gv0 - vx * gv2);
+                acc[5] += (double)(vx * gv1 - vy * gv0);
+                acc[6] += (double)(nx * gk0);
+                acc[7] += (double)(ny * gk1);
+                acc[8] += (double)gk0;
+                acc[9] += (double)gk1;
+                acc[10] += (double)(ny * gk0);
+            }
+        }
         if (tex < 0) continue;
-        const float gc = eg[4];
-        if (gc != 0.f) atomicAdd(bb.g_conf + tex, gc);
+        if (s4.w != 0.f) atomicAdd(bb.g_conf + tex, s4.w);
         float gt[(C + 3) & ~3];
         bool any = false;
 #pragma unroll
         for (int c = 0; c < ((C + 3) & ~3); c += 4)
         {
-            const float4 v4 = *reinterpret_cast<const float4*>(eg + 8 + c);
+            const float4 v4 = *reinterpret_cast<const float4*>(eg + 4 + c);
             gt[c] = v4.x, gt[c + 1] = v4.y, gt[c + 2] = v4.z, gt[c + 3] = v4.w;
             any |= (v4.x != 0.f || v4.y != 0.f || v4.z != 0.f || v4.w != 0.f);
         }
@@ -380,6 +363,29 @@ __global__ __launch_bounds__(256) void entry_grad_scatter_indirect(FwdBuffers fb
 #pragma unroll
             for (int c = 0; c < C; ++c) gtc[c] = gt[c];
             atomic_add_row<C>(bb.g_tex_packed + (size_t)tex * C, gtc);
+        }
+    }
+    if constexpr (CAM_GRADS)
+    {
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+        for (int k = 0; k < 11; ++k)
+        {
+            const double v = warp_sum_d(acc[k]);
+            if (lane == 0) s_acc[warp][k] = v;
+        }
+        __syncthreads();
+        if (threadIdx.x < 11)
+        {
+            double v = 0.0;
+            for (int w = 0; w < 8; ++w) v += s_acc[w][threadIdx.x];
+            if (v != 0.0)
+            {
+                if (threadIdx.x < 6)
+                    atomicAdd(bb.g_pose + (size_t)b * 6 + threadIdx.x, v);
+                else
+                    atomicAdd(bb.g_k + (size_t)b * 5 + (threadIdx.x - 6), v);
+            }
         }
     }
 }
@@ -426,22 +432,31 @@ __global__ void unpack_small_kernel(int C, int B, const CamConst* __restrict__ c
 cudaError_t launch_unpack_grads(const ScenePtrs& sc, const CamConst* cams, int B, const FwdBuffers& fb, const BwdBuffers& bb,
                                 const TripsGrads& out, int sm_count, cudaStream_t st)
 {
-    // fb.entry_base lives on the device; the launch covers the worst case and threads stop at the real count
+    // the entry counts live on the device: the grid covers a fixed share of the worst case and threads stride
     {
-        const unsigned long long cap = (unsigned long long)B * (unsigned long long)sc.N;
-        int blocks = (int)min((unsigned long long)sm_count * 16, (cap + 255) / 256);
-        if (blocks > 0)
+        const bool cam_grads = out.pose_tangent || out.intrinsics;
+        int bx = max(1, min(sm_count * 8 / max(1, min(B, 8)) + 1, (sc.N + 255) / 256));
+        dim3 grid(bx, B);
+#define TRIPS_FIN_CASE(CC)                                                                                      \
+    case CC:                                                                                                    \
+        if (cam_grads)                                                                                          \
+            entry_grad_finish_kernel<CC, true><<<grid, 256, 0, st>>>(fb, bb, cams, B);                          \
+        else                                                                                                    \
+            entry_grad_finish_kernel<CC, false><<<grid, 256, 0, st>>>(fb, bb, cams, B);                         \
+        break;
+        if (sc.N > 0)
         {
             switch (sc.C)
             {
-                case 3: entry_grad_scatter_indirect<3><<<blocks, 256, 0, st>>>(fb, bb, B); break;
-                case 4: entry_grad_scatter_indirect<4><<<blocks, 256, 0, st>>>(fb, bb, B); break;
-                case 6: entry_grad_scatter_indirect<6><<<blocks, 256, 0, st>>>(fb, bb, B); break;
-                case 8: entry_grad_scatter_indirect<8><<<blocks, 256, 0, st>>>(fb, bb, B); break;
-                case 16: entry_grad_scatter_indirect<16><<<blocks, 256, 0, st>>>(fb, bb, B); break;
+                TRIPS_FIN_CASE(3)
+                TRIPS_FIN_CASE(4)
+                TRIPS_FIN_CASE(6)
+                TRIPS_FIN_CASE(8)
+                TRIPS_FIN_CASE(16)
                 default: return cudaErrorInvalidValue;
             }
         }
+#undef TRIPS_FIN_CASE
     }
     if (out.texture)
     {

@@ -65,8 +65,8 @@ struct DevStats
 //   float  8..11  world position x, y, z, texture index (bits)
 //   float 12..    descriptor row (C floats, padded to a multiple of 4)
 __host__ __device__ constexpr int entry_stride(int C) { return 12 + ((C + 3) & ~3); }
-// Gradient accumulator of an entry: xyz + raw size | confidence, 3 pad | descriptor row.
-__host__ __device__ constexpr int egrad_stride(int C) { return 8 + ((C + 3) & ~3); }
+// Gradient accumulator of an entry: sums over its fragments of (J0 gbs, J1 gbs, bf conf lf' ga, bf lf ga) | descriptor row.
+__host__ __device__ constexpr int egrad_stride(int C) { return 4 + ((C + 3) & ~3); }
 
 // Everything the forward kernels need besides the scene (all device pointers into context scratch).
 struct FwdBuffers

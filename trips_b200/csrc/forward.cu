@@ -475,7 +475,13 @@ typedef unsigned long long u64;
 constexpr u64 kInfKey    = 0xffffffffffffffffull;
 constexpr int kRankMax   = 192;  // longest list ranked by counting; longer lists use the streaming path
 constexpr int kSortedPad = 17;   // row pitch (entries) of the per-pixel sorted lists in shared memory
-constexpr int kSbThreads = 128;
+#ifndef TRIPS_SB_STAGE_MAX_C
+#define TRIPS_SB_STAGE_MAX_C 0
+#endif
+#ifndef TRIPS_SB_THREADS
+#define TRIPS_SB_THREADS 128
+#endif
+constexpr int kSbThreads = TRIPS_SB_THREADS;
 constexpr int kSbWarps   = kSbThreads / 32;
 
 struct KeyVal
@@ -526,7 +532,7 @@ __device__ __forceinline__ KeyVal bitonic_merge16(KeyVal v, int j)
 template <int C>
 struct SbEntry
 {
-    static constexpr bool kStaged = (C <= 4);
+    static constexpr bool kStaged = (C <= TRIPS_SB_STAGE_MAX_C);
     static constexpr int kFloats  = kStaged ? (1 + C) : 2;
 };
 
