@@ -129,8 +129,10 @@ def stage_bytes(stage, N, P, C, B, F, Kf):
     """Algorithmic bytes of one launch of a stage over B views (F, Kf are totals over those views)."""
     if stage == "bin_points":
         return 24 * N * B
+    if stage == "count":
+        return 4 * P * B
     if stage == "scan":
-        return 12 * P * B
+        return 8 * P * B
     if stage == "collect":
         return 8 * F
     if stage == "sort_blend":
@@ -369,7 +371,7 @@ def run_ours(args, rank, world, local_rank):
         launches_total += launches
         if calls:
             per_stage[name] = {"ms_per_launch": ms / calls, "launches": int(launches)}
-    dom = max((k for k in per_stage if k in ("bin_points", "scan", "collect", "sort_blend", "blend_backward", "adam")),
+    dom = max((k for k in per_stage if k in ("bin_points", "count", "scan", "collect", "sort_blend", "blend_backward", "adam")),
               key=lambda k: per_stage[k]["ms_per_launch"])
     dom_bytes = stage_bytes(dom, N, P, C, B, F, Kf)
     achieved = dom_bytes / (per_stage[dom]["ms_per_launch"] * 1e-3) / 1e9
@@ -377,7 +379,7 @@ def run_ours(args, rank, world, local_rank):
         b_ = stage_bytes(k, N, P, C, B, F, Kf)
         v["alg_gb"] = b_ / 1e9
         v["gbs"] = (b_ / (v["ms_per_launch"] * 1e-3) / 1e9) if b_ else None
-    total_alg = sum(stage_bytes(k, N, P, C, B, F, Kf) for k in ("bin_points", "scan", "collect", "sort_blend", "blend_backward", "adam"))
+    total_alg = sum(stage_bytes(k, N, P, C, B, F, Kf) for k in ("bin_points", "count", "scan", "collect", "sort_blend", "blend_backward", "adam"))
     roofline = {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "peak_kind": peak_kind, "traffic": None, "alg_bytes_per_launch": dom_bytes,
                 "step_alg_bytes": total_alg, "step_gbs": total_alg / (ms_step * 1e-3) / 1e9, "stages": per_stage}

@@ -35,6 +35,7 @@ typedef enum
 #define TRIPS_DEV_BAD_TEXTURE_INDEX 1u /* RenderBackward.cu:217-218 */
 #define TRIPS_DEV_NONZERO_DISTORTION 2u /* distortion model not implemented: coefficients were ignored */
 #define TRIPS_DEV_FRAGMENT_OVERFLOW 4u /* a view's fragment count exceeded the list buffer */
+#define TRIPS_DEV_BAD_FRAGMENT 8u /* a fragment referred to a point outside the view's visible set (internal error) */
 
 typedef struct TripsContext TripsContext;
 
@@ -158,6 +159,7 @@ enum
 {
     TRIPS_STAGE_SETUP = 0,
     TRIPS_STAGE_BIN_POINTS,
+    TRIPS_STAGE_COUNT,
     TRIPS_STAGE_SCAN,
     TRIPS_STAGE_COLLECT,
     TRIPS_STAGE_SORT_BLEND,

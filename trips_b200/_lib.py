@@ -14,7 +14,7 @@ LIB_PATH = os.environ.get("TRIPS_B200_LIB") or os.path.join(HERE, "libtrips_b200
 
 MAX_LAYERS = 8
 MAX_KEEP = 16
-NUM_STAGES = 9
+NUM_STAGES = 10
 
 OK = 0
 ERR_INVALID_ARG = -1

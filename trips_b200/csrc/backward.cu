@@ -74,6 +74,7 @@ __global__ __launch_bounds__(kBwdThreads) void blend_backward_kernel(ScenePtrs s
     const size_t bP      = (size_t)b * g.P;
     const float* entries = fb.entries + fb.entry_base[b] * ES;
     float* egrad         = bb.egrad + fb.entry_base[b] * GS;
+    const uint32_t n_ent = (uint32_t)(fb.entry_base[b + 1] - fb.entry_base[b]);
     float* my_d          = s_d[warp] + lane * kPad;
     float* my_W          = s_W[warp] + lane * kPad;
     float* my_w          = s_w[warp] + lane * kPad;
@@ -135,7 +136,8 @@ __global__ __launch_bounds__(kBwdThreads) void blend_backward_kernel(ScenePtrs s
             const int seg_p = __shfl_sync(kFull, p, seg);
             if (e < n_entry)
             {
-                const uint2 rc   = fb.records[(bP + seg_p) * 16 + j];
+                uint2 rc = fb.records[(bP + seg_p) * 16 + j];
+                if (rc.x >= n_ent) rc = make_uint2(0u, 0u);  // corrupted record (flagged by the forward pass): no contribution
                 const float* row = entries + (size_t)rc.x * ES + 12;
                 float G          = 0.f;
 #pragma unroll
@@ -210,6 +212,7 @@ __global__ __launch_bounds__(kBwdThreads) void blend_backward_kernel(ScenePtrs s
             const int gy_s    = __shfl_sync(kFull, gy, seg);
             if (!valid) continue;
             const uint2 rc  = fb.records[(bP + seg_p) * 16 + j];
+            if (rc.x >= n_ent) continue;
             const float* en = entries + (size_t)rc.x * ES;
             float* eg       = egrad + (size_t)rc.x * GS;
             const float ga  = s_d[warp][seg * kPad + j];

@@ -109,7 +109,7 @@ struct TripsContext
     int sm_count = 148;
     std::string error;
     // forward scratch
-    DevBuf views, cams, bin_count, bin_cursor, entry_base, entries, counts, offsets, partial, view_base, frags, rec_n, records, stats, ticket;
+    DevBuf views, cams, bin_count, bin_base, view_total, bin_cursor, entry_base, entries, counts, offsets, partial, view_base, frags, rec_n, records, stats, ticket;
     // backward scratch
     DevBuf egrad, g_tex, g_conf, g_pos, g_small;
     // adam
@@ -185,6 +185,8 @@ static FwdBuffers fwd_buffers(TripsContext* c)
 {
     FwdBuffers fb;
     fb.bin_count  = (uint32_t*)c->bin_count.p;
+    fb.bin_base   = (uint32_t*)c->bin_base.p;
+    fb.view_total = (uint32_t*)c->view_total.p;
     fb.bin_cursor = (uint32_t*)c->bin_cursor.p;
     fb.entry_base = (unsigned long long*)c->entry_base.p;
     fb.entries    = (float*)c->entries.p;
@@ -244,7 +246,7 @@ int trips_context_create(TripsContext** out, int device)
 void trips_context_destroy(TripsContext* c)
 {
     if (!c) return;
-    DevBuf* all[] = {&c->views, &c->cams, &c->bin_count, &c->bin_cursor, &c->entry_base, &c->entries, &c->counts, &c->offsets,
+    DevBuf* all[] = {&c->views, &c->cams, &c->bin_count, &c->bin_base, &c->view_total, &c->bin_cursor, &c->entry_base, &c->entries, &c->counts, &c->offsets,
                      &c->partial, &c->view_base, &c->frags, &c->rec_n, &c->records, &c->stats, &c->ticket, &c->egrad, &c->g_tex,
                      &c->g_conf, &c->g_pos, &c->g_small, &c->adam_tab};
     for (DevBuf* b : all) free_buf(*b);
@@ -327,7 +329,9 @@ int trips_forward(TripsContext* ctx, const TripsScene* scene, const TripsView* v
 
     CU_CHECK(ctx, ensure(ctx->views, sizeof(TripsView) * B));
     CU_CHECK(ctx, ensure(ctx->cams, sizeof(CamConst) * B));
-    CU_CHECK(ctx, ensure(ctx->bin_count, sizeof(uint32_t) * (size_t)g.n_bins * B));
+    CU_CHECK(ctx, ensure(ctx->bin_count, sizeof(uint32_t) * (size_t)g.n_bins * B * bin_blocks_per_view(B, ctx->sm_count)));
+    CU_CHECK(ctx, ensure(ctx->bin_base, sizeof(uint32_t) * (size_t)g.n_bins * B * bin_blocks_per_view(B, ctx->sm_count)));
+    CU_CHECK(ctx, ensure(ctx->view_total, sizeof(uint32_t) * B));
     CU_CHECK(ctx, ensure(ctx->bin_cursor, sizeof(uint32_t) * (size_t)g.n_bins * B));
     CU_CHECK(ctx, ensure(ctx->entry_base, sizeof(unsigned long long) * (B + 1)));
     // entries are sized for the worst case (every point visible in every view): no host round trip is needed to size them
@@ -362,7 +366,8 @@ int trips_forward(TripsContext* ctx, const TripsScene* scene, const TripsView* v
     STAGE(ctx, TRIPS_STAGE_SETUP, 1, st,
           launch_setup_cams((const TripsView*)ctx->views.p, B, scene->poses, scene->n_images, scene->intrinsics,
                             scene->n_cameras, (CamConst*)ctx->cams.p, fb.stats, st));
-    STAGE(ctx, TRIPS_STAGE_BIN_POINTS, N > 0 ? 3 : 1, st, launch_bin_points(sp, (const CamConst*)ctx->cams.p, g, *params, B, fb, st));
+    STAGE(ctx, TRIPS_STAGE_BIN_POINTS, N > 0 ? 4 : 2, st, launch_bin_points(sp, (const CamConst*)ctx->cams.p, g, *params, B, fb, ctx->sm_count, st));
+    if (N > 0) STAGE(ctx, TRIPS_STAGE_COUNT, 1, st, launch_count(sp, g, B, fb, ctx->sm_count, st));
     {
         FwdBuffers fscan = fb;
         fscan.frag_cap   = ~0ull;  // sizing pass: the list buffer is grown below, nothing can overflow yet
@@ -531,7 +536,7 @@ int trips_get_stage_times(TripsContext* ctx, double* ms, int64_t* timed_calls, i
 
 const char* trips_stage_name(int stage)
 {
-    static const char* names[TRIPS_NUM_STAGES] = {"setup_cams", "bin_points", "scan", "collect", "sort_blend",
+    static const char* names[TRIPS_NUM_STAGES] = {"setup_cams", "bin_points", "count", "scan", "collect", "sort_blend",
                                                   "blend_backward", "unpack_grads", "adam", "l1_loss"};
     return (stage >= 0 && stage < TRIPS_NUM_STAGES) ? names[stage] : "?";
 }

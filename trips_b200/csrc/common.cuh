@@ -71,8 +71,10 @@ __host__ __device__ constexpr int egrad_stride(int C) { return 4 + ((C + 3) & ~3
 // Everything the forward kernels need besides the scene (all device pointers into context scratch).
 struct FwdBuffers
 {
-    uint32_t* bin_count;              // [B,n_bins] visible points per screen bin
-    uint32_t* bin_cursor;             // [B,n_bins] first entry of the bin within the view, advanced while scattering
+    uint32_t* bin_count;              // [B,blocks,n_bins] visible points per (binning block, screen bin)
+    uint32_t* bin_base;               // [B,blocks,n_bins] first entry (within the view) of every (block, bin) pair
+    uint32_t* view_total;             // [B] visible points per view
+    uint32_t* bin_cursor;             // [B,n_bins] first entry of every bin within the view
     unsigned long long* entry_base;   // [B+1] first entry of each view
     float* entries;                   // [sum V_b, entry_stride]
     uint32_t* counts;                 // [B,P] list lengths
@@ -212,8 +214,10 @@ __device__ __forceinline__ void tile_pixel(const Geom& g, int tile, int lane, in
 cudaError_t launch_setup_cams(const TripsView* d_views, int B, const double* poses, int n_images, const float* intrinsics,
                               int n_cameras, CamConst* cams, DevStats* stats, cudaStream_t st);
 cudaError_t launch_bin_points(const ScenePtrs& sc, const CamConst* cams, const Geom& g, const TripsRenderParams& pr, int B,
-                              const FwdBuffers& fb, cudaStream_t st);
+                              const FwdBuffers& fb, int sm_count, cudaStream_t st);
+int bin_blocks_per_view(int B, int sm_count);
 cudaError_t launch_scan(const Geom& g, int B, int k_keep, const FwdBuffers& fb, int nchunks, cudaStream_t st);
+cudaError_t launch_count(const ScenePtrs& sc, const Geom& g, int B, const FwdBuffers& fb, int sm_count, cudaStream_t st);
 cudaError_t launch_collect(const ScenePtrs& sc, const Geom& g, int B, const FwdBuffers& fb, int sm_count, cudaStream_t st);
 cudaError_t launch_sort_blend(const ScenePtrs& sc, const Geom& g, const TripsRenderParams& pr, int B, const FwdBuffers& fb,
                               const LayerPtrs& out, int sm_count, cudaStream_t st);

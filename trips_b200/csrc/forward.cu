@@ -118,101 +118,137 @@ __device__ __forceinline__ Projected project_visible(const ScenePtrs& sc, const 
     return r;
 }
 
-__global__ __launch_bounds__(256) void bin_count_kernel(ScenePtrs sc, const CamConst* __restrict__ cams,
-                                                        const __grid_constant__ Geom g, TripsRenderParams pr, FwdBuffers fb)
+constexpr int kBinThreads = 512;
+
+// Every block owns a contiguous chunk of the point cloud (the same chunk in the count and in the scatter pass) and
+// keeps the histogram over screen bins in shared memory, so binning needs no global atomics: the count pass
+// stores one histogram row per block, the scan turns rows into per-(block, bin) first-entry offsets, and the scatter
+// pass hands out slots from a shared-memory copy of its row.
+__device__ __forceinline__ void block_chunk(int N, int& first, int& last)
 {
+    const int chunk = (N + gridDim.x - 1) / gridDim.x;
+    first           = blockIdx.x * chunk;
+    last            = min(N, first + chunk);
+}
+
+__global__ __launch_bounds__(kBinThreads) void bin_count_kernel(ScenePtrs sc, const CamConst* __restrict__ cams,
+                                                                const __grid_constant__ Geom g, TripsRenderParams pr, FwdBuffers fb)
+{
+    extern __shared__ uint32_t s_hist[];
     __shared__ CamConst cam;
     const int b = blockIdx.y;
     if (threadIdx.x < sizeof(CamConst) / 4) ((int*)&cam)[threadIdx.x] = ((const int*)&cams[b])[threadIdx.x];
+    for (int i = threadIdx.x; i < g.n_bins; i += blockDim.x) s_hist[i] = 0;
     __syncthreads();
     const size_t bN = (size_t)b * sc.N;
     const float fxc = cam.fx * cam.cfx;
-    uint32_t* bins  = fb.bin_count + (size_t)b * g.n_bins;
-    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < sc.N; i += gridDim.x * blockDim.x)
+    int first, last;
+    block_chunk(sc.N, first, last);
+    for (int i = first + threadIdx.x; i < last; i += blockDim.x)
     {
         const Projected r = project_visible(sc, cam, g, pr, bN, i, fxc);
-        if (r.ok) atomicAdd(bins + (__float2int_rd(r.v) >> kBinShift) * g.bins_x + (__float2int_rd(r.u) >> kBinShift), 1u);
+        if (r.ok) atomicAdd(s_hist + (__float2int_rd(r.v) >> kBinShift) * g.bins_x + (__float2int_rd(r.u) >> kBinShift), 1u);
     }
+    __syncthreads();
+    uint32_t* row = fb.bin_count + ((size_t)b * gridDim.x + blockIdx.x) * g.n_bins;
+    for (int i = threadIdx.x; i < g.n_bins; i += blockDim.x) row[i] = s_hist[i];
 }
 
-// one block: per view, exclusive scan of the bin counts -> first entry of every bin; entry_base = running total
-__global__ __launch_bounds__(1024) void bin_scan_kernel(const uint32_t* __restrict__ bin_count, uint32_t* __restrict__ bin_cursor,
-                                                        int n_bins, int B, unsigned long long* __restrict__ entry_base,
-                                                        DevStats* stats)
+// one block per view: rows [n_blocks, n_bins] of per-block counts -> first entry (within the view) of every
+// (block, bin) pair, ordered by bin first and block second; view_total[b] = visible points of the view
+__global__ __launch_bounds__(1024) void bin_scan_kernel(const uint32_t* __restrict__ rows_in, uint32_t* __restrict__ rows_out,
+                                                        uint32_t* __restrict__ bin_first, int n_bins, int n_blocks,
+                                                        uint32_t* __restrict__ view_total)
 {
     __shared__ uint32_t sm[32];
     __shared__ uint32_t carry_s;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int b    = blockIdx.x;
+    const uint32_t* r = rows_in + (size_t)b * n_blocks * n_bins;
+    uint32_t* w       = rows_out + (size_t)b * n_blocks * n_bins;
+    uint32_t* o       = bin_first + (size_t)b * n_bins;
+    if (threadIdx.x == 0) carry_s = 0;
+    __syncthreads();
+    for (int s = 0; s < n_bins; s += 1024)
+    {
+        const int i = s + threadIdx.x;
+        uint32_t v  = 0;  // visible points of bin i (sum over blocks)
+        if (i < n_bins)
+            for (int k = 0; k < n_blocks; ++k) v += r[(size_t)k * n_bins + i];
+        uint32_t inc = v;
+#pragma unroll
+        for (int k = 1; k < 32; k <<= 1)
+        {
+            uint32_t t = __shfl_up_sync(kFull, inc, k);
+            if (lane >= k) inc += t;
+        }
+        if (lane == 31) sm[warp] = inc;
+        __syncthreads();
+        uint32_t wsum = sm[lane];
+        uint32_t winc = wsum;
+#pragma unroll
+        for (int k = 1; k < 32; k <<= 1)
+        {
+            uint32_t t = __shfl_up_sync(kFull, winc, k);
+            if (lane >= k) winc += t;
+        }
+        const uint32_t tot   = __shfl_sync(kFull, winc, 31);
+        const uint32_t woff  = __shfl_sync(kFull, winc - wsum, warp);
+        const uint32_t carry = carry_s;
+        if (i < n_bins)
+        {
+            uint32_t run = carry + woff + inc - v;  // first entry of bin i
+            o[i]         = run;
+            for (int k = 0; k < n_blocks; ++k)
+            {
+                w[(size_t)k * n_bins + i] = run;
+                run += r[(size_t)k * n_bins + i];
+            }
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) carry_s = carry + tot;
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) view_total[b] = carry_s;
+}
+
+__global__ void entry_base_kernel(const uint32_t* __restrict__ view_total, int B, unsigned long long* __restrict__ entry_base,
+                                  DevStats* stats)
+{
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
     unsigned long long base = 0;
     for (int b = 0; b < B; ++b)
     {
-        const uint32_t* c = bin_count + (size_t)b * n_bins;
-        uint32_t* o       = bin_cursor + (size_t)b * n_bins;
-        if (threadIdx.x == 0) carry_s = 0;
-        __syncthreads();
-        for (int s = 0; s < n_bins; s += 1024)
-        {
-            const int i  = s + threadIdx.x;
-            uint32_t v   = (i < n_bins) ? c[i] : 0u;
-            uint32_t inc = v;
-#pragma unroll
-            for (int k = 1; k < 32; k <<= 1)
-            {
-                uint32_t t = __shfl_up_sync(kFull, inc, k);
-                if (lane >= k) inc += t;
-            }
-            if (lane == 31) sm[warp] = inc;
-            __syncthreads();
-            uint32_t wsum = sm[lane];
-            uint32_t winc = wsum;
-#pragma unroll
-            for (int k = 1; k < 32; k <<= 1)
-            {
-                uint32_t t = __shfl_up_sync(kFull, winc, k);
-                if (lane >= k) winc += t;
-            }
-            const uint32_t tot   = __shfl_sync(kFull, winc, 31);
-            const uint32_t woff  = __shfl_sync(kFull, winc - wsum, warp);
-            const uint32_t carry = carry_s;
-            if (i < n_bins) o[i] = carry + woff + inc - v;
-            __syncthreads();
-            if (threadIdx.x == 0) carry_s = carry + tot;
-            __syncthreads();
-        }
-        if (threadIdx.x == 0)
-        {
-            entry_base[b] = base;
-            base += carry_s;
-        }
-        __syncthreads();
+        entry_base[b] = base;
+        base += view_total[b];
     }
-    if (threadIdx.x == 0)
-    {
-        entry_base[B]  = base;
-        stats->visible = base;
-    }
+    entry_base[B]  = base;
+    stats->visible = base;
 }
 
 template <int C>
-__global__ __launch_bounds__(256) void bin_scatter_kernel(ScenePtrs sc, const CamConst* __restrict__ cams,
-                                                          const __grid_constant__ Geom g, TripsRenderParams pr, FwdBuffers fb)
+__global__ __launch_bounds__(kBinThreads) void bin_scatter_kernel(ScenePtrs sc, const CamConst* __restrict__ cams,
+                                                                  const __grid_constant__ Geom g, TripsRenderParams pr, FwdBuffers fb)
 {
     constexpr int ES = entry_stride(C);
+    extern __shared__ uint32_t s_cursor[];
     __shared__ CamConst cam;
     const int b = blockIdx.y;
     if (threadIdx.x < sizeof(CamConst) / 4) ((int*)&cam)[threadIdx.x] = ((const int*)&cams[b])[threadIdx.x];
+    const uint32_t* row = fb.bin_base + ((size_t)b * gridDim.x + blockIdx.x) * g.n_bins;
+    for (int i = threadIdx.x; i < g.n_bins; i += blockDim.x) s_cursor[i] = row[i];
     __syncthreads();
     const size_t bN  = (size_t)b * sc.N;
     const float fxc  = cam.fx * cam.cfx;
-    uint32_t* cursor = fb.bin_cursor + (size_t)b * g.n_bins;
-    uint32_t* counts = fb.counts + (size_t)b * g.P;
     float* entries   = fb.entries + fb.entry_base[b] * ES;
-    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < sc.N; i += gridDim.x * blockDim.x)
+    int first, last;
+    block_chunk(sc.N, first, last);
+    for (int i = first + threadIdx.x; i < last; i += blockDim.x)
     {
         const Projected r = project_visible(sc, cam, g, pr, bN, i, fxc);
         if (!r.ok) continue;
         const int bin       = (__float2int_rd(r.v) >> kBinShift) * g.bins_x + (__float2int_rd(r.u) >> kBinShift);
-        const uint32_t slot = atomicAdd(cursor + bin, 1u);
+        const uint32_t slot = atomicAdd(s_cursor + bin, 1u);
         // layers 0..hi, stopping where the 2x2 footprint leaves the layer (RenderForward.cu:342-363)
         int hi = 0;
         if (r.ps > 1.f) hi = min(tm_ceil_log2(r.ps), g.L - 1);
@@ -223,11 +259,6 @@ __global__ __launch_bounds__(256) void bin_scatter_kernel(ScenePtrs sc, const Ca
             const int px = __float2int_rd(x), py = __float2int_rd(y);
             if (px < 0 || px >= g.W[layer] - 1 || py < 0 || py >= g.H[layer] - 1) break;
             if (pr.drop_out_points_by_radius && (float)(int)rad < pr.drop_out_radius_threshold) break;
-            uint32_t* c0 = counts + g.base[layer] + py * g.W[layer] + px;
-            atomicAdd(c0, 1u);
-            atomicAdd(c0 + 1, 1u);
-            atomicAdd(c0 + g.W[layer], 1u);
-            atomicAdd(c0 + g.W[layer] + 1, 1u);
         }
         float conf = 0.f;
         const bool tex_ok = (unsigned)r.tex < (unsigned)sc.n_tex;
@@ -240,31 +271,39 @@ __global__ __launch_bounds__(256) void bin_scatter_kernel(ScenePtrs sc, const Ca
         e[0]           = make_float4(r.u, r.v, r.ps, r.z);
         e[1]           = make_float4(__int_as_float(i), conf, __ldg(sc.point_size + i), __int_as_float(layer));
         e[2]           = make_float4(p.x, p.y, p.z, __int_as_float(tex_ok ? r.tex : -1));
-        float row[(C + 3) & ~3];
+        float row_t[(C + 3) & ~3];
 #pragma unroll
-        for (int c = 0; c < ((C + 3) & ~3); ++c) row[c] = (c < C && tex_ok) ? __ldg(sc.texture + (size_t)c * sc.n_tex + r.tex) : 0.f;
+        for (int c = 0; c < ((C + 3) & ~3); ++c) row_t[c] = (c < C && tex_ok) ? __ldg(sc.texture + (size_t)c * sc.n_tex + r.tex) : 0.f;
 #pragma unroll
-        for (int c = 0; c < ((C + 3) & ~3); c += 4) e[3 + c / 4] = make_float4(row[c], row[c + 1], row[c + 2], row[c + 3]);
+        for (int c = 0; c < ((C + 3) & ~3); c += 4) e[3 + c / 4] = make_float4(row_t[c], row_t[c + 1], row_t[c + 2], row_t[c + 3]);
     }
 }
 
+int bin_blocks_per_view(int B, int sm_count) { return max(4, min(128, (4 * sm_count + B - 1) / B)); }
+
 cudaError_t launch_bin_points(const ScenePtrs& sc, const CamConst* cams, const Geom& g, const TripsRenderParams& pr, int B,
-                              const FwdBuffers& fb, cudaStream_t st)
+                              const FwdBuffers& fb, int sm_count, cudaStream_t st)
 {
-    cudaError_t e = cudaMemsetAsync(fb.bin_count, 0, sizeof(uint32_t) * (size_t)B * g.n_bins, st);
-    if (e != cudaSuccess) return e;
-    int bx = max(1, min((sc.N + 255) / 256, 148 * 8));
-    if (sc.N > 0) bin_count_kernel<<<dim3(bx, B), 256, 0, st>>>(sc, cams, g, pr, fb);
-    bin_scan_kernel<<<1, 1024, 0, st>>>(fb.bin_count, fb.bin_cursor, g.n_bins, B, fb.entry_base, fb.stats);
+    const int nb       = bin_blocks_per_view(B, sm_count);
+    const size_t smem  = sizeof(uint32_t) * (size_t)g.n_bins;
+    if (sc.N > 0)
+        bin_count_kernel<<<dim3(nb, B), kBinThreads, smem, st>>>(sc, cams, g, pr, fb);
+    else
+    {
+        cudaError_t e = cudaMemsetAsync(fb.bin_count, 0, sizeof(uint32_t) * (size_t)B * nb * g.n_bins, st);
+        if (e != cudaSuccess) return e;
+    }
+    bin_scan_kernel<<<B, 1024, 0, st>>>(fb.bin_count, fb.bin_base, fb.bin_cursor, g.n_bins, nb, fb.view_total);
+    entry_base_kernel<<<1, 32, 0, st>>>(fb.view_total, B, fb.entry_base, fb.stats);
     if (sc.N > 0)
     {
         switch (sc.C)
         {
-            case 3: bin_scatter_kernel<3><<<dim3(bx, B), 256, 0, st>>>(sc, cams, g, pr, fb); break;
-            case 4: bin_scatter_kernel<4><<<dim3(bx, B), 256, 0, st>>>(sc, cams, g, pr, fb); break;
-            case 6: bin_scatter_kernel<6><<<dim3(bx, B), 256, 0, st>>>(sc, cams, g, pr, fb); break;
-            case 8: bin_scatter_kernel<8><<<dim3(bx, B), 256, 0, st>>>(sc, cams, g, pr, fb); break;
-            case 16: bin_scatter_kernel<16><<<dim3(bx, B), 256, 0, st>>>(sc, cams, g, pr, fb); break;
+            case 3: bin_scatter_kernel<3><<<dim3(nb, B), kBinThreads, smem, st>>>(sc, cams, g, pr, fb); break;
+            case 4: bin_scatter_kernel<4><<<dim3(nb, B), kBinThreads, smem, st>>>(sc, cams, g, pr, fb); break;
+            case 6: bin_scatter_kernel<6><<<dim3(nb, B), kBinThreads, smem, st>>>(sc, cams, g, pr, fb); break;
+            case 8: bin_scatter_kernel<8><<<dim3(nb, B), kBinThreads, smem, st>>>(sc, cams, g, pr, fb); break;
+            case 16: bin_scatter_kernel<16><<<dim3(nb, B), kBinThreads, smem, st>>>(sc, cams, g, pr, fb); break;
             default: return cudaErrorInvalidValue;
         }
     }
@@ -409,52 +448,207 @@ cudaError_t launch_scan(const Geom& g, int B, int k_keep, const FwdBuffers& fb, 
 }
 
 // ------------------------------------------------------------------------------------------------------------
-// collect: four threads per visible point (entry) write one 16-byte fragment per (layer, footprint pixel) into the
-// per-pixel lists: the 64-bit sort key (depth bits << 32 | point id), the fragment's alpha and the entry index.
-// Computing alpha here, where every lane holds a fragment, keeps the per-fragment arithmetic (bilinear weight,
-// confidence, layer factor) out of the per-pixel blend.  alpha = bilinear * confidence * layer factor, in the
-// operation order of FastSortFusedNew (RenderForward.cu:882-899).  Replaces SplattingPass (RenderForward.cu:368-436).
-// Entries are in screen-bin order, so the list cursors and the fragment stores of a block stay within a small
-// window of the pixel arrays.
+// count and collect: fragments into per-pixel lists, with the list counters of a screen bin held in shared memory
+//
+// Entries are in bin order, and every fragment of a bin's points lands inside the bin's window: on layer l the
+// pixels [x0, x0 + w_l) x [y0, y0 + w_l) with x0 = (32 bx) >> l and w_l = (31 >> l) + 3 (the 2x2 footprint adds one
+// pixel).  A block takes a chunk of consecutive entries, and for each bin the chunk touches it
+//   count pass:   counts the fragments per window pixel with shared-memory atomics and adds every non-zero window
+//                 counter to the global list length once;
+//   collect pass: counts the same way, reserves for each window pixel a contiguous range of its list with ONE
+//                 returning global atomic, then hands out slots inside the ranges with shared-memory atomics and
+//                 writes the 16-byte fragments: the 64-bit sort key (depth bits << 32 | point id), alpha and the
+//                 entry index.
+// This replaces one global atomic per fragment (SplattingPass, RenderForward.cu:368-436, and the counting half of
+// CountAndCollectTiled, :347-362) by one per (chunk, touched pixel).  alpha = bilinear * confidence * layer factor
+// in the operation order of FastSortFusedNew (RenderForward.cu:882-899) is computed here, where every thread holds
+// a whole point, and travels with the fragment.
 // ------------------------------------------------------------------------------------------------------------
-__global__ __launch_bounds__(256) void collect_kernel(int ES, const __grid_constant__ Geom g, FwdBuffers fb)
+constexpr int kWinChunk   = 2048;  // entries per block ticket
+constexpr int kWinThreads = 256;
+constexpr int kWinMax     = 34 * 34 + 18 * 18 + 10 * 10 + 6 * 6 + 4 * 4 + 3 * 3 * 3;  // 1659 window pixels over 8 layers
+
+struct Window
 {
-    const int b      = blockIdx.y;
-    uint32_t* cursor = fb.offsets + (size_t)b * g.P;
-    const unsigned long long vbase = fb.view_base[b];
-    const unsigned long long vend  = fb.view_base[b + 1];
-    if (vend > fb.frag_cap) return;  // list buffer too small: the overflow status bit is already raised
-    uint4* frags         = fb.frags + vbase;
-    const size_t n_entry = (size_t)(fb.entry_base[b + 1] - fb.entry_base[b]);
-    const float* entries = fb.entries + fb.entry_base[b] * ES;
-    const size_t total   = n_entry * 4;
-    for (size_t t = (size_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (size_t)gridDim.x * blockDim.x)
+    int x0[TRIPS_MAX_LAYERS], y0[TRIPS_MAX_LAYERS], off[TRIPS_MAX_LAYERS + 1];
+};
+
+__device__ __forceinline__ int win_w(int l) { return (31 >> l) + 3; }
+
+__device__ __forceinline__ Window make_window(const Geom& g, int bin)
+{
+    Window w;
+    const int by = bin / g.bins_x, bx = bin - by * g.bins_x;
+    int o = 0;
+#pragma unroll
+    for (int l = 0; l < TRIPS_MAX_LAYERS; ++l)
     {
-        const size_t ei = t >> 2;
-        const int sub   = (int)(t & 3);
-        const float4 e0 = *reinterpret_cast<const float4*>(entries + ei * ES);      // u v ps z
-        const float4 e1 = *reinterpret_cast<const float4*>(entries + ei * ES + 4);  // pid conf raw nl
-        const int nl     = __float_as_int(e1.w);
-        const float conf = e1.y;
-        float x = e0.x, y = e0.y;
-        for (int layer = 0; layer < nl; ++layer, x *= 0.5f, y *= 0.5f)
+        w.x0[l]  = (bx << kBinShift) >> l;
+        w.y0[l]  = (by << kBinShift) >> l;
+        w.off[l] = o;
+        if (l < g.L) o += win_w(l) * win_w(l);
+    }
+    w.off[TRIPS_MAX_LAYERS] = o;
+    return w;
+}
+
+// window counter -> global pixel index of the view, -1 if outside the layer
+__device__ __forceinline__ int window_pixel(const Geom& g, const Window& w, int i)
+{
+    int l = 0;
+#pragma unroll
+    for (int k = 1; k < TRIPS_MAX_LAYERS; ++k)
+        if (k < g.L && i >= w.off[k]) l = k;
+    const int r  = i - w.off[l];
+    const int ww = win_w(l);
+    const int dy = r / ww, dx = r - dy * ww;
+    const int x = w.x0[l] + dx, y = w.y0[l] + dy;
+    return (x < g.W[l] && y < g.H[l]) ? g.base[l] + y * g.W[l] + x : -1;
+}
+
+// the chunk [c0, c1) of the view's entries and the first bin it touches; false when the view has no more chunks
+__device__ __forceinline__ bool next_chunk(const FwdBuffers& fb, const Geom& g, int b, uint32_t n_entry, uint32_t* s_tmp,
+                                           uint32_t& c0, uint32_t& c1, int& first_bin)
+{
+    __syncthreads();
+    if (threadIdx.x == 0)
+    {
+        const uint32_t t = atomicAdd(fb.ticket + b, 1u);
+        uint32_t lo      = (uint32_t)min((unsigned long long)t * kWinChunk, (unsigned long long)n_entry);
+        s_tmp[0]         = lo;
+        // last bin whose first entry is <= lo (empty bins share their first entry with the next non-empty one)
+        const uint32_t* bf = fb.bin_cursor + (size_t)b * g.n_bins;
+        int a = 0, z = g.n_bins;  // invariant: bf[a] <= lo
+        while (z - a > 1)
         {
-            const int px = __float2int_rd(x) + (sub & 1), py = __float2int_rd(y) + (sub >> 1);
-            const uint32_t slot = atomicAdd(cursor + g.base[layer] + py * g.W[layer] + px, 1u);
-            // x, y equal (u, v) * 2^-layer exactly (power-of-two scaling)
-            const float dx = fabsf(x - (float)px), dy = fabsf(y - (float)py);
-            float bl = (1.f - dx) * (1.f - dy);
-            if (dx > 1.f || dy > 1.f) bl = 0.f;
-            float a = bl * conf;
-            a *= layer_factor(e0.z, layer, g.L, nullptr);
-            frags[slot] = make_uint4(__float_as_uint(e1.x), __float_as_uint(e0.w), __float_as_uint(a), (unsigned)ei);
+            const int mid = (a + z) >> 1;
+            if (bf[mid] <= lo)
+                a = mid;
+            else
+                z = mid;
+        }
+        s_tmp[1] = (uint32_t)a;
+    }
+    __syncthreads();
+    c0        = s_tmp[0];
+    first_bin = (int)s_tmp[1];
+    c1        = min(n_entry, c0 + (uint32_t)kWinChunk);
+    return c0 < n_entry;
+}
+
+template <bool COLLECT>
+__global__ __launch_bounds__(kWinThreads) void window_kernel(int ES, const __grid_constant__ Geom g, FwdBuffers fb)
+{
+    __shared__ uint32_t s_cnt[kWinMax];
+    __shared__ uint32_t s_base[COLLECT ? kWinMax : 1];
+    __shared__ uint32_t s_tmp[2];
+    const int b = blockIdx.y;
+    if (COLLECT && fb.view_base[b + 1] > fb.frag_cap) return;  // list buffer too small: the overflow status bit is already raised
+    uint32_t* pixel_ctr   = (COLLECT ? fb.offsets : fb.counts) + (size_t)b * g.P;
+    uint4* frags          = fb.frags + fb.view_base[COLLECT ? b : 0];
+    const uint32_t n_entry = (uint32_t)(fb.entry_base[b + 1] - fb.entry_base[b]);
+    const float* entries   = fb.entries + fb.entry_base[b] * ES;
+    const uint32_t* bfirst = fb.bin_cursor + (size_t)b * g.n_bins;
+    uint32_t c0, c1;
+    int bin;
+    while (next_chunk(fb, g, b, n_entry, s_tmp, c0, c1, bin))
+    {
+        for (; bin < g.n_bins && bfirst[bin] < c1; ++bin)
+        {
+            const uint32_t bin_end = (bin + 1 < g.n_bins) ? bfirst[bin + 1] : n_entry;
+            const uint32_t lo = max(c0, bfirst[bin]), hi = min(c1, bin_end);
+            if (lo >= hi) continue;  // uniform: all threads read the same values
+            const Window w = make_window(g, bin);
+            const int n_win = w.off[TRIPS_MAX_LAYERS];
+            for (int i = threadIdx.x; i < n_win; i += kWinThreads) s_cnt[i] = 0;
+            __syncthreads();
+            // ---- fragments per window pixel ----
+            for (uint32_t ei = lo + threadIdx.x; ei < hi; ei += kWinThreads)
+            {
+                const float4 e0 = *reinterpret_cast<const float4*>(entries + (size_t)ei * ES);  // u v ps z
+                const int nl    = __float_as_int(entries[(size_t)ei * ES + 7]);
+                float x = e0.x, y = e0.y;
+                for (int layer = 0; layer < nl; ++layer, x *= 0.5f, y *= 0.5f)
+                {
+                    const int ww = win_w(layer);
+                    uint32_t* c  = s_cnt + w.off[layer] + (__float2int_rd(y) - w.y0[layer]) * ww + (__float2int_rd(x) - w.x0[layer]);
+                    atomicAdd(c, 1u);
+                    atomicAdd(c + 1, 1u);
+                    atomicAdd(c + ww, 1u);
+                    atomicAdd(c + ww + 1, 1u);
+                }
+            }
+            __syncthreads();
+            // ---- one global atomic per touched pixel ----
+            for (int i = threadIdx.x; i < n_win; i += kWinThreads)
+            {
+                const uint32_t c = s_cnt[i];
+                if (c)
+                {
+                    const int pix = window_pixel(g, w, i);
+                    if (COLLECT)
+                    {
+                        s_base[i] = (pix >= 0) ? atomicAdd(pixel_ctr + pix, c) : 0u;
+                        s_cnt[i]  = 0;
+                    }
+                    else if (pix >= 0)
+                        atomicAdd(pixel_ctr + pix, c);
+                }
+            }
+            __syncthreads();
+            if (COLLECT)
+            {
+                // ---- slots inside the reserved ranges; alpha and the fragment itself ----
+                for (uint32_t ei = lo + threadIdx.x; ei < hi; ei += kWinThreads)
+                {
+                    const float4 e0 = *reinterpret_cast<const float4*>(entries + (size_t)ei * ES);      // u v ps z
+                    const float4 e1 = *reinterpret_cast<const float4*>(entries + (size_t)ei * ES + 4);  // pid conf raw nl
+                    const int nl     = __float_as_int(e1.w);
+                    const float conf = e1.y;
+                    const uint32_t pid = __float_as_uint(e1.x), zb = __float_as_uint(e0.w);
+                    float x = e0.x, y = e0.y;
+                    for (int layer = 0; layer < nl; ++layer, x *= 0.5f, y *= 0.5f)
+                    {
+                        // x, y equal (u, v) * 2^-layer exactly (power-of-two scaling)
+                        const int px = __float2int_rd(x), py = __float2int_rd(y);
+                        const int ww = win_w(layer);
+                        const int li = w.off[layer] + (py - w.y0[layer]) * ww + (px - w.x0[layer]);
+                        const float lf  = layer_factor(e0.z, layer, g.L, nullptr);
+                        const float dx0 = fabsf(x - (float)px), dx1 = fabsf(x - (float)(px + 1));
+                        const float dy0 = fabsf(y - (float)py), dy1 = fabsf(y - (float)(py + 1));
+                        auto emit = [&](int idx, float dx, float dy) {
+                            float bl = (1.f - dx) * (1.f - dy);
+                            if (dx > 1.f || dy > 1.f) bl = 0.f;
+                            float a = bl * conf;
+                            a *= lf;
+                            const uint32_t slot = s_base[idx] + atomicAdd(s_cnt + idx, 1u);
+                            frags[slot]         = make_uint4(pid, zb, __float_as_uint(a), ei);
+                        };
+                        emit(li, dx0, dy0);
+                        emit(li + 1, dx1, dy0);
+                        emit(li + ww, dx0, dy1);
+                        emit(li + ww + 1, dx1, dy1);
+                    }
+                }
+                __syncthreads();  // the next bin of this chunk reuses s_cnt / s_base
+            }
         }
     }
 }
 
+cudaError_t launch_count(const ScenePtrs& sc, const Geom& g, int B, const FwdBuffers& fb, int sm_count, cudaStream_t st)
+{
+    cudaError_t e = cudaMemsetAsync(fb.ticket, 0, sizeof(unsigned) * B, st);
+    if (e != cudaSuccess) return e;
+    window_kernel<false><<<dim3(max(1, (sm_count * 8 + B - 1) / B), B), kWinThreads, 0, st>>>(entry_stride(sc.C), g, fb);
+    return cudaGetLastError();
+}
+
 cudaError_t launch_collect(const ScenePtrs& sc, const Geom& g, int B, const FwdBuffers& fb, int sm_count, cudaStream_t st)
 {
-    collect_kernel<<<dim3(sm_count * 8 / max(1, min(B, 8)) + 1, B), 256, 0, st>>>(entry_stride(sc.C), g, fb);
+    cudaError_t e = cudaMemsetAsync(fb.ticket, 0, sizeof(unsigned) * B, st);
+    if (e != cudaSuccess) return e;
+    window_kernel<true><<<dim3(max(1, (sm_count * 8 + B - 1) / B), B), kWinThreads, 0, st>>>(entry_stride(sc.C), g, fb);
     return cudaGetLastError();
 }
 
@@ -582,6 +776,7 @@ __global__ __launch_bounds__(kSbThreads) void sort_blend_kernel(ScenePtrs sc, co
         const size_t bP      = (size_t)b * g.P;
         const uint4* frags   = fb.frags + fb.view_base[b];
         const float* entries = fb.entries + fb.entry_base[b] * ES;
+        const uint32_t n_entry = (uint32_t)(fb.entry_base[b + 1] - fb.entry_base[b]);
         int layer, gx, gy, p;
         tile_pixel(g, tile, lane, layer, gx, gy, p);  // lane i owns one pixel of the tile
         uint32_t cnt = 0, start = 0;
@@ -634,7 +829,9 @@ __global__ __launch_bounds__(kSbThreads) void sort_blend_kernel(ScenePtrs sc, co
                         const uint2 o = kp[(size_t)i * 2];
                         rank += ((((u64)o.y << 32) | o.x) < mine) ? 1 : 0;
                     }
-                    if (rank < K)
+                    if (f.w >= n_entry)
+                        atomicOr(&fb.stats->status, TRIPS_DEV_BAD_FRAGMENT);  // corrupted list: skip instead of gathering out of bounds
+                    else if (rank < K)
                     {
                         sb_store_entry<C>(sorted + (seg * kSortedPad + rank) * E, entries, f.w, f.z);
                         if (pr.train) fb.records[(bP + seg_p) * 16 + rank] = make_uint2(f.w, f.z);
@@ -692,6 +889,12 @@ __global__ __launch_bounds__(kSbThreads) void sort_blend_kernel(ScenePtrs sc, co
                 }
                 if (j < min((int)cnt_s, K))
                 {
+                    if (v.eidx >= n_entry)
+                    {
+                        atomicOr(&fb.stats->status, TRIPS_DEV_BAD_FRAGMENT);
+                        v.eidx  = 0;
+                        v.alpha = 0;
+                    }
                     sb_store_entry<C>(sorted + (src * kSortedPad + j) * E, entries, v.eidx, v.alpha);
                     if (pr.train && p_s >= 0) fb.records[(bP + p_s) * 16 + j] = make_uint2(v.eidx, v.alpha);
                 }
@@ -732,8 +935,13 @@ __global__ __launch_bounds__(kSbThreads) void sort_blend_kernel(ScenePtrs sc, co
                 }
                 else
                 {
-                    const unsigned eidx = __float_as_uint(e[0]);
-                    a                   = e[1];
+                    unsigned eidx = __float_as_uint(e[0]);
+                    a             = e[1];
+                    if (eidx >= n_entry)  // only after a corrupted list was flagged in phase A: draw nothing, read in bounds
+                    {
+                        eidx = 0;
+                        a    = 0.f;
+                    }
                     const float* rp     = entries + (size_t)eidx * ES + 12;
 #pragma unroll
                     for (int c = 0; c < C; c += 4)
