@@ -152,6 +152,19 @@ typedef struct
  * launch over all tensors.  `tensors` is a HOST array. */
 int trips_adam_step(TripsContext* ctx, const TripsAdamTensor* tensors, int n_tensors, void* stream);
 
+/* No counterpart in the reference.  Same update as trips_adam_step for callers that cannot allocate device
+ * memory at the time of the step: code running while the application's own pool owns all free memory, hosts that
+ * forbid cudaMalloc after start-up, or a step issued inside a stream capture.  The table describing the tensors,
+ * which trips_adam_step keeps in cudaMalloc'ed context scratch, lives here in a fixed array inside the library's
+ * device image, so the call performs no cudaMalloc / cudaFree and needs no TripsContext.
+ * Limits and rules: at most TRIPS_ADAM_STATIC_MAX_TENSORS tensors per call (more returns TRIPS_ERR_TOO_LARGE); the
+ * array costs about 6 KB on every GPU that loads the library, until the process exits; the first call on a device
+ * looks up the array's device address (with that device current) and should be made before any stream capture;
+ * all calls on a device share the one array, which is rewritten by each call, so two calls that may overlap on
+ * the GPU (different streams without ordering) race on it and must be serialised by the caller. */
+#define TRIPS_ADAM_STATIC_MAX_TENSORS 64
+int trips_adam_step_static(const TripsAdamTensor* tensors, int n_tensors, void* stream);
+
 /* Stage timers: CUDA-event pairs around every kernel stage, the counterpart of the reference's
  * SAIGA_OPTIONAL_TIME_MEASURE scopes (src/lib/rendering/RenderForward.cu:1090,1166,1238,1271,
  * PointRenderer.cu:1338) carried in NeuralRenderInfo::timer_system.  Off by default. */

@@ -15,6 +15,7 @@ LIB_PATH = os.environ.get("TRIPS_B200_LIB") or os.path.join(HERE, "libtrips_b200
 MAX_LAYERS = 8
 MAX_KEEP = 16
 NUM_STAGES = 10
+ADAM_STATIC_MAX_TENSORS = 64
 
 OK = 0
 ERR_INVALID_ARG = -1
@@ -77,6 +78,7 @@ SYMBOLS = {
     "trips_last_status": (C.c_uint32, [C.c_void_p, C.c_void_p]),
     "trips_get_stats": (C.c_int, [C.c_void_p, C.POINTER(TripsStats), C.c_void_p]),
     "trips_adam_step": (C.c_int, [C.c_void_p, C.POINTER(TripsAdamTensor), C.c_int, C.c_void_p]),
+    "trips_adam_step_static": (C.c_int, [C.POINTER(TripsAdamTensor), C.c_int, C.c_void_p]),
     "trips_enable_stage_timers": (C.c_int, [C.c_void_p, C.c_int]),
     "trips_get_stage_times": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int]),
     "trips_stage_name": (C.c_char_p, [C.c_int]),
