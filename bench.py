@@ -210,6 +210,7 @@ def run_ours(args, rank, world, local_rank):
     import torch
     import torch.distributed as dist
     from trips_b200 import build as tb
+    from trips_b200.dist import FlatGradLayout
     from trips_b200.modules import NeuralScene, images_for
     from trips_b200.optim import MyAdam
     from trips_b200.renderer import NeuralRenderInfo, PointRendererCache, RenderParams
@@ -235,14 +236,9 @@ def run_ours(args, rank, world, local_rank):
     info = NeuralRenderInfo(scene=ns, images=images_for(s, my_views), params=RenderParams(num_texture_channels=C, k_keep=s.k_keep),
                             num_layers=L, train=True, cache=cache)
     # all point gradients live in one flat buffer so that one collective sums them over ranks
-    n_flat = C * N + N + 4 * N + N + C
-    flat = torch.zeros(n_flat, device=dev)
-    o = 0
-    gout = {}
-    for key, shape in (("texture", (C, N)), ("confidence", (1, N)), ("points", (N, 4)), ("point_size", (N, 1)), ("background", (C,))):
-        n = int(np.prod(shape))
-        gout[key] = flat[o:o + n].view(shape)
-        o += n
+    layout = FlatGradLayout(N, N, C)
+    flat = torch.zeros(layout.numel, device=dev)
+    gout = layout.views(flat)
     params = [tex.texture_raw, tex.confidence_raw, pc.t_position, pc.t_point_size, tex.background_color_raw]
     for p_, k in zip(params, ("texture", "confidence", "points", "point_size", "background")):
         p_.grad = gout[k]

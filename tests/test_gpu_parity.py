@@ -165,6 +165,48 @@ def test_config1_forward(oracle_lib, cuda_lib):
         assert np.max(np.abs(got - o) / np.maximum(np.abs(o), 1e-3)) <= TOL_PYRAMID
 
 
+def test_against_frozen_fixture(cuda_lib):
+    """The committed fixture tests/golden/tiny_scene.npz (oracle outputs frozen by tests/golden/make_golden.py):
+    the CUDA path must reproduce it without the oracle being involved at run time."""
+    import importlib.util
+    import os
+    import torch
+    here = os.path.join(os.path.dirname(__file__), "golden")
+    spec = importlib.util.spec_from_file_location("make_golden", os.path.join(here, "make_golden.py"))
+    mg = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mg)
+    gold = np.load(os.path.join(here, "tiny_scene.npz"))
+    s = mg.scene()
+    ns, info, blend = gpu_render(s, train=True)
+    params = (ns.texture.texture_raw, ns.texture.confidence_raw, ns.texture.background_color_raw,
+              ns.point_cloud_cuda.t_position, ns.point_cloud_cuda.t_point_size)
+    outs = blend(info)
+    C, P = s.channels, scenes.num_pyramid_pixels(s.width, s.height, s.num_layers)
+    sizes = scenes.layer_sizes(s.width, s.height, s.num_layers)
+    loss = 0
+    for b in range(s.n_views):
+        depth, nl, rec = info.cache.debug_points(b, s.n_points)
+        assert np.array_equal(depth.view(np.uint32), gold[f"depth_{b}"].view(np.uint32))
+        assert np.array_equal(nl, gold[f"nlayers_{b}"])
+        counts, offsets, frags = info.cache.debug_lists(b, P)
+        assert np.array_equal(counts, gold[f"counts_{b}"]) and np.array_equal(offsets, gold[f"offsets_{b}"])
+        assert np.array_equal(sort_lists(counts, offsets, frags), gold[f"frags_{b}"])
+        nrec, pid, alpha = info.cache.debug_records(b, P)
+        assert np.array_equal(nrec, gold[f"nrec_{b}"]) and np.array_equal(pid, gold[f"rec_pid_{b}"])
+        flat = np.concatenate([o[b].detach().cpu().numpy().reshape(-1) for o in outs])
+        ref = gold[f"pyramid_{b}"]
+        assert np.max(np.abs(flat - ref) / np.maximum(np.abs(ref), 1e-3)) <= TOL_PYRAMID
+        g = scenes.target_gradient(s, b)
+        base = 0
+        for l, (w, h) in enumerate(sizes):
+            loss = loss + (outs[l][b] * torch.from_numpy(g[C * base:C * (base + w * h)].reshape(C, h, w)).cuda()).sum()
+            base += w * h
+    loss.backward()
+    for name, p_ in zip(("texture", "confidence", "background", "position", "point_size"), params):
+        ref = sum(gold[f"grad_{name}_{b}"] for b in range(s.n_views))
+        assert rel_err(p_.grad.cpu().numpy().reshape(ref.shape), ref) <= TOL_GRAD, name
+
+
 def test_adam_matches_reference_update(oracle_lib, cuda_lib):
     """Three consecutive steps with zero-gradient holes against the scalar restatement of adam_step."""
     import torch
