@@ -223,6 +223,9 @@ def run_ours(args, rank, world, local_rank):
     if rank == 0:
         tb.build()
     if world > 1:
+        # NCCL announces its version on stdout at VERSION / INFO level; rank 0's stdout must hold the JSON line only
+        if os.environ.get("NCCL_DEBUG", "").upper() in ("VERSION", "INFO", "TRACE") and not os.environ.get("NCCL_DEBUG_FILE"):
+            os.environ["NCCL_DEBUG"] = "WARN"
         dist.init_process_group("nccl", device_id=dev)
         dist.barrier()
 
