@@ -52,8 +52,11 @@ constexpr int kBwdWarps   = kBwdThreads / 32;
 //   phase 2 (lane = kept fragment): descriptor gradient and the image-space sums of the fragment's entry
 //     (RenderBackward.cu:335-393), accumulated with two vector atomics into the per-entry gradient rows, which are
 //     in screen-bin order like the entries and therefore stay hot in L2 while a region of the image is processed.
+#ifndef TRIPS_BWD_MIN_BLOCKS
+#define TRIPS_BWD_MIN_BLOCKS 1
+#endif
 template <int C>
-__global__ __launch_bounds__(kBwdThreads) void blend_backward_kernel(ScenePtrs sc, const CamConst* __restrict__ cams,
+__global__ __launch_bounds__(kBwdThreads, TRIPS_BWD_MIN_BLOCKS) void blend_backward_kernel(ScenePtrs sc, const CamConst* __restrict__ cams,
                                                                      const __grid_constant__ Geom g, TripsRenderParams pr, int B,
                                                                      FwdBuffers fb, BwdBuffers bb,
                                                                      const __grid_constant__ ConstLayerPtrs grad_in)
@@ -292,6 +295,7 @@ __global__ __launch_bounds__(256) void entry_grad_finish_kernel(FwdBuffers fb, B
 {
     constexpr int ES = entry_stride(C);
     constexpr int GS = egrad_stride(C);
+    constexpr int PS = egrad_stride(C);  // per-point row: xyz + size | descriptor row
     __shared__ CamConst cam;
     __shared__ double s_acc[8][11];
     const int b = blockIdx.y;
@@ -332,7 +336,7 @@ __global__ __launch_bounds__(256) void entry_grad_finish_kernel(FwdBuffers fb, B
             const float gp1 = cam.R[1] * gv0 + cam.R[4] * gv1 + cam.R[7] * gv2;
             const float gp2 = cam.R[2] * gv0 + cam.R[5] * gv1 + cam.R[8] * gv2;
             const float gl  = tm_softplus_grad(e1.z) * (fxc / vz) * s4.z;
-            atomicAdd(bb.g_pos_size + pid, make_float4(gp0, gp1, gp2, gl));
+            atomicAdd(reinterpret_cast<float4*>(bb.g_point + (size_t)pid * PS), make_float4(gp0, gp1, gp2, gl));
             if constexpr (CAM_GRADS)
             {
                 const float nx = vx * iz, ny = vy * iz;
@@ -350,7 +354,7 @@ __global__ __launch_bounds__(256) void entry_grad_finish_kernel(FwdBuffers fb, B
             }
         }
         if (tex < 0) continue;
-        if (s4.w != 0.f) atomicAdd(bb.g_conf + tex, s4.w);
+        if (s4.w != 0.f) atomicAdd(bb.g_conf_pt + pid, s4.w);
         float gt[(C + 3) & ~3];
         bool any = false;
 #pragma unroll
@@ -360,13 +364,8 @@ __global__ __launch_bounds__(256) void entry_grad_finish_kernel(FwdBuffers fb, B
             gt[c] = v4.x, gt[c + 1] = v4.y, gt[c + 2] = v4.z, gt[c + 3] = v4.w;
             any |= (v4.x != 0.f || v4.y != 0.f || v4.z != 0.f || v4.w != 0.f);
         }
-        if (any)
-        {
-            float gtc[C];
-#pragma unroll
-            for (int c = 0; c < C; ++c) gtc[c] = gt[c];
-            atomic_add_row<C>(bb.g_tex_packed + (size_t)tex * C, gtc);
-        }
+        // descriptor gradients share the point's row with the position gradient: both atomics hit one 32-byte sector
+        if (any) atomic_add_row<((C + 3) & ~3)>(bb.g_point + (size_t)pid * PS + 4, gt);
     }
     if constexpr (CAM_GRADS)
     {
@@ -393,27 +392,50 @@ __global__ __launch_bounds__(256) void entry_grad_finish_kernel(FwdBuffers fb, B
     }
 }
 
+// per-point rows (keyed by point id) -> the reference's output layouts (PointRenderer.cu:1423-1426).  With a
+// texture index the descriptor / confidence gradients of all points sharing a column are added (atomics into
+// zeroed outputs); with the identity index they are plain stores.
 template <int C>
-__global__ void unpack_tex_kernel(const float* __restrict__ g_packed, int n_tex, float* __restrict__ g_texture)
+__global__ __launch_bounds__(256) void unpack_point_kernel(const float* __restrict__ g_point, const float* __restrict__ g_conf_pt,
+                                                           const int32_t* __restrict__ index, int N, int n_tex,
+                                                           float4* __restrict__ g_points, float* __restrict__ g_size,
+                                                           float* __restrict__ g_texture, float* __restrict__ g_confidence)
 {
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < (size_t)n_tex; i += (size_t)gridDim.x * blockDim.x)
-    {
-        float v[C];
-#pragma unroll
-        for (int c = 0; c < C; ++c) v[c] = g_packed[i * C + c];
-#pragma unroll
-        for (int c = 0; c < C; ++c) g_texture[(size_t)c * n_tex + i] = v[c];
-    }
-}
-
-__global__ void unpack_pos_kernel(const float4* __restrict__ g_pos_size, int N, float4* __restrict__ g_points,
-                                  float* __restrict__ g_size)
-{
+    constexpr int PS = egrad_stride(C);
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < (size_t)N; i += (size_t)gridDim.x * blockDim.x)
     {
-        float4 v = g_pos_size[i];
+        const float4 v = *reinterpret_cast<const float4*>(g_point + i * PS);
         if (g_points) g_points[i] = make_float4(v.x, v.y, v.z, 0.f);
         if (g_size) g_size[i] = v.w;
+        float gt[(C + 3) & ~3];
+#pragma unroll
+        for (int c = 0; c < ((C + 3) & ~3); c += 4)
+        {
+            const float4 t4 = *reinterpret_cast<const float4*>(g_point + i * PS + 4 + c);
+            gt[c] = t4.x, gt[c + 1] = t4.y, gt[c + 2] = t4.z, gt[c + 3] = t4.w;
+        }
+        const float gc = g_conf_pt[i];
+        if (!index)
+        {
+            if (g_texture)
+            {
+#pragma unroll
+                for (int c = 0; c < C; ++c) g_texture[(size_t)c * n_tex + i] = gt[c];
+            }
+            if (g_confidence) g_confidence[i] = gc;
+        }
+        else
+        {
+            const int tex = index[i];
+            if ((unsigned)tex >= (unsigned)n_tex) continue;
+            if (g_texture)
+            {
+#pragma unroll
+                for (int c = 0; c < C; ++c)
+                    if (gt[c] != 0.f) atomicAdd(g_texture + (size_t)c * n_tex + tex, gt[c]);
+            }
+            if (g_confidence && gc != 0.f) atomicAdd(g_confidence + tex, gc);
+        }
     }
 }
 
@@ -461,28 +483,38 @@ cudaError_t launch_unpack_grads(const ScenePtrs& sc, const CamConst* cams, int B
         }
 #undef TRIPS_FIN_CASE
     }
-    if (out.texture)
+    if (sc.N > 0 && (out.texture || out.confidence || out.points || out.point_size))
     {
-        int blocks = max(1, (int)min((size_t)148 * 16, ((size_t)sc.n_tex + 255) / 256));
+        if (sc.index || sc.n_tex != sc.N)
+        {
+            // columns are accumulated (or not covered by the identity mapping): start from zero
+            if (out.texture)
+            {
+                cudaError_t e = cudaMemsetAsync(out.texture, 0, sizeof(float) * (size_t)sc.C * sc.n_tex, st);
+                if (e != cudaSuccess) return e;
+            }
+            if (out.confidence)
+            {
+                cudaError_t e = cudaMemsetAsync(out.confidence, 0, sizeof(float) * (size_t)sc.n_tex, st);
+                if (e != cudaSuccess) return e;
+            }
+        }
+        int blocks = max(1, (int)min((size_t)sm_count * 16, ((size_t)sc.N + 255) / 256));
+#define TRIPS_UNPACK_CASE(CC)                                                                                           \
+    case CC:                                                                                                            \
+        unpack_point_kernel<CC><<<blocks, 256, 0, st>>>(bb.g_point, bb.g_conf_pt, sc.index, sc.N, sc.n_tex,              \
+                                                        (float4*)out.points, out.point_size, out.texture, out.confidence); \
+        break;
         switch (sc.C)
         {
-            case 3: unpack_tex_kernel<3><<<blocks, 256, 0, st>>>(bb.g_tex_packed, sc.n_tex, out.texture); break;
-            case 4: unpack_tex_kernel<4><<<blocks, 256, 0, st>>>(bb.g_tex_packed, sc.n_tex, out.texture); break;
-            case 6: unpack_tex_kernel<6><<<blocks, 256, 0, st>>>(bb.g_tex_packed, sc.n_tex, out.texture); break;
-            case 8: unpack_tex_kernel<8><<<blocks, 256, 0, st>>>(bb.g_tex_packed, sc.n_tex, out.texture); break;
-            case 16: unpack_tex_kernel<16><<<blocks, 256, 0, st>>>(bb.g_tex_packed, sc.n_tex, out.texture); break;
+            TRIPS_UNPACK_CASE(3)
+            TRIPS_UNPACK_CASE(4)
+            TRIPS_UNPACK_CASE(6)
+            TRIPS_UNPACK_CASE(8)
+            TRIPS_UNPACK_CASE(16)
             default: return cudaErrorInvalidValue;
         }
-    }
-    if (out.confidence)
-    {
-        cudaError_t e = cudaMemcpyAsync(out.confidence, bb.g_conf, sizeof(float) * sc.n_tex, cudaMemcpyDeviceToDevice, st);
-        if (e != cudaSuccess) return e;
-    }
-    if (out.points || out.point_size)
-    {
-        int blocks = max(1, (int)min((size_t)148 * 16, ((size_t)sc.N + 255) / 256));
-        unpack_pos_kernel<<<blocks, 256, 0, st>>>(bb.g_pos_size, sc.N, (float4*)out.points, out.point_size);
+#undef TRIPS_UNPACK_CASE
     }
     unpack_small_kernel<<<1, 1, 0, st>>>(sc.C, B, cams, bb.g_bg, bb.g_pose, bb.g_k, out.background, out.pose_tangent,
                                          out.intrinsics);

@@ -111,7 +111,7 @@ struct TripsContext
     // forward scratch
     DevBuf views, cams, bin_count, bin_base, view_total, bin_cursor, entry_base, entries, counts, offsets, partial, view_base, frags, rec_n, records, stats, ticket;
     // backward scratch
-    DevBuf egrad, g_tex, g_conf, g_pos, g_small;
+    DevBuf egrad, g_point, g_conf_pt, g_small;
     // adam
     DevBuf adam_tab;
     // pinned host mirror: view_base[B+1] then DevStats
@@ -247,8 +247,8 @@ void trips_context_destroy(TripsContext* c)
 {
     if (!c) return;
     DevBuf* all[] = {&c->views, &c->cams, &c->bin_count, &c->bin_base, &c->view_total, &c->bin_cursor, &c->entry_base, &c->entries, &c->counts, &c->offsets,
-                     &c->partial, &c->view_base, &c->frags, &c->rec_n, &c->records, &c->stats, &c->ticket, &c->egrad, &c->g_tex,
-                     &c->g_conf, &c->g_pos, &c->g_small, &c->adam_tab};
+                     &c->partial, &c->view_base, &c->frags, &c->rec_n, &c->records, &c->stats, &c->ticket, &c->egrad, &c->g_point,
+                     &c->g_conf_pt, &c->g_small, &c->adam_tab};
     for (DevBuf* b : all) free_buf(*b);
     c->timers.destroy();
     if (c->h_pinned) cudaFreeHost(c->h_pinned);
@@ -426,23 +426,20 @@ int trips_backward(TripsContext* ctx, const TripsScene* scene, const float* cons
 
     const size_t GS = (size_t)egrad_stride(C);
     CU_CHECK(ctx, ensure(ctx->egrad, sizeof(float) * GS * (size_t)ctx->total_entries + 16, 1.25));
-    CU_CHECK(ctx, ensure(ctx->g_tex, sizeof(float) * n_tex * C));
-    CU_CHECK(ctx, ensure(ctx->g_conf, sizeof(float) * n_tex));
-    CU_CHECK(ctx, ensure(ctx->g_pos, sizeof(float4) * N + 16));
+    CU_CHECK(ctx, ensure(ctx->g_point, sizeof(float) * GS * N + 16));
+    CU_CHECK(ctx, ensure(ctx->g_conf_pt, sizeof(float) * N + 16));
     const size_t small_bytes = sizeof(double) * (TRIPS_MAX_CHANNELS + (size_t)B * 11);
     CU_CHECK(ctx, ensure(ctx->g_small, small_bytes));
     BwdBuffers bb;
     bb.egrad        = (float*)ctx->egrad.p;
-    bb.g_tex_packed = (float*)ctx->g_tex.p;
-    bb.g_conf       = (float*)ctx->g_conf.p;
-    bb.g_pos_size   = (float4*)ctx->g_pos.p;
+    bb.g_point      = (float*)ctx->g_point.p;
+    bb.g_conf_pt    = (float*)ctx->g_conf_pt.p;
     bb.g_bg         = (double*)ctx->g_small.p;
     bb.g_pose       = bb.g_bg + TRIPS_MAX_CHANNELS;
     bb.g_k          = bb.g_pose + (size_t)B * 6;
     if (ctx->total_entries) CU_CHECK(ctx, cudaMemsetAsync(ctx->egrad.p, 0, sizeof(float) * GS * (size_t)ctx->total_entries, st));
-    CU_CHECK(ctx, cudaMemsetAsync(ctx->g_tex.p, 0, sizeof(float) * n_tex * C, st));
-    CU_CHECK(ctx, cudaMemsetAsync(ctx->g_conf.p, 0, sizeof(float) * n_tex, st));
-    if (N > 0) CU_CHECK(ctx, cudaMemsetAsync(ctx->g_pos.p, 0, sizeof(float4) * N, st));
+    if (N > 0) CU_CHECK(ctx, cudaMemsetAsync(ctx->g_point.p, 0, sizeof(float) * GS * N, st));
+    if (N > 0) CU_CHECK(ctx, cudaMemsetAsync(ctx->g_conf_pt.p, 0, sizeof(float) * N, st));
     CU_CHECK(ctx, cudaMemsetAsync(ctx->g_small.p, 0, small_bytes, st));
     if (grads->pose_tangent) CU_CHECK(ctx, cudaMemsetAsync(grads->pose_tangent, 0, sizeof(double) * 6 * scene->n_images, st));
     if (grads->intrinsics) CU_CHECK(ctx, cudaMemsetAsync(grads->intrinsics, 0, sizeof(float) * 13 * scene->n_cameras, st));
@@ -454,7 +451,7 @@ int trips_backward(TripsContext* ctx, const TripsScene* scene, const float* cons
     const bool cam_grads = grads->pose_tangent || grads->intrinsics;
     STAGE(ctx, TRIPS_STAGE_BACKWARD, 1, st,
           launch_blend_backward(sp, (const CamConst*)ctx->cams.p, g, ctx->params, B, fb, bb, gin, cam_grads, ctx->sm_count, st));
-    const int n_unpack = (N > 0 ? 1 : 0) + (grads->texture ? 1 : 0) + ((grads->points || grads->point_size) ? 1 : 0) + 1;
+    const int n_unpack = (N > 0 ? 2 : 0) + 1;
     STAGE(ctx, TRIPS_STAGE_UNPACK, n_unpack, st,
           launch_unpack_grads(sp, (const CamConst*)ctx->cams.p, B, fb, bb, *grads, ctx->sm_count, st));
     return TRIPS_OK;

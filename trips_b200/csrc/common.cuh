@@ -104,9 +104,8 @@ struct ScenePtrs
 struct BwdBuffers
 {
     float* egrad;         // [sum V_b, egrad_stride] per-entry gradient accumulators
-    float* g_tex_packed;  // [n_tex,C]
-    float* g_conf;        // [n_tex]
-    float4* g_pos_size;   // [N] xyz gradient + raw point-size gradient
+    float* g_point;       // [N, egrad_stride] per-point sums keyed by point id: xyz + raw size | descriptor row
+    float* g_conf_pt;     // [N] confidence gradient keyed by point id
     double* g_bg;         // [C]
     double* g_pose;       // [B,6]
     double* g_k;          // [B,5]
