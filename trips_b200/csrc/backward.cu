@@ -65,7 +65,7 @@ __global__ __launch_bounds__(kBwdThreads, TRIPS_BWD_MIN_BLOCKS) void blend_backw
     constexpr int GS = egrad_stride(C);
     __shared__ float s_g[kBwdWarps][C][32];
     __shared__ float s_d[kBwdWarps][32 * kPad];   // G_j, then dA_j = G_j T_j, finally d_j
-    __shared__ float s_W[kBwdWarps][32 * kPad];   // alpha_j
+    __shared__ uint2 s_rec[kBwdWarps][32 * kPad]; // the tile's records: (entry index, alpha_j bits)
     __shared__ float s_w[kBwdWarps][32 * kPad];   // w_j = T_j * alpha_j
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
@@ -79,7 +79,7 @@ __global__ __launch_bounds__(kBwdThreads, TRIPS_BWD_MIN_BLOCKS) void blend_backw
     float* egrad         = bb.egrad + fb.entry_base[b] * GS;
     const uint32_t n_ent = (uint32_t)(fb.entry_base[b + 1] - fb.entry_base[b]);
     float* my_d          = s_d[warp] + lane * kPad;
-    float* my_W          = s_W[warp] + lane * kPad;
+    uint2* my_rec        = s_rec[warp] + lane * kPad;
     float* my_w          = s_w[warp] + lane * kPad;
 
     double acc_bg[C];
@@ -121,13 +121,26 @@ __global__ __launch_bounds__(kBwdThreads, TRIPS_BWD_MIN_BLOCKS) void blend_backw
         }
         const int rel     = incl - m;
         const int n_entry = __shfl_sync(kFull, incl, 31);
-        __syncwarp();
-
-        // ---- phase 0 (lane = kept fragment) ----
-        for (int e0 = 0; e0 < n_entry; e0 += 32)
+        // the tile's records (entry index, alpha) -> shared memory: every lane copies its pixel's row with
+        // independent 16-byte loads, so the whole tile costs one memory latency
+        if (p >= 0)
         {
-            const int e = e0 + lane;
-            int seg     = 0;
+            const uint4* src = reinterpret_cast<const uint4*>(fb.records + (bP + p) * 16);
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+            {
+                if (2 * k < m)
+                {
+                    const uint4 v        = src[k];
+                    my_rec[2 * k]     = make_uint2(v.x < n_ent ? v.x : 0u, v.x < n_ent ? v.y : 0u);  // a corrupted record contributes nothing
+                    my_rec[2 * k + 1] = make_uint2(v.z < n_ent ? v.z : 0u, v.z < n_ent ? v.w : 0u);
+                }
+            }
+        }
+        __syncwarp();
+        // (pixel, index in its list) of the e-th kept fragment of the tile
+        auto locate = [&](int e, int& seg, int& j) {
+            seg = 0;
 #pragma unroll
             for (int step = 16; step > 0; step >>= 1)
             {
@@ -135,25 +148,51 @@ __global__ __launch_bounds__(kBwdThreads, TRIPS_BWD_MIN_BLOCKS) void blend_backw
                 const int pstart = __shfl_sync(kFull, rel, probe & 31);
                 if (probe < 32 && pstart <= e) seg = probe;
             }
-            const int j     = e - __shfl_sync(kFull, rel, seg);
-            const int seg_p = __shfl_sync(kFull, p, seg);
-            if (e < n_entry)
+            j = e - __shfl_sync(kFull, rel, seg);
+        };
+
+        // ---- phase 0 (lane = kept fragment): G_j = <descriptor row of the entry, g>; the row of the next round is
+        //      requested before the current one is consumed ----
+        {
+            int seg_n, j_n;
+            locate(lane, seg_n, j_n);
+            float4 row_n[(C + 3) / 4];
+            if (lane < n_entry)
             {
-                uint2 rc = fb.records[(bP + seg_p) * 16 + j];
-                if (rc.x >= n_ent) rc = make_uint2(0u, 0u);  // corrupted record (flagged by the forward pass): no contribution
-                const float* row = entries + (size_t)rc.x * ES + 12;
-                float G          = 0.f;
+                const float* rp = entries + (size_t)s_rec[warp][seg_n * kPad + j_n].x * ES + 12;
 #pragma unroll
-                for (int c = 0; c < C; c += 4)
+                for (int c = 0; c < (C + 3) / 4; ++c) row_n[c] = *reinterpret_cast<const float4*>(rp + 4 * c);
+            }
+            for (int e0 = 0; e0 < n_entry; e0 += 32)
+            {
+                const int seg = seg_n, j = j_n;
+                float4 row[(C + 3) / 4];
+#pragma unroll
+                for (int c = 0; c < (C + 3) / 4; ++c) row[c] = row_n[c];
+                if (e0 + 32 < n_entry)
                 {
-                    const float4 v4 = *reinterpret_cast<const float4*>(row + c);
-                    G += v4.x * s_g[warp][c][seg];
-                    if (c + 1 < C) G += v4.y * s_g[warp][c + 1][seg];
-                    if (c + 2 < C) G += v4.z * s_g[warp][c + 2][seg];
-                    if (c + 3 < C) G += v4.w * s_g[warp][c + 3][seg];
+                    locate(e0 + 32 + lane, seg_n, j_n);
+                    if (e0 + 32 + lane < n_entry)
+                    {
+                        const float* rp = entries + (size_t)s_rec[warp][seg_n * kPad + j_n].x * ES + 12;
+#pragma unroll
+                        for (int c = 0; c < (C + 3) / 4; ++c) row_n[c] = *reinterpret_cast<const float4*>(rp + 4 * c);
+                    }
                 }
-                s_d[warp][seg * kPad + j] = G;
-                s_W[warp][seg * kPad + j] = __uint_as_float(rc.y);
+                if (e0 + lane < n_entry)
+                {
+                    float G = 0.f;
+#pragma unroll
+                    for (int c = 0; c < C; c += 4)
+                    {
+                        const float4 v4 = row[c / 4];
+                        G += v4.x * s_g[warp][c][seg];
+                        if (c + 1 < C) G += v4.y * s_g[warp][c + 1][seg];
+                        if (c + 2 < C) G += v4.z * s_g[warp][c + 2][seg];
+                        if (c + 3 < C) G += v4.w * s_g[warp][c + 3][seg];
+                    }
+                    s_d[warp][seg * kPad + j] = G;
+                }
             }
         }
         __syncwarp();
@@ -164,7 +203,7 @@ __global__ __launch_bounds__(kBwdThreads, TRIPS_BWD_MIN_BLOCKS) void blend_backw
         {
             if (j < m)
             {
-                const float a = my_W[j];
+                const float a = __uint_as_float(my_rec[j].y);
                 my_d[j]       = my_d[j] * run;
                 my_w[j]       = run * a;
                 run           = (1.f - a) * run;
@@ -186,7 +225,7 @@ __global__ __launch_bounds__(kBwdThreads, TRIPS_BWD_MIN_BLOCKS) void blend_backw
         {
             if (j < m)
             {
-                const float a   = my_W[j];
+                const float a   = __uint_as_float(my_rec[j].y);
                 const float dA  = my_d[j];
                 const float dem = 1.f / (1.f - a + 1e-9f);
                 my_d[j]         = dA - R * dem;
@@ -195,54 +234,67 @@ __global__ __launch_bounds__(kBwdThreads, TRIPS_BWD_MIN_BLOCKS) void blend_backw
         }
         __syncwarp();
 
-        // ---- phase 2 (lane = kept fragment) ----
-        for (int e0 = 0; e0 < n_entry; e0 += 32)
+        // ---- phase 2 (lane = kept fragment): the header of the next round's entry is requested early ----
         {
-            const int e      = e0 + lane;
-            const bool valid = e < n_entry;
-            int seg          = 0;
-#pragma unroll
-            for (int step = 16; step > 0; step >>= 1)
+            int seg_n, j_n;
+            locate(lane, seg_n, j_n);
+            float4 e0_n = make_float4(0.f, 0.f, 0.f, 0.f);
+            float conf_n = 0.f;
+            unsigned eidx_n = 0;
+            if (lane < n_entry)
             {
-                const int probe  = seg + step;
-                const int pstart = __shfl_sync(kFull, rel, probe & 31);
-                if (probe < 32 && pstart <= e) seg = probe;
+                eidx_n          = s_rec[warp][seg_n * kPad + j_n].x;
+                const float* en = entries + (size_t)eidx_n * ES;
+                e0_n            = *reinterpret_cast<const float4*>(en);
+                conf_n          = en[5];
             }
-            const int j       = e - __shfl_sync(kFull, rel, seg);
-            const int seg_p   = __shfl_sync(kFull, p, seg);
-            const int layer_s = __shfl_sync(kFull, layer, seg);
-            const int gx_s    = __shfl_sync(kFull, gx, seg);
-            const int gy_s    = __shfl_sync(kFull, gy, seg);
-            if (!valid) continue;
-            const uint2 rc  = fb.records[(bP + seg_p) * 16 + j];
-            if (rc.x >= n_ent) continue;
-            const float* en = entries + (size_t)rc.x * ES;
-            float* eg       = egrad + (size_t)rc.x * GS;
-            const float ga  = s_d[warp][seg * kPad + j];
-            const float w   = s_w[warp][seg * kPad + j];
-            const float4 e0v = *reinterpret_cast<const float4*>(en);      // u v ps z
-            const float conf = en[5];
-            // bilinear weight of this pixel and its Jacobian at uv (compute_blending_fac, PointBlending.h:216-257)
-            const float fac = __int_as_float((127 - layer_s) << 23);
-            const float ux = e0v.x * fac, uy = e0v.y * fac;
-            const float ps = e0v.z;
-            const int q    = ((float)gx_s < ux ? 0 : 1) + ((float)gy_s < uy ? 0 : 2);
-            const float sx = ux - floorf(ux), sy = uy - floorf(uy);
-            float bf = ((q & 1) ? sx : (1.f - sx)) * ((q & 2) ? sy : (1.f - sy));
-            const float J0 = (q & 1) ? ((q & 2) ? sy : (1.f - sy)) : ((q & 2) ? -sy : (sy - 1.f));
-            const float J1 = (q & 2) ? ((q & 1) ? sx : (1.f - sx)) : ((q & 1) ? -sx : (sx - 1.f));
-            if (fabsf(ux - (float)gx_s) > 1.f || fabsf(uy - (float)gy_s) > 1.f) bf *= 0.f;
-            float lf_grad    = 0.f;
-            const float lf   = layer_factor(ps, layer_s, g.L, &lf_grad);
-            const float gbs  = conf * lf * ga;  // dLoss / d(bilinear weight) (RenderBackward.cu:385)
-            // image-space sums of the entry: the chain to position / size / pose is linear in them and is applied
-            // once per entry by entry_grad_finish_kernel
-            atomicAdd(reinterpret_cast<float4*>(eg), make_float4(J0 * gbs, J1 * gbs, bf * conf * lf_grad * ga, bf * lf * ga));
+            for (int e0 = 0; e0 < n_entry; e0 += 32)
             {
-                float gt[(C + 3) & ~3];
+                const int seg = seg_n, j = j_n;
+                const float4 e0v = e0_n;  // u v ps z
+                const float conf = conf_n;
+                const unsigned eidx = eidx_n;
+                const bool valid = e0 + lane < n_entry;
+                if (e0 + 32 < n_entry)
+                {
+                    locate(e0 + 32 + lane, seg_n, j_n);
+                    if (e0 + 32 + lane < n_entry)
+                    {
+                        eidx_n          = s_rec[warp][seg_n * kPad + j_n].x;
+                        const float* en = entries + (size_t)eidx_n * ES;
+                        e0_n            = *reinterpret_cast<const float4*>(en);
+                        conf_n          = en[5];
+                    }
+                }
+                const int layer_s = __shfl_sync(kFull, layer, seg);
+                const int gx_s    = __shfl_sync(kFull, gx, seg);
+                const int gy_s    = __shfl_sync(kFull, gy, seg);
+                if (!valid) continue;
+                float* eg      = egrad + (size_t)eidx * GS;
+                const float ga = s_d[warp][seg * kPad + j];
+                const float w  = s_w[warp][seg * kPad + j];
+                // bilinear weight of this pixel and its Jacobian at uv (compute_blending_fac, PointBlending.h:216-257)
+                const float fac = __int_as_float((127 - layer_s) << 23);
+                const float ux = e0v.x * fac, uy = e0v.y * fac;
+                const float ps = e0v.z;
+                const int q    = ((float)gx_s < ux ? 0 : 1) + ((float)gy_s < uy ? 0 : 2);
+                const float sx = ux - floorf(ux), sy = uy - floorf(uy);
+                float bf = ((q & 1) ? sx : (1.f - sx)) * ((q & 2) ? sy : (1.f - sy));
+                const float J0 = (q & 1) ? ((q & 2) ? sy : (1.f - sy)) : ((q & 2) ? -sy : (sy - 1.f));
+                const float J1 = (q & 2) ? ((q & 1) ? sx : (1.f - sx)) : ((q & 1) ? -sx : (sx - 1.f));
+                if (fabsf(ux - (float)gx_s) > 1.f || fabsf(uy - (float)gy_s) > 1.f) bf *= 0.f;
+                float lf_grad   = 0.f;
+                const float lf  = layer_factor(ps, layer_s, g.L, &lf_grad);
+                const float gbs = conf * lf * ga;  // dLoss / d(bilinear weight) (RenderBackward.cu:385)
+                // image-space sums of the entry: the chain to position / size / pose is linear in them and is applied
+                // once per entry by entry_grad_finish_kernel
+                atomicAdd(reinterpret_cast<float4*>(eg), make_float4(J0 * gbs, J1 * gbs, bf * conf * lf_grad * ga, bf * lf * ga));
+                {
+                    float gt[(C + 3) & ~3];
 #pragma unroll
-                for (int c = 0; c < ((C + 3) & ~3); ++c) gt[c] = (c < C) ? w * s_g[warp][c < C ? c : 0][seg] : 0.f;
-                atomic_add_row<((C + 3) & ~3)>(eg + 4, gt);
+                    for (int c = 0; c < ((C + 3) & ~3); ++c) gt[c] = (c < C) ? w * s_g[warp][c < C ? c : 0][seg] : 0.f;
+                    atomic_add_row<((C + 3) & ~3)>(eg + 4, gt);
+                }
             }
         }
         __syncwarp();

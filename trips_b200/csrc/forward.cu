@@ -803,11 +803,15 @@ __global__ __launch_bounds__(kSbThreads, TRIPS_SB_MIN_BLOCKS) void sort_blend_ke
 
         if (max_cnt <= (uint32_t)kRankMax)
         {
-            // ---- phase A, counting path: lane = fragment ----
-            for (uint32_t t0 = 0; t0 < tile_total; t0 += 32)
+            // ---- phase A, counting path: lane = fragment.  The fragment of the next round is fetched before the
+            //      ranking loop of the current one, so that its DRAM latency hides behind the loop ----
+            struct Loc
             {
-                const uint32_t t = t0 + lane;
-                const bool valid = t < tile_total;
+                uint32_t seg_start, seg_cnt, idx;
+                int seg, seg_p;
+            };
+            auto locate = [&](uint32_t t) {
+                Loc L;
                 // pixel of this fragment: the last lane whose list starts at or before t
                 int seg = 0;
 #pragma unroll
@@ -817,17 +821,32 @@ __global__ __launch_bounds__(kSbThreads, TRIPS_SB_MIN_BLOCKS) void sort_blend_ke
                     const uint32_t pstart = __shfl_sync(kFull, rel_start, probe & 31);
                     if (probe < 32 && pstart <= t) seg = probe;
                 }
-                const uint32_t seg_rel   = __shfl_sync(kFull, rel_start, seg);
-                const uint32_t seg_start = __shfl_sync(kFull, start, seg);
-                const uint32_t seg_cnt   = __shfl_sync(kFull, cnt, seg);
-                const int seg_p          = __shfl_sync(kFull, p, seg);
+                L.seg       = seg;
+                L.idx       = t - __shfl_sync(kFull, rel_start, seg);
+                L.seg_start = __shfl_sync(kFull, start, seg);
+                L.seg_cnt   = __shfl_sync(kFull, cnt, seg);
+                L.seg_p     = __shfl_sync(kFull, p, seg);
+                return L;
+            };
+            Loc nxt      = locate(lane);
+            uint4 f_next = make_uint4(0u, 0u, 0u, 0u);
+            if (lane < tile_total) f_next = frags[nxt.seg_start + nxt.idx];
+            for (uint32_t t0 = 0; t0 < tile_total; t0 += 32)
+            {
+                const Loc cur    = nxt;
+                const uint4 f    = f_next;
+                const bool valid = t0 + lane < tile_total;
+                if (t0 + 32 < tile_total)
+                {
+                    nxt = locate(t0 + 32 + lane);
+                    if (t0 + 32 + lane < tile_total) f_next = frags[nxt.seg_start + nxt.idx];
+                }
                 if (valid)
                 {
-                    const uint4 f   = frags[seg_start + (t - seg_rel)];
                     const u64 mine  = ((u64)f.y << 32) | f.x;
-                    const uint2* kp = reinterpret_cast<const uint2*>(frags + seg_start);
+                    const uint2* kp = reinterpret_cast<const uint2*>(frags + cur.seg_start);
                     int rank        = 0;
-                    for (uint32_t i = 0; i < seg_cnt; ++i)
+                    for (uint32_t i = 0; i < cur.seg_cnt; ++i)
                     {
                         const uint2 o = kp[(size_t)i * 2];
                         rank += ((((u64)o.y << 32) | o.x) < mine) ? 1 : 0;
@@ -836,8 +855,8 @@ __global__ __launch_bounds__(kSbThreads, TRIPS_SB_MIN_BLOCKS) void sort_blend_ke
                         atomicOr(&fb.stats->status, TRIPS_DEV_BAD_FRAGMENT);  // corrupted list: skip instead of gathering out of bounds
                     else if (rank < K)
                     {
-                        sb_store_entry<C>(sorted + (seg * kSortedPad + rank) * E, entries, f.w, f.z);
-                        if (pr.train) fb.records[(bP + seg_p) * 16 + rank] = make_uint2(f.w, f.z);
+                        sb_store_entry<C>(sorted + (cur.seg * kSortedPad + rank) * E, entries, f.w, f.z);
+                        if (pr.train) fb.records[(bP + cur.seg_p) * 16 + rank] = make_uint2(f.w, f.z);
                     }
                 }
             }
