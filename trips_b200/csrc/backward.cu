@@ -86,12 +86,14 @@ __global__ __launch_bounds__(kBwdThreads, TRIPS_BWD_MIN_BLOCKS) void blend_backw
 #pragma unroll
     for (int c = 0; c < C; ++c) acc_bg[c] = 0.0;
 
+    unsigned next_tile = 0;
+    if (lane == 0) next_tile = atomicAdd(fb.ticket + b, 1u);
     for (;;)
     {
-        unsigned tile = 0;
-        if (lane == 0) tile = atomicAdd(fb.ticket + b, 1u);
-        tile = __shfl_sync(kFull, tile, 0);
+        // the ticket of the following tile is requested now, a whole tile ahead of its use
+        const unsigned tile = __shfl_sync(kFull, next_tile, 0);
         if (tile >= (unsigned)g.n_tiles) break;
+        if (lane == 0) next_tile = atomicAdd(fb.ticket + b, 1u);
         int layer, gx, gy, p;
         tile_pixel(g, (int)tile, lane, layer, gx, gy, p);
         int m = 0;

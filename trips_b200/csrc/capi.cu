@@ -422,7 +422,7 @@ int trips_backward(TripsContext* ctx, const TripsScene* scene, const float* cons
         if (!grad_layers[l]) return fail(ctx, TRIPS_ERR_INVALID_ARG, "null gradient layer");
     cudaStream_t st = (cudaStream_t)stream;
     const int B = ctx->B, C = ctx->C;
-    const size_t N = (size_t)ctx->N, n_tex = (size_t)ctx->n_tex;
+    const size_t N = (size_t)ctx->N;
 
     const size_t GS = (size_t)egrad_stride(C);
     CU_CHECK(ctx, ensure(ctx->egrad, sizeof(float) * GS * (size_t)ctx->total_entries + 16, 1.25));

@@ -694,7 +694,13 @@ cudaError_t launch_collect(const ScenePtrs& sc, const Geom& g, int B, const FwdB
 // ------------------------------------------------------------------------------------------------------------
 typedef unsigned long long u64;
 constexpr u64 kInfKey    = 0xffffffffffffffffull;
-constexpr int kRankMax   = 192;  // longest list ranked by counting; longer lists use the streaming path
+#ifndef TRIPS_SB_RING
+#define TRIPS_SB_RING 2
+#endif
+#ifndef TRIPS_RANK_MAX
+#define TRIPS_RANK_MAX 48
+#endif
+constexpr int kRankMax   = TRIPS_RANK_MAX;  // longest list ranked by counting; longer lists use the streaming path
 constexpr int kSortedPad = 17;   // row pitch (entries) of the per-pixel sorted lists in shared memory
 #ifndef TRIPS_SB_STAGE_MAX_C
 #define TRIPS_SB_STAGE_MAX_C 0
@@ -795,12 +801,14 @@ __global__ __launch_bounds__(kSbThreads, TRIPS_SB_MIN_BLOCKS) void sort_blend_ke
 #pragma unroll
     for (int c = 0; c < C; ++c) bg[c] = __ldg(sc.background + c);
 
+    unsigned next_ticket = 0;
+    if (lane == 0) next_ticket = atomicAdd(fb.ticket, 1u);
     for (;;)
     {
-        unsigned ticket = 0;
-        if (lane == 0) ticket = atomicAdd(fb.ticket, 1u);
-        ticket = __shfl_sync(kFull, ticket, 0);
+        // the ticket of the following tile is requested now, a whole tile ahead of its use
+        const unsigned ticket = __shfl_sync(kFull, next_ticket, 0);
         if (ticket >= n_tiles_total) break;
+        if (lane == 0) next_ticket = atomicAdd(fb.ticket, 1u);
         const int b          = ticket / (unsigned)g.n_tiles;
         const int tile       = ticket - b * (unsigned)g.n_tiles;
         const size_t bP      = (size_t)b * g.P;
@@ -873,6 +881,7 @@ __global__ __launch_bounds__(kSbThreads, TRIPS_SB_MIN_BLOCKS) void sort_blend_ke
                     const u64 mine  = ((u64)f.y << 32) | f.x;
                     const uint2* kp = reinterpret_cast<const uint2*>(frags + cur.seg_start);
                     int rank        = 0;
+#pragma unroll 4
                     for (uint32_t i = 0; i < cur.seg_cnt; ++i)
                     {
                         const uint2 o = kp[(size_t)i * 2];
@@ -964,6 +973,22 @@ __global__ __launch_bounds__(kSbThreads, TRIPS_SB_MIN_BLOCKS) void sort_blend_ke
 #pragma unroll
         for (int c = 0; c < C; ++c) s0[c] = s1[c] = s2[c] = s3[c] = 0.f;
         const float* my_sorted = sorted + lane * kSortedPad * E;
+        // descriptor rows are requested kRing entries ahead of their use (the gathers are independent of the recurrence)
+        constexpr int kRows = (C + 3) / 4;
+        constexpr int kRing = SbEntry<C>::kStaged ? 1 : (C <= 4 ? TRIPS_SB_RING : (C <= 8 ? 2 : 1));
+        float4 ring[kRing][kRows];
+        auto fetch_row = [&](int j, float4 (&dst)[kRows]) {
+            if (!SbEntry<C>::kStaged && j < n)
+            {
+                unsigned eidx = __float_as_uint(my_sorted[j * E]);
+                if (eidx >= n_entry) eidx = 0;  // only after a corrupted list was flagged in phase A: read in bounds
+                const float* rp = entries + (size_t)eidx * ES + 12;
+#pragma unroll
+                for (int r = 0; r < kRows; ++r) dst[r] = *reinterpret_cast<const float4*>(rp + 4 * r);
+            }
+        };
+#pragma unroll
+        for (int d = 0; d < kRing; ++d) fetch_row(d, ring[d]);
 #pragma unroll
         for (int j = 0; j < 16; ++j)
         {
@@ -984,18 +1009,11 @@ __global__ __launch_bounds__(kSbThreads, TRIPS_SB_MIN_BLOCKS) void sort_blend_ke
                 }
                 else
                 {
-                    unsigned eidx = __float_as_uint(e[0]);
-                    a             = e[1];
-                    if (eidx >= n_entry)  // only after a corrupted list was flagged in phase A: draw nothing, read in bounds
-                    {
-                        eidx = 0;
-                        a    = 0.f;
-                    }
-                    const float* rp     = entries + (size_t)eidx * ES + 12;
+                    a = (__float_as_uint(e[0]) < n_entry) ? e[1] : 0.f;  // a corrupted entry draws nothing
 #pragma unroll
                     for (int c = 0; c < C; c += 4)
                     {
-                        const float4 v4 = *reinterpret_cast<const float4*>(rp + c);
+                        const float4 v4 = ring[j % kRing][c / 4];
                         row[c] = v4.x;
                         if (c + 1 < C) row[c + 1] = v4.y;
                         if (c + 2 < C) row[c + 2] = v4.z;
@@ -1017,6 +1035,7 @@ __global__ __launch_bounds__(kSbThreads, TRIPS_SB_MIN_BLOCKS) void sort_blend_ke
                 }
                 run = run * (1.f - a);
             }
+            if (j + kRing < 16) fetch_row(j + kRing, ring[j % kRing]);
             // binary-counter accumulation = pairwise tree over leaves 0..15
 #pragma unroll
             for (int c = 0; c < C; ++c)
