@@ -42,6 +42,9 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--cpu-views", type=int, default=1, help="views of the workload the CPU baseline renders")
+    ap.add_argument("--collective", default="auto", choices=["auto", "fused", "nccl"],
+                    help="N>1: 'fused' = one kernel sums the gradients over peer memory, applies Adam and broadcasts; "
+                         "'nccl' = all-reduce then Adam; 'auto' = fused when symmetric memory can be set up")
     return ap.parse_args()
 
 
@@ -144,6 +147,11 @@ def stage_bytes(stage, N, P, C, B, F, Kf):
     return 0
 
 
+def fused_adam_bytes(numel, world):
+    """One rank's launch: its slice of every rank's gradient, its parameters and state in, state and every replica out."""
+    return (numel // world) * 4 * (world + 1 + 3 + 3 + world)
+
+
 # ----------------------------------------------------------------------------------------------------------------
 # CPU arm: the oracle (restatement of the reference kernels) on the host cores
 # ----------------------------------------------------------------------------------------------------------------
@@ -238,14 +246,42 @@ def run_ours(args, rank, world, local_rank):
     cache = PointRendererCache(dev)
     info = NeuralRenderInfo(scene=ns, images=images_for(s, my_views), params=RenderParams(num_texture_channels=C, k_keep=s.k_keep),
                             num_layers=L, train=True, cache=cache)
-    # all point gradients live in one flat buffer so that one collective sums them over ranks
-    layout = FlatGradLayout(N, N, C)
-    flat = torch.zeros(layout.numel, device=dev)
-    gout = layout.views(flat)
+    # all point gradients live in one flat buffer so that one collective (or one fused kernel) sums them over ranks
     params = [tex.texture_raw, tex.confidence_raw, pc.t_position, pc.t_point_size, tex.background_color_raw]
-    for p_, k in zip(params, ("texture", "confidence", "points", "point_size", "background")):
-        p_.grad = gout[k]
-    opt = MyAdam(params, lr=1e-3, betas=(0.9, 0.999), cache=cache)
+    keys = ("texture", "confidence", "points", "point_size", "background")
+    fused, collective = None, "none"
+    if world > 1 and args.collective in ("auto", "fused"):
+        from trips_b200.dist import FusedPointOptimizer
+        ok = torch.ones(1, device=dev)
+        try:
+            fused = FusedPointOptimizer(list(zip(keys, params)), cache, lr=1e-3, betas=(0.9, 0.999))
+        except Exception as e:  # noqa: BLE001 - symmetric memory is optional plumbing; the NCCL path is always there
+            if args.collective == "fused":
+                raise
+            print(f"[bench] rank {rank}: symmetric memory unavailable ({type(e).__name__}: {e}); using NCCL all-reduce", file=sys.stderr)
+            ok.zero_()
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if ok.item() == 0:
+            fused = None
+    if fused is not None:
+        gout, collective = fused.grad_views, "fused peer-memory reduce + Adam + broadcast (trips_fused_reduce_adam)"
+        opt, flat = None, fused.grad_flat
+    else:
+        layout = FlatGradLayout(N, N, C)
+        flat = torch.zeros(layout.numel, device=dev)
+        gout = layout.views(flat)
+        for p_, k in zip(params, keys):
+            p_.grad = gout[k]
+        opt = MyAdam(params, lr=1e-3, betas=(0.9, 0.999), cache=cache)
+        collective = "nccl all_reduce + trips_adam_step" if world > 1 else "none (single GPU)"
+
+    def reduce_and_update():
+        if fused is not None:
+            fused.step()
+            return
+        if world > 1:
+            dist.all_reduce(flat)
+        opt.step()
     sizes = layer_sizes(s.width, s.height, L)
     gen = torch.Generator(device=dev)
     gen.manual_seed(1234 + rank)
@@ -257,9 +293,7 @@ def run_ours(args, rank, world, local_rank):
     def step_resident():
         outs = cache.forward(info, *scene_args())
         cache.backward(grads_in, *scene_args(), out=gout)
-        if world > 1:
-            dist.all_reduce(flat)
-        opt.step()
+        reduce_and_update()
         return outs
 
     def barrier():
@@ -327,9 +361,7 @@ def run_ours(args, rank, world, local_rank):
             cache.l1_loss_backward(outs, dev_t[slot], grads_e, loss_dev)
             consumed[slot].record(cur)
             cache.backward(grads_e, *scene_args(), out=gout)
-            if world > 1:
-                dist.all_reduce(flat)
-            opt.step()
+            reduce_and_update()
             loss_host.copy_(loss_dev, non_blocking=True)
             cur.synchronize()  # the caller reads the loss every step
             return float(loss_host)
@@ -370,15 +402,23 @@ def run_ours(args, rank, world, local_rank):
         launches_total += launches
         if calls:
             per_stage[name] = {"ms_per_launch": ms / calls, "launches": int(launches)}
-    dom = max((k for k in per_stage if k in ("bin_points", "count", "scan", "collect", "sort_blend", "blend_backward", "adam")),
-              key=lambda k: per_stage[k]["ms_per_launch"])
-    dom_bytes = stage_bytes(dom, N, P, C, B, F, Kf)
+    step_stages = ("bin_points", "count", "scan", "collect", "sort_blend", "blend_backward", "adam", "fused_reduce_adam")
+
+    def bytes_of(k):
+        if k == "fused_reduce_adam":
+            return fused_adam_bytes(fused.numel, world) if fused is not None else 0
+        if k == "adam" and fused is not None:
+            return 0
+        return stage_bytes(k, N, P, C, B, F, Kf)
+
+    dom = max((k for k in per_stage if k in step_stages), key=lambda k: per_stage[k]["ms_per_launch"])
+    dom_bytes = bytes_of(dom)
     achieved = dom_bytes / (per_stage[dom]["ms_per_launch"] * 1e-3) / 1e9
     for k, v in per_stage.items():
-        b_ = stage_bytes(k, N, P, C, B, F, Kf)
+        b_ = bytes_of(k)
         v["alg_gb"] = b_ / 1e9
         v["gbs"] = (b_ / (v["ms_per_launch"] * 1e-3) / 1e9) if b_ else None
-    total_alg = sum(stage_bytes(k, N, P, C, B, F, Kf) for k in ("bin_points", "count", "scan", "collect", "sort_blend", "blend_backward", "adam"))
+    total_alg = sum(bytes_of(k) for k in step_stages)
     roofline = {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "peak_kind": peak_kind, "traffic": None, "alg_bytes_per_launch": dom_bytes,
                 "step_alg_bytes": total_alg, "step_gbs": total_alg / (ms_step * 1e-3) / 1e9, "stages": per_stage}
@@ -396,7 +436,7 @@ def run_ours(args, rank, world, local_rank):
         "ms_per_step": ms_step, "ms_per_view": ms_step / B, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
         "config": {"workload": s.name, "points": N, "views_per_gpu": B, "global_views_per_step": B * world, "width": s.width,
-                   "height": s.height, "layers": L, "k_keep": s.k_keep, "channels": C, "parallelism": f"view-dp{world}",
+                   "height": s.height, "layers": L, "k_keep": s.k_keep, "channels": C, "parallelism": f"view-dp{world}", "collective": collective,
                    "l2_policy": "inputs (>2 GB touched per step) larger than the 126 MB L2; no explicit flush",
                    "fragments_per_step": int(F), "kept_fragments_per_step": int(Kf), "visible_points_per_step": int(stats["visible_points"]),
                    "max_list_length": int(stats["max_list_length"]), "fragments_per_s": F * world / (ms_step * 1e-3)},

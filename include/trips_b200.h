@@ -152,6 +152,32 @@ typedef struct
  * launch over all tensors.  `tensors` is a HOST array. */
 int trips_adam_step(TripsContext* ctx, const TripsAdamTensor* tensors, int n_tensors, void* stream);
 
+/* View-parallel training over several GPUs of one node (no counterpart in the reference, which is single-GPU:
+ * its views meet only in the gradient buffers filled by the sequential view loop, PointRenderer.cu:1339-1344).
+ * All point parameters live in ONE flat fp32 buffer per rank and all their gradients in another, both mapped into
+ * every rank's address space (peer memory).  A segment describes one parameter tensor inside the flat space. */
+#define TRIPS_MAX_RANKS 16
+#define TRIPS_MAX_SEGMENTS 8
+typedef struct
+{
+    int64_t offset; /* first flat element of the tensor; segments are sorted by offset, the first one starts at 0 */
+    float lr;
+    float beta1, beta2, eps;
+    float relative_weight_decay, absolute_weight_decay, weight_clipping_magnitude;
+    float lower_lr_bound, upper_lr_bound;
+} TripsAdamSegment;
+
+/* Sums the gradients of all ranks for the flat elements [lo, hi) owned by this rank (peer loads, rank order),
+ * applies the MyAdam update (src/lib/models/MyAdam.cu:41-88) with this rank's slice of the optimizer state
+ * (first_moments / second_moments / steps hold hi - lo elements) and stores the new weights into the parameter
+ * buffer of every rank (peer stores).  grad_ptrs / param_ptrs: HOST arrays of `world` device pointers to the flat
+ * buffers of ranks 0..world-1 as mapped on THIS device.  The caller must order the call after the backward pass of
+ * every rank and the next forward pass of every rank after it (a barrier before and after); the kernel itself
+ * never waits on a peer.  lo and hi need no alignment. */
+int trips_fused_reduce_adam(TripsContext* ctx, const float* const* grad_ptrs, float* const* param_ptrs, int world, int rank,
+                            const TripsAdamSegment* segments, int n_segments, int64_t lo, int64_t hi, float* first_moments,
+                            float* second_moments, int32_t* steps, void* stream);
+
 /* No counterpart in the reference.  Same update as trips_adam_step for callers that cannot allocate device
  * memory at the time of the step: code running while the application's own pool owns all free memory, hosts that
  * forbid cudaMalloc after start-up, or a step issued inside a stream capture.  The table describing the tensors,
@@ -180,6 +206,7 @@ enum
     TRIPS_STAGE_UNPACK,
     TRIPS_STAGE_ADAM,
     TRIPS_STAGE_LOSS,
+    TRIPS_STAGE_FUSED_ADAM,
     TRIPS_NUM_STAGES
 };
 int trips_enable_stage_timers(TripsContext* ctx, int enable);

@@ -14,7 +14,9 @@ LIB_PATH = os.environ.get("TRIPS_B200_LIB") or os.path.join(HERE, "libtrips_b200
 
 MAX_LAYERS = 8
 MAX_KEEP = 16
-NUM_STAGES = 10
+NUM_STAGES = 11
+MAX_RANKS = 16
+MAX_SEGMENTS = 8
 ADAM_STATIC_MAX_TENSORS = 64
 
 OK = 0
@@ -66,6 +68,12 @@ class TripsAdamTensor(C.Structure):
                 ("lower_lr_bound", C.c_float), ("upper_lr_bound", C.c_float)]
 
 
+class TripsAdamSegment(C.Structure):
+    _fields_ = [("offset", C.c_int64), ("lr", C.c_float), ("beta1", C.c_float), ("beta2", C.c_float), ("eps", C.c_float),
+                ("relative_weight_decay", C.c_float), ("absolute_weight_decay", C.c_float),
+                ("weight_clipping_magnitude", C.c_float), ("lower_lr_bound", C.c_float), ("upper_lr_bound", C.c_float)]
+
+
 # every symbol include/trips_b200.h declares: name -> (restype, argtypes)
 SYMBOLS = {
     "trips_context_create": (C.c_int, [C.POINTER(C.c_void_p), C.c_int]),
@@ -78,6 +86,9 @@ SYMBOLS = {
     "trips_last_status": (C.c_uint32, [C.c_void_p, C.c_void_p]),
     "trips_get_stats": (C.c_int, [C.c_void_p, C.POINTER(TripsStats), C.c_void_p]),
     "trips_adam_step": (C.c_int, [C.c_void_p, C.POINTER(TripsAdamTensor), C.c_int, C.c_void_p]),
+    "trips_fused_reduce_adam": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.c_int, C.c_int,
+                                          C.POINTER(TripsAdamSegment), C.c_int, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p,
+                                          C.c_void_p, C.c_void_p]),
     "trips_adam_step_static": (C.c_int, [C.POINTER(TripsAdamTensor), C.c_int, C.c_void_p]),
     "trips_enable_stage_timers": (C.c_int, [C.c_void_p, C.c_int]),
     "trips_get_stage_times": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int]),

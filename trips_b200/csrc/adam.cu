@@ -95,6 +95,105 @@ cudaError_t launch_adam(const TripsAdamTensor* d_tensors, const int64_t* d_block
     return cudaGetLastError();
 }
 
+// ------------------------------------------------------------------------------------------------------------
+// Gradient sum over ranks + Adam + parameter broadcast in ONE kernel over peer memory (NVLink / NVSwitch).
+//
+// Every rank owns the slice [lo, hi) of the flat parameter space (and only that slice of the Adam state).  For its
+// slice it reads the gradient of every rank through peer pointers (plain P2P loads, summed in rank order, so that
+// all replicas see bit-identical sums), applies the reference update (adam_step, MyAdam.cu:41-88; elements whose
+// summed gradient is zero stay untouched) and stores the new weight into the parameter buffer of every rank (P2P
+// stores).  This is reduce-scatter + sharded Adam + all-gather with the wire traffic of one all-reduce and 1/G of
+// the optimizer traffic per GPU.  The kernel never waits on another GPU: the caller orders it after every rank's
+// backward pass and orders the next forward pass after it on every rank (a barrier on both sides).
+// ------------------------------------------------------------------------------------------------------------
+struct FusedArgs
+{
+    const float* grad[TRIPS_MAX_RANKS];
+    float* param[TRIPS_MAX_RANKS];
+    TripsAdamSegment seg[TRIPS_MAX_SEGMENTS];
+    int world, rank, n_seg;
+    int64_t lo, hi;
+};
+
+__device__ __forceinline__ void fused_element(const TripsAdamSegment& sg, float& w, float g, float& m, float& v, int& step)
+{
+    TripsAdamTensor t;
+    t.lr = sg.lr, t.beta1 = sg.beta1, t.beta2 = sg.beta2, t.eps = sg.eps;
+    t.relative_weight_decay = sg.relative_weight_decay, t.absolute_weight_decay = sg.absolute_weight_decay;
+    t.weight_clipping_magnitude = sg.weight_clipping_magnitude;
+    t.lower_lr_bound = sg.lower_lr_bound, t.upper_lr_bound = sg.upper_lr_bound;
+    adam_element(t, w, g, m, v, step);
+}
+
+__global__ __launch_bounds__(256) void fused_reduce_adam_kernel(const __grid_constant__ FusedArgs a, float* __restrict__ m_state,
+                                                                float* __restrict__ v_state, int32_t* __restrict__ steps)
+{
+    // 16-byte vectors over the aligned interior of [lo, hi), scalars at the ragged ends
+    const int64_t lo4 = min(a.hi, (a.lo + 3) & ~(int64_t)3), hi4 = max(lo4, a.hi & ~(int64_t)3);
+    const int64_t n_vec = (hi4 - lo4) >> 2;
+    auto segment_of = [&](int64_t i) {
+        int k = 0;
+        for (int s = 1; s < a.n_seg; ++s)
+            if (i >= a.seg[s].offset) k = s;
+        return k;
+    };
+    for (int64_t q = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; q < n_vec; q += (int64_t)gridDim.x * blockDim.x)
+    {
+        const int64_t i = lo4 + 4 * q;
+        float4 g = *reinterpret_cast<const float4*>(a.grad[0] + i);
+        for (int r = 1; r < a.world; ++r)
+        {
+            const float4 o = *reinterpret_cast<const float4*>(a.grad[r] + i);
+            g.x += o.x, g.y += o.y, g.z += o.z, g.w += o.w;
+        }
+        if (g.x == 0.f && g.y == 0.f && g.z == 0.f && g.w == 0.f) continue;  // unseen on every rank: nothing moves anywhere
+        const int64_t j = i - a.lo;  // the optimizer state is stored for the owned slice only
+        float4 w = *reinterpret_cast<const float4*>(a.param[a.rank] + i);
+        float mm[4], vv[4];
+        int ss[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) mm[k] = m_state[j + k], vv[k] = v_state[j + k], ss[k] = steps[j + k];
+        const int s0 = segment_of(i), s3 = segment_of(i + 3);
+        fused_element(a.seg[s0], w.x, g.x, mm[0], vv[0], ss[0]);
+        fused_element(a.seg[s0 == s3 ? s0 : segment_of(i + 1)], w.y, g.y, mm[1], vv[1], ss[1]);
+        fused_element(a.seg[s0 == s3 ? s0 : segment_of(i + 2)], w.z, g.z, mm[2], vv[2], ss[2]);
+        fused_element(a.seg[s3], w.w, g.w, mm[3], vv[3], ss[3]);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) m_state[j + k] = mm[k], v_state[j + k] = vv[k], steps[j + k] = ss[k];
+        for (int r = 0; r < a.world; ++r) *reinterpret_cast<float4*>(a.param[r] + i) = w;
+    }
+    // ragged ends (at most 3 + 3 elements)
+    const int64_t n_edge = (lo4 - a.lo) + (a.hi - hi4);
+    for (int64_t q = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; q < n_edge; q += (int64_t)gridDim.x * blockDim.x)
+    {
+        const int64_t i = q < (lo4 - a.lo) ? a.lo + q : hi4 + (q - (lo4 - a.lo));
+        float g = a.grad[0][i];
+        for (int r = 1; r < a.world; ++r) g += a.grad[r][i];
+        if (g == 0.f) continue;
+        const int64_t j = i - a.lo;
+        float w = a.param[a.rank][i], mm = m_state[j], vv = v_state[j];
+        int ss = steps[j];
+        fused_element(a.seg[segment_of(i)], w, g, mm, vv, ss);
+        m_state[j] = mm, v_state[j] = vv, steps[j] = ss;
+        for (int r = 0; r < a.world; ++r) a.param[r][i] = w;
+    }
+}
+
+cudaError_t launch_fused_reduce_adam(const float* const* grad_ptrs, float* const* param_ptrs, int world, int rank,
+                                     const TripsAdamSegment* segs, int n_seg, int64_t lo, int64_t hi, float* m_state,
+                                     float* v_state, int32_t* steps, int sm_count, cudaStream_t st)
+{
+    if (hi <= lo) return cudaSuccess;
+    FusedArgs a{};
+    for (int r = 0; r < world; ++r) a.grad[r] = grad_ptrs[r], a.param[r] = param_ptrs[r];
+    for (int s = 0; s < n_seg; ++s) a.seg[s] = segs[s];
+    a.world = world, a.rank = rank, a.n_seg = n_seg, a.lo = lo, a.hi = hi;
+    const int64_t n_vec = (hi - lo + 3) / 4;
+    const int blocks    = (int)max((int64_t)1, min((int64_t)sm_count * 8, (n_vec + 255) / 256));
+    fused_reduce_adam_kernel<<<blocks, 256, 0, st>>>(a, m_state, v_state, steps);
+    return cudaGetLastError();
+}
+
 // L1 loss against a target pyramid and its gradient, all layers in one launch (benchmark helper).
 __global__ __launch_bounds__(256) void l1_loss_kernel(const __grid_constant__ L1Args a, int64_t total, float inv_total,
                                                       double* __restrict__ loss_out)

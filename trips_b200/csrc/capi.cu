@@ -505,6 +505,28 @@ int trips_adam_step(TripsContext* ctx, const TripsAdamTensor* tensors, int n_ten
     return TRIPS_OK;
 }
 
+int trips_fused_reduce_adam(TripsContext* ctx, const float* const* grad_ptrs, float* const* param_ptrs, int world, int rank,
+                            const TripsAdamSegment* segments, int n_segments, int64_t lo, int64_t hi, float* first_moments,
+                            float* second_moments, int32_t* steps, void* stream)
+{
+    if (!ctx) return TRIPS_ERR_INVALID_ARG;
+    if (!grad_ptrs || !param_ptrs || !segments) return fail(ctx, TRIPS_ERR_INVALID_ARG, "null argument");
+    if (world < 1 || world > TRIPS_MAX_RANKS || rank < 0 || rank >= world) return fail(ctx, TRIPS_ERR_INVALID_ARG, "bad world / rank");
+    if (n_segments < 1 || n_segments > TRIPS_MAX_SEGMENTS || segments[0].offset != 0) return fail(ctx, TRIPS_ERR_INVALID_ARG, "bad segment table");
+    for (int s = 1; s < n_segments; ++s)
+        if (segments[s].offset <= segments[s - 1].offset) return fail(ctx, TRIPS_ERR_INVALID_ARG, "segments must be sorted by offset");
+    if (lo < 0 || hi < lo) return fail(ctx, TRIPS_ERR_INVALID_ARG, "bad slice");
+    for (int r = 0; r < world; ++r)
+        if (!grad_ptrs[r] || !param_ptrs[r] || (((uintptr_t)grad_ptrs[r] | (uintptr_t)param_ptrs[r]) & 15))
+            return fail(ctx, TRIPS_ERR_INVALID_ARG, "flat buffers must be non-null and 16-byte aligned");
+    if (hi > lo && (!first_moments || !second_moments || !steps)) return fail(ctx, TRIPS_ERR_INVALID_ARG, "null optimizer state");
+    cudaStream_t st = (cudaStream_t)stream;
+    STAGE(ctx, TRIPS_STAGE_FUSED_ADAM, hi > lo ? 1 : 0, st,
+          launch_fused_reduce_adam(grad_ptrs, param_ptrs, world, rank, segments, n_segments, lo, hi, first_moments, second_moments,
+                                   steps, ctx->sm_count, st));
+    return TRIPS_OK;
+}
+
 int trips_enable_stage_timers(TripsContext* ctx, int enable)
 {
     if (!ctx) return TRIPS_ERR_INVALID_ARG;
@@ -534,7 +556,7 @@ int trips_get_stage_times(TripsContext* ctx, double* ms, int64_t* timed_calls, i
 const char* trips_stage_name(int stage)
 {
     static const char* names[TRIPS_NUM_STAGES] = {"setup_cams", "bin_points", "count", "scan", "collect", "sort_blend",
-                                                  "blend_backward", "unpack_grads", "adam", "l1_loss"};
+                                                  "blend_backward", "unpack_grads", "adam", "l1_loss", "fused_reduce_adam"};
     return (stage >= 0 && stage < TRIPS_NUM_STAGES) ? names[stage] : "?";
 }
 

@@ -227,6 +227,9 @@ cudaError_t launch_unpack_grads(const ScenePtrs& sc, const CamConst* cams, int B
                                 const TripsGrads& out, int sm_count, cudaStream_t st);
 cudaError_t launch_adam(const TripsAdamTensor* d_tensors, const int64_t* d_block_start, int n_tensors, int64_t total_blocks,
                         cudaStream_t st);
+cudaError_t launch_fused_reduce_adam(const float* const* grad_ptrs, float* const* param_ptrs, int world, int rank,
+                                     const TripsAdamSegment* segs, int n_seg, int64_t lo, int64_t hi, float* m_state,
+                                     float* v_state, int32_t* steps, int sm_count, cudaStream_t st);
 struct L1Args
 {
     const float* out[TRIPS_MAX_LAYERS];

@@ -61,3 +61,90 @@ def allreduce_sum(flat, group=None):
     if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
         dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=group)
     return flat
+
+
+def slice_bounds(numel: int, world: int, rank: int, align: int = 4):
+    """Flat elements [lo, hi) owned by `rank`: equal shares rounded to `align` elements (16-byte vectors)."""
+    per = -(-numel // world)
+    per = -(-per // align) * align
+    lo = min(numel, rank * per)
+    return lo, min(numel, lo + per)
+
+
+class FusedPointOptimizer:
+    """Gradient sum over ranks + MyAdam + parameter broadcast as one kernel over peer memory.
+
+    All point parameters of the scene are re-homed into one flat buffer (`self.param_flat`), their gradients are
+    written into another (`self.grad_flat`, use `self.grad_views` as the `out=` of PointRendererCache.backward); with
+    more than one rank both buffers are symmetric-memory allocations, so every rank holds peer pointers to all of
+    them.  `step()` = barrier, trips_fused_reduce_adam on this rank's slice, barrier.  Update semantics are MyAdam's
+    (src/lib/models/MyAdam.cu:41-88) evaluated after the sum, i.e. those of a single process that saw all views.
+    The optimizer state exists only for the owned slice."""
+
+    def __init__(self, named_params, cache, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, lrs=None, group=None):
+        import ctypes as C
+
+        import torch
+        import torch.distributed as dist
+
+        from . import _lib
+        self._C, self._lib, self.torch, self.dist = C, _lib, torch, dist
+        self.cache = cache
+        self.names = [n for n, _ in named_params]
+        params = [p for _, p in named_params]
+        dev = params[0].device
+        self.world = dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if self.world > 1 else 0
+        self.numel = sum(-(-p.numel() // 4) * 4 for p in params)  # every tensor starts on a 16-byte boundary
+        self.handles = None
+        if self.world > 1:
+            import torch.distributed._symmetric_memory as symm
+            g = group if group is not None else dist.group.WORLD
+            self.param_flat = symm.empty(self.numel, dtype=torch.float32, device=dev)
+            self.grad_flat = symm.empty(self.numel, dtype=torch.float32, device=dev)
+            hp, hg = symm.rendezvous(self.param_flat, g), symm.rendezvous(self.grad_flat, g)
+            self.handles = (hp, hg)
+            self.param_ptrs = [int(x) for x in hp.buffer_ptrs]
+            self.grad_ptrs = [int(x) for x in hg.buffer_ptrs]
+        else:
+            self.param_flat = torch.empty(self.numel, dtype=torch.float32, device=dev)
+            self.grad_flat = torch.empty(self.numel, dtype=torch.float32, device=dev)
+            self.param_ptrs = [self.param_flat.data_ptr()]
+            self.grad_ptrs = [self.grad_flat.data_ptr()]
+        self.param_flat.zero_()
+        self.grad_flat.zero_()
+        self.offsets, self.grad_views, segs = {}, {}, []
+        o = 0
+        with torch.no_grad():
+            for name, p in zip(self.names, params):
+                n = p.numel()
+                view = self.param_flat[o:o + n].view(p.shape)
+                view.copy_(p.data)
+                p.data = view  # the module's parameter now lives in the flat buffer
+                self.grad_views[name] = self.grad_flat[o:o + n].view(p.shape)
+                self.offsets[name] = o
+                seg_lr = (lrs or {}).get(name, lr)
+                segs.append(_lib.TripsAdamSegment(o, seg_lr, betas[0], betas[1], eps, 0.0, 0.0, 0.0, 0.0, 3.4028234663852886e38))
+                o += -(-n // 4) * 4
+        self.segments = (_lib.TripsAdamSegment * len(segs))(*segs)
+        self.lo, self.hi = slice_bounds(self.numel, self.world, self.rank)
+        n_own = max(1, self.hi - self.lo)
+        self.first_moments = torch.zeros(n_own, dtype=torch.float32, device=dev)
+        self.second_moments = torch.zeros(n_own, dtype=torch.float32, device=dev)
+        self.steps = torch.zeros(n_own, dtype=torch.int32, device=dev)
+        self._gp = (C.c_void_p * self.world)(*self.grad_ptrs)
+        self._pp = (C.c_void_p * self.world)(*self.param_ptrs)
+
+    def barrier(self):
+        if self.handles is not None:
+            self.handles[1].barrier(channel=0)
+
+    def step(self):
+        """Every rank must call this after its backward pass wrote `grad_views`."""
+        C, _lib, torch = self._C, self._lib, self.torch
+        self.barrier()  # all gradients are complete and visible
+        stream = C.c_void_p(torch.cuda.current_stream(self.param_flat.device).cuda_stream)
+        _lib.check(_lib.lib().trips_fused_reduce_adam(self.cache._h, self._gp, self._pp, self.world, self.rank, self.segments,
+                                                     len(self.segments), self.lo, self.hi, self.first_moments.data_ptr(),
+                                                     self.second_moments.data_ptr(), self.steps.data_ptr(), stream), self.cache._h)
+        self.barrier()  # every replica holds the new parameters before anybody renders again
