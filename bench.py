@@ -41,7 +41,7 @@ def parse_args():
     ap.add_argument("--views-per-gpu", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--cpu-views", type=int, default=1, help="views of the workload the CPU baseline renders")
+    ap.add_argument("--cpu-views", type=int, default=12, help="views of the workload the CPU baseline renders")
     ap.add_argument("--collective", default="auto", choices=["auto", "fused", "nccl"],
                     help="N>1: 'fused' = one kernel sums the gradients over peer memory, applies Adam and broadcasts; "
                          "'nccl' = all-reduce then Adam; 'auto' = fused when symmetric memory can be set up")
@@ -183,6 +183,7 @@ def run_reference(args, rank):
     import oracle
     from trips_b200 import scenes
     oracle.build()
+    cores = oracle.use_all_cores()
     s, my_views, vpg = make_workload(args.workload, 1, 0, args.points, args.views_per_gpu)
     sa = oracle.SceneArrays.from_scene(s)
     p = oracle.make_params(s.num_layers, s.k_keep, True)
@@ -199,16 +200,15 @@ def run_reference(args, rank):
             times.append(dt)
     ms = 1000.0 * float(np.mean(times))
     value = 1000.0 / ms
-    cores = oracle.max_threads()
     sample = f"1 view of {s.name} per step (forward + backward, no Adam), {args.steps} steps"
-    print(json.dumps({
+    emit({
         "impl": "reference", "metric": METRIC, "value": value, "unit": "views/s", "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic", "config": {"workload": s.name, "views_per_step": 1, "points": s.n_points},
         "cpu_baseline": {"value": value, "unit": "views/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "views/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
-    }))
+    })
 
 
 # ----------------------------------------------------------------------------------------------------------------
@@ -231,9 +231,6 @@ def run_ours(args, rank, world, local_rank):
     if rank == 0:
         tb.build()
     if world > 1:
-        # NCCL announces its version on stdout at VERSION / INFO level; rank 0's stdout must hold the JSON line only
-        if os.environ.get("NCCL_DEBUG", "").upper() in ("VERSION", "INFO", "TRACE") and not os.environ.get("NCCL_DEBUG_FILE"):
-            os.environ["NCCL_DEBUG"] = "WARN"
         dist.init_process_group("nccl", device_id=dev)
         dist.barrier()
 
@@ -427,7 +424,8 @@ def run_ours(args, rank, world, local_rank):
     if world == 1 and not args.no_cpu_baseline:
         import oracle
         oracle.build()
-        vps, secs, cfr = cpu_views_per_second(s, my_views[:args.cpu_views])
+        oracle.use_all_cores()
+        vps, secs, cfr = cpu_views_per_second(s, [my_views[i % B] for i in range(args.cpu_views)])
         cpu = {"value": vps, "unit": "views/s", "cores": oracle.max_threads(), "kind": "port",
                "sample": f"{args.cpu_views} view(s) of {s.name}, forward + backward with the OpenMP oracle ({secs:.1f} s)"}
 
@@ -442,14 +440,33 @@ def run_ours(args, rank, world, local_rank):
                    "max_list_length": int(stats["max_list_length"]), "fragments_per_s": F * world / (ms_step * 1e-3)},
         "e2e": e2e, "gpu_launches": int(launches_total), "roofline": roofline, "cpu_baseline": cpu, "clocks": clocks,
     }
-    print(json.dumps(out))
+    emit(out)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
 
 
+_JSON_FD = None
+
+
+def emit(obj):
+    """The one JSON line, written to the process's original stdout."""
+    line = (json.dumps(obj) + "\n").encode()
+    if _JSON_FD is None:
+        sys.stdout.write(line.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_JSON_FD, line)
+
+
 def main():
+    global _JSON_FD
     args = parse_args()
+    # Libraries write to stdout behind our back (NCCL prints its version banner there at the WARN and VERSION debug
+    # levels).  Stdout must carry the JSON line only: keep the original descriptor for it and point fd 1 at stderr.
+    sys.stdout.flush()
+    _JSON_FD = os.dup(1)
+    os.dup2(2, 1)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

@@ -67,6 +67,8 @@ def lib():
             getattr(L, name).argtypes = [C.c_float]
         L.or_project.argtypes = [C.POINTER(OrView), C.c_void_p, C.POINTER(C.c_float), C.POINTER(C.c_float), C.POINTER(C.c_float)]
         L.or_max_threads.restype = C.c_int
+        L.or_set_threads.restype = None
+        L.or_set_threads.argtypes = [C.c_int]
         _lib = L
     return _lib
 
@@ -200,3 +202,11 @@ def adam(w, g, m, v, steps, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, rel_decay
 
 def max_threads() -> int:
     return lib().or_max_threads()
+
+
+def use_all_cores() -> int:
+    """Sets the OpenMP team size to the cores this process may run on (torchrun exports OMP_NUM_THREADS=1)."""
+    import os
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    lib().or_set_threads(n)
+    return max_threads()

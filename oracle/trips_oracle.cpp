@@ -204,6 +204,15 @@ int or_max_threads(void)
 #endif
 }
 
+void or_set_threads(int n)
+{
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 float or_layer_factor(float ps, int layer, int num_layers, float* grad) { return layer_factor(ps, layer, num_layers, grad); }
 float or_softplus(float x) { return tm_softplus(x); }
 float or_expf(float x) { return tm_expf(x); }
