@@ -61,7 +61,7 @@ __global__ __launch_bounds__(kBwdThreads, TRIPS_BWD_MIN_BLOCKS) void blend_backw
                                                                      FwdBuffers fb, BwdBuffers bb,
                                                                      const __grid_constant__ ConstLayerPtrs grad_in)
 {
-    constexpr int ES = entry_stride(C);
+    constexpr int DS = tail_stride(C);
     constexpr int GS = egrad_stride(C);
     __shared__ float s_g[kBwdWarps][C][32];
     __shared__ float s_d[kBwdWarps][32 * kPad];   // G_j, then dA_j = G_j T_j, finally d_j
@@ -73,11 +73,6 @@ __global__ __launch_bounds__(kBwdThreads, TRIPS_BWD_MIN_BLOCKS) void blend_backw
 #pragma unroll
     for (int c = 0; c < C; ++c) bg[c] = __ldg(sc.background + c);
 
-    const int b = blockIdx.y;
-    const size_t bP      = (size_t)b * g.P;
-    const float* entries = fb.entries + fb.entry_base[b] * ES;
-    float* egrad         = bb.egrad + fb.entry_base[b] * GS;
-    const uint32_t n_ent = (uint32_t)(fb.entry_base[b + 1] - fb.entry_base[b]);
     float* my_d          = s_d[warp] + lane * kPad;
     uint2* my_rec        = s_rec[warp] + lane * kPad;
     float* my_w          = s_w[warp] + lane * kPad;
@@ -86,14 +81,24 @@ __global__ __launch_bounds__(kBwdThreads, TRIPS_BWD_MIN_BLOCKS) void blend_backw
 #pragma unroll
     for (int c = 0; c < C; ++c) acc_bg[c] = 0.0;
 
+    // one ticket counter over all views: the views are processed one after the other, so the entries, gradient rows and
+    // records in flight belong to one view
+    const unsigned n_total = (unsigned)g.n_tiles * (unsigned)B;
     unsigned next_tile = 0;
-    if (lane == 0) next_tile = atomicAdd(fb.ticket + b, 1u);
+    if (lane == 0) next_tile = atomicAdd(fb.ticket, 1u);
     for (;;)
     {
         // the ticket of the following tile is requested now, a whole tile ahead of its use
-        const unsigned tile = __shfl_sync(kFull, next_tile, 0);
-        if (tile >= (unsigned)g.n_tiles) break;
-        if (lane == 0) next_tile = atomicAdd(fb.ticket + b, 1u);
+        const unsigned ticket = __shfl_sync(kFull, next_tile, 0);
+        if (ticket >= n_total) break;
+        if (lane == 0) next_tile = atomicAdd(fb.ticket, 1u);
+        const int b          = ticket / (unsigned)g.n_tiles;
+        const unsigned tile  = ticket - b * (unsigned)g.n_tiles;
+        const size_t bP      = (size_t)b * g.P;
+        const float* desc    = fb.ent_tail + fb.entry_base[b] * DS + 4;  // descriptor row of entry e at desc + e * DS
+        const float4* head   = fb.ent_head + fb.entry_base[b] * 2;
+        float* egrad         = bb.egrad + fb.entry_base[b] * GS;
+        const uint32_t n_ent = (uint32_t)(fb.entry_base[b + 1] - fb.entry_base[b]);
         int layer, gx, gy, p;
         tile_pixel(g, (int)tile, lane, layer, gx, gy, p);
         int m = 0;
@@ -161,7 +166,7 @@ __global__ __launch_bounds__(kBwdThreads, TRIPS_BWD_MIN_BLOCKS) void blend_backw
             float4 row_n[(C + 3) / 4];
             if (lane < n_entry)
             {
-                const float* rp = entries + (size_t)s_rec[warp][seg_n * kPad + j_n].x * ES + 12;
+                const float* rp = desc + (size_t)s_rec[warp][seg_n * kPad + j_n].x * DS;
 #pragma unroll
                 for (int c = 0; c < (C + 3) / 4; ++c) row_n[c] = *reinterpret_cast<const float4*>(rp + 4 * c);
             }
@@ -176,7 +181,7 @@ __global__ __launch_bounds__(kBwdThreads, TRIPS_BWD_MIN_BLOCKS) void blend_backw
                     locate(e0 + 32 + lane, seg_n, j_n);
                     if (e0 + 32 + lane < n_entry)
                     {
-                        const float* rp = entries + (size_t)s_rec[warp][seg_n * kPad + j_n].x * ES + 12;
+                        const float* rp = desc + (size_t)s_rec[warp][seg_n * kPad + j_n].x * DS;
 #pragma unroll
                         for (int c = 0; c < (C + 3) / 4; ++c) row_n[c] = *reinterpret_cast<const float4*>(rp + 4 * c);
                     }
@@ -246,9 +251,8 @@ __global__ __launch_bounds__(kBwdThreads, TRIPS_BWD_MIN_BLOCKS) void blend_backw
             if (lane < n_entry)
             {
                 eidx_n          = s_rec[warp][seg_n * kPad + j_n].x;
-                const float* en = entries + (size_t)eidx_n * ES;
-                e0_n            = *reinterpret_cast<const float4*>(en);
-                conf_n          = en[5];
+                e0_n            = head[2 * (size_t)eidx_n];
+                conf_n          = head[2 * (size_t)eidx_n + 1].y;
             }
             for (int e0 = 0; e0 < n_entry; e0 += 32)
             {
@@ -263,9 +267,8 @@ __global__ __launch_bounds__(kBwdThreads, TRIPS_BWD_MIN_BLOCKS) void blend_backw
                     if (e0 + 32 + lane < n_entry)
                     {
                         eidx_n          = s_rec[warp][seg_n * kPad + j_n].x;
-                        const float* en = entries + (size_t)eidx_n * ES;
-                        e0_n            = *reinterpret_cast<const float4*>(en);
-                        conf_n          = en[5];
+                        e0_n            = head[2 * (size_t)eidx_n];
+                        conf_n          = head[2 * (size_t)eidx_n + 1].y;
                     }
                 }
                 const int layer_s = __shfl_sync(kFull, layer, seg);
@@ -314,10 +317,9 @@ cudaError_t launch_blend_backward(const ScenePtrs& sc, const CamConst* cams, con
                                   int B, const FwdBuffers& fb, const BwdBuffers& bb, const ConstLayerPtrs& grad_in,
                                   bool want_cam_grads, int sm_count, cudaStream_t st)
 {
-    cudaError_t e = cudaMemsetAsync(fb.ticket, 0, sizeof(unsigned) * B, st);
+    cudaError_t e = cudaMemsetAsync(fb.ticket, 0, sizeof(unsigned), st);
     if (e != cudaSuccess) return e;
-    int bx = max(1, min((sm_count * 12 + B - 1) / B, (g.n_tiles + kBwdWarps - 1) / kBwdWarps));
-    dim3 grid(bx, B);
+    const int grid = (int)max(1u, min((unsigned)(sm_count * 12), ((unsigned)g.n_tiles * (unsigned)B + kBwdWarps - 1) / kBwdWarps));
 #define TRIPS_BWD_CASE(CC)                                                                                         \
     case CC:                                                                                                       \
         blend_backward_kernel<CC><<<grid, kBwdThreads, 0, st>>>(sc, cams, g, pr, B, fb, bb, grad_in);             \
@@ -347,7 +349,6 @@ cudaError_t launch_blend_backward(const ScenePtrs& sc, const CamConst* cams, con
 template <int C, bool CAM_GRADS>
 __global__ __launch_bounds__(256) void entry_grad_finish_kernel(FwdBuffers fb, BwdBuffers bb, const CamConst* __restrict__ cams, int B)
 {
-    constexpr int ES = entry_stride(C);
     constexpr int GS = egrad_stride(C);
     constexpr int PS = egrad_stride(C);  // per-point row: xyz + size | descriptor row
     __shared__ CamConst cam;
@@ -357,7 +358,8 @@ __global__ __launch_bounds__(256) void entry_grad_finish_kernel(FwdBuffers fb, B
     __syncthreads();
     const float fxc = cam.fx * cam.cfx;
     const unsigned long long first = fb.entry_base[b], n = fb.entry_base[b + 1] - first;
-    const float* entries = fb.entries + first * ES;
+    const float4* head   = fb.ent_head + first * 2;
+    const float* tail    = fb.ent_tail + first * tail_stride(C);
     const float* egrad   = bb.egrad + first * GS;
     double acc[CAM_GRADS ? 11 : 1];
 #pragma unroll
@@ -365,11 +367,10 @@ __global__ __launch_bounds__(256) void entry_grad_finish_kernel(FwdBuffers fb, B
     for (unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
          i += (unsigned long long)gridDim.x * blockDim.x)
     {
-        const float* en = entries + i * ES;
         const float* eg = egrad + i * GS;
         const float4 s4 = *reinterpret_cast<const float4*>(eg);      // sum J0 gbs, sum J1 gbs, sum bf conf lf' ga, sum bf lf ga
-        const float4 e1 = *reinterpret_cast<const float4*>(en + 4);  // pid conf raw nl
-        const float4 e2 = *reinterpret_cast<const float4*>(en + 8);  // x y z tex
+        const float4 e1 = head[2 * i + 1];  // pid conf raw nl
+        const float4 e2 = *reinterpret_cast<const float4*>(tail + i * tail_stride(C));  // x y z tex
         const int pid   = __float_as_int(e1.x);
         const int tex   = __float_as_int(e2.w);
         float vx, vy, vz;

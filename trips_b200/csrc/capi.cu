@@ -124,6 +124,7 @@ struct TripsContext
     int B = 0, N = 0, n_tex = 0, C = 0;
     int nchunks = 0;
     unsigned long long total_frags = 0;
+    size_t entry_cap = 0;                  // entries the two entry arrays (head | tail, in this order) are laid out for
     unsigned long long total_entries = 0;  // visible points summed over the views of the last forward call
     TripsStats host_stats{};
 };
@@ -189,7 +190,8 @@ static FwdBuffers fwd_buffers(TripsContext* c)
     fb.view_total = (uint32_t*)c->view_total.p;
     fb.bin_cursor = (uint32_t*)c->bin_cursor.p;
     fb.entry_base = (unsigned long long*)c->entry_base.p;
-    fb.entries    = (float*)c->entries.p;
+    fb.ent_head   = (float4*)c->entries.p;
+    fb.ent_tail   = (float*)c->entries.p + 8 * c->entry_cap;
     fb.counts     = (uint32_t*)c->counts.p;
     fb.offsets    = (uint32_t*)c->offsets.p;
     fb.partial    = (uint32_t*)c->partial.p;
@@ -301,12 +303,17 @@ int trips_forward(TripsContext* ctx, const TripsScene* scene, const TripsView* v
         for (int l = g.L; l <= TRIPS_MAX_LAYERS; ++l) g.base[l] = (int)base;
         if (base > (1ll << 30)) return fail(ctx, TRIPS_ERR_TOO_LARGE, "pyramid has more than 2^30 pixels");
         g.P = (int)base;
-        int tb = 0;
+        static const int kRegTiles[5] = {0, 128, 160, 168, 170};
+        g.reg_layers = g.L < 4 ? g.L : 4;
+        g.reg_x      = (w + 63) / 64;
+        g.reg_tiles  = kRegTiles[g.reg_layers];
+        g.reg_total  = g.reg_x * ((h + 63) / 64) * g.reg_tiles;
+        int tb = g.reg_total;
         for (int l = 0; l < TRIPS_MAX_LAYERS; ++l)
         {
             g.tile_base[l] = tb;
             g.tiles_x[l]   = 1;
-            if (l < g.L)
+            if (l >= g.reg_layers && l < g.L)
             {
                 g.tiles_x[l] = (g.W[l] + kTileW - 1) / kTileW;
                 tb += g.tiles_x[l] * ((g.H[l] + kTileH - 1) / kTileH);
@@ -336,6 +343,7 @@ int trips_forward(TripsContext* ctx, const TripsScene* scene, const TripsView* v
     CU_CHECK(ctx, ensure(ctx->entry_base, sizeof(unsigned long long) * (B + 1)));
     // entries are sized for the worst case (every point visible in every view): no host round trip is needed to size them
     CU_CHECK(ctx, ensure(ctx->entries, sizeof(float) * ES * N * B + 16));
+    ctx->entry_cap = (size_t)N * B;
     CU_CHECK(ctx, ensure(ctx->counts, sizeof(uint32_t) * P * B));
     CU_CHECK(ctx, ensure(ctx->offsets, sizeof(uint32_t) * P * B));
     CU_CHECK(ctx, ensure(ctx->partial, sizeof(uint32_t) * (size_t)nchunks * B));
@@ -594,13 +602,19 @@ int trips_debug_points(TripsContext* ctx, int view, float* depth, int32_t* nlaye
     if (!ctx->have_forward) return fail(ctx, TRIPS_ERR_NO_FORWARD, "no forward pass");
     if (view < 0 || view >= ctx->B) return fail(ctx, TRIPS_ERR_INVALID_ARG, "view out of range");
     cudaStream_t st = (cudaStream_t)stream;
-    const size_t N = (size_t)ctx->N, ES = (size_t)entry_stride(ctx->C);
+    const size_t N = (size_t)ctx->N, ES = 8;  // the two float4 of an entry's head
     unsigned long long eb[2];
     CU_CHECK(ctx, cudaMemcpyAsync(eb, (unsigned long long*)ctx->entry_base.p + view, sizeof(eb), cudaMemcpyDeviceToHost, st));
     CU_CHECK(ctx, cudaStreamSynchronize(st));
     const size_t n = (size_t)(eb[1] - eb[0]);
-    std::vector<float> e(n * ES);
-    if (n) CU_CHECK(ctx, cudaMemcpyAsync(e.data(), (float*)ctx->entries.p + eb[0] * ES, sizeof(float) * n * ES, cudaMemcpyDeviceToHost, st));
+    const size_t TS = (size_t)tail_stride(ctx->C);
+    std::vector<float> e(n * ES), tl(n * TS);
+    if (n)
+    {
+        CU_CHECK(ctx, cudaMemcpyAsync(e.data(), (float*)ctx->entries.p + eb[0] * ES, sizeof(float) * n * ES, cudaMemcpyDeviceToHost, st));
+        CU_CHECK(ctx, cudaMemcpyAsync(tl.data(), (float*)ctx->entries.p + 8 * ctx->entry_cap + eb[0] * TS, sizeof(float) * n * TS,
+                                      cudaMemcpyDeviceToHost, st));
+    }
     CU_CHECK(ctx, cudaStreamSynchronize(st));
     // the per-point arrays of the reference (depth = -1 for culled points) are rebuilt from the view's entries
     for (size_t i = 0; i < N; ++i)
@@ -623,7 +637,7 @@ int trips_debug_points(TripsContext* ctx, int view, float* depth, int32_t* nlaye
             record[4 * (size_t)pid + 0] = en[0];
             record[4 * (size_t)pid + 1] = en[1];
             record[4 * (size_t)pid + 2] = en[2];
-            record[4 * (size_t)pid + 3] = en[11];
+            record[4 * (size_t)pid + 3] = tl[k * TS + 3];  // texture index
         }
     }
     return TRIPS_OK;
@@ -669,7 +683,7 @@ int trips_debug_records(TripsContext* ctx, int view, int32_t* nrec, int32_t* rec
     const size_t P = (size_t)ctx->geom.P, off = (size_t)view * P;
     std::vector<uint8_t> n(P);
     std::vector<uint2> r(P * 16);
-    const size_t ES = (size_t)entry_stride(ctx->C);
+    const size_t ES = 8;  // the two float4 of an entry's head
     unsigned long long eb[2];
     CU_CHECK(ctx, cudaMemcpyAsync(eb, (unsigned long long*)ctx->entry_base.p + view, sizeof(eb), cudaMemcpyDeviceToHost, st));
     CU_CHECK(ctx, cudaMemcpyAsync(n.data(), (uint8_t*)ctx->rec_n.p + off, P, cudaMemcpyDeviceToHost, st));

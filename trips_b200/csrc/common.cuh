@@ -22,8 +22,15 @@ struct Geom
     int H[TRIPS_MAX_LAYERS];
     int base[TRIPS_MAX_LAYERS + 1];     // first pixel of every layer in the per-view pixel arrays (row-major)
     int P;                              // pixels per view
-    int tiles_x[TRIPS_MAX_LAYERS];      // 8x4 pixel tiles per layer row
-    int tile_base[TRIPS_MAX_LAYERS + 1];
+    // Tile order of a view: first the 64x64-pixel regions of layer 0 in row-major order, each with its tiles of
+    // layers 0..reg_layers-1 (a region is (64 >> l) pixels wide on layer l), so that the entries of a region stay in L2
+    // while all its fine layers are processed; then the remaining coarse layers, layer by layer.
+    int reg_layers;                     // min(L, 4)
+    int reg_x;                          // regions per row
+    int reg_tiles;                      // tiles of one region: 128 + 32 + 8 + 2 for four layers
+    int reg_total;                      // tiles of all regions of a view
+    int tiles_x[TRIPS_MAX_LAYERS];      // 8x4 pixel tiles per layer row (coarse layers)
+    int tile_base[TRIPS_MAX_LAYERS + 1];  // first tile of every coarse layer (layers below reg_layers: reg_total)
     int n_tiles;                        // tiles per view
     int bins_x, bins_y, n_bins;         // 32x32 screen bins of layer 0
 };
@@ -58,13 +65,15 @@ struct DevStats
     unsigned int status;
 };
 
-// A visible point of one view ("entry"): everything the later stages need, gathered once, 16-byte aligned, and
-// stored in screen-bin order so that fragments of neighbouring pixels read neighbouring entries.
-//   float  0..3   u, v (layer-0 image position), size in pixels, view-space depth
-//   float  4..7   point id (bits), confidence, raw point size, number of layers written (bits)
-//   float  8..11  world position x, y, z, texture index (bits)
-//   float 12..    descriptor row (C floats, padded to a multiple of 4)
-__host__ __device__ constexpr int entry_stride(int C) { return 12 + ((C + 3) & ~3); }
+// A visible point of one view ("entry"): everything the later stages need, gathered once and stored in screen-bin
+// order so that fragments of neighbouring pixels read neighbouring entries.  The fields live in two arrays, split by
+// the stage that reads them, so that a stage's gathers touch fewer bytes it does not use (DRAM is read in 64-byte
+// pieces), while the binning pass still writes whole 32-byte sectors:
+//   head [2 x float4]     u, v (layer-0 image position), size in pixels, view-space depth |
+//                         point id (bits), confidence, raw point size, number of layers written (bits)
+//   tail [1 + C4/4 float4] world position x, y, z, texture index (bits) | descriptor row (C floats, padded to 4)
+__host__ __device__ constexpr int tail_stride(int C) { return 4 + ((C + 3) & ~3); }
+__host__ __device__ constexpr int entry_stride(int C) { return 8 + tail_stride(C); }  // floats per entry over both arrays
 // Gradient accumulator of an entry: sums over its fragments of (J0 gbs, J1 gbs, bf conf lf' ga, bf lf ga) | descriptor row.
 __host__ __device__ constexpr int egrad_stride(int C) { return 4 + ((C + 3) & ~3); }
 
@@ -76,7 +85,8 @@ struct FwdBuffers
     uint32_t* view_total;             // [B] visible points per view
     uint32_t* bin_cursor;             // [B,n_bins] first entry of every bin within the view
     unsigned long long* entry_base;   // [B+1] first entry of each view
-    float* entries;                   // [sum V_b, entry_stride]
+    float4* ent_head;                 // [sum V_b, 2]
+    float* ent_tail;                  // [sum V_b, tail_stride]
     uint32_t* counts;                 // [B,P] list lengths
     uint32_t* offsets;                // [B,P] list start within the view (list end after the collect pass)
     uint32_t* partial;                // [B,nchunks] scan partials
@@ -196,13 +206,26 @@ __device__ __forceinline__ float layer_factor(float ps, int layer, int L, float*
 // Pixel handled by `lane` of the warp that owns 8x4 tile `tile` of a view; p = -1 outside the image.
 __device__ __forceinline__ void tile_pixel(const Geom& g, int tile, int lane, int& layer, int& gx, int& gy, int& p)
 {
-    int l = 0;
+    int l, tx, ty;
+    if (tile < g.reg_total)
+    {
+        const int r = tile / g.reg_tiles, k = tile - r * g.reg_tiles;
+        l           = k < 128 ? 0 : (k < 160 ? 1 : (k < 168 ? 2 : 3));
+        const int kk = k - (l == 0 ? 0 : (l == 1 ? 128 : (l == 2 ? 160 : 168)));
+        const int ry = r / g.reg_x, rx = r - ry * g.reg_x;
+        tx = rx * (8 >> l) + (kk & ((8 >> l) - 1));   // a region is 8 >> l tiles wide and 16 >> l tiles high on layer l
+        ty = ry * (16 >> l) + (kk >> (3 - l));
+    }
+    else
+    {
+        l = g.reg_layers;
 #pragma unroll
-    for (int i = 1; i < TRIPS_MAX_LAYERS; ++i)
-        if (i < g.L && tile >= g.tile_base[i]) l = i;
-    const int t  = tile - g.tile_base[l];
-    const int ty = t / g.tiles_x[l];
-    const int tx = t - ty * g.tiles_x[l];
+        for (int i = 1; i < TRIPS_MAX_LAYERS; ++i)
+            if (i > g.reg_layers && i < g.L && tile >= g.tile_base[i]) l = i;
+        const int t = tile - g.tile_base[l];
+        ty          = t / g.tiles_x[l];
+        tx          = t - ty * g.tiles_x[l];
+    }
     layer        = l;
     gx           = tx * kTileW + (lane & (kTileW - 1));
     gy           = ty * kTileH + (lane >> 3);

@@ -230,7 +230,7 @@ template <int C>
 __global__ __launch_bounds__(kBinThreads) void bin_scatter_kernel(ScenePtrs sc, const CamConst* __restrict__ cams,
                                                                   const __grid_constant__ Geom g, TripsRenderParams pr, FwdBuffers fb)
 {
-    constexpr int ES = entry_stride(C);
+    constexpr int TS = tail_stride(C);
     extern __shared__ uint32_t s_cursor[];
     __shared__ CamConst cam;
     const int b = blockIdx.y;
@@ -240,7 +240,8 @@ __global__ __launch_bounds__(kBinThreads) void bin_scatter_kernel(ScenePtrs sc, 
     __syncthreads();
     const size_t bN  = (size_t)b * sc.N;
     const float fxc  = cam.fx * cam.cfx;
-    float* entries   = fb.entries + fb.entry_base[b] * ES;
+    float4* head     = fb.ent_head + fb.entry_base[b] * 2;
+    float* tail      = fb.ent_tail + fb.entry_base[b] * TS;
     int first, last;
     block_chunk(sc.N, first, last);
     for (int i = first + threadIdx.x; i < last; i += blockDim.x)
@@ -267,15 +268,15 @@ __global__ __launch_bounds__(kBinThreads) void bin_scatter_kernel(ScenePtrs sc, 
         else
             atomicOr(&fb.stats->status, TRIPS_DEV_BAD_TEXTURE_INDEX);  // the point is drawn with alpha 0
         const float4 p = __ldg(sc.position + i);
-        float4* e      = reinterpret_cast<float4*>(entries + (size_t)slot * ES);
-        e[0]           = make_float4(r.u, r.v, r.ps, r.z);
-        e[1]           = make_float4(__int_as_float(i), conf, __ldg(sc.point_size + i), __int_as_float(layer));
-        e[2]           = make_float4(p.x, p.y, p.z, __int_as_float(tex_ok ? r.tex : -1));
+        head[2 * (size_t)slot]     = make_float4(r.u, r.v, r.ps, r.z);
+        head[2 * (size_t)slot + 1] = make_float4(__int_as_float(i), conf, __ldg(sc.point_size + i), __int_as_float(layer));
+        float4* e = reinterpret_cast<float4*>(tail + (size_t)slot * TS);
+        e[0]      = make_float4(p.x, p.y, p.z, __int_as_float(tex_ok ? r.tex : -1));
         float row_t[(C + 3) & ~3];
 #pragma unroll
         for (int c = 0; c < ((C + 3) & ~3); ++c) row_t[c] = (c < C && tex_ok) ? __ldg(sc.texture + (size_t)c * sc.n_tex + r.tex) : 0.f;
 #pragma unroll
-        for (int c = 0; c < ((C + 3) & ~3); c += 4) e[3 + c / 4] = make_float4(row_t[c], row_t[c + 1], row_t[c + 2], row_t[c + 3]);
+        for (int c = 0; c < ((C + 3) & ~3); c += 4) e[1 + c / 4] = make_float4(row_t[c], row_t[c + 1], row_t[c + 2], row_t[c + 3]);
     }
 }
 
@@ -538,17 +539,20 @@ __device__ __forceinline__ bool next_chunk(const FwdBuffers& fb, const Geom& g, 
 }
 
 template <bool COLLECT>
-__global__ __launch_bounds__(kWinThreads) void window_kernel(int ES, const __grid_constant__ Geom g, FwdBuffers fb)
+__global__ __launch_bounds__(kWinThreads) void window_kernel(const __grid_constant__ Geom g, FwdBuffers fb, int B)
 {
     __shared__ uint32_t s_cnt[kWinMax];
     __shared__ uint32_t s_base[COLLECT ? kWinMax : 1];
     __shared__ uint32_t s_tmp[2];
-    const int b = blockIdx.y;
-    if (COLLECT && fb.view_base[b + 1] > fb.frag_cap) return;  // list buffer too small: the overflow status bit is already raised
+    // all blocks walk the views in the same order: the lists, counters and entries in flight belong to one view (or two,
+    // where blocks cross over), which keeps the partially written list sectors of a view in L2 until they are complete
+    for (int b = 0; b < B; ++b)
+    {
+    if (COLLECT && fb.view_base[b + 1] > fb.frag_cap) continue;  // list buffer too small: the overflow status bit is already raised
     uint32_t* pixel_ctr   = (COLLECT ? fb.offsets : fb.counts) + (size_t)b * g.P;
     uint4* frags          = fb.frags + fb.view_base[COLLECT ? b : 0];
     const uint32_t n_entry = (uint32_t)(fb.entry_base[b + 1] - fb.entry_base[b]);
-    const float* entries   = fb.entries + fb.entry_base[b] * ES;
+    const float4* head     = fb.ent_head + fb.entry_base[b] * 2;
     const uint32_t* bfirst = fb.bin_cursor + (size_t)b * g.n_bins;
     uint32_t c0, c1;
     int bin;
@@ -570,8 +574,8 @@ __global__ __launch_bounds__(kWinThreads) void window_kernel(int ES, const __gri
                 int nln     = 0;
                 if (ei < hi)
                 {
-                    e0n = *reinterpret_cast<const float4*>(entries + (size_t)ei * ES);  // u v ps z
-                    nln = __float_as_int(entries[(size_t)ei * ES + 7]);
+                    e0n = head[2 * (size_t)ei];  // u v ps z
+                    nln = __float_as_int(head[2 * (size_t)ei + 1].w);
                 }
                 for (; ei < hi; ei += kWinThreads)
                 {
@@ -579,8 +583,8 @@ __global__ __launch_bounds__(kWinThreads) void window_kernel(int ES, const __gri
                     const int nl    = nln;
                     if (ei + kWinThreads < hi)
                     {
-                        e0n = *reinterpret_cast<const float4*>(entries + (size_t)(ei + kWinThreads) * ES);
-                        nln = __float_as_int(entries[(size_t)(ei + kWinThreads) * ES + 7]);
+                        e0n = head[2 * (size_t)(ei + kWinThreads)];
+                        nln = __float_as_int(head[2 * (size_t)(ei + kWinThreads) + 1].w);
                     }
                     float x = e0.x, y = e0.y;
                     for (int layer = 0; layer < nl; ++layer, x *= 0.5f, y *= 0.5f)
@@ -619,16 +623,16 @@ __global__ __launch_bounds__(kWinThreads) void window_kernel(int ES, const __gri
                 float4 e0n = make_float4(0.f, 0.f, 0.f, 0.f), e1n = e0n;
                 if (ei < hi)
                 {
-                    e0n = *reinterpret_cast<const float4*>(entries + (size_t)ei * ES);      // u v ps z
-                    e1n = *reinterpret_cast<const float4*>(entries + (size_t)ei * ES + 4);  // pid conf raw nl
+                    e0n = head[2 * (size_t)ei];      // u v ps z
+                    e1n = head[2 * (size_t)ei + 1];  // pid conf raw nl
                 }
                 for (; ei < hi; ei += kWinThreads)
                 {
                     const float4 e0 = e0n, e1 = e1n;
                     if (ei + kWinThreads < hi)
                     {
-                        e0n = *reinterpret_cast<const float4*>(entries + (size_t)(ei + kWinThreads) * ES);
-                        e1n = *reinterpret_cast<const float4*>(entries + (size_t)(ei + kWinThreads) * ES + 4);
+                        e0n = head[2 * (size_t)(ei + kWinThreads)];
+                        e1n = head[2 * (size_t)(ei + kWinThreads) + 1];
                     }
                     const int nl     = __float_as_int(e1.w);
                     const float conf = e1.y;
@@ -661,13 +665,14 @@ __global__ __launch_bounds__(kWinThreads) void window_kernel(int ES, const __gri
             }
         }
     }
+    }
 }
 
 cudaError_t launch_count(const ScenePtrs& sc, const Geom& g, int B, const FwdBuffers& fb, int sm_count, cudaStream_t st)
 {
     cudaError_t e = cudaMemsetAsync(fb.ticket, 0, sizeof(unsigned) * B, st);
     if (e != cudaSuccess) return e;
-    window_kernel<false><<<dim3(max(1, (sm_count * 8 + B - 1) / B), B), kWinThreads, 0, st>>>(entry_stride(sc.C), g, fb);
+    window_kernel<false><<<sm_count * 8, kWinThreads, 0, st>>>(g, fb, B);
     return cudaGetLastError();
 }
 
@@ -675,7 +680,7 @@ cudaError_t launch_collect(const ScenePtrs& sc, const Geom& g, int B, const FwdB
 {
     cudaError_t e = cudaMemsetAsync(fb.ticket, 0, sizeof(unsigned) * B, st);
     if (e != cudaSuccess) return e;
-    window_kernel<true><<<dim3(max(1, (sm_count * 8 + B - 1) / B), B), kWinThreads, 0, st>>>(entry_stride(sc.C), g, fb);
+    window_kernel<true><<<sm_count * 8, kWinThreads, 0, st>>>(g, fb, B);
     return cudaGetLastError();
 }
 
@@ -768,7 +773,7 @@ __device__ __forceinline__ void sb_store_entry(float* dst, const float* entries,
 {
     if constexpr (SbEntry<C>::kStaged)
     {
-        const float4 v4 = *reinterpret_cast<const float4*>(entries + (size_t)eidx * entry_stride(C) + 12);
+        const float4 v4 = *reinterpret_cast<const float4*>(entries + (size_t)eidx * tail_stride(C) + 4);
         dst[0]          = __uint_as_float(alpha_bits);
         dst[1]          = v4.x;
         if (C > 1) dst[2] = v4.y;
@@ -791,7 +796,7 @@ __global__ __launch_bounds__(kSbThreads, TRIPS_SB_MIN_BLOCKS) void sort_blend_ke
                                                                 unsigned n_tiles_total)
 {
     constexpr int E  = SbEntry<C>::kFloats;
-    constexpr int ES = entry_stride(C);
+    constexpr int ES = tail_stride(C);
     __shared__ float s_sorted[kSbWarps][32 * kSortedPad * E];  // per warp: 32 pixels x K entries, nearest first
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
@@ -813,7 +818,7 @@ __global__ __launch_bounds__(kSbThreads, TRIPS_SB_MIN_BLOCKS) void sort_blend_ke
         const int tile       = ticket - b * (unsigned)g.n_tiles;
         const size_t bP      = (size_t)b * g.P;
         const uint4* frags   = fb.frags + fb.view_base[b];
-        const float* entries = fb.entries + fb.entry_base[b] * ES;
+        const float* entries = fb.ent_tail + fb.entry_base[b] * ES;  // (position, descriptor row) of the view's entries
         const uint32_t n_entry = (uint32_t)(fb.entry_base[b + 1] - fb.entry_base[b]);
         int layer, gx, gy, p;
         tile_pixel(g, tile, lane, layer, gx, gy, p);  // lane i owns one pixel of the tile
@@ -982,7 +987,7 @@ __global__ __launch_bounds__(kSbThreads, TRIPS_SB_MIN_BLOCKS) void sort_blend_ke
             {
                 unsigned eidx = __float_as_uint(my_sorted[j * E]);
                 if (eidx >= n_entry) eidx = 0;  // only after a corrupted list was flagged in phase A: read in bounds
-                const float* rp = entries + (size_t)eidx * ES + 12;
+                const float* rp = entries + (size_t)eidx * ES + 4;
 #pragma unroll
                 for (int r = 0; r < kRows; ++r) dst[r] = *reinterpret_cast<const float4*>(rp + 4 * r);
             }
