@@ -52,6 +52,9 @@ constexpr int kBwdWarps   = kBwdThreads / 32;
 //   phase 2 (lane = kept fragment): descriptor gradient and the image-space sums of the fragment's entry
 //     (RenderBackward.cu:335-393), accumulated with two vector atomics into the per-entry gradient rows, which are
 //     in screen-bin order like the entries and therefore stay hot in L2 while a region of the image is processed.
+#ifndef TRIPS_BWD_BLOCKS_PER_SM
+#define TRIPS_BWD_BLOCKS_PER_SM 12
+#endif
 #ifndef TRIPS_BWD_MIN_BLOCKS
 #define TRIPS_BWD_MIN_BLOCKS 1
 #endif
@@ -319,7 +322,7 @@ cudaError_t launch_blend_backward(const ScenePtrs& sc, const CamConst* cams, con
 {
     cudaError_t e = cudaMemsetAsync(fb.ticket, 0, sizeof(unsigned), st);
     if (e != cudaSuccess) return e;
-    const int grid = (int)max(1u, min((unsigned)(sm_count * 12), ((unsigned)g.n_tiles * (unsigned)B + kBwdWarps - 1) / kBwdWarps));
+    const int grid = (int)max(1u, min((unsigned)(sm_count * TRIPS_BWD_BLOCKS_PER_SM), ((unsigned)g.n_tiles * (unsigned)B + kBwdWarps - 1) / kBwdWarps));
 #define TRIPS_BWD_CASE(CC)                                                                                         \
     case CC:                                                                                                       \
         blend_backward_kernel<CC><<<grid, kBwdThreads, 0, st>>>(sc, cams, g, pr, B, fb, bb, grad_in);             \

@@ -466,8 +466,21 @@ cudaError_t launch_scan(const Geom& g, int B, int k_keep, const FwdBuffers& fb, 
 // in the operation order of FastSortFusedNew (RenderForward.cu:882-899) is computed here, where every thread holds
 // a whole point, and travels with the fragment.
 // ------------------------------------------------------------------------------------------------------------
-constexpr int kWinChunk   = 2048;  // entries per block ticket
-constexpr int kWinThreads = 256;
+#ifndef TRIPS_WIN_CHUNK
+#define TRIPS_WIN_CHUNK 4096
+#endif
+#ifndef TRIPS_WIN_THREADS
+#define TRIPS_WIN_THREADS 256
+#endif
+#ifndef TRIPS_WIN_BLOCKS_PER_SM
+#define TRIPS_WIN_BLOCKS_PER_SM 8
+#endif
+#ifndef TRIPS_WIN_CHUNK_COLLECT
+#define TRIPS_WIN_CHUNK_COLLECT 512
+#endif
+constexpr int kWinChunkCount   = TRIPS_WIN_CHUNK;          // entries per block ticket, counting pass
+constexpr int kWinChunkCollect = TRIPS_WIN_CHUNK_COLLECT;  // and collecting pass (measured: 1024 beats 512, 2048 and 4096)
+constexpr int kWinThreads = TRIPS_WIN_THREADS;
 constexpr int kWinMax     = 34 * 34 + 18 * 18 + 10 * 10 + 6 * 6 + 4 * 4 + 3 * 3 * 3;  // 1659 window pixels over 8 layers
 
 struct Window
@@ -509,7 +522,7 @@ __device__ __forceinline__ int window_pixel(const Geom& g, const Window& w, int 
 }
 
 // the chunk [c0, c1) of the view's entries and the first bin it touches; false when the view has no more chunks
-__device__ __forceinline__ bool next_chunk(const FwdBuffers& fb, const Geom& g, int b, uint32_t n_entry, uint32_t* s_tmp,
+__device__ __forceinline__ bool next_chunk(const FwdBuffers& fb, const Geom& g, int b, uint32_t n_entry, uint32_t* s_tmp, int kWinChunk,
                                            uint32_t& c0, uint32_t& c1, int& first_bin)
 {
     __syncthreads();
@@ -538,12 +551,79 @@ __device__ __forceinline__ bool next_chunk(const FwdBuffers& fb, const Geom& g, 
     return c0 < n_entry;
 }
 
+
+// Calls body(e0, e1, x, y, layer, entry) for every (entry, layer) pair of the entries [lo, hi), with (x, y) the entry's
+// position on that layer.  A warp takes 32 entries at a time: layer 0 directly (every entry has it), the higher layers
+// through a per-warp queue of (lane, layer) items that all 32 lanes drain together, so that an entry with many layers
+// does not hold up the 31 other lanes.  WITH_E1 = false: body only needs x, y, layer.
+template <bool WITH_E1, class Body>
+__device__ __forceinline__ void for_each_footprint(const float4* __restrict__ head, uint32_t lo, uint32_t hi, uint8_t* queue, Body&& body)
+{
+    const int lane = threadIdx.x & 31;
+    uint32_t base  = lo + (threadIdx.x & ~31);
+    float4 e0n = make_float4(0.f, 0.f, 0.f, 0.f), e1n = e0n;
+    if (base + lane < hi)
+    {
+        e0n = head[2 * (size_t)(base + lane)];      // u v ps z
+        e1n = head[2 * (size_t)(base + lane) + 1];  // pid conf raw nl
+    }
+    for (; base < hi; base += kWinThreads)
+    {
+        const uint32_t ei = base + lane;
+        const float4 e0 = e0n, e1 = e1n;
+        const int nl = ei < hi ? __float_as_int(e1.w) : 0;
+        if (base + kWinThreads + lane < hi)  // the next round's entry travels while this one is processed
+        {
+            e0n = head[2 * (size_t)(ei + kWinThreads)];
+            e1n = head[2 * (size_t)(ei + kWinThreads) + 1];
+        }
+        if (nl > 0) body(e0, e1, e0.x, e0.y, 0, ei);
+        const int extra = max(nl - 1, 0);
+        int incl = extra;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1)
+        {
+            const int t = __shfl_up_sync(kFull, incl, o);
+            if (lane >= o) incl += t;
+        }
+        const int total = __shfl_sync(kFull, incl, 31);
+        if (total == 0) continue;  // uniform
+        int pos = incl - extra;
+        for (int l = 1; l < nl; ++l) queue[pos++] = (uint8_t)(lane | (l << 5));
+        __syncwarp();
+        for (int i0 = 0; i0 < total; i0 += 32)
+        {
+            const int i        = i0 + lane;
+            const unsigned it  = i < total ? queue[i] : 0u;
+            const int src = it & 31, layer = it >> 5;
+            float4 s0, s1 = make_float4(0.f, 0.f, 0.f, 0.f);
+            s0.x = __shfl_sync(kFull, e0.x, src);
+            s0.y = __shfl_sync(kFull, e0.y, src);
+            s0.z = s0.w = 0.f;
+            if (WITH_E1)
+            {
+                s0.z = __shfl_sync(kFull, e0.z, src);
+                s0.w = __shfl_sync(kFull, e0.w, src);
+                s1.x = __shfl_sync(kFull, e1.x, src);
+                s1.y = __shfl_sync(kFull, e1.y, src);
+            }
+            if (i < total)
+            {
+                const float sc = __int_as_float((127 - layer) << 23);  // 2^-layer: the same value as `layer` halvings
+                body(s0, s1, s0.x * sc, s0.y * sc, layer, base + src);
+            }
+        }
+        __syncwarp();
+    }
+}
+
 template <bool COLLECT>
 __global__ __launch_bounds__(kWinThreads) void window_kernel(const __grid_constant__ Geom g, FwdBuffers fb, int B)
 {
     __shared__ uint32_t s_cnt[kWinMax];
     __shared__ uint32_t s_base[COLLECT ? kWinMax : 1];
     __shared__ uint32_t s_tmp[2];
+    __shared__ uint8_t s_queue[kWinThreads / 32][32 * (TRIPS_MAX_LAYERS - 1)];
     // all blocks walk the views in the same order: the lists, counters and entries in flight belong to one view (or two,
     // where blocks cross over), which keeps the partially written list sectors of a view in L2 until they are complete
     for (int b = 0; b < B; ++b)
@@ -556,7 +636,7 @@ __global__ __launch_bounds__(kWinThreads) void window_kernel(const __grid_consta
     const uint32_t* bfirst = fb.bin_cursor + (size_t)b * g.n_bins;
     uint32_t c0, c1;
     int bin;
-    while (next_chunk(fb, g, b, n_entry, s_tmp, c0, c1, bin))
+    while (next_chunk(fb, g, b, n_entry, s_tmp, COLLECT ? kWinChunkCollect : kWinChunkCount, c0, c1, bin))
     {
         for (; bin < g.n_bins && bfirst[bin] < c1; ++bin)
         {
@@ -567,37 +647,16 @@ __global__ __launch_bounds__(kWinThreads) void window_kernel(const __grid_consta
             const int n_win = w.off[TRIPS_MAX_LAYERS];
             for (int i = threadIdx.x; i < n_win; i += kWinThreads) s_cnt[i] = 0;
             __syncthreads();
-            // ---- fragments per window pixel (the next entry is loaded while the current one is counted) ----
-            {
-                uint32_t ei = lo + threadIdx.x;
-                float4 e0n  = make_float4(0.f, 0.f, 0.f, 0.f);
-                int nln     = 0;
-                if (ei < hi)
-                {
-                    e0n = head[2 * (size_t)ei];  // u v ps z
-                    nln = __float_as_int(head[2 * (size_t)ei + 1].w);
-                }
-                for (; ei < hi; ei += kWinThreads)
-                {
-                    const float4 e0 = e0n;
-                    const int nl    = nln;
-                    if (ei + kWinThreads < hi)
-                    {
-                        e0n = head[2 * (size_t)(ei + kWinThreads)];
-                        nln = __float_as_int(head[2 * (size_t)(ei + kWinThreads) + 1].w);
-                    }
-                    float x = e0.x, y = e0.y;
-                    for (int layer = 0; layer < nl; ++layer, x *= 0.5f, y *= 0.5f)
-                    {
-                        const int ww = win_w(layer);
-                        uint32_t* c  = s_cnt + w.off[layer] + (__float2int_rd(y) - w.y0[layer]) * ww + (__float2int_rd(x) - w.x0[layer]);
-                        atomicAdd(c, 1u);
-                        atomicAdd(c + 1, 1u);
-                        atomicAdd(c + ww, 1u);
-                        atomicAdd(c + ww + 1, 1u);
-                    }
-                }
-            }
+            // ---- fragments per window pixel ----
+            for_each_footprint<false>(head, lo, hi, s_queue[threadIdx.x >> 5],
+                                      [&](const float4&, const float4&, float x, float y, int layer, uint32_t) {
+                                          const int ww = win_w(layer);
+                                          uint32_t* c  = s_cnt + w.off[layer] + (__float2int_rd(y) - w.y0[layer]) * ww + (__float2int_rd(x) - w.x0[layer]);
+                                          atomicAdd(c, 1u);
+                                          atomicAdd(c + 1, 1u);
+                                          atomicAdd(c + ww, 1u);
+                                          atomicAdd(c + ww + 1, 1u);
+                                      });
             __syncthreads();
             // ---- one global atomic per touched pixel ----
             for (int i = threadIdx.x; i < n_win; i += kWinThreads)
@@ -619,48 +678,34 @@ __global__ __launch_bounds__(kWinThreads) void window_kernel(const __grid_consta
             if (COLLECT)
             {
                 // ---- slots inside the reserved ranges; alpha and the fragment itself ----
-                uint32_t ei = lo + threadIdx.x;
-                float4 e0n = make_float4(0.f, 0.f, 0.f, 0.f), e1n = e0n;
-                if (ei < hi)
-                {
-                    e0n = head[2 * (size_t)ei];      // u v ps z
-                    e1n = head[2 * (size_t)ei + 1];  // pid conf raw nl
-                }
-                for (; ei < hi; ei += kWinThreads)
-                {
-                    const float4 e0 = e0n, e1 = e1n;
-                    if (ei + kWinThreads < hi)
-                    {
-                        e0n = head[2 * (size_t)(ei + kWinThreads)];
-                        e1n = head[2 * (size_t)(ei + kWinThreads) + 1];
-                    }
-                    const int nl     = __float_as_int(e1.w);
-                    const float conf = e1.y;
-                    const uint32_t pid = __float_as_uint(e1.x), zb = __float_as_uint(e0.w);
-                    float x = e0.x, y = e0.y;
-                    for (int layer = 0; layer < nl; ++layer, x *= 0.5f, y *= 0.5f)
-                    {
-                        // x, y equal (u, v) * 2^-layer exactly (power-of-two scaling)
-                        const int px = __float2int_rd(x), py = __float2int_rd(y);
-                        const int ww = win_w(layer);
-                        const int li = w.off[layer] + (py - w.y0[layer]) * ww + (px - w.x0[layer]);
-                        const float lf  = layer_factor(e0.z, layer, g.L, nullptr);
-                        const float dx0 = fabsf(x - (float)px), dx1 = fabsf(x - (float)(px + 1));
-                        const float dy0 = fabsf(y - (float)py), dy1 = fabsf(y - (float)(py + 1));
-                        auto emit = [&](int idx, float dx, float dy) {
-                            float bl = (1.f - dx) * (1.f - dy);
-                            if (dx > 1.f || dy > 1.f) bl = 0.f;
-                            float a = bl * conf;
-                            a *= lf;
-                            const uint32_t slot = s_base[idx] + atomicAdd(s_cnt + idx, 1u);
-                            frags[slot]         = make_uint4(pid, zb, __float_as_uint(a), ei);
-                        };
-                        emit(li, dx0, dy0);
-                        emit(li + 1, dx1, dy0);
-                        emit(li + ww, dx0, dy1);
-                        emit(li + ww + 1, dx1, dy1);
-                    }
-                }
+                for_each_footprint<true>(head, lo, hi, s_queue[threadIdx.x >> 5],
+                                         [&](const float4& e0, const float4& e1, float x, float y, int layer, uint32_t ei) {
+                                             // x, y equal (u, v) * 2^-layer exactly (power-of-two scaling)
+                                             const float conf   = e1.y;
+                                             const uint32_t pid = __float_as_uint(e1.x), zb = __float_as_uint(e0.w);
+                                             const int px = __float2int_rd(x), py = __float2int_rd(y);
+                                             const int ww = win_w(layer);
+                                             const int li = w.off[layer] + (py - w.y0[layer]) * ww + (px - w.x0[layer]);
+                                             const float lf  = layer_factor(e0.z, layer, g.L, nullptr);
+                                             const float dx0 = fabsf(x - (float)px), dx1 = fabsf(x - (float)(px + 1));
+                                             const float dy0 = fabsf(y - (float)py), dy1 = fabsf(y - (float)(py + 1));
+                                             auto alpha = [&](float dx, float dy) {
+                                                 float bl = (1.f - dx) * (1.f - dy);
+                                                 if (dx > 1.f || dy > 1.f) bl = 0.f;
+                                                 float a = bl * conf;
+                                                 a *= lf;
+                                                 return __float_as_uint(a);
+                                             };
+                                             // the four slots first, then the four stores: the shared-memory atomics do not wait for one another
+                                             const uint32_t s00 = s_base[li] + atomicAdd(s_cnt + li, 1u);
+                                             const uint32_t s10 = s_base[li + 1] + atomicAdd(s_cnt + li + 1, 1u);
+                                             const uint32_t s01 = s_base[li + ww] + atomicAdd(s_cnt + li + ww, 1u);
+                                             const uint32_t s11 = s_base[li + ww + 1] + atomicAdd(s_cnt + li + ww + 1, 1u);
+                                             frags[s00] = make_uint4(pid, zb, alpha(dx0, dy0), ei);
+                                             frags[s10] = make_uint4(pid, zb, alpha(dx1, dy0), ei);
+                                             frags[s01] = make_uint4(pid, zb, alpha(dx0, dy1), ei);
+                                             frags[s11] = make_uint4(pid, zb, alpha(dx1, dy1), ei);
+                                         });
                 __syncthreads();  // the next bin of this chunk reuses s_cnt / s_base
             }
         }
@@ -672,7 +717,7 @@ cudaError_t launch_count(const ScenePtrs& sc, const Geom& g, int B, const FwdBuf
 {
     cudaError_t e = cudaMemsetAsync(fb.ticket, 0, sizeof(unsigned) * B, st);
     if (e != cudaSuccess) return e;
-    window_kernel<false><<<sm_count * 8, kWinThreads, 0, st>>>(g, fb, B);
+    window_kernel<false><<<sm_count * TRIPS_WIN_BLOCKS_PER_SM, kWinThreads, 0, st>>>(g, fb, B);
     return cudaGetLastError();
 }
 
@@ -680,7 +725,7 @@ cudaError_t launch_collect(const ScenePtrs& sc, const Geom& g, int B, const FwdB
 {
     cudaError_t e = cudaMemsetAsync(fb.ticket, 0, sizeof(unsigned) * B, st);
     if (e != cudaSuccess) return e;
-    window_kernel<true><<<sm_count * 8, kWinThreads, 0, st>>>(g, fb, B);
+    window_kernel<true><<<sm_count * TRIPS_WIN_BLOCKS_PER_SM, kWinThreads, 0, st>>>(g, fb, B);
     return cudaGetLastError();
 }
 
