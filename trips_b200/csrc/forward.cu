@@ -107,18 +107,25 @@ __device__ __forceinline__ Projected project_visible(const ScenePtrs& sc, const 
     {
         if (__ldg(sc.dropout + bN + i) == 1.f) return r;
     }
-    const float4 p = __ldg(sc.position + i);
-    const float s  = tm_softplus(__ldg(sc.point_size + i));
+    const float4 p  = __ldg(sc.position + i);
+    const float raw = __ldg(sc.point_size + i);
     project_point(cam, p.x, p.y, p.z, r.u, r.v, r.z);
     r.rad = fxc * p.w / r.z;
-    r.ps  = fxc * s / r.z;
+    r.ps  = 0.f;
     bool ok = !(r.z <= 0.f || r.u < 0.f || r.u >= (float)(g.W[0] - 1) || r.v < 0.f || r.v >= (float)(g.H[0] - 1));
     if (ok && pr.drop_out_points_by_radius && (float)(int)r.rad < pr.drop_out_radius_threshold) ok = false;
+    if (ok) r.ps = fxc * tm_softplus(raw) / r.z;  // only visible points pay for the softplus
     r.ok = ok;
     return r;
 }
 
-constexpr int kBinThreads = 512;
+#ifndef TRIPS_BIN_THREADS
+#define TRIPS_BIN_THREADS 512
+#endif
+#ifndef TRIPS_BIN_BLOCKS_PER_SM
+#define TRIPS_BIN_BLOCKS_PER_SM 4
+#endif
+constexpr int kBinThreads = TRIPS_BIN_THREADS;
 
 // Every block owns a contiguous chunk of the point cloud (the same chunk in the count and in the scatter pass) and
 // keeps the histogram over screen bins in shared memory, so binning needs no global atomics: the count pass
@@ -281,7 +288,7 @@ __global__ __launch_bounds__(kBinThreads) void bin_scatter_kernel(ScenePtrs sc, 
 }
 
 // measured: 4 blocks of 512 threads per SM over all views beats a single resident wave (1.93 vs 2.40 ms at 8 views)
-int bin_blocks_per_view(int B, int sm_count) { return max(4, min(128, (4 * sm_count + B - 1) / max(B, 1))); }
+int bin_blocks_per_view(int B, int sm_count) { return max(4, min(256, (TRIPS_BIN_BLOCKS_PER_SM * sm_count + B - 1) / max(B, 1))); }
 
 cudaError_t launch_bin_points(const ScenePtrs& sc, const CamConst* cams, const Geom& g, const TripsRenderParams& pr, int B,
                               const FwdBuffers& fb, int sm_count, cudaStream_t st)
@@ -479,31 +486,34 @@ cudaError_t launch_scan(const Geom& g, int B, int k_keep, const FwdBuffers& fb, 
 #define TRIPS_WIN_CHUNK_COLLECT 512
 #endif
 constexpr int kWinChunkCount   = TRIPS_WIN_CHUNK;          // entries per block ticket, counting pass
-constexpr int kWinChunkCollect = TRIPS_WIN_CHUNK_COLLECT;  // and collecting pass (measured: 1024 beats 512, 2048 and 4096)
+constexpr int kWinChunkCollect = TRIPS_WIN_CHUNK_COLLECT;  // and collecting pass: the lists a chunk writes to must stay in L2 until complete (measured: 512 2.7 ms, 1024 3.3 ms, 2048 3.7 ms, 256 2.9 ms)
 constexpr int kWinThreads = TRIPS_WIN_THREADS;
 constexpr int kWinMax     = 34 * 34 + 18 * 18 + 10 * 10 + 6 * 6 + 4 * 4 + 3 * 3 * 3;  // 1659 window pixels over 8 layers
 
+// Window of a bin: on layer l it starts at ((32 bx) >> l, (32 by) >> l) and is win_w(l) pixels wide; the counters of
+// the layers follow one another in shared memory.  Everything is computed from (bx32, by32) with shifts and selects:
+// arrays indexed by the layer would live in local memory.
 struct Window
 {
-    int x0[TRIPS_MAX_LAYERS], y0[TRIPS_MAX_LAYERS], off[TRIPS_MAX_LAYERS + 1];
+    int bx32, by32;
+    __device__ __forceinline__ int x0(int l) const { return bx32 >> l; }
+    __device__ __forceinline__ int y0(int l) const { return by32 >> l; }
 };
 
 __device__ __forceinline__ int win_w(int l) { return (31 >> l) + 3; }
+
+// first counter of layer l: sum of win_w(k)^2 over k < l = 0, 1156, 1480, 1580, 1616, 1632, 1641, 1650, 1659
+__device__ __forceinline__ int win_off(int l)
+{
+    return l < 4 ? (l < 2 ? (l == 0 ? 0 : 1156) : (l == 2 ? 1480 : 1580)) : (l < 6 ? (l == 4 ? 1616 : 1632) : (l == 6 ? 1641 : (l == 7 ? 1650 : 1659)));
+}
 
 __device__ __forceinline__ Window make_window(const Geom& g, int bin)
 {
     Window w;
     const int by = bin / g.bins_x, bx = bin - by * g.bins_x;
-    int o = 0;
-#pragma unroll
-    for (int l = 0; l < TRIPS_MAX_LAYERS; ++l)
-    {
-        w.x0[l]  = (bx << kBinShift) >> l;
-        w.y0[l]  = (by << kBinShift) >> l;
-        w.off[l] = o;
-        if (l < g.L) o += win_w(l) * win_w(l);
-    }
-    w.off[TRIPS_MAX_LAYERS] = o;
+    w.bx32 = bx << kBinShift;
+    w.by32 = by << kBinShift;
     return w;
 }
 
@@ -513,12 +523,12 @@ __device__ __forceinline__ int window_pixel(const Geom& g, const Window& w, int 
     int l = 0;
 #pragma unroll
     for (int k = 1; k < TRIPS_MAX_LAYERS; ++k)
-        if (k < g.L && i >= w.off[k]) l = k;
-    const int r  = i - w.off[l];
+        if (i >= win_off(k)) l = k;
+    const int r  = i - win_off(l);
     const int ww = win_w(l);
     const int dy = r / ww, dx = r - dy * ww;
-    const int x = w.x0[l] + dx, y = w.y0[l] + dy;
-    return (x < g.W[l] && y < g.H[l]) ? g.base[l] + y * g.W[l] + x : -1;
+    const int x = w.x0(l) + dx, y = w.y0(l) + dy;
+    return (l < g.L && x < g.W[l] && y < g.H[l]) ? g.base[l] + y * g.W[l] + x : -1;
 }
 
 // the chunk [c0, c1) of the view's entries and the first bin it touches; false when the view has no more chunks
@@ -617,12 +627,39 @@ __device__ __forceinline__ void for_each_footprint(const float4* __restrict__ he
     }
 }
 
+#ifndef TRIPS_FRAG_EVICT_LAST
+#define TRIPS_FRAG_EVICT_LAST 1
+#endif
+
+// 16-byte store that asks L2 to keep the line: a pixel's list is written 16 bytes at a time by many threads, and a
+// sector that leaves L2 half written costs a read-modify-write in DRAM.
+__device__ __forceinline__ void store_frag(uint4* p, const uint4& v, uint64_t policy)
+{
+#if TRIPS_FRAG_EVICT_LAST
+    asm volatile("st.global.L2::cache_hint.v4.b32 [%0], {%1, %2, %3, %4}, %5;" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w), "l"(policy) : "memory");
+#else
+    *p = v;
+#endif
+}
+__device__ __forceinline__ uint64_t evict_last_policy()
+{
+    uint64_t policy = 0;
+#if TRIPS_FRAG_EVICT_LAST
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(policy));
+#endif
+    return policy;
+}
+
+#ifndef TRIPS_WIN_MIN_BLOCKS
+#define TRIPS_WIN_MIN_BLOCKS 5
+#endif
 template <bool COLLECT>
-__global__ __launch_bounds__(kWinThreads) void window_kernel(const __grid_constant__ Geom g, FwdBuffers fb, int B)
+__global__ __launch_bounds__(kWinThreads, TRIPS_WIN_MIN_BLOCKS) void window_kernel(const __grid_constant__ Geom g, FwdBuffers fb, int B)
 {
     __shared__ uint32_t s_cnt[kWinMax];
     __shared__ uint32_t s_base[COLLECT ? kWinMax : 1];
     __shared__ uint32_t s_tmp[2];
+    const uint64_t keep = evict_last_policy();
     __shared__ uint8_t s_queue[kWinThreads / 32][32 * (TRIPS_MAX_LAYERS - 1)];
     // all blocks walk the views in the same order: the lists, counters and entries in flight belong to one view (or two,
     // where blocks cross over), which keeps the partially written list sectors of a view in L2 until they are complete
@@ -644,14 +681,14 @@ __global__ __launch_bounds__(kWinThreads) void window_kernel(const __grid_consta
             const uint32_t lo = max(c0, bfirst[bin]), hi = min(c1, bin_end);
             if (lo >= hi) continue;  // uniform: all threads read the same values
             const Window w = make_window(g, bin);
-            const int n_win = w.off[TRIPS_MAX_LAYERS];
+            const int n_win = win_off(g.L);
             for (int i = threadIdx.x; i < n_win; i += kWinThreads) s_cnt[i] = 0;
             __syncthreads();
             // ---- fragments per window pixel ----
             for_each_footprint<false>(head, lo, hi, s_queue[threadIdx.x >> 5],
                                       [&](const float4&, const float4&, float x, float y, int layer, uint32_t) {
                                           const int ww = win_w(layer);
-                                          uint32_t* c  = s_cnt + w.off[layer] + (__float2int_rd(y) - w.y0[layer]) * ww + (__float2int_rd(x) - w.x0[layer]);
+                                          uint32_t* c  = s_cnt + win_off(layer) + (__float2int_rd(y) - w.y0(layer)) * ww + (__float2int_rd(x) - w.x0(layer));
                                           atomicAdd(c, 1u);
                                           atomicAdd(c + 1, 1u);
                                           atomicAdd(c + ww, 1u);
@@ -685,7 +722,7 @@ __global__ __launch_bounds__(kWinThreads) void window_kernel(const __grid_consta
                                              const uint32_t pid = __float_as_uint(e1.x), zb = __float_as_uint(e0.w);
                                              const int px = __float2int_rd(x), py = __float2int_rd(y);
                                              const int ww = win_w(layer);
-                                             const int li = w.off[layer] + (py - w.y0[layer]) * ww + (px - w.x0[layer]);
+                                             const int li = win_off(layer) + (py - w.y0(layer)) * ww + (px - w.x0(layer));
                                              const float lf  = layer_factor(e0.z, layer, g.L, nullptr);
                                              const float dx0 = fabsf(x - (float)px), dx1 = fabsf(x - (float)(px + 1));
                                              const float dy0 = fabsf(y - (float)py), dy1 = fabsf(y - (float)(py + 1));
@@ -701,10 +738,10 @@ __global__ __launch_bounds__(kWinThreads) void window_kernel(const __grid_consta
                                              const uint32_t s10 = s_base[li + 1] + atomicAdd(s_cnt + li + 1, 1u);
                                              const uint32_t s01 = s_base[li + ww] + atomicAdd(s_cnt + li + ww, 1u);
                                              const uint32_t s11 = s_base[li + ww + 1] + atomicAdd(s_cnt + li + ww + 1, 1u);
-                                             frags[s00] = make_uint4(pid, zb, alpha(dx0, dy0), ei);
-                                             frags[s10] = make_uint4(pid, zb, alpha(dx1, dy0), ei);
-                                             frags[s01] = make_uint4(pid, zb, alpha(dx0, dy1), ei);
-                                             frags[s11] = make_uint4(pid, zb, alpha(dx1, dy1), ei);
+                                             store_frag(frags + s00, make_uint4(pid, zb, alpha(dx0, dy0), ei), keep);
+                                             store_frag(frags + s10, make_uint4(pid, zb, alpha(dx1, dy0), ei), keep);
+                                             store_frag(frags + s01, make_uint4(pid, zb, alpha(dx0, dy1), ei), keep);
+                                             store_frag(frags + s11, make_uint4(pid, zb, alpha(dx1, dy1), ei), keep);
                                          });
                 __syncthreads();  // the next bin of this chunk reuses s_cnt / s_base
             }
@@ -832,8 +869,9 @@ __device__ __forceinline__ void sb_store_entry(float* dst, const float* entries,
     }
 }
 
+// measured: 7 resident blocks (72 registers) 3.18 ms, 6 blocks (80) 3.46 ms, 5 blocks 3.83 ms, 8 blocks (64, spills) 3.76 ms
 #ifndef TRIPS_SB_MIN_BLOCKS
-#define TRIPS_SB_MIN_BLOCKS 1
+#define TRIPS_SB_MIN_BLOCKS 7
 #endif
 template <int C>
 __global__ __launch_bounds__(kSbThreads, TRIPS_SB_MIN_BLOCKS) void sort_blend_kernel(ScenePtrs sc, const __grid_constant__ Geom g, TripsRenderParams pr,
