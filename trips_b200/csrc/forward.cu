@@ -874,7 +874,7 @@ __device__ __forceinline__ void sb_store_entry(float* dst, const float* entries,
 #define TRIPS_SB_MIN_BLOCKS 7
 #endif
 template <int C>
-__global__ __launch_bounds__(kSbThreads, TRIPS_SB_MIN_BLOCKS) void sort_blend_kernel(ScenePtrs sc, const __grid_constant__ Geom g, TripsRenderParams pr,
+__global__ __launch_bounds__(kSbThreads, (C <= 8 ? TRIPS_SB_MIN_BLOCKS : 1)) void sort_blend_kernel(ScenePtrs sc, const __grid_constant__ Geom g, TripsRenderParams pr,
                                                                 int B, FwdBuffers fb, const __grid_constant__ LayerPtrs out,
                                                                 unsigned n_tiles_total)
 {
