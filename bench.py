@@ -147,6 +147,19 @@ def stage_bytes(stage, N, P, C, B, F, Kf):
     return 0
 
 
+# DRAM bytes (read + write) per unit of work, from the single-pass ncu capture of the full workload summarised in
+# profiles/rasterizer_kernels_c3_full_dram_traffic.md; traffic grows in proportion to the unit count
+DRAM_BYTES_PER_UNIT = {"collect": (26.7, "F"), "sort_blend": (36.8, "F"), "blend_backward": (42.5, "Kf"), "count": (5.5, "F"),
+                       "bin_points": (61.5, "NB"), "adam": (347.9, "N")}
+
+
+def stage_traffic(stage, N, B, F, Kf):
+    if stage not in DRAM_BYTES_PER_UNIT:
+        return None
+    per, unit = DRAM_BYTES_PER_UNIT[stage]
+    return per * {"F": F, "Kf": Kf, "NB": N * B, "N": N}[unit]
+
+
 def fused_adam_bytes(numel, world):
     """One rank's launch: its slice of every rank's gradient, its parameters and state in, state and every replica out."""
     return (numel // world) * 4 * (world + 1 + 3 + 3 + world)
@@ -417,7 +430,9 @@ def run_ours(args, rank, world, local_rank):
         v["gbs"] = (b_ / (v["ms_per_launch"] * 1e-3) / 1e9) if b_ else None
     total_alg = sum(bytes_of(k) for k in step_stages)
     roofline = {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "peak_kind": peak_kind, "traffic": None, "alg_bytes_per_launch": dom_bytes,
+                "peak_kind": peak_kind, "traffic": stage_traffic(dom, N, B, F, Kf),
+                "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum per unit of work (profiles/rasterizer_kernels_c3_full_dram_traffic.md) x units of this run",
+                "alg_bytes_per_launch": dom_bytes,
                 "step_alg_bytes": total_alg, "step_gbs": total_alg / (ms_step * 1e-3) / 1e9, "stages": per_stage}
 
     cpu = None
