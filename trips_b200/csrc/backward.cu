@@ -375,6 +375,8 @@ __global__ __launch_bounds__(256) void entry_grad_finish_kernel(FwdBuffers fb, B
         const float4 e1 = head[2 * i + 1];  // pid conf raw nl
         const float4 e2 = *reinterpret_cast<const float4*>(tail + i * tail_stride(C));  // x y z tex
         const int pid   = __float_as_int(e1.x);
+        // row of the point: by spatial rank when the forward pass stored one (rows of a screen bin then share L2 lines)
+        const size_t row = fb.point_rank ? (size_t)(__float_as_uint(e1.w) >> kRankShift) : (size_t)pid;
         const int tex   = __float_as_int(e2.w);
         float vx, vy, vz;
         transform_point(cam, e2.x, e2.y, e2.z, vx, vy, vz);
@@ -394,7 +396,7 @@ __global__ __launch_bounds__(256) void entry_grad_finish_kernel(FwdBuffers fb, B
             const float gp1 = cam.R[1] * gv0 + cam.R[4] * gv1 + cam.R[7] * gv2;
             const float gp2 = cam.R[2] * gv0 + cam.R[5] * gv1 + cam.R[8] * gv2;
             const float gl  = tm_softplus_grad(e1.z) * (fxc / vz) * s4.z;
-            atomicAdd(reinterpret_cast<float4*>(bb.g_point + (size_t)pid * PS), make_float4(gp0, gp1, gp2, gl));
+            atomicAdd(reinterpret_cast<float4*>(bb.g_point + row * PS), make_float4(gp0, gp1, gp2, gl));
             if constexpr (CAM_GRADS)
             {
                 const float nx = vx * iz, ny = vy * iz;
@@ -412,7 +414,7 @@ __global__ __launch_bounds__(256) void entry_grad_finish_kernel(FwdBuffers fb, B
             }
         }
         if (tex < 0) continue;
-        if (s4.w != 0.f) atomicAdd(bb.g_conf_pt + pid, s4.w);
+        if (s4.w != 0.f) atomicAdd(bb.g_conf_pt + row, s4.w);
         float gt[(C + 3) & ~3];
         bool any = false;
 #pragma unroll
@@ -423,7 +425,7 @@ __global__ __launch_bounds__(256) void entry_grad_finish_kernel(FwdBuffers fb, B
             any |= (v4.x != 0.f || v4.y != 0.f || v4.z != 0.f || v4.w != 0.f);
         }
         // descriptor gradients share the point's row with the position gradient: both atomics hit one 32-byte sector
-        if (any) atomic_add_row<((C + 3) & ~3)>(bb.g_point + (size_t)pid * PS + 4, gt);
+        if (any) atomic_add_row<((C + 3) & ~3)>(bb.g_point + row * PS + 4, gt);
     }
     if constexpr (CAM_GRADS)
     {
@@ -455,24 +457,25 @@ __global__ __launch_bounds__(256) void entry_grad_finish_kernel(FwdBuffers fb, B
 // zeroed outputs); with the identity index they are plain stores.
 template <int C>
 __global__ __launch_bounds__(256) void unpack_point_kernel(const float* __restrict__ g_point, const float* __restrict__ g_conf_pt,
-                                                           const int32_t* __restrict__ index, int N, int n_tex,
+                                                           const uint32_t* __restrict__ rank, const int32_t* __restrict__ index, int N, int n_tex,
                                                            float4* __restrict__ g_points, float* __restrict__ g_size,
                                                            float* __restrict__ g_texture, float* __restrict__ g_confidence)
 {
     constexpr int PS = egrad_stride(C);
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < (size_t)N; i += (size_t)gridDim.x * blockDim.x)
     {
-        const float4 v = *reinterpret_cast<const float4*>(g_point + i * PS);
+        const size_t r = rank ? (size_t)rank[i] : i;  // where the point's row lives
+        const float4 v = *reinterpret_cast<const float4*>(g_point + r * PS);
         if (g_points) g_points[i] = make_float4(v.x, v.y, v.z, 0.f);
         if (g_size) g_size[i] = v.w;
         float gt[(C + 3) & ~3];
 #pragma unroll
         for (int c = 0; c < ((C + 3) & ~3); c += 4)
         {
-            const float4 t4 = *reinterpret_cast<const float4*>(g_point + i * PS + 4 + c);
+            const float4 t4 = *reinterpret_cast<const float4*>(g_point + r * PS + 4 + c);
             gt[c] = t4.x, gt[c + 1] = t4.y, gt[c + 2] = t4.z, gt[c + 3] = t4.w;
         }
-        const float gc = g_conf_pt[i];
+        const float gc = g_conf_pt[r];
         if (!index)
         {
             if (g_texture)
@@ -560,7 +563,7 @@ cudaError_t launch_unpack_grads(const ScenePtrs& sc, const CamConst* cams, int B
         int blocks = max(1, (int)min((size_t)sm_count * 16, ((size_t)sc.N + 255) / 256));
 #define TRIPS_UNPACK_CASE(CC)                                                                                           \
     case CC:                                                                                                            \
-        unpack_point_kernel<CC><<<blocks, 256, 0, st>>>(bb.g_point, bb.g_conf_pt, sc.index, sc.N, sc.n_tex,              \
+        unpack_point_kernel<CC><<<blocks, 256, 0, st>>>(bb.g_point, bb.g_conf_pt, fb.point_rank, sc.index, sc.N, sc.n_tex,              \
                                                         (float4*)out.points, out.point_size, out.texture, out.confidence); \
         break;
         switch (sc.C)

@@ -109,7 +109,7 @@ struct TripsContext
     int sm_count = 148;
     std::string error;
     // forward scratch
-    DevBuf views, cams, bin_count, bin_base, view_total, bin_cursor, entry_base, entries, counts, offsets, partial, view_base, frags, rec_n, records, stats, ticket;
+    DevBuf views, cams, bin_count, bin_base, view_total, bin_cursor, entry_base, entries, counts, offsets, partial, view_base, frags, rec_n, records, stats, ticket, rank, rank_scratch, rank_temp;
     // backward scratch
     DevBuf egrad, g_point, g_conf_pt, g_small;
     // adam
@@ -124,6 +124,8 @@ struct TripsContext
     int B = 0, N = 0, n_tex = 0, C = 0;
     int nchunks = 0;
     unsigned long long total_frags = 0;
+    int rank_points = -1;                  // number of points the spatial ranks were computed for (-1: none yet)
+    int rank_age    = 0;                   // training forward passes since then
     size_t entry_cap = 0;                  // entries the two entry arrays (head | tail, in this order) are laid out for
     unsigned long long total_entries = 0;  // visible points summed over the views of the last forward call
     TripsStats host_stats{};
@@ -202,6 +204,7 @@ static FwdBuffers fwd_buffers(TripsContext* c)
     fb.records    = (uint2*)c->records.p;
     fb.stats      = (DevStats*)c->stats.p;
     fb.ticket     = (unsigned int*)c->ticket.p;
+    fb.point_rank = c->rank_points >= 0 ? (const uint32_t*)c->rank.p : nullptr;
     return fb;
 }
 
@@ -250,7 +253,7 @@ void trips_context_destroy(TripsContext* c)
     if (!c) return;
     DevBuf* all[] = {&c->views, &c->cams, &c->bin_count, &c->bin_base, &c->view_total, &c->bin_cursor, &c->entry_base, &c->entries, &c->counts, &c->offsets,
                      &c->partial, &c->view_base, &c->frags, &c->rec_n, &c->records, &c->stats, &c->ticket, &c->egrad, &c->g_point,
-                     &c->g_conf_pt, &c->g_small, &c->adam_tab};
+                     &c->g_conf_pt, &c->g_small, &c->adam_tab, &c->rank, &c->rank_scratch, &c->rank_temp};
     for (DevBuf* b : all) free_buf(*b);
     c->timers.destroy();
     if (c->h_pinned) cudaFreeHost(c->h_pinned);
@@ -366,6 +369,27 @@ int trips_forward(TripsContext* ctx, const TripsScene* scene, const TripsView* v
     }
 
     ScenePtrs sp  = scene_ptrs(scene);
+    // Spatial ranks of the points (where their gradient rows live, rank.cu): training only; refreshed when the number
+    // of points changes and every kRankRefresh forward passes, since points move slowly and a stale rank is still a
+    // valid permutation.  Entries carry the rank, so the backward pass of this forward pass sees the same ranks.
+    constexpr int kRankRefresh = 512;
+    if (params->train && N > 0 && N < (size_t)kMaxRankedPoints)
+    {
+        if (ctx->rank_points != (int)N || ctx->rank_age >= kRankRefresh)
+        {
+            const size_t tb = rank_temp_bytes((int)N);
+            CU_CHECK(ctx, ensure(ctx->rank, sizeof(uint32_t) * N));
+            CU_CHECK(ctx, ensure(ctx->rank_scratch, sizeof(uint32_t) * (4 * N + 8)));
+            CU_CHECK(ctx, ensure(ctx->rank_temp, tb));
+            CU_CHECK(ctx, launch_point_rank((const float4*)scene->position, (int)N, (unsigned*)ctx->rank_scratch.p, ctx->rank_temp.p, tb,
+                                            (unsigned*)ctx->rank.p, ctx->sm_count, st));
+            ctx->rank_points = (int)N;
+            ctx->rank_age    = 0;
+        }
+        ++ctx->rank_age;
+    }
+    else
+        ctx->rank_points = -1;
     FwdBuffers fb = fwd_buffers(ctx);
     CU_CHECK(ctx, cudaMemsetAsync(ctx->stats.p, 0, sizeof(DevStats), st));
     CU_CHECK(ctx, cudaMemsetAsync(ctx->counts.p, 0, sizeof(uint32_t) * P * B, st));
@@ -629,6 +653,7 @@ int trips_debug_points(TripsContext* ctx, int view, float* depth, int32_t* nlaye
         int32_t pid, nl;
         memcpy(&pid, en + 4, 4);
         memcpy(&nl, en + 7, 4);
+        nl &= (1 << kRankShift) - 1;  // the spatial rank shares the word
         if (pid < 0 || (size_t)pid >= N) continue;
         if (depth) depth[pid] = en[3];
         if (nlayers) nlayers[pid] = nl;

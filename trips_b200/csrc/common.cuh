@@ -13,6 +13,8 @@ constexpr unsigned kFull  = 0xffffffffu;
 constexpr int kBinShift   = 5;   // visible points are bucketed by 32x32-pixel screen bins of layer 0
 constexpr int kTileW      = 8;   // one warp renders / differentiates an 8x4 pixel tile
 constexpr int kTileH      = 4;
+constexpr int kRankShift  = 4;   // entry head: number of layers in the low 4 bits, spatial rank above
+constexpr int kMaxRankedPoints = 1 << 28;
 
 // Pyramid geometry shared by all views of a call.
 struct Geom
@@ -70,7 +72,8 @@ struct DevStats
 // the stage that reads them, so that a stage's gathers touch fewer bytes it does not use (DRAM is read in 64-byte
 // pieces), while the binning pass still writes whole 32-byte sectors:
 //   head [2 x float4]     u, v (layer-0 image position), size in pixels, view-space depth |
-//                         point id (bits), confidence, raw point size, number of layers written (bits)
+//                         point id (bits), confidence, raw point size, number of layers written (bits 0-3) and
+//                         spatial rank of the point (bits 4-31, see rank.cu; 0 when ranks are not in use)
 //   tail [1 + C4/4 float4] world position x, y, z, texture index (bits) | descriptor row (C floats, padded to 4)
 __host__ __device__ constexpr int tail_stride(int C) { return 4 + ((C + 3) & ~3); }
 __host__ __device__ constexpr int entry_stride(int C) { return 8 + tail_stride(C); }  // floats per entry over both arrays
@@ -97,6 +100,7 @@ struct FwdBuffers
     uint2* records;                   // [B,P,16] (entry index within the view, alpha bits)
     DevStats* stats;
     unsigned int* ticket;
+    const uint32_t* point_rank;       // [N] spatial rank of every point, or nullptr: gradient rows are keyed by point id
 };
 
 struct ScenePtrs
@@ -238,6 +242,9 @@ cudaError_t launch_setup_cams(const TripsView* d_views, int B, const double* pos
 cudaError_t launch_bin_points(const ScenePtrs& sc, const CamConst* cams, const Geom& g, const TripsRenderParams& pr, int B,
                               const FwdBuffers& fb, int sm_count, cudaStream_t st);
 int bin_blocks_per_view(int B, int sm_count);
+size_t rank_temp_bytes(int N);
+cudaError_t launch_point_rank(const float4* position, int N, unsigned* scratch, void* temp, size_t temp_bytes, unsigned* rank,
+                              int sm_count, cudaStream_t st);
 cudaError_t launch_scan(const Geom& g, int B, int k_keep, const FwdBuffers& fb, int nchunks, cudaStream_t st);
 cudaError_t launch_count(const ScenePtrs& sc, const Geom& g, int B, const FwdBuffers& fb, int sm_count, cudaStream_t st);
 cudaError_t launch_collect(const ScenePtrs& sc, const Geom& g, int B, const FwdBuffers& fb, int sm_count, cudaStream_t st);

@@ -276,7 +276,8 @@ __global__ __launch_bounds__(kBinThreads) void bin_scatter_kernel(ScenePtrs sc, 
             atomicOr(&fb.stats->status, TRIPS_DEV_BAD_TEXTURE_INDEX);  // the point is drawn with alpha 0
         const float4 p = __ldg(sc.position + i);
         head[2 * (size_t)slot]     = make_float4(r.u, r.v, r.ps, r.z);
-        head[2 * (size_t)slot + 1] = make_float4(__int_as_float(i), conf, __ldg(sc.point_size + i), __int_as_float(layer));
+        const uint32_t rk          = fb.point_rank ? __ldg(fb.point_rank + i) : 0u;
+        head[2 * (size_t)slot + 1] = make_float4(__int_as_float(i), conf, __ldg(sc.point_size + i), __uint_as_float((uint32_t)layer | (rk << kRankShift)));
         float4* e = reinterpret_cast<float4*>(tail + (size_t)slot * TS);
         e[0]      = make_float4(p.x, p.y, p.z, __int_as_float(tex_ok ? r.tex : -1));
         float row_t[(C + 3) & ~3];
@@ -581,7 +582,7 @@ __device__ __forceinline__ void for_each_footprint(const float4* __restrict__ he
     {
         const uint32_t ei = base + lane;
         const float4 e0 = e0n, e1 = e1n;
-        const int nl = ei < hi ? __float_as_int(e1.w) : 0;
+        const int nl = ei < hi ? (__float_as_int(e1.w) & ((1 << kRankShift) - 1)) : 0;
         if (base + kWinThreads + lane < hi)  // the next round's entry travels while this one is processed
         {
             e0n = head[2 * (size_t)(ei + kWinThreads)];
