@@ -9,15 +9,28 @@
 
 namespace trips
 {
-__device__ __forceinline__ void adam_element(const TripsAdamTensor& t, float& w, float g, float& m, float& v, int& step)
+// Bias-corrected learning rate of the last step count seen by this thread: neighbouring elements (the coordinates of a
+// point, the channels of a descriptor) almost always share their step count, and the two powf dominate the update.
+struct LrCache
+{
+    int step = -1;
+    float lr = 0.f;
+};
+
+__device__ __forceinline__ void adam_element(const TripsAdamTensor& t, float& w, float g, float& m, float& v, int& step, LrCache& cache)
 {
     if (g == 0.f) return;
     const float gsq = g * g;
     m               = t.beta1 * m + (1.f - t.beta1) * g;
     v               = t.beta2 * v + (1.f - t.beta2) * gsq;
     step            = step + 1;
-    const float fs  = (float)(unsigned)step;
-    const float lr  = t.lr * (sqrtf(1.f - powf(t.beta2, fs)) / (1.f - powf(t.beta1, fs)));
+    if (step != cache.step)
+    {
+        const float fs = (float)(unsigned)step;
+        cache.step     = step;
+        cache.lr       = t.lr * (sqrtf(1.f - powf(t.beta2, fs)) / (1.f - powf(t.beta1, fs)));
+    }
+    const float lr  = cache.lr;
     const float eff = fminf(fmaxf(lr / (sqrtf(v) + t.eps), t.lower_lr_bound), t.upper_lr_bound);
     const float dec = (1.f - t.relative_weight_decay * lr) * w - copysignf(t.absolute_weight_decay * lr, w);
     float nw        = dec - eff * m;
@@ -41,6 +54,7 @@ __global__ __launch_bounds__(256) void adam_kernel(const TripsAdamTensor* __rest
     __syncthreads();
     const int64_t base = ((int64_t)blockIdx.x - first_block) * kAdamPerBlock;
     const int64_t end  = min(base + (int64_t)kAdamPerBlock, t.n);
+    LrCache cache;
     const bool aligned = ((((uintptr_t)t.weights) | ((uintptr_t)t.gradients) | ((uintptr_t)t.first_moments) |
                            ((uintptr_t)t.second_moments) | ((uintptr_t)t.steps)) & 15) == 0;
     if (aligned)
@@ -54,10 +68,10 @@ __global__ __launch_bounds__(256) void adam_kernel(const TripsAdamTensor* __rest
             float4 m = *reinterpret_cast<float4*>(t.first_moments + i);
             float4 v = *reinterpret_cast<float4*>(t.second_moments + i);
             int4 s   = *reinterpret_cast<int4*>(t.steps + i);
-            adam_element(t, w.x, g.x, m.x, v.x, s.x);
-            adam_element(t, w.y, g.y, m.y, v.y, s.y);
-            adam_element(t, w.z, g.z, m.z, v.z, s.z);
-            adam_element(t, w.w, g.w, m.w, v.w, s.w);
+            adam_element(t, w.x, g.x, m.x, v.x, s.x, cache);
+            adam_element(t, w.y, g.y, m.y, v.y, s.y, cache);
+            adam_element(t, w.z, g.z, m.z, v.z, s.z, cache);
+            adam_element(t, w.w, g.w, m.w, v.w, s.w, cache);
             *reinterpret_cast<float4*>(t.weights + i)        = w;
             *reinterpret_cast<float4*>(t.first_moments + i)  = m;
             *reinterpret_cast<float4*>(t.second_moments + i) = v;
@@ -69,7 +83,7 @@ __global__ __launch_bounds__(256) void adam_kernel(const TripsAdamTensor* __rest
             int s   = t.steps[i];
             float g = t.gradients[i];
             if (g == 0.f) continue;
-            adam_element(t, w, g, m, v, s);
+            adam_element(t, w, g, m, v, s, cache);
             t.weights[i] = w, t.first_moments[i] = m, t.second_moments[i] = v, t.steps[i] = s;
         }
     }
@@ -81,7 +95,7 @@ __global__ __launch_bounds__(256) void adam_kernel(const TripsAdamTensor* __rest
             if (g == 0.f) continue;
             float w = t.weights[i], m = t.first_moments[i], v = t.second_moments[i];
             int s   = t.steps[i];
-            adam_element(t, w, g, m, v, s);
+            adam_element(t, w, g, m, v, s, cache);
             t.weights[i] = w, t.first_moments[i] = m, t.second_moments[i] = v, t.steps[i] = s;
         }
     }
@@ -115,14 +129,14 @@ struct FusedArgs
     int64_t lo, hi;
 };
 
-__device__ __forceinline__ void fused_element(const TripsAdamSegment& sg, float& w, float g, float& m, float& v, int& step)
+__device__ __forceinline__ void fused_element(const TripsAdamSegment& sg, float& w, float g, float& m, float& v, int& step, LrCache& cache)
 {
     TripsAdamTensor t;
     t.lr = sg.lr, t.beta1 = sg.beta1, t.beta2 = sg.beta2, t.eps = sg.eps;
     t.relative_weight_decay = sg.relative_weight_decay, t.absolute_weight_decay = sg.absolute_weight_decay;
     t.weight_clipping_magnitude = sg.weight_clipping_magnitude;
     t.lower_lr_bound = sg.lower_lr_bound, t.upper_lr_bound = sg.upper_lr_bound;
-    adam_element(t, w, g, m, v, step);
+    adam_element(t, w, g, m, v, step, cache);
 }
 
 __global__ __launch_bounds__(256) void fused_reduce_adam_kernel(const __grid_constant__ FusedArgs a, float* __restrict__ m_state,
@@ -137,6 +151,8 @@ __global__ __launch_bounds__(256) void fused_reduce_adam_kernel(const __grid_con
             if (i >= a.seg[s].offset) k = s;
         return k;
     };
+    LrCache cache;
+    int cache_seg = -1;
     for (int64_t q = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; q < n_vec; q += (int64_t)gridDim.x * blockDim.x)
     {
         const int64_t i = lo4 + 4 * q;
@@ -154,10 +170,15 @@ __global__ __launch_bounds__(256) void fused_reduce_adam_kernel(const __grid_con
 #pragma unroll
         for (int k = 0; k < 4; ++k) mm[k] = m_state[j + k], vv[k] = v_state[j + k], ss[k] = steps[j + k];
         const int s0 = segment_of(i), s3 = segment_of(i + 3);
-        fused_element(a.seg[s0], w.x, g.x, mm[0], vv[0], ss[0]);
-        fused_element(a.seg[s0 == s3 ? s0 : segment_of(i + 1)], w.y, g.y, mm[1], vv[1], ss[1]);
-        fused_element(a.seg[s0 == s3 ? s0 : segment_of(i + 2)], w.z, g.z, mm[2], vv[2], ss[2]);
-        fused_element(a.seg[s3], w.w, g.w, mm[3], vv[3], ss[3]);
+        if (s0 != s3 || s0 != cache_seg) cache.step = -1;  // the cached learning rate belongs to one segment
+        cache_seg = s3;
+        fused_element(a.seg[s0], w.x, g.x, mm[0], vv[0], ss[0], cache);
+        if (s0 != s3) cache.step = -1;
+        fused_element(a.seg[s0 == s3 ? s0 : segment_of(i + 1)], w.y, g.y, mm[1], vv[1], ss[1], cache);
+        if (s0 != s3) cache.step = -1;
+        fused_element(a.seg[s0 == s3 ? s0 : segment_of(i + 2)], w.z, g.z, mm[2], vv[2], ss[2], cache);
+        if (s0 != s3) cache.step = -1;
+        fused_element(a.seg[s3], w.w, g.w, mm[3], vv[3], ss[3], cache);
 #pragma unroll
         for (int k = 0; k < 4; ++k) m_state[j + k] = mm[k], v_state[j + k] = vv[k], steps[j + k] = ss[k];
         for (int r = 0; r < a.world; ++r) *reinterpret_cast<float4*>(a.param[r] + i) = w;
@@ -173,7 +194,8 @@ __global__ __launch_bounds__(256) void fused_reduce_adam_kernel(const __grid_con
         const int64_t j = i - a.lo;
         float w = a.param[a.rank][i], mm = m_state[j], vv = v_state[j];
         int ss = steps[j];
-        fused_element(a.seg[segment_of(i)], w, g, mm, vv, ss);
+        LrCache one;
+        fused_element(a.seg[segment_of(i)], w, g, mm, vv, ss, one);
         m_state[j] = mm, v_state[j] = vv, steps[j] = ss;
         for (int r = 0; r < a.world; ++r) a.param[r][i] = w;
     }

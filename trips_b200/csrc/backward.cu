@@ -68,8 +68,7 @@ __global__ __launch_bounds__(kBwdThreads, TRIPS_BWD_MIN_BLOCKS) void blend_backw
     constexpr int GS = egrad_stride(C);
     __shared__ float s_g[kBwdWarps][C][32];
     __shared__ float s_d[kBwdWarps][32 * kPad];   // G_j, then dA_j = G_j T_j, finally d_j
-    __shared__ uint2 s_rec[kBwdWarps][32 * kPad]; // the tile's records: (entry index, alpha_j bits)
-    __shared__ float s_w[kBwdWarps][32 * kPad];   // w_j = T_j * alpha_j
+    __shared__ uint2 s_rec[kBwdWarps][32 * kPad]; // the tile's records: (entry index, alpha_j bits; after phase 1: w_j = T_j * alpha_j)
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
     float bg[C];
@@ -78,7 +77,6 @@ __global__ __launch_bounds__(kBwdThreads, TRIPS_BWD_MIN_BLOCKS) void blend_backw
 
     float* my_d          = s_d[warp] + lane * kPad;
     uint2* my_rec        = s_rec[warp] + lane * kPad;
-    float* my_w          = s_w[warp] + lane * kPad;
 
     double acc_bg[C];
 #pragma unroll
@@ -207,15 +205,21 @@ __global__ __launch_bounds__(kBwdThreads, TRIPS_BWD_MIN_BLOCKS) void blend_backw
         }
         __syncwarp();
 
-        // ---- phase 1 (lane = pixel), forward: T_j, dA_j = G_j T_j, w_j = T_j a_j ----
+        // ---- phase 1 (lane = pixel), forward: T_j, dA_j = G_j T_j, w_j = T_j a_j.  The alphas move to registers (the
+        //      reverse sweep needs them again) and w_j takes their place in shared memory. ----
         float run = 1.f;
-        for (int j = 0; j < m_max; ++j)
+        float al[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
         {
+            al[j] = 0.f;
+            if (j >= m_max) continue;  // uniform
             if (j < m)
             {
                 const float a = __uint_as_float(my_rec[j].y);
+                al[j]         = a;
                 my_d[j]       = my_d[j] * run;
-                my_w[j]       = run * a;
+                my_rec[j].y   = __float_as_uint(run * a);
                 run           = (1.f - a) * run;
             }
         }
@@ -231,11 +235,12 @@ __global__ __launch_bounds__(kBwdThreads, TRIPS_BWD_MIN_BLOCKS) void blend_backw
             }
         }
         // ---- phase 1, reverse: d_j = dA_j - R_j / (1 - a_j + eps), R_j = W_bg + sum_{i>j} W_i, W_i = dA_i a_i ----
-        for (int j = m_max - 1; j >= 0; --j)
+#pragma unroll
+        for (int j = 15; j >= 0; --j)
         {
             if (j < m)
             {
-                const float a   = __uint_as_float(my_rec[j].y);
+                const float a   = al[j];
                 const float dA  = my_d[j];
                 const float dem = 1.f / (1.f - a + 1e-9f);
                 my_d[j]         = dA - R * dem;
@@ -280,7 +285,7 @@ __global__ __launch_bounds__(kBwdThreads, TRIPS_BWD_MIN_BLOCKS) void blend_backw
                 if (!valid) continue;
                 float* eg      = egrad + (size_t)eidx * GS;
                 const float ga = s_d[warp][seg * kPad + j];
-                const float w  = s_w[warp][seg * kPad + j];
+                const float w  = __uint_as_float(s_rec[warp][seg * kPad + j].y);
                 // bilinear weight of this pixel and its Jacobian at uv (compute_blending_fac, PointBlending.h:216-257)
                 const float fac = __int_as_float((127 - layer_s) << 23);
                 const float ux = e0v.x * fac, uy = e0v.y * fac;
