@@ -129,20 +129,22 @@ __global__ __launch_bounds__(kBwdThreads, TRIPS_BWD_MIN_BLOCKS) void blend_backw
         }
         const int rel     = incl - m;
         const int n_entry = __shfl_sync(kFull, incl, 31);
-        // the tile's records (entry index, alpha) -> shared memory: every lane copies its pixel's row with
-        // independent 16-byte loads, so the whole tile costs one memory latency
-        if (p >= 0)
-        {
-            const uint4* src = reinterpret_cast<const uint4*>(fb.records + (bP + p) * 16);
+        // the tile's records (entry index, alpha) -> shared memory.  The 16 records of a pixel are one 128-byte line: eight
+        // lanes read the eight 16-byte pieces of one pixel's line, so a load instruction touches 4 lines instead of 32
+        // (the load/store unit handles one line per cycle); pieces beyond the pixel's record count are not read.
 #pragma unroll
-            for (int k = 0; k < 8; ++k)
+        for (int it = 0; it < 8; ++it)
+        {
+            const int q   = it * 4 + (lane >> 3);  // pixel of the tile
+            const int k   = lane & 7;              // piece: records 2k, 2k+1
+            const int m_q = __shfl_sync(kFull, m, q);
+            const int p_q = __shfl_sync(kFull, p, q);
+            if (2 * k < m_q)
             {
-                if (2 * k < m)
-                {
-                    const uint4 v        = src[k];
-                    my_rec[2 * k]     = make_uint2(v.x < n_ent ? v.x : 0u, v.x < n_ent ? v.y : 0u);  // a corrupted record contributes nothing
-                    my_rec[2 * k + 1] = make_uint2(v.z < n_ent ? v.z : 0u, v.z < n_ent ? v.w : 0u);
-                }
+                const uint4 v = *(reinterpret_cast<const uint4*>(fb.records + (bP + p_q) * 16) + k);
+                uint2* dst    = s_rec[warp] + q * kPad + 2 * k;
+                dst[0]        = make_uint2(v.x < n_ent ? v.x : 0u, v.x < n_ent ? v.y : 0u);  // a corrupted record contributes nothing
+                dst[1]        = make_uint2(v.z < n_ent ? v.z : 0u, v.z < n_ent ? v.w : 0u);
             }
         }
         __syncwarp();
@@ -254,19 +256,17 @@ __global__ __launch_bounds__(kBwdThreads, TRIPS_BWD_MIN_BLOCKS) void blend_backw
             int seg_n, j_n;
             locate(lane, seg_n, j_n);
             float4 e0_n = make_float4(0.f, 0.f, 0.f, 0.f);
-            float conf_n = 0.f;
             unsigned eidx_n = 0;
             if (lane < n_entry)
             {
                 eidx_n          = s_rec[warp][seg_n * kPad + j_n].x;
-                e0_n            = head[2 * (size_t)eidx_n];
-                conf_n          = head[2 * (size_t)eidx_n + 1].y;
+                e0_n            = head[2 * (size_t)eidx_n];  // u v ps conf
             }
             for (int e0 = 0; e0 < n_entry; e0 += 32)
             {
                 const int seg = seg_n, j = j_n;
-                const float4 e0v = e0_n;  // u v ps z
-                const float conf = conf_n;
+                const float4 e0v = e0_n;  // u v ps conf
+                const float conf = e0v.w;
                 const unsigned eidx = eidx_n;
                 const bool valid = e0 + lane < n_entry;
                 if (e0 + 32 < n_entry)
@@ -276,7 +276,6 @@ __global__ __launch_bounds__(kBwdThreads, TRIPS_BWD_MIN_BLOCKS) void blend_backw
                     {
                         eidx_n          = s_rec[warp][seg_n * kPad + j_n].x;
                         e0_n            = head[2 * (size_t)eidx_n];
-                        conf_n          = head[2 * (size_t)eidx_n + 1].y;
                     }
                 }
                 const int layer_s = __shfl_sync(kFull, layer, seg);
@@ -377,7 +376,7 @@ __global__ __launch_bounds__(256) void entry_grad_finish_kernel(FwdBuffers fb, B
     {
         const float* eg = egrad + i * GS;
         const float4 s4 = *reinterpret_cast<const float4*>(eg);      // sum J0 gbs, sum J1 gbs, sum bf conf lf' ga, sum bf lf ga
-        const float4 e1 = head[2 * i + 1];  // pid conf raw nl
+        const float4 e1 = head[2 * i + 1];  // pid z raw nl|rank
         const float4 e2 = *reinterpret_cast<const float4*>(tail + i * tail_stride(C));  // x y z tex
         const int pid   = __float_as_int(e1.x);
         // row of the point: by spatial rank when the forward pass stored one (rows of a screen bin then share L2 lines)

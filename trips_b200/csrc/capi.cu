@@ -655,7 +655,7 @@ int trips_debug_points(TripsContext* ctx, int view, float* depth, int32_t* nlaye
         memcpy(&nl, en + 7, 4);
         nl &= (1 << kRankShift) - 1;  // the spatial rank shares the word
         if (pid < 0 || (size_t)pid >= N) continue;
-        if (depth) depth[pid] = en[3];
+        if (depth) depth[pid] = en[5];
         if (nlayers) nlayers[pid] = nl;
         if (record)
         {

@@ -71,8 +71,8 @@ struct DevStats
 // order so that fragments of neighbouring pixels read neighbouring entries.  The fields live in two arrays, split by
 // the stage that reads them, so that a stage's gathers touch fewer bytes it does not use (DRAM is read in 64-byte
 // pieces), while the binning pass still writes whole 32-byte sectors:
-//   head [2 x float4]     u, v (layer-0 image position), size in pixels, view-space depth |
-//                         point id (bits), confidence, raw point size, number of layers written (bits 0-3) and
+//   head [2 x float4]     u, v (layer-0 image position), size in pixels, confidence (all the backward pass reads) |
+//                         point id (bits), view-space depth, raw point size, number of layers written (bits 0-3) and
 //                         spatial rank of the point (bits 4-31, see rank.cu; 0 when ranks are not in use)
 //   tail [1 + C4/4 float4] world position x, y, z, texture index (bits) | descriptor row (C floats, padded to 4)
 __host__ __device__ constexpr int tail_stride(int C) { return 4 + ((C + 3) & ~3); }

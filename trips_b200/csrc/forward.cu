@@ -275,9 +275,9 @@ __global__ __launch_bounds__(kBinThreads) void bin_scatter_kernel(ScenePtrs sc, 
         else
             atomicOr(&fb.stats->status, TRIPS_DEV_BAD_TEXTURE_INDEX);  // the point is drawn with alpha 0
         const float4 p = __ldg(sc.position + i);
-        head[2 * (size_t)slot]     = make_float4(r.u, r.v, r.ps, r.z);
+        head[2 * (size_t)slot]     = make_float4(r.u, r.v, r.ps, conf);
         const uint32_t rk          = fb.point_rank ? __ldg(fb.point_rank + i) : 0u;
-        head[2 * (size_t)slot + 1] = make_float4(__int_as_float(i), conf, __ldg(sc.point_size + i), __uint_as_float((uint32_t)layer | (rk << kRankShift)));
+        head[2 * (size_t)slot + 1] = make_float4(__int_as_float(i), r.z, __ldg(sc.point_size + i), __uint_as_float((uint32_t)layer | (rk << kRankShift)));
         float4* e = reinterpret_cast<float4*>(tail + (size_t)slot * TS);
         e[0]      = make_float4(p.x, p.y, p.z, __int_as_float(tex_ok ? r.tex : -1));
         float row_t[(C + 3) & ~3];
@@ -575,8 +575,8 @@ __device__ __forceinline__ void for_each_footprint(const float4* __restrict__ he
     float4 e0n = make_float4(0.f, 0.f, 0.f, 0.f), e1n = e0n;
     if (base + lane < hi)
     {
-        e0n = head[2 * (size_t)(base + lane)];      // u v ps z
-        e1n = head[2 * (size_t)(base + lane) + 1];  // pid conf raw nl
+        e0n = head[2 * (size_t)(base + lane)];      // u v ps conf
+        e1n = head[2 * (size_t)(base + lane) + 1];  // pid z raw nl|rank
     }
     for (; base < hi; base += kWinThreads)
     {
@@ -719,8 +719,8 @@ __global__ __launch_bounds__(kWinThreads, TRIPS_WIN_MIN_BLOCKS) void window_kern
                 for_each_footprint<true>(head, lo, hi, s_queue[threadIdx.x >> 5],
                                          [&](const float4& e0, const float4& e1, float x, float y, int layer, uint32_t ei) {
                                              // x, y equal (u, v) * 2^-layer exactly (power-of-two scaling)
-                                             const float conf   = e1.y;
-                                             const uint32_t pid = __float_as_uint(e1.x), zb = __float_as_uint(e0.w);
+                                             const float conf   = e0.w;
+                                             const uint32_t pid = __float_as_uint(e1.x), zb = __float_as_uint(e1.y);
                                              const int px = __float2int_rd(x), py = __float2int_rd(y);
                                              const int ww = win_w(layer);
                                              const int li = win_off(layer) + (py - w.y0(layer)) * ww + (px - w.x0(layer));
