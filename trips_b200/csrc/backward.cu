@@ -281,10 +281,9 @@ __global__ __launch_bounds__(kBwdThreads, TRIPS_BWD_MIN_BLOCKS) void blend_backw
                 const int layer_s = __shfl_sync(kFull, layer, seg);
                 const int gx_s    = __shfl_sync(kFull, gx, seg);
                 const int gy_s    = __shfl_sync(kFull, gy, seg);
-                if (!valid) continue;
-                float* eg      = egrad + (size_t)eidx * GS;
-                const float ga = s_d[warp][seg * kPad + j];
-                const float w  = __uint_as_float(s_rec[warp][seg * kPad + j].y);
+                // (lanes without a fragment run through with zero weights: the exchange below needs all lanes)
+                const float ga = valid ? s_d[warp][seg * kPad + j] : 0.f;
+                const float w  = valid ? __uint_as_float(s_rec[warp][seg * kPad + j].y) : 0.f;
                 // bilinear weight of this pixel and its Jacobian at uv (compute_blending_fac, PointBlending.h:216-257)
                 const float fac = __int_as_float((127 - layer_s) << 23);
                 const float ux = e0v.x * fac, uy = e0v.y * fac;
@@ -300,11 +299,34 @@ __global__ __launch_bounds__(kBwdThreads, TRIPS_BWD_MIN_BLOCKS) void blend_backw
                 const float gbs = conf * lf * ga;  // dLoss / d(bilinear weight) (RenderBackward.cu:385)
                 // image-space sums of the entry: the chain to position / size / pose is linear in them and is applied
                 // once per entry by entry_grad_finish_kernel
-                atomicAdd(reinterpret_cast<float4*>(eg), make_float4(J0 * gbs, J1 * gbs, bf * conf * lf_grad * ga, bf * lf * ga));
-                {
-                    float gt[(C + 3) & ~3];
+                const float4 h0 = make_float4(J0 * gbs, J1 * gbs, bf * conf * lf_grad * ga, bf * lf * ga);
+                float gt[(C + 3) & ~3];
 #pragma unroll
-                    for (int c = 0; c < ((C + 3) & ~3); ++c) gt[c] = (c < C) ? w * s_g[warp][c < C ? c : 0][seg] : 0.f;
+                for (int c = 0; c < ((C + 3) & ~3); ++c) gt[c] = (c < C) ? w * s_g[warp][c < C ? c : 0][seg] : 0.f;
+                if constexpr (((C + 3) & ~3) == 4)
+                {
+                    // The row of an entry is 32 bytes: two 16-byte atomics.  Lanes work in pairs: the even lane adds the
+                    // first half and the odd lane the second half of the SAME row (first the even lane's fragment, then
+                    // the odd lane's), so an atomic instruction touches 16 rows instead of 32.  The load/store unit
+                    // handles one 128-byte line per cycle, and that, not DRAM or the L2 atomic rate, bounds this kernel.
+                    const bool odd       = lane & 1;
+                    const unsigned mine  = valid ? eidx : 0xffffffffu;
+                    const unsigned other = __shfl_xor_sync(kFull, mine, 1);
+                    float4 x;  // even lane receives the partner's first half, odd lane the partner's second half
+                    x.x = __shfl_xor_sync(kFull, odd ? h0.x : gt[0], 1);
+                    x.y = __shfl_xor_sync(kFull, odd ? h0.y : gt[1], 1);
+                    x.z = __shfl_xor_sync(kFull, odd ? h0.z : gt[2], 1);
+                    x.w = __shfl_xor_sync(kFull, odd ? h0.w : gt[3], 1);
+                    const unsigned row_a = odd ? other : mine;  // the even lane's fragment
+                    const unsigned row_b = odd ? mine : other;  // the odd lane's fragment
+                    const float4 own     = odd ? make_float4(gt[0], gt[1], gt[2], gt[3]) : h0;
+                    if (row_a != 0xffffffffu) atomicAdd(reinterpret_cast<float4*>(egrad + (size_t)row_a * GS + (odd ? 4 : 0)), odd ? x : own);
+                    if (row_b != 0xffffffffu) atomicAdd(reinterpret_cast<float4*>(egrad + (size_t)row_b * GS + (odd ? 4 : 0)), odd ? own : x);
+                }
+                else if (valid)
+                {
+                    float* eg = egrad + (size_t)eidx * GS;
+                    atomicAdd(reinterpret_cast<float4*>(eg), h0);
                     atomic_add_row<((C + 3) & ~3)>(eg + 4, gt);
                 }
             }
