@@ -33,7 +33,7 @@ RECORD_BYTES = 8  # bytes per kept fragment saved for backward (point id + alpha
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c3", choices=["c3", "c2", "c1", "tiny"])
@@ -244,7 +244,9 @@ def run_ours(args, rank, world, local_rank):
     if rank == 0:
         tb.build()
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        import datetime
+        # a rank that never arrives ends the others' next collective with an error after this time instead of a hang
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=300))
         dist.barrier()
 
     s, my_views, vpg = make_workload(args.workload, world, rank, args.points, args.views_per_gpu)
@@ -324,13 +326,19 @@ def run_ours(args, rank, world, local_rank):
     if sampler:
         sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
     barrier()
     e0.record()
-    for _ in range(args.steps):
+    marks[0].record()
+    for i in range(args.steps):
         step_resident()
+        marks[i + 1].record()
     e1.record()
     barrier()
     ms_total = e0.elapsed_time(e1)
+    per_step = sorted(marks[i].elapsed_time(marks[i + 1]) for i in range(args.steps))
+    pct = lambda q: per_step[min(len(per_step) - 1, int(round(q * (len(per_step) - 1))))]  # noqa: E731
+    step_stats = {"median": pct(0.5), "p10": pct(0.1), "p90": pct(0.9)}
     clocks = sampler.stop() if sampler else None
     st = cache.stage_times(reset=True)
     cache.enable_stage_timers(False)
@@ -446,13 +454,14 @@ def run_ours(args, rank, world, local_rank):
 
     out = {
         "metric": METRIC, "value": value, "unit": "views/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
-        "ms_per_step": ms_step, "ms_per_view": ms_step / B, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "ms_per_step": ms_step, "ms_per_view": ms_step / B, "step_ms": step_stats, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
         "config": {"workload": s.name, "points": N, "views_per_gpu": B, "global_views_per_step": B * world, "width": s.width,
                    "height": s.height, "layers": L, "k_keep": s.k_keep, "channels": C, "parallelism": f"view-dp{world}", "collective": collective,
                    "l2_policy": "inputs (>2 GB touched per step) larger than the 126 MB L2; no explicit flush",
                    "fragments_per_step": int(F), "kept_fragments_per_step": int(Kf), "visible_points_per_step": int(stats["visible_points"]),
-                   "max_list_length": int(stats["max_list_length"]), "fragments_per_s": F * world / (ms_step * 1e-3)},
+                   "max_list_length": int(stats["max_list_length"]), "fragments_per_s": F * world / (ms_step * 1e-3),
+                   "backward_atomic_floats_per_s": (C + 5) * Kf / (per_stage["blend_backward"]["ms_per_launch"] * 1e-3) if "blend_backward" in per_stage else None},
         "e2e": e2e, "gpu_launches": int(launches_total), "roofline": roofline, "cpu_baseline": cpu, "clocks": clocks,
     }
     emit(out)

@@ -115,3 +115,54 @@ def test_two_rank_step_equals_single_process(oracle_lib, tmp_path):
                  "point_size": s.point_size.reshape(-1, 1), "background": s.background}[k]
         assert np.array_equal(r0[k][~seen], start[~seen]), f"{k}: elements unseen on every rank must not move"
         assert (r0[k][seen] != start[seen]).mean() > 0.99
+
+
+def test_slice_bounds_cover_the_flat_vector_once():
+    from trips_b200.dist import slice_bounds
+    for numel in (0, 3, 4, 1001, 60_000_004):
+        for world in (1, 2, 3, 8, 16):
+            b = [slice_bounds(numel, world, r) for r in range(world)]
+            assert b[0][0] == 0 and b[-1][1] == numel
+            for (lo, hi), (lo2, _) in zip(b, b[1:]):
+                assert lo <= hi == lo2 and (lo % 4 == 0 or lo == hi)  # contiguous; non-empty slices start 16-byte aligned
+
+
+def _failing_worker(rank, world, port, out_dir):
+    """Rank 1 leaves before the gradient sum (between steps, nothing in flight); rank 0 must get an error, not a hang."""
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    import datetime
+
+    import torch
+    import torch.distributed as dist
+    from trips_b200.dist import allreduce_sum
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=5))
+    t = torch.ones(1000)
+    allreduce_sum(t)  # step 0: everybody is there
+    assert float(t[0]) == world
+    if rank == 1:
+        os._exit(0)  # dies without saying goodbye
+    outcome = "no error"
+    try:
+        allreduce_sum(t)  # step 1: the peer is gone
+    except Exception as e:  # noqa: BLE001 - any error type is fine, a hang is not
+        outcome = type(e).__name__
+    with open(os.path.join(out_dir, "rank0.txt"), "w") as f:
+        f.write(outcome)
+    os._exit(0)  # the process group cannot be shut down cleanly without the peer
+
+
+@pytest.mark.timeout(120)
+def test_lost_rank_surfaces_as_an_error_on_the_survivor(tmp_path):
+    """Failure detection without touching a GPU: the collective of the surviving rank ends with an exception within
+    the process-group timeout (the GPU path uses the same host-side mechanism: NCCL's timeout set at init)."""
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    port = _free_port()
+    procs = [ctx.Process(target=_failing_worker, args=(r, 2, port, str(tmp_path))) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(90)
+        assert not p.is_alive(), "a rank hung instead of failing"
+    assert (tmp_path / "rank0.txt").read_text() != "no error"

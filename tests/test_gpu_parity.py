@@ -264,3 +264,66 @@ def test_error_paths(cuda_lib):
     with pytest.raises(TripsError) as e:  # backward after an inference forward
         BlendPointCloudBackward(None, info, [torch.zeros_like(o) for o in outs])
     assert e.value.status == -5
+
+
+def test_config2_full_size_properties(cuda_lib):
+    """Config 2 in full (2 M points, 4 views 1280x720, 6 layers, K = 16), where the CPU oracle would take minutes:
+    size-independent properties instead of element-wise parity.  (1) the counters agree with one another; (2) every
+    kept list is sorted by (depth, point id) and has min(length, K) elements; (3) the forward pass is deterministic bit
+    for bit although list slots are handed out by atomics; (4) the backward pass is linear in the incoming gradient;
+    (5) a zero gradient gives zero gradients."""
+    import torch
+    from trips_b200 import scenes
+    from trips_b200.modules import NeuralScene, images_for
+    from trips_b200.renderer import NeuralRenderInfo, PointRendererCache, RenderParams
+    from trips_b200.scenes import layer_sizes
+    s = scenes.config2()
+    dev = torch.device("cuda")
+    ns = NeuralScene.from_synthetic(s, device=dev)
+    pc, tex = ns.point_cloud_cuda, ns.texture
+    cache = PointRendererCache(dev)
+    views = list(range(s.n_views))
+    info = NeuralRenderInfo(scene=ns, images=images_for(s, views), params=RenderParams(num_texture_channels=s.channels, k_keep=s.k_keep),
+                            num_layers=s.num_layers, train=True, cache=cache)
+    args = (tex.texture, tex.background_color, pc.t_position, ns.intrinsics.intrinsics, tex.confidence_value_of_point, pc.t_point_size,
+            pc.t_index, ns.poses.poses_se3)
+    outs = [o.clone() for o in cache.forward(info, *args)]
+    assert cache.last_status() == 0
+    st = cache.stats()
+    B, K = len(views), s.k_keep
+    P = sum(w * h for w, h in layer_sizes(s.width, s.height, s.num_layers))
+    # (1), (2) on every view: list lengths, kept counts, sortedness
+    total_f = total_k = 0
+    for b in range(B):
+        counts, offsets, _ = cache.debug_lists(b, P)
+        nrec, rec_pid, rec_alpha = cache.debug_records(b, P)
+        depth, nl, _ = cache.debug_points(b, s.n_points)
+        total_f += int(counts.sum())
+        total_k += int(np.minimum(counts, K).sum())
+        assert int(nl.sum()) * 4 == int(counts.sum()), "every (point, layer) pair writes exactly four fragments"
+        assert np.all(nrec <= np.minimum(counts, K))
+        idx = np.arange(16)[None, :] < nrec[:, None]
+        d = np.where(idx, depth[np.clip(rec_pid, 0, s.n_points - 1)], np.inf)
+        assert np.all(d[:, 1:] >= d[:, :-1]), "records must be in depth order"
+        ties = idx[:, 1:] & (d[:, 1:] == d[:, :-1])
+        assert np.all(rec_pid[:, 1:][ties] > rec_pid[:, :-1][ties]), "equal depths are ordered by point id"
+        assert np.all((rec_alpha[idx] >= 0) & (rec_alpha[idx] <= 1))
+    assert st["fragments"] == total_f and st["kept_fragments"] == total_k
+    # (3) determinism
+    outs2 = cache.forward(info, *args)
+    for a, c in zip(outs, outs2):
+        assert torch.equal(a, c)
+    # (4), (5) linearity of the backward pass
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(5)
+    g1 = [torch.randn(o.shape, device=dev, generator=gen) for o in outs]
+    names = ("texture", "background", "points", "pose", "intrinsics", "confidence", "point_size")
+    as_dict = lambda t: {k: v.clone() for k, v in zip(names, t) if v is not None}  # noqa: E731
+    r1 = as_dict(cache.backward(g1, *args))
+    r2 = as_dict(cache.backward([2.0 * g for g in g1], *args))
+    r0 = as_dict(cache.backward([torch.zeros_like(g) for g in g1], *args))
+    for k, v in r1.items():
+        scale = float(v.abs().max())
+        assert scale > 0, k
+        assert float((r2[k] - 2.0 * v).abs().max()) <= 1e-4 * 2.0 * scale, f"{k}: backward is not linear"
+        assert float(r0[k].abs().max()) == 0.0, f"{k}: zero in, zero out"
