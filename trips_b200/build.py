@@ -74,5 +74,36 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
+SHIM = os.path.join(HERE, "libtrips_b200_torch.so")
+SHIM_SRC = os.path.join(CSRC, "torch_shim.cpp")
+
+
+def build_torch_shim(force: bool = False) -> str:
+    """Compile the libtorch host side (csrc/torch_shim.cpp: NeuralRenderInfo, PointRender, BlendPointCloud on top of
+    the C ABI) with the host compiler and link it against libtrips_b200.so and libtorch."""
+    build()
+    deps = [SHIM_SRC, os.path.join(HERE, "..", "include", "trips_b200.h"), __file__]
+    if not force and os.path.exists(SHIM) and all(os.path.getmtime(d) <= os.path.getmtime(SHIM) for d in deps):
+        return SHIM
+    import torch
+    from torch.utils import cpp_extension as ce
+    cxx = "/usr/bin/g++" if os.path.exists("/usr/bin/g++") else (shutil.which("g++") or "g++")
+    cmd = [cxx, "-O2", "-std=c++17", "-fPIC", "-shared", f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}",
+           "-I", os.path.join(HERE, "..", "include")]
+    for inc in ce.include_paths("cuda"):
+        cmd += ["-isystem", inc]
+    cmd += [SHIM_SRC, "-o", SHIM, "-L", HERE, "-ltrips_b200", "-Wl,-rpath,$ORIGIN"]
+    for lp in ce.library_paths("cuda"):
+        cmd += ["-L", lp, f"-Wl,-rpath,{lp}"]
+    cmd += ["-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch_cuda", "-ltorch", "-lcudart"]
+    r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if r.returncode != 0:
+        sys.stderr.write(r.stdout[-4000:])
+        raise RuntimeError("build of libtrips_b200_torch.so failed")
+    return SHIM
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    if "--shim" in sys.argv:
+        print(build_torch_shim(force="--force" in sys.argv))
