@@ -339,8 +339,8 @@ int trips_forward(TripsContext* ctx, const TripsScene* scene, const TripsView* v
 
     CU_CHECK(ctx, ensure(ctx->views, sizeof(TripsView) * B));
     CU_CHECK(ctx, ensure(ctx->cams, sizeof(CamConst) * B));
-    CU_CHECK(ctx, ensure(ctx->bin_count, sizeof(uint32_t) * (size_t)g.n_bins * B * bin_blocks_per_view(B, ctx->sm_count)));
-    CU_CHECK(ctx, ensure(ctx->bin_base, sizeof(uint32_t) * (size_t)g.n_bins * B * bin_blocks_per_view(B, ctx->sm_count)));
+    CU_CHECK(ctx, ensure(ctx->bin_count, sizeof(uint32_t) * (size_t)g.n_bins * 32 * B));  // one counter per (bin, 8x4 tile of the bin)
+    CU_CHECK(ctx, ensure(ctx->bin_base, sizeof(uint32_t) * (size_t)g.n_bins * 32 * B));
     CU_CHECK(ctx, ensure(ctx->view_total, sizeof(uint32_t) * B));
     CU_CHECK(ctx, ensure(ctx->bin_cursor, sizeof(uint32_t) * (size_t)g.n_bins * B));
     CU_CHECK(ctx, ensure(ctx->entry_base, sizeof(unsigned long long) * (B + 1)));

@@ -83,8 +83,8 @@ __host__ __device__ constexpr int egrad_stride(int C) { return 4 + ((C + 3) & ~3
 // Everything the forward kernels need besides the scene (all device pointers into context scratch).
 struct FwdBuffers
 {
-    uint32_t* bin_count;              // [B,blocks,n_bins] visible points per (binning block, screen bin)
-    uint32_t* bin_base;               // [B,blocks,n_bins] first entry (within the view) of every (block, bin) pair
+    uint32_t* bin_count;              // [B,n_bins,32] visible points per (screen bin, 8x4 tile of the bin)
+    uint32_t* bin_base;               // [B,n_bins,32] next free entry (within the view) of every (bin, tile) group
     uint32_t* view_total;             // [B] visible points per view
     uint32_t* bin_cursor;             // [B,n_bins] first entry of every bin within the view
     unsigned long long* entry_base;   // [B+1] first entry of each view

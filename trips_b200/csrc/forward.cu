@@ -138,34 +138,41 @@ __device__ __forceinline__ void block_chunk(int N, int& first, int& last)
     last            = min(N, first + chunk);
 }
 
+// Sort key of a visible point: its 32x32 screen bin, then its 8x4 pixel tile inside the bin.  Entries of a tile are
+// contiguous, so the fragments a tile kernel works on refer to a short range of entries and gradient rows: the 32
+// gathers (or atomics) of a warp instruction touch a handful of 128-byte lines instead of 32 different ones.
+constexpr int kSubShift = 5;  // 32 tiles (4 x 8) per bin
+__device__ __forceinline__ int bin_key(const Geom& g, float u, float v)
+{
+    const int px = __float2int_rd(u), py = __float2int_rd(v);
+    const int bin = (py >> kBinShift) * g.bins_x + (px >> kBinShift);
+    return (bin << kSubShift) | (((py >> 2) & 7) << 2) | ((px >> 3) & 3);
+}
+
 __global__ __launch_bounds__(kBinThreads) void bin_count_kernel(ScenePtrs sc, const CamConst* __restrict__ cams,
                                                                 const __grid_constant__ Geom g, TripsRenderParams pr, FwdBuffers fb)
 {
-    extern __shared__ uint32_t s_hist[];
     __shared__ CamConst cam;
     const int b = blockIdx.y;
     if (threadIdx.x < sizeof(CamConst) / 4) ((int*)&cam)[threadIdx.x] = ((const int*)&cams[b])[threadIdx.x];
-    for (int i = threadIdx.x; i < g.n_bins; i += blockDim.x) s_hist[i] = 0;
     __syncthreads();
     const size_t bN = (size_t)b * sc.N;
     const float fxc = cam.fx * cam.cfx;
+    uint32_t* hist  = fb.bin_count + ((size_t)b * g.n_bins << kSubShift);
     int first, last;
     block_chunk(sc.N, first, last);
     for (int i = first + threadIdx.x; i < last; i += blockDim.x)
     {
         const Projected r = project_visible(sc, cam, g, pr, bN, i, fxc);
-        if (r.ok) atomicAdd(s_hist + (__float2int_rd(r.v) >> kBinShift) * g.bins_x + (__float2int_rd(r.u) >> kBinShift), 1u);
+        if (r.ok) atomicAdd(hist + bin_key(g, r.u, r.v), 1u);
     }
-    __syncthreads();
-    uint32_t* row = fb.bin_count + ((size_t)b * gridDim.x + blockIdx.x) * g.n_bins;
-    for (int i = threadIdx.x; i < g.n_bins; i += blockDim.x) row[i] = s_hist[i];
 }
 
 // one block per view: rows [n_blocks, n_bins] of per-block counts -> first entry (within the view) of every
 // (block, bin) pair, ordered by bin first and block second; view_total[b] = visible points of the view
 __global__ __launch_bounds__(1024) void bin_scan_kernel(const uint32_t* __restrict__ rows_in, uint32_t* __restrict__ rows_out,
                                                         uint32_t* __restrict__ bin_first, int n_bins, int n_blocks,
-                                                        uint32_t* __restrict__ view_total)
+                                                        uint32_t* __restrict__ view_total, int first_shift)
 {
     __shared__ uint32_t sm[32];
     __shared__ uint32_t carry_s;
@@ -173,7 +180,7 @@ __global__ __launch_bounds__(1024) void bin_scan_kernel(const uint32_t* __restri
     const int b    = blockIdx.x;
     const uint32_t* r = rows_in + (size_t)b * n_blocks * n_bins;
     uint32_t* w       = rows_out + (size_t)b * n_blocks * n_bins;
-    uint32_t* o       = bin_first + (size_t)b * n_bins;
+    uint32_t* o       = bin_first + (size_t)b * (n_bins >> first_shift);  // first entry of every group of 2^first_shift keys
     if (threadIdx.x == 0) carry_s = 0;
     __syncthreads();
     for (int s = 0; s < n_bins; s += 1024)
@@ -205,7 +212,7 @@ __global__ __launch_bounds__(1024) void bin_scan_kernel(const uint32_t* __restri
         if (i < n_bins)
         {
             uint32_t run = carry + woff + inc - v;  // first entry of bin i
-            o[i]         = run;
+            if ((i & ((1 << first_shift) - 1)) == 0) o[i >> first_shift] = run;
             for (int k = 0; k < n_blocks; ++k)
             {
                 w[(size_t)k * n_bins + i] = run;
@@ -238,12 +245,10 @@ __global__ __launch_bounds__(kBinThreads) void bin_scatter_kernel(ScenePtrs sc, 
                                                                   const __grid_constant__ Geom g, TripsRenderParams pr, FwdBuffers fb)
 {
     constexpr int TS = tail_stride(C);
-    extern __shared__ uint32_t s_cursor[];
     __shared__ CamConst cam;
     const int b = blockIdx.y;
     if (threadIdx.x < sizeof(CamConst) / 4) ((int*)&cam)[threadIdx.x] = ((const int*)&cams[b])[threadIdx.x];
-    const uint32_t* row = fb.bin_base + ((size_t)b * gridDim.x + blockIdx.x) * g.n_bins;
-    for (int i = threadIdx.x; i < g.n_bins; i += blockDim.x) s_cursor[i] = row[i];
+    uint32_t* cursor = fb.bin_base + ((size_t)b * g.n_bins << kSubShift);  // next free entry of every (bin, tile) group
     __syncthreads();
     const size_t bN  = (size_t)b * sc.N;
     const float fxc  = cam.fx * cam.cfx;
@@ -255,8 +260,7 @@ __global__ __launch_bounds__(kBinThreads) void bin_scatter_kernel(ScenePtrs sc, 
     {
         const Projected r = project_visible(sc, cam, g, pr, bN, i, fxc);
         if (!r.ok) continue;
-        const int bin       = (__float2int_rd(r.v) >> kBinShift) * g.bins_x + (__float2int_rd(r.u) >> kBinShift);
-        const uint32_t slot = atomicAdd(s_cursor + bin, 1u);
+        const uint32_t slot = atomicAdd(cursor + bin_key(g, r.u, r.v), 1u);
         // layers 0..hi, stopping where the 2x2 footprint leaves the layer (RenderForward.cu:342-363)
         int hi = 0;
         if (r.ps > 1.f) hi = min(tm_ceil_log2(r.ps), g.L - 1);
@@ -295,15 +299,12 @@ cudaError_t launch_bin_points(const ScenePtrs& sc, const CamConst* cams, const G
                               const FwdBuffers& fb, int sm_count, cudaStream_t st)
 {
     const int nb       = bin_blocks_per_view(B, sm_count);
-    const size_t smem  = sizeof(uint32_t) * (size_t)g.n_bins;
-    if (sc.N > 0)
-        bin_count_kernel<<<dim3(nb, B), kBinThreads, smem, st>>>(sc, cams, g, pr, fb);
-    else
-    {
-        cudaError_t e = cudaMemsetAsync(fb.bin_count, 0, sizeof(uint32_t) * (size_t)B * nb * g.n_bins, st);
-        if (e != cudaSuccess) return e;
-    }
-    bin_scan_kernel<<<B, 1024, 0, st>>>(fb.bin_count, fb.bin_base, fb.bin_cursor, g.n_bins, nb, fb.view_total);
+    const size_t smem  = 0;
+    const int n_keys   = g.n_bins << kSubShift;
+    cudaError_t e      = cudaMemsetAsync(fb.bin_count, 0, sizeof(uint32_t) * (size_t)B * n_keys, st);
+    if (e != cudaSuccess) return e;
+    if (sc.N > 0) bin_count_kernel<<<dim3(nb, B), kBinThreads, 0, st>>>(sc, cams, g, pr, fb);
+    bin_scan_kernel<<<B, 1024, 0, st>>>(fb.bin_count, fb.bin_base, fb.bin_cursor, n_keys, 1, fb.view_total, kSubShift);
     entry_base_kernel<<<1, 32, 0, st>>>(fb.view_total, B, fb.entry_base, fb.stats);
     if (sc.N > 0)
     {
