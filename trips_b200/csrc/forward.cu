@@ -120,22 +120,28 @@ __device__ __forceinline__ Projected project_visible(const ScenePtrs& sc, const 
 }
 
 #ifndef TRIPS_BIN_THREADS
-#define TRIPS_BIN_THREADS 512
+#define TRIPS_BIN_THREADS 256
 #endif
 #ifndef TRIPS_BIN_BLOCKS_PER_SM
-#define TRIPS_BIN_BLOCKS_PER_SM 4
+#define TRIPS_BIN_BLOCKS_PER_SM 8
 #endif
 constexpr int kBinThreads = TRIPS_BIN_THREADS;
 
-// Every block owns a contiguous chunk of the point cloud (the same chunk in the count and in the scatter pass) and
-// keeps the histogram over screen bins in shared memory, so binning needs no global atomics: the count pass
-// stores one histogram row per block, the scan turns rows into per-(block, bin) first-entry offsets, and the scatter
-// pass hands out slots from a shared-memory copy of its row.
-__device__ __forceinline__ void block_chunk(int N, int& first, int& last)
+// The binning kernels take chunks of the point cloud from a ticket counter, view after view, so that every SM is busy
+// until the last chunk whatever the number of resident blocks is (a static split left a partial last wave).
+constexpr int kBinChunk = 8192;  // points per ticket
+__device__ __forceinline__ bool next_point_chunk(unsigned* ticket, int N, int B, unsigned* s_ticket, int& b, int& first, int& last)
 {
-    const int chunk = (N + gridDim.x - 1) / gridDim.x;
-    first           = blockIdx.x * chunk;
-    last            = min(N, first + chunk);
+    __syncthreads();
+    if (threadIdx.x == 0) *s_ticket = atomicAdd(ticket, 1u);
+    __syncthreads();
+    const unsigned t        = *s_ticket;
+    const unsigned per_view = ((unsigned)N + kBinChunk - 1) / kBinChunk;
+    if (t >= per_view * (unsigned)B) return false;
+    b     = (int)(t / per_view);
+    first = (int)((t - (unsigned)b * per_view) * kBinChunk);
+    last  = min(N, first + kBinChunk);
+    return true;
 }
 
 // Sort key of a visible point: its 32x32 screen bin, then its 8x4 pixel tile inside the bin.  Entries of a tile are
@@ -150,21 +156,27 @@ __device__ __forceinline__ int bin_key(const Geom& g, float u, float v)
 }
 
 __global__ __launch_bounds__(kBinThreads) void bin_count_kernel(ScenePtrs sc, const CamConst* __restrict__ cams,
-                                                                const __grid_constant__ Geom g, TripsRenderParams pr, FwdBuffers fb)
+                                                                const __grid_constant__ Geom g, TripsRenderParams pr, FwdBuffers fb, int B)
 {
     __shared__ CamConst cam;
-    const int b = blockIdx.y;
-    if (threadIdx.x < sizeof(CamConst) / 4) ((int*)&cam)[threadIdx.x] = ((const int*)&cams[b])[threadIdx.x];
-    __syncthreads();
-    const size_t bN = (size_t)b * sc.N;
-    const float fxc = cam.fx * cam.cfx;
-    uint32_t* hist  = fb.bin_count + ((size_t)b * g.n_bins << kSubShift);
-    int first, last;
-    block_chunk(sc.N, first, last);
-    for (int i = first + threadIdx.x; i < last; i += blockDim.x)
+    __shared__ unsigned s_ticket;
+    int b, first, last, cur_b = -1;
+    while (next_point_chunk(fb.ticket, sc.N, B, &s_ticket, b, first, last))
     {
-        const Projected r = project_visible(sc, cam, g, pr, bN, i, fxc);
-        if (r.ok) atomicAdd(hist + bin_key(g, r.u, r.v), 1u);
+        if (b != cur_b)  // uniform
+        {
+            if (threadIdx.x < sizeof(CamConst) / 4) ((int*)&cam)[threadIdx.x] = ((const int*)&cams[b])[threadIdx.x];
+            __syncthreads();
+            cur_b = b;
+        }
+        const size_t bN = (size_t)b * sc.N;
+        const float fxc = cam.fx * cam.cfx;
+        uint32_t* hist  = fb.bin_count + ((size_t)b * g.n_bins << kSubShift);
+        for (int i = first + threadIdx.x; i < last; i += blockDim.x)
+        {
+            const Projected r = project_visible(sc, cam, g, pr, bN, i, fxc);
+            if (r.ok) atomicAdd(hist + bin_key(g, r.u, r.v), 1u);
+        }
     }
 }
 
@@ -242,20 +254,25 @@ __global__ void entry_base_kernel(const uint32_t* __restrict__ view_total, int B
 
 template <int C>
 __global__ __launch_bounds__(kBinThreads) void bin_scatter_kernel(ScenePtrs sc, const CamConst* __restrict__ cams,
-                                                                  const __grid_constant__ Geom g, TripsRenderParams pr, FwdBuffers fb)
+                                                                  const __grid_constant__ Geom g, TripsRenderParams pr, FwdBuffers fb, int B)
 {
     constexpr int TS = tail_stride(C);
     __shared__ CamConst cam;
-    const int b = blockIdx.y;
-    if (threadIdx.x < sizeof(CamConst) / 4) ((int*)&cam)[threadIdx.x] = ((const int*)&cams[b])[threadIdx.x];
+    __shared__ unsigned s_ticket;
+    int b, first, last, cur_b = -1;
+    while (next_point_chunk(fb.ticket, sc.N, B, &s_ticket, b, first, last))
+    {
+    if (b != cur_b)  // uniform
+    {
+        if (threadIdx.x < sizeof(CamConst) / 4) ((int*)&cam)[threadIdx.x] = ((const int*)&cams[b])[threadIdx.x];
+        __syncthreads();
+        cur_b = b;
+    }
     uint32_t* cursor = fb.bin_base + ((size_t)b * g.n_bins << kSubShift);  // next free entry of every (bin, tile) group
-    __syncthreads();
     const size_t bN  = (size_t)b * sc.N;
     const float fxc  = cam.fx * cam.cfx;
     float4* head     = fb.ent_head + fb.entry_base[b] * 2;
     float* tail      = fb.ent_tail + fb.entry_base[b] * TS;
-    int first, last;
-    block_chunk(sc.N, first, last);
     for (int i = first + threadIdx.x; i < last; i += blockDim.x)
     {
         const Projected r = project_visible(sc, cam, g, pr, bN, i, fxc);
@@ -290,31 +307,34 @@ __global__ __launch_bounds__(kBinThreads) void bin_scatter_kernel(ScenePtrs sc, 
 #pragma unroll
         for (int c = 0; c < ((C + 3) & ~3); c += 4) e[1 + c / 4] = make_float4(row_t[c], row_t[c + 1], row_t[c + 2], row_t[c + 3]);
     }
+    }
 }
 
-// measured: 4 blocks of 512 threads per SM over all views beats a single resident wave (1.93 vs 2.40 ms at 8 views)
 int bin_blocks_per_view(int B, int sm_count) { return max(4, min(256, (TRIPS_BIN_BLOCKS_PER_SM * sm_count + B - 1) / max(B, 1))); }
 
 cudaError_t launch_bin_points(const ScenePtrs& sc, const CamConst* cams, const Geom& g, const TripsRenderParams& pr, int B,
                               const FwdBuffers& fb, int sm_count, cudaStream_t st)
 {
-    const int nb       = bin_blocks_per_view(B, sm_count);
-    const size_t smem  = 0;
-    const int n_keys   = g.n_bins << kSubShift;
-    cudaError_t e      = cudaMemsetAsync(fb.bin_count, 0, sizeof(uint32_t) * (size_t)B * n_keys, st);
+    const int n_keys = g.n_bins << kSubShift;
+    const int grid   = sm_count * TRIPS_BIN_BLOCKS_PER_SM;
+    cudaError_t e    = cudaMemsetAsync(fb.bin_count, 0, sizeof(uint32_t) * (size_t)B * n_keys, st);
     if (e != cudaSuccess) return e;
-    if (sc.N > 0) bin_count_kernel<<<dim3(nb, B), kBinThreads, 0, st>>>(sc, cams, g, pr, fb);
+    e = cudaMemsetAsync(fb.ticket, 0, 2 * sizeof(unsigned), st);  // one counter per pass
+    if (e != cudaSuccess) return e;
+    FwdBuffers f2 = fb;
+    f2.ticket     = fb.ticket + 1;
+    if (sc.N > 0) bin_count_kernel<<<grid, kBinThreads, 0, st>>>(sc, cams, g, pr, fb, B);
     bin_scan_kernel<<<B, 1024, 0, st>>>(fb.bin_count, fb.bin_base, fb.bin_cursor, n_keys, 1, fb.view_total, kSubShift);
     entry_base_kernel<<<1, 32, 0, st>>>(fb.view_total, B, fb.entry_base, fb.stats);
     if (sc.N > 0)
     {
         switch (sc.C)
         {
-            case 3: bin_scatter_kernel<3><<<dim3(nb, B), kBinThreads, smem, st>>>(sc, cams, g, pr, fb); break;
-            case 4: bin_scatter_kernel<4><<<dim3(nb, B), kBinThreads, smem, st>>>(sc, cams, g, pr, fb); break;
-            case 6: bin_scatter_kernel<6><<<dim3(nb, B), kBinThreads, smem, st>>>(sc, cams, g, pr, fb); break;
-            case 8: bin_scatter_kernel<8><<<dim3(nb, B), kBinThreads, smem, st>>>(sc, cams, g, pr, fb); break;
-            case 16: bin_scatter_kernel<16><<<dim3(nb, B), kBinThreads, smem, st>>>(sc, cams, g, pr, fb); break;
+            case 3: bin_scatter_kernel<3><<<grid, kBinThreads, 0, st>>>(sc, cams, g, pr, f2, B); break;
+            case 4: bin_scatter_kernel<4><<<grid, kBinThreads, 0, st>>>(sc, cams, g, pr, f2, B); break;
+            case 6: bin_scatter_kernel<6><<<grid, kBinThreads, 0, st>>>(sc, cams, g, pr, f2, B); break;
+            case 8: bin_scatter_kernel<8><<<grid, kBinThreads, 0, st>>>(sc, cams, g, pr, f2, B); break;
+            case 16: bin_scatter_kernel<16><<<grid, kBinThreads, 0, st>>>(sc, cams, g, pr, f2, B); break;
             default: return cudaErrorInvalidValue;
         }
     }
@@ -485,10 +505,10 @@ cudaError_t launch_scan(const Geom& g, int B, int k_keep, const FwdBuffers& fb, 
 #define TRIPS_WIN_BLOCKS_PER_SM 8
 #endif
 #ifndef TRIPS_WIN_CHUNK_COLLECT
-#define TRIPS_WIN_CHUNK_COLLECT 512
+#define TRIPS_WIN_CHUNK_COLLECT 1024
 #endif
 constexpr int kWinChunkCount   = TRIPS_WIN_CHUNK;          // entries per block ticket, counting pass
-constexpr int kWinChunkCollect = TRIPS_WIN_CHUNK_COLLECT;  // and collecting pass: the lists a chunk writes to must stay in L2 until complete (measured: 512 2.7 ms, 1024 3.3 ms, 2048 3.7 ms, 256 2.9 ms)
+constexpr int kWinChunkCollect = TRIPS_WIN_CHUNK_COLLECT;  // and collecting pass: the lists a chunk writes to must stay in L2 until complete (measured with tile-ordered entries: 256 1.80 ms, 512 1.46 ms, 1024 1.35 ms, 2048 1.47 ms)
 constexpr int kWinThreads = TRIPS_WIN_THREADS;
 constexpr int kWinMax     = 34 * 34 + 18 * 18 + 10 * 10 + 6 * 6 + 4 * 4 + 3 * 3 * 3;  // 1659 window pixels over 8 layers
 
