@@ -68,6 +68,7 @@ __global__ __launch_bounds__(kBwdThreads, TRIPS_BWD_MIN_BLOCKS) void blend_backw
     constexpr int GS = egrad_stride(C);
     __shared__ float s_g[kBwdWarps][C][32];
     __shared__ float s_d[kBwdWarps][32 * kPad];   // G_j, then dA_j = G_j T_j, finally d_j
+    __shared__ uint16_t s_map[kBwdWarps][32 * 16];
     __shared__ uint2 s_rec[kBwdWarps][32 * kPad]; // the tile's records: (entry index, alpha_j bits; after phase 1: w_j = T_j * alpha_j)
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
@@ -102,6 +103,7 @@ __global__ __launch_bounds__(kBwdThreads, TRIPS_BWD_MIN_BLOCKS) void blend_backw
         const uint32_t n_ent = (uint32_t)(fb.entry_base[b + 1] - fb.entry_base[b]);
         int layer, gx, gy, p;
         tile_pixel(g, (int)tile, lane, layer, gx, gy, p);
+        const int gx0 = __shfl_sync(kFull, gx, 0), gy0 = __shfl_sync(kFull, gy, 0);  // tile origin: lane l is pixel (gx0 + (l & 7), gy0 + (l >> 3))
         int m = 0;
         float gin[C];
 #pragma unroll
@@ -148,17 +150,19 @@ __global__ __launch_bounds__(kBwdThreads, TRIPS_BWD_MIN_BLOCKS) void blend_backw
             }
         }
         __syncwarp();
-        // (pixel, index in its list) of the e-th kept fragment of the tile
-        auto locate = [&](int e, int& seg, int& j) {
-            seg = 0;
+        // (pixel, slot in the padded per-pixel arrays) of the e-th kept fragment of the tile: a table written by the
+        // pixels' lanes replaces a binary search over warp shuffles in every round of both fragment phases
+        {
+            uint16_t* mp = s_map[warp] + rel;
 #pragma unroll
-            for (int step = 16; step > 0; step >>= 1)
-            {
-                const int probe  = seg + step;
-                const int pstart = __shfl_sync(kFull, rel, probe & 31);
-                if (probe < 32 && pstart <= e) seg = probe;
-            }
-            j = e - __shfl_sync(kFull, rel, seg);
+            for (int j = 0; j < 16; ++j)
+                if (j < m) mp[j] = (uint16_t)((lane << 10) | (lane * kPad + j));
+        }
+        __syncwarp();
+        auto locate = [&](int e, int& seg, int& slot) {
+            const unsigned v = e < n_entry ? s_map[warp][e] : 0u;  // lanes beyond the last fragment point at slot 0
+            seg  = v >> 10;
+            slot = v & 1023;
         };
 
         // ---- phase 0 (lane = kept fragment): G_j = <descriptor row of the entry, g>; the row of the next round is
@@ -169,7 +173,7 @@ __global__ __launch_bounds__(kBwdThreads, TRIPS_BWD_MIN_BLOCKS) void blend_backw
             float4 row_n[(C + 3) / 4];
             if (lane < n_entry)
             {
-                const float* rp = desc + (size_t)s_rec[warp][seg_n * kPad + j_n].x * DS;
+                const float* rp = desc + (size_t)s_rec[warp][j_n].x * DS;
 #pragma unroll
                 for (int c = 0; c < (C + 3) / 4; ++c) row_n[c] = *reinterpret_cast<const float4*>(rp + 4 * c);
             }
@@ -184,7 +188,7 @@ __global__ __launch_bounds__(kBwdThreads, TRIPS_BWD_MIN_BLOCKS) void blend_backw
                     locate(e0 + 32 + lane, seg_n, j_n);
                     if (e0 + 32 + lane < n_entry)
                     {
-                        const float* rp = desc + (size_t)s_rec[warp][seg_n * kPad + j_n].x * DS;
+                        const float* rp = desc + (size_t)s_rec[warp][j_n].x * DS;
 #pragma unroll
                         for (int c = 0; c < (C + 3) / 4; ++c) row_n[c] = *reinterpret_cast<const float4*>(rp + 4 * c);
                     }
@@ -201,7 +205,7 @@ __global__ __launch_bounds__(kBwdThreads, TRIPS_BWD_MIN_BLOCKS) void blend_backw
                         if (c + 2 < C) G += v4.z * s_g[warp][c + 2][seg];
                         if (c + 3 < C) G += v4.w * s_g[warp][c + 3][seg];
                     }
-                    s_d[warp][seg * kPad + j] = G;
+                    s_d[warp][j] = G;
                 }
             }
         }
@@ -259,7 +263,7 @@ __global__ __launch_bounds__(kBwdThreads, TRIPS_BWD_MIN_BLOCKS) void blend_backw
             unsigned eidx_n = 0;
             if (lane < n_entry)
             {
-                eidx_n          = s_rec[warp][seg_n * kPad + j_n].x;
+                eidx_n          = s_rec[warp][j_n].x;
                 e0_n            = head[2 * (size_t)eidx_n];  // u v ps conf
             }
             for (int e0 = 0; e0 < n_entry; e0 += 32)
@@ -274,16 +278,15 @@ __global__ __launch_bounds__(kBwdThreads, TRIPS_BWD_MIN_BLOCKS) void blend_backw
                     locate(e0 + 32 + lane, seg_n, j_n);
                     if (e0 + 32 + lane < n_entry)
                     {
-                        eidx_n          = s_rec[warp][seg_n * kPad + j_n].x;
+                        eidx_n          = s_rec[warp][j_n].x;
                         e0_n            = head[2 * (size_t)eidx_n];
                     }
                 }
-                const int layer_s = __shfl_sync(kFull, layer, seg);
-                const int gx_s    = __shfl_sync(kFull, gx, seg);
-                const int gy_s    = __shfl_sync(kFull, gy, seg);
+                const int layer_s = layer;  // a tile lies on one layer
+                const int gx_s = gx0 + (seg & (kTileW - 1)), gy_s = gy0 + (seg >> 3);
                 // (lanes without a fragment run through with zero weights: the exchange below needs all lanes)
-                const float ga = valid ? s_d[warp][seg * kPad + j] : 0.f;
-                const float w  = valid ? __uint_as_float(s_rec[warp][seg * kPad + j].y) : 0.f;
+                const float ga = valid ? s_d[warp][j] : 0.f;
+                const float w  = valid ? __uint_as_float(s_rec[warp][j].y) : 0.f;
                 // bilinear weight of this pixel and its Jacobian at uv (compute_blending_fac, PointBlending.h:216-257)
                 const float fac = __int_as_float((127 - layer_s) << 23);
                 const float ux = e0v.x * fac, uy = e0v.y * fac;
@@ -295,7 +298,7 @@ __global__ __launch_bounds__(kBwdThreads, TRIPS_BWD_MIN_BLOCKS) void blend_backw
                 const float J1 = (q & 2) ? ((q & 1) ? sx : (1.f - sx)) : ((q & 1) ? -sx : (sx - 1.f));
                 if (fabsf(ux - (float)gx_s) > 1.f || fabsf(uy - (float)gy_s) > 1.f) bf *= 0.f;
                 float lf_grad   = 0.f;
-                const float lf  = layer_factor(ps, layer_s, g.L, &lf_grad);
+                const float lf  = layer_factor<true>(ps, layer_s, g.L, &lf_grad);
                 const float gbs = conf * lf * ga;  // dLoss / d(bilinear weight) (RenderBackward.cu:385)
                 // image-space sums of the entry: the chain to position / size / pose is linear in them and is applied
                 // once per entry by entry_grad_finish_kernel

@@ -168,6 +168,9 @@ __device__ __forceinline__ void project_point(const CamConst& c, float px, float
 }
 
 // compute_point_size_fac (PointBlending.h:81-149); floor / ceil of log2 taken from the float's bits.
+// FAST_EXP: the hardware exponential (about 2 ulp) instead of the reproducible one; only for values that do not decide
+// list membership, i.e. in the backward pass (gradient tolerance 1e-4), never in the forward pass.
+template <bool FAST_EXP = false>
 __device__ __forceinline__ float layer_factor(float ps, int layer, int L, float* grad)
 {
     int lo = 0, hi = 0;
@@ -184,7 +187,7 @@ __device__ __forceinline__ float layer_factor(float ps, int layer, int L, float*
     float f = 1.f;
     if (hi == 0)
     {
-        f = 0.75f * tm_expf(ps - 1.f) + 0.25f;
+        f = 0.75f * (FAST_EXP ? __expf(ps - 1.f) : tm_expf(ps - 1.f)) + 0.25f;
         if (grad) *grad = 0.27591f * ps;
     }
     else if (lo == hi)
