@@ -39,10 +39,12 @@ __device__ __forceinline__ double warp_sum_d(double v)
 }
 
 constexpr int kPad        = 17;   // row pitch (entries) of the per-pixel arrays in shared memory
-constexpr int kBwdThreads = 128;  // 4 warps: 3 x 4 x 32 x 17 floats of per-entry scratch stay below 48 KB of static shared memory
+constexpr int kBwdThreads = 128;  // 4 warps x (32 x 17 slots x 12 bytes + fragment table + gradient tile) = 32 KB of static shared memory
 constexpr int kBwdWarps   = kBwdThreads / 32;
 
-// One warp differentiates an 8x4 pixel tile of one view (blockIdx.y = view).
+// One warp differentiates an 8x4 pixel tile; tiles come from one ticket counter over all views, in the order of
+// tile_pixel (region-major), so the entries and gradient rows a tile touches are a short, L2-resident range.
+//   staging: the tile's records go to shared memory (8 lanes per pixel row: 4 lines per load instruction).
 //   phase 0 (lane = kept fragment, lanes densely packed over the tile's fragments): gather the descriptor row of
 //     the fragment's entry, G_j = <col_j, g> and alpha_j go to shared memory.
 //   phase 1 (lane = pixel, shared memory only): the sequential recurrences over the pixel's kept fragments:
@@ -52,14 +54,18 @@ constexpr int kBwdWarps   = kBwdThreads / 32;
 //   phase 2 (lane = kept fragment): descriptor gradient and the image-space sums of the fragment's entry
 //     (RenderBackward.cu:335-393), accumulated with two vector atomics into the per-entry gradient rows, which are
 //     in screen-bin order like the entries and therefore stay hot in L2 while a region of the image is processed.
+// What bounds the kernel (ncu): about 50 % of the issue slots and 48 % of the load/store unit's line rate are in use
+// at 16-20 resident warps per SM; DRAM is at 20-30 %.  Hence the care for lines per instruction (entries ordered by
+// tile, paired atomics, coalesced staging) and for instructions per fragment (fragment table, no shuffle searches).
 #ifndef TRIPS_BWD_BLOCKS_PER_SM
 #define TRIPS_BWD_BLOCKS_PER_SM 12
 #endif
+// measured: 5 resident blocks (96 registers) 3.59 ms, 4 blocks (108) 3.63 ms, 6 blocks (80) 3.76 ms
 #ifndef TRIPS_BWD_MIN_BLOCKS
-#define TRIPS_BWD_MIN_BLOCKS 1
+#define TRIPS_BWD_MIN_BLOCKS 5
 #endif
 template <int C>
-__global__ __launch_bounds__(kBwdThreads, TRIPS_BWD_MIN_BLOCKS) void blend_backward_kernel(ScenePtrs sc, const CamConst* __restrict__ cams,
+__global__ __launch_bounds__(kBwdThreads, (C <= 4 ? TRIPS_BWD_MIN_BLOCKS : 1)) void blend_backward_kernel(ScenePtrs sc, const CamConst* __restrict__ cams,
                                                                      const __grid_constant__ Geom g, TripsRenderParams pr, int B,
                                                                      FwdBuffers fb, BwdBuffers bb,
                                                                      const __grid_constant__ ConstLayerPtrs grad_in)
