@@ -149,8 +149,8 @@ def stage_bytes(stage, N, P, C, B, F, Kf):
 
 # DRAM bytes (read + write) per unit of work, from the single-pass ncu capture of the full workload summarised in
 # profiles/rasterizer_kernels_c3_full_dram_traffic.md; traffic grows in proportion to the unit count
-DRAM_BYTES_PER_UNIT = {"collect": (26.7, "F"), "sort_blend": (36.8, "F"), "blend_backward": (42.5, "Kf"), "count": (5.5, "F"),
-                       "bin_points": (61.5, "NB"), "adam": (347.9, "N")}
+DRAM_BYTES_PER_UNIT = {"collect": (22.4, "F"), "sort_blend": (36.3, "F"), "blend_backward": (42.7, "Kf"), "count": (5.5, "F"),
+                       "bin_points": (95.9, "NB"), "adam": (347.9, "N")}
 
 
 def stage_traffic(stage, N, B, F, Kf):
