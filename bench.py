@@ -42,6 +42,9 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--cpu-views", type=int, default=12, help="views of the workload the CPU baseline renders")
+    ap.add_argument("--op", default="step", choices=["step", "resize_points"],
+                    help="'step' (default): the training-step benchmark; 'resize_points': removal of 10 % of the points over all "
+                         "per-point tensors and the Adam state (trips_resize_points) against the numpy restatement")
     ap.add_argument("--collective", default="auto", choices=["auto", "fused", "nccl"],
                     help="N>1: 'fused' = one kernel sums the gradients over peer memory, applies Adam and broadcasts; "
                          "'nccl' = all-reduce then Adam; 'auto' = fused when symmetric memory can be set up")
@@ -470,6 +473,63 @@ def run_ours(args, rank, world, local_rank):
         dist.destroy_process_group()
 
 
+def run_resize(args):
+    """Secondary measurement: one device pass that removes 10 % of the points of the workload's scene from position,
+    size, texture, confidence and their Adam state (16 tensors), against numpy on the host."""
+    import torch
+    import oracle
+    from trips_b200 import build as tb
+    from trips_b200.modules import NeuralScene
+    from trips_b200.optim import MyAdam
+    from trips_b200.renderer import PointRendererCache
+    tb.build()
+    oracle.build()
+    dev = torch.device("cuda", 0)
+    s, _, _ = make_workload(args.workload, 1, 0, args.points, 1)
+    N, C = s.n_points, s.channels
+    rng = np.random.Generator(np.random.Philox(7))
+    remove = rng.permutation(N)[: N // 10]
+    rem_dev = torch.from_numpy(remove).to(dev)
+    times = []
+    for it in range(max(args.warmup, 3) + args.steps):
+        ns = NeuralScene.from_synthetic(s, device=dev)
+        pc, tex = ns.point_cloud_cuda, ns.texture
+        cache = PointRendererCache(dev)
+        params = [tex.texture_raw, tex.confidence_raw, pc.t_position, pc.t_point_size]
+        opt = MyAdam(params, lr=1e-3, cache=cache)
+        for p_ in params:
+            p_.grad = torch.ones_like(p_)
+        opt.step()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        ns.ResizePoints(cache, rem_dev, optimizers=[opt])
+        e1.record()
+        torch.cuda.synchronize()
+        if it >= max(args.warmup, 3):
+            times.append(e0.elapsed_time(e1))
+        assert cache.last_status() == 0
+        del ns, opt, cache
+    ms = float(np.median(times))
+    rows = 4 * (C + 1 + 4 + 1) + 4  # parameters + three state tensors each, + original colour
+    alg = 4 * rows * (N + (N - N // 10))  # every element read once, kept elements written once
+    spec = []
+    for shape, pm in (((N, 4), True), ((N, 1), True), ((C, N), False), ((1, N), False)):
+        for _ in range(4):
+            spec.append((np.zeros(shape, np.float32), pm, 0.0))
+    t0 = time.perf_counter()
+    oracle.resize_points(spec, remove, N - N // 10)
+    cpu_s = time.perf_counter() - t0
+    peak, kind = measured_peak()
+    emit({"metric": "points/s through removal of 10 % of the points over all per-point tensors and Adam state", "value": N / (ms * 1e-3),
+          "unit": "points/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+          "dtype": "u32", "data": "synthetic", "config": {"workload": s.name, "points": N, "removed": int(N // 10), "tensors": 17},
+          "roofline": {"bound": "hbm", "achieved": alg / (ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s", "frac": alg / (ms * 1e-3) / 1e9 / peak,
+                       "peak_kind": kind, "traffic": None, "note": "includes torch allocation of the 17 destination tensors"},
+          "cpu_baseline": {"value": N / cpu_s, "unit": "points/s", "cores": 1, "kind": "port",
+                           "sample": f"numpy take over 16 float32 tensors of the same shapes ({cpu_s:.2f} s)"}})
+
+
 _JSON_FD = None
 
 
@@ -496,6 +556,10 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank)
+        return
+    if args.op == "resize_points":
+        if rank == 0:
+            run_resize(args)
         return
     if world != args.gpus and world == 1 and args.gpus > 1:
         raise SystemExit("launch with torch.distributed.run --nproc-per-node N for --gpus N")

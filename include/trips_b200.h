@@ -36,6 +36,7 @@ typedef enum
 #define TRIPS_DEV_NONZERO_DISTORTION 2u /* distortion model not implemented: coefficients were ignored */
 #define TRIPS_DEV_FRAGMENT_OVERFLOW 4u /* a view's fragment count exceeded the list buffer */
 #define TRIPS_DEV_BAD_FRAGMENT 8u /* a fragment referred to a point outside the view's visible set (internal error) */
+#define TRIPS_DEV_BAD_POINT_INDEX 16u /* trips_resize_points: a removal index is out of range or listed twice */
 
 typedef struct TripsContext TripsContext;
 
@@ -178,6 +179,30 @@ int trips_fused_reduce_adam(TripsContext* ctx, const float* const* grad_ptrs, fl
                             const TripsAdamSegment* segments, int n_segments, int64_t lo, int64_t hi, float* first_moments,
                             float* second_moments, int32_t* steps, void* stream);
 
+/* One per-point tensor of the scene or of the optimizer state for trips_resize_points. */
+typedef struct
+{
+    const void* src;     /* old tensor */
+    void* dst;           /* new tensor, n_new points, allocated by the caller; must not overlap src */
+    int rows;            /* values per point: 4 for t_position, C for the texture, 1 for sizes / confidences / step counters */
+    int elem_bytes;      /* 4 or 8 */
+    int point_major;     /* 1: [N, rows] (t_position, t_point_size); 0: [rows, N] (texture, confidence and their Adam state) */
+    uint32_t fill_bits;  /* bit pattern of the value for appended points (0.5f for the texture, 0 for optimizer state) */
+} TripsPointTensor;
+#define TRIPS_MAX_POINT_TENSORS 32
+
+/* Replaces the removal / growth of points over all per-point tensors and the optimizer state:
+ * NeuralScene::RemovePoints (src/lib/data/NeuralScene.cpp:1375-1431: host sort, CPU mesh rebuild, one index_select
+ * per tensor), NeuralPointTextureImpl::RemoveAndFlatten / ResizeAndFill (src/lib/models/NeuralTexture.cpp:153-208),
+ * MyAdam::shrinkInternalState / appendToInternalState (src/lib/models/MyAdam.cu:346-415).
+ * indices_to_remove: device array of n_remove distinct point indices in any order (the reference sorts them on the
+ * host), may be NULL when n_remove is 0.  Every dst receives the kept points in their old order followed by
+ * n_new - (n_points - n_remove) appended points holding the tensor's fill value; n_new must not be smaller than the
+ * number of kept points.  One scan and one gather launch cover all tensors; nothing is copied to the host.  An index
+ * out of range or listed twice raises TRIPS_DEV_BAD_POINT_INDEX in trips_last_status. */
+int trips_resize_points(TripsContext* ctx, const int64_t* indices_to_remove, int64_t n_remove, int64_t n_points, int64_t n_new,
+                        const TripsPointTensor* tensors, int n_tensors, void* stream);
+
 /* No counterpart in the reference.  Same update as trips_adam_step for callers that cannot allocate device
  * memory at the time of the step: code running while the application's own pool owns all free memory, hosts that
  * forbid cudaMalloc after start-up, or a step issued inside a stream capture.  The table describing the tensors,
@@ -207,6 +232,7 @@ enum
     TRIPS_STAGE_ADAM,
     TRIPS_STAGE_LOSS,
     TRIPS_STAGE_FUSED_ADAM,
+    TRIPS_STAGE_RESIZE,
     TRIPS_NUM_STAGES
 };
 int trips_enable_stage_timers(TripsContext* ctx, int enable);

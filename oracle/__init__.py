@@ -210,3 +210,20 @@ def use_all_cores() -> int:
     n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
     lib().or_set_threads(n)
     return max_threads()
+
+
+def resize_points(tensors, indices_to_remove, n_new):
+    """CPU restatement of point removal / growth over per-point tensors (numpy; checker for trips_resize_points).
+
+    tensors: list of (array, point_major, fill).  Kept points keep their order (index_select with the ascending list of
+    kept indices: NeuralScene.cpp:1390-1405,1425-1431; NeuralTexture.cpp:195-208; MyAdam.cu:346-373); points beyond
+    the kept ones are filled with the tensor's constant (NeuralTexture.cpp:153-193; MyAdam.cu:376-415)."""
+    out = []
+    for a, point_major, fill in tensors:
+        n_old = a.shape[0] if point_major else a.shape[-1]
+        keep = np.setdiff1d(np.arange(n_old), np.asarray(indices_to_remove, dtype=np.int64))
+        kept = np.take(a, keep, axis=0 if point_major else a.ndim - 1)
+        pad_shape = list(kept.shape)
+        pad_shape[0 if point_major else -1] = n_new - keep.size
+        out.append(np.concatenate([kept, np.full(pad_shape, fill, dtype=a.dtype)], axis=0 if point_major else a.ndim - 1))
+    return out

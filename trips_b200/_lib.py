@@ -14,7 +14,7 @@ LIB_PATH = os.environ.get("TRIPS_B200_LIB") or os.path.join(HERE, "libtrips_b200
 
 MAX_LAYERS = 8
 MAX_KEEP = 16
-NUM_STAGES = 11
+NUM_STAGES = 12
 MAX_RANKS = 16
 MAX_SEGMENTS = 8
 ADAM_STATIC_MAX_TENSORS = 64
@@ -74,6 +74,11 @@ class TripsAdamSegment(C.Structure):
                 ("weight_clipping_magnitude", C.c_float), ("lower_lr_bound", C.c_float), ("upper_lr_bound", C.c_float)]
 
 
+class TripsPointTensor(C.Structure):
+    _fields_ = [("src", C.c_void_p), ("dst", C.c_void_p), ("rows", C.c_int), ("elem_bytes", C.c_int), ("point_major", C.c_int),
+                ("fill_bits", C.c_uint32)]
+
+
 # every symbol include/trips_b200.h declares: name -> (restype, argtypes)
 SYMBOLS = {
     "trips_context_create": (C.c_int, [C.POINTER(C.c_void_p), C.c_int]),
@@ -89,6 +94,7 @@ SYMBOLS = {
     "trips_fused_reduce_adam": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.c_int, C.c_int,
                                           C.POINTER(TripsAdamSegment), C.c_int, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p,
                                           C.c_void_p, C.c_void_p]),
+    "trips_resize_points": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.POINTER(TripsPointTensor), C.c_int, C.c_void_p]),
     "trips_adam_step_static": (C.c_int, [C.POINTER(TripsAdamTensor), C.c_int, C.c_void_p]),
     "trips_enable_stage_timers": (C.c_int, [C.c_void_p, C.c_int]),
     "trips_get_stage_times": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int]),

@@ -109,7 +109,7 @@ struct TripsContext
     int sm_count = 148;
     std::string error;
     // forward scratch
-    DevBuf views, cams, bin_count, bin_base, view_total, bin_cursor, entry_base, entries, counts, offsets, partial, view_base, frags, rec_n, records, stats, ticket, rank, rank_scratch, rank_temp;
+    DevBuf views, cams, bin_count, bin_base, view_total, bin_cursor, entry_base, entries, counts, offsets, partial, view_base, frags, rec_n, records, stats, ticket, rank, rank_scratch, rank_temp, resize_scratch;
     // backward scratch
     DevBuf egrad, g_point, g_conf_pt, g_small;
     // adam
@@ -253,7 +253,7 @@ void trips_context_destroy(TripsContext* c)
     if (!c) return;
     DevBuf* all[] = {&c->views, &c->cams, &c->bin_count, &c->bin_base, &c->view_total, &c->bin_cursor, &c->entry_base, &c->entries, &c->counts, &c->offsets,
                      &c->partial, &c->view_base, &c->frags, &c->rec_n, &c->records, &c->stats, &c->ticket, &c->egrad, &c->g_point,
-                     &c->g_conf_pt, &c->g_small, &c->adam_tab, &c->rank, &c->rank_scratch, &c->rank_temp};
+                     &c->g_conf_pt, &c->g_small, &c->adam_tab, &c->rank, &c->rank_scratch, &c->rank_temp, &c->resize_scratch};
     for (DevBuf* b : all) free_buf(*b);
     c->timers.destroy();
     if (c->h_pinned) cudaFreeHost(c->h_pinned);
@@ -537,6 +537,31 @@ int trips_adam_step(TripsContext* ctx, const TripsAdamTensor* tensors, int n_ten
     return TRIPS_OK;
 }
 
+int trips_resize_points(TripsContext* ctx, const int64_t* indices_to_remove, int64_t n_remove, int64_t n_points, int64_t n_new,
+                        const TripsPointTensor* tensors, int n_tensors, void* stream)
+{
+    if (!ctx) return TRIPS_ERR_INVALID_ARG;
+    if (n_points < 0 || n_remove < 0 || n_remove > n_points || n_new < n_points - n_remove) return fail(ctx, TRIPS_ERR_INVALID_ARG, "bad point counts");
+    if (n_remove > 0 && !indices_to_remove) return fail(ctx, TRIPS_ERR_INVALID_ARG, "null removal list");
+    if (n_tensors < 0 || n_tensors > TRIPS_MAX_POINT_TENSORS || (n_tensors > 0 && !tensors)) return fail(ctx, TRIPS_ERR_INVALID_ARG, "bad tensor table");
+    if (n_points >= (1ll << 32) || n_new >= (1ll << 32)) return fail(ctx, TRIPS_ERR_TOO_LARGE, "more than 2^32 points");
+    for (int i = 0; i < n_tensors; ++i)
+    {
+        const TripsPointTensor& t = tensors[i];
+        if (t.rows < 1 || (t.elem_bytes != 4 && t.elem_bytes != 8)) return fail(ctx, TRIPS_ERR_INVALID_ARG, "rows >= 1 and 4- or 8-byte elements");
+        if ((n_new > 0 && !t.dst) || (n_points > n_remove && !t.src)) return fail(ctx, TRIPS_ERR_INVALID_ARG, "null tensor");
+    }
+    cudaStream_t st = (cudaStream_t)stream;
+    CU_CHECK(ctx, ensure(ctx->stats, sizeof(DevStats)));
+    CU_CHECK(ctx, ensure(ctx->resize_scratch, resize_scratch_bytes(n_points)));
+    CU_CHECK(ctx, cudaMemsetAsync(ctx->stats.p, 0, sizeof(DevStats), st));
+    STAGE(ctx, TRIPS_STAGE_RESIZE, 5, st,
+          launch_resize_points(indices_to_remove, n_remove, n_points, n_new, tensors, n_tensors, ctx->resize_scratch.p, (DevStats*)ctx->stats.p,
+                               ctx->sm_count, st));
+    ctx->have_forward = false;  // the scratch of the last forward pass describes the old point set
+    return TRIPS_OK;
+}
+
 int trips_fused_reduce_adam(TripsContext* ctx, const float* const* grad_ptrs, float* const* param_ptrs, int world, int rank,
                             const TripsAdamSegment* segments, int n_segments, int64_t lo, int64_t hi, float* first_moments,
                             float* second_moments, int32_t* steps, void* stream)
@@ -588,7 +613,7 @@ int trips_get_stage_times(TripsContext* ctx, double* ms, int64_t* timed_calls, i
 const char* trips_stage_name(int stage)
 {
     static const char* names[TRIPS_NUM_STAGES] = {"setup_cams", "bin_points", "count", "scan", "collect", "sort_blend",
-                                                  "blend_backward", "unpack_grads", "adam", "l1_loss", "fused_reduce_adam"};
+                                                  "blend_backward", "unpack_grads", "adam", "l1_loss", "fused_reduce_adam", "resize_points"};
     return (stage >= 0 && stage < TRIPS_NUM_STAGES) ? names[stage] : "?";
 }
 

@@ -158,6 +158,73 @@ class NeuralScene(nn.Module):
         intr = IntrinsicsModule(torch.from_numpy(s.intrinsics).to(dev))
         return cls(pc, tex, poses, intr)
 
+    # -- point removal / growth on the device (NeuralScene::RemovePoints / AddNewPoints, NeuralScene.cpp:1224-1431) ----
+    def _point_tensors(self, optimizers=()):
+        """(holder, attribute or state key, tensor, rows, point_major, fill value) of every per-point tensor."""
+        pc, tex = self.point_cloud_cuda, self.texture
+        out = [(pc.t_position, None, pc.t_position.data, 4, True, 0.0), (pc.t_point_size, None, pc.t_point_size.data, 1, True, 0.0),
+               (pc, "t_original_color", pc.t_original_color, 4, True, 1.0),
+               (tex.texture_raw, None, tex.texture_raw.data, tex.texture_raw.shape[0], False, 0.5),  # NeuralTexture.cpp:160
+               (tex.confidence_raw, None, tex.confidence_raw.data, 1, False, 0.5)]
+        params = {id(pc.t_position): (4, True), id(pc.t_point_size): (1, True), id(tex.texture_raw): (tex.texture_raw.shape[0], False),
+                  id(tex.confidence_raw): (1, False)}
+        for opt in optimizers:
+            for group in opt.param_groups:
+                for p in group["params"]:
+                    st = opt.state.get(p)
+                    if st and id(p) in params:
+                        rows, pm = params[id(p)]
+                        for k in ("first_moments", "second_moments", "param_steps"):
+                            out.append((st, k, st[k], rows, pm, 0.0))  # MyAdam.cu:346-415: kept entries, zeros for new ones
+        return out
+
+    @torch.no_grad()
+    def ResizePoints(self, cache, indices_to_remove: Optional[torch.Tensor] = None, new_size: Optional[int] = None, optimizers=()):
+        """Removes the listed points (distinct indices, any order) and / or grows the scene to `new_size` points in one
+        device pass over all per-point parameters and the Adam state of `optimizers` (trips_resize_points).  New points
+        get 0.5 in texture and confidence, zeros elsewhere; the caller writes their positions and sizes afterwards.
+        Returns the number of kept points."""
+        import ctypes as C
+
+        import numpy as np
+
+        from . import _lib
+        pc = self.point_cloud_cuda
+        n_old = pc.t_position.shape[0]
+        n_remove = 0 if indices_to_remove is None else int(indices_to_remove.numel())
+        n_keep = n_old - n_remove
+        n_new = n_keep if new_size is None else int(new_size)
+        rem = None
+        if n_remove:
+            rem = indices_to_remove.reshape(-1).to(device=pc.t_position.device, dtype=torch.int64).contiguous()
+        items = self._point_tensors(optimizers)
+        table, new_tensors = [], []
+        for holder, key, t, rows, pm, fill in items:
+            assert t.is_contiguous() and t.element_size() in (4, 8)
+            shape = (n_new, rows) if pm else (rows, n_new)
+            nt = torch.empty(shape, dtype=t.dtype, device=t.device)
+            bits = int(np.float32(fill).view(np.uint32)) if t.dtype.is_floating_point else int(fill)
+            table.append(_lib.TripsPointTensor(t.data_ptr(), nt.data_ptr(), rows, t.element_size(), int(pm), bits))
+            new_tensors.append(nt)
+        arr = (_lib.TripsPointTensor * len(table))(*table)
+        stream = C.c_void_p(torch.cuda.current_stream(pc.t_position.device).cuda_stream)
+        _lib.check(_lib.lib().trips_resize_points(cache._h, None if rem is None else rem.data_ptr(), n_remove, n_old, n_new, arr, len(table),
+                                                  stream), cache._h)
+        for (holder, key, t, rows, pm, fill), nt in zip(items, new_tensors):
+            nt = nt.view((n_new,) + tuple(t.shape[1:])) if pm else nt
+            if key is None:
+                holder.data = nt  # same Parameter object: optimizer state stays keyed to it
+            elif isinstance(holder, dict):
+                holder[key] = nt
+            else:
+                setattr(holder, key, nt)
+        if pc.t_index is not None:
+            pc.t_index = torch.arange(n_new, dtype=torch.int32, device=pc.t_position.device).reshape(n_new, 1)  # points and texture columns stay aligned
+        for p in (pc.t_position, pc.t_point_size, self.texture.texture_raw, self.texture.confidence_raw):
+            p.grad = None  # the reference resets the gradients to zeros of the new shape (NeuralScene.cpp:1440-1466)
+        self.texture._prepared.clear()
+        return n_keep
+
 
 def images_for(s: Scene, views=None) -> List[ReducedImageInfo]:
     views = range(s.n_views) if views is None else views
