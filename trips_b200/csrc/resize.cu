@@ -158,7 +158,13 @@ __global__ __launch_bounds__(256) void resize_gather_kernel(const __grid_constan
     {
         const bool live     = j < n_keep;
         const int64_t src_i = live ? (int64_t)kept[j] : 0;
-        if (t.elem_bytes == 4)
+        if (t.elem_bytes == 4 && t.point_major && t.rows == 4 && (((uintptr_t)t.src | (uintptr_t)t.dst) & 15) == 0)
+        {
+            // [N,4] float tensors (positions and their Adam state): one 16-byte load and store per point
+            const uint32_t f = t.fill_bits;
+            static_cast<uint4*>(t.dst)[j] = live ? static_cast<const uint4*>(t.src)[src_i] : make_uint4(f, f, f, f);
+        }
+        else if (t.elem_bytes == 4)
             resize_one<uint32_t>(t, j, live, src_i, n_old, n_new);
         else
             resize_one<unsigned long long>(t, j, live, src_i, n_old, n_new);
