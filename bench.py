@@ -42,7 +42,7 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--cpu-views", type=int, default=12, help="views of the workload the CPU baseline renders")
-    ap.add_argument("--op", default="step", choices=["step", "resize_points"],
+    ap.add_argument("--op", default="step", choices=["step", "resize_points", "texture_prepare"],
                     help="'step' (default): the training-step benchmark; 'resize_points': removal of 10 % of the points over all "
                          "per-point tensors and the Adam state (trips_resize_points) against the numpy restatement")
     ap.add_argument("--collective", default="auto", choices=["auto", "fused", "nccl"],
@@ -530,6 +530,65 @@ def run_resize(args):
                            "sample": f"numpy take over 16 float32 tensors of the same shapes ({cpu_s:.2f} s)"}})
 
 
+def run_texture_prepare(args):
+    """Secondary measurement: forward + backward of the workload with the texture preparation (sigmoid(10 raw) on the
+    confidences, |raw| on the descriptors, NeuralTexture.h:40-57) done by torch ops with autograd, as the reference
+    does, against the same step with the preparation fused into the rasterizer (confidence_is_raw / texture_abs)."""
+    import torch
+    from trips_b200 import build as tb
+    from trips_b200.modules import NeuralScene, images_for
+    from trips_b200.renderer import NeuralRenderInfo, PointRendererCache, RenderParams
+    from trips_b200.scenes import layer_sizes
+    tb.build()
+    dev = torch.device("cuda", 0)
+    s, my_views, _ = make_workload(args.workload, 1, 0, args.points, args.views_per_gpu)
+    C, L, B = s.channels, s.num_layers, len(my_views)
+    ns = NeuralScene.from_synthetic(s, device=dev)
+    pc, tex = ns.point_cloud_cuda, ns.texture
+    with torch.no_grad():  # raw parameters whose activations are the workload's values
+        tex.confidence_raw.copy_(torch.logit(tex.confidence_raw.clamp(1e-4, 1 - 1e-4)) / 10.0)
+    cache = PointRendererCache(dev)
+    grads_in = [torch.full((B, C, h, w), 1e-6, device=dev) for (w, h) in layer_sizes(s.width, s.height, L)]
+    results = {}
+    for fused in (False, True):
+        info = NeuralRenderInfo(scene=ns, images=images_for(s, my_views),
+                                params=RenderParams(num_texture_channels=C, k_keep=s.k_keep, confidence_is_raw=fused, confidence_scale=10.0,
+                                                    texture_abs=fused), num_layers=L, train=True, cache=cache)
+
+        def step():
+            if fused:
+                t, c = tex.texture_raw, tex.confidence_raw
+            else:
+                t, c = torch.abs(tex.texture_raw), torch.sigmoid(10.0 * tex.confidence_raw)
+            cache.forward(info, t, tex.background_color, pc.t_position, ns.intrinsics.intrinsics, c, pc.t_point_size, pc.t_index,
+                          ns.poses.poses_se3)
+            g = cache.backward(grads_in, t, tex.background_color, pc.t_position, ns.intrinsics.intrinsics, c, pc.t_point_size, pc.t_index,
+                               ns.poses.poses_se3)
+            if not fused:  # the backward of the two torch ops, as autograd would run them
+                g_tex, g_conf = g[0], g[5]
+                g_tex = g_tex * torch.sign(tex.texture_raw)
+                sg = torch.sigmoid(10.0 * tex.confidence_raw)
+                g_conf = g_conf * (10.0 * sg * (1.0 - sg))
+            return g
+
+        for _ in range(max(args.warmup, 3)):
+            step()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+        results[fused] = e0.elapsed_time(e1) / args.steps
+        assert cache.last_status() == 0
+    emit({"metric": "fwd+bwd views/s with the texture preparation fused into the rasterizer", "value": B / (results[True] * 1e-3),
+          "unit": "views/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": results[True],
+          "higher_is_better": True, "dtype": "f32", "data": "synthetic",
+          "config": {"workload": s.name, "points": s.n_points, "views_per_gpu": B, "unfused_ms_per_step": results[False],
+                     "saved_ms_per_step": results[False] - results[True]}})
+
+
 _JSON_FD = None
 
 
@@ -560,6 +619,10 @@ def main():
     if args.op == "resize_points":
         if rank == 0:
             run_resize(args)
+        return
+    if args.op == "texture_prepare":
+        if rank == 0:
+            run_texture_prepare(args)
         return
     if world != args.gpus and world == 1 and args.gpus > 1:
         raise SystemExit("launch with torch.distributed.run --nproc-per-node N for --gpus N")

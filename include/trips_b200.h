@@ -85,6 +85,13 @@ typedef struct
     int viewer_only;                 /* 1: discard points with confidence < stability_cutoff_value */
     float stability_cutoff_value;
     int bg_uses_Tn;                  /* 0 = reference behaviour for the background weight */
+    /* Texture preparation fused into the pass that gathers the per-point data (NeuralTexture.h:40-57: the reference
+     * runs sigmoid((10 + narrowing) * raw) over [1,N] and abs over [C,N] as separate torch ops every step, and their
+     * backward).  When set, TripsScene.confidence / .texture hold the RAW parameters and the gradients returned by
+     * trips_backward are those of the raw parameters. */
+    int confidence_is_raw;           /* 1: confidence = sigmoid(confidence_scale * raw) */
+    float confidence_scale;          /* 10 + narrowing factor */
+    int texture_abs;                 /* 1: descriptor = |raw| */
 } TripsRenderParams;
 
 /* Gradient outputs of BlendPointCloudBackward (src/lib/rendering/PointRenderer.cu:1423-1426).

@@ -68,6 +68,8 @@ def lib():
         L.or_project.argtypes = [C.POINTER(OrView), C.c_void_p, C.POINTER(C.c_float), C.POINTER(C.c_float), C.POINTER(C.c_float)]
         L.or_max_threads.restype = C.c_int
         L.or_set_threads.restype = None
+        L.or_sigmoid.restype = None
+        L.or_sigmoid.argtypes = [C.c_void_p, C.c_float, C.c_void_p, C.c_longlong]
         L.or_set_threads.argtypes = [C.c_int]
         _lib = L
     return _lib
@@ -198,6 +200,14 @@ def adam(w, g, m, v, steps, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, rel_decay
     assert steps.dtype == np.int64
     lib().or_adam(w.size, _ptr(w), _ptr(g), _ptr(m), _ptr(v), _ptr(steps), lr, beta1, beta2, eps, rel_decay, abs_decay,
                   clip, lower_lr, upper_lr)
+
+
+def sigmoid(raw: np.ndarray, scale: float) -> np.ndarray:
+    """sigmoid(scale * raw) as PrepareConfidence computes it (NeuralTexture.h:40-43), float32."""
+    raw = np.ascontiguousarray(raw, dtype=np.float32)
+    out = np.empty_like(raw)
+    lib().or_sigmoid(_ptr(raw), scale, _ptr(out), raw.size)
+    return out
 
 
 def max_threads() -> int:

@@ -204,6 +204,12 @@ int or_max_threads(void)
 #endif
 }
 
+// PrepareConfidence (NeuralTexture.h:40-43): out = sigmoid(scale * raw), with the library's reproducible exponential
+void or_sigmoid(const float* raw, float scale, float* out, long long n)
+{
+    for (long long i = 0; i < n; ++i) out[i] = tm_sigmoid(scale * raw[i]);
+}
+
 void or_set_threads(int n)
 {
 #ifdef _OPENMP

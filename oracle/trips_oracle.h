@@ -54,6 +54,7 @@ typedef struct
 typedef struct OrFrame OrFrame; /* all intermediates of one rendered view */
 
 int or_max_threads(void);
+void or_sigmoid(const float* raw, float scale, float* out, long long n); /* NeuralTexture.h:40-43 */
 void or_set_threads(int n); /* OpenMP team size of the following calls (launchers may export OMP_NUM_THREADS=1) */
 
 OrFrame* or_forward(const OrScene* scene, const OrView* view, const OrParams* params);

@@ -327,3 +327,51 @@ def test_config2_full_size_properties(cuda_lib):
         assert scale > 0, k
         assert float((r2[k] - 2.0 * v).abs().max()) <= 1e-4 * 2.0 * scale, f"{k}: backward is not linear"
         assert float(r0[k].abs().max()) == 0.0, f"{k}: zero in, zero out"
+
+
+@pytest.mark.parametrize("with_index", [False, True])
+def test_fused_texture_preparation(oracle_lib, cuda_lib, with_index):
+    """confidence = sigmoid(10 * raw) and descriptor = |raw| computed inside the rasterizer (NeuralTexture.h:40-57):
+    the scene holds raw parameters; the oracle renders the activated copy.  Forward: the usual bars.  Backward: the
+    gradients arrive at the raw parameters, i.e. the oracle's gradients times the activation derivatives."""
+    import copy
+
+    import torch
+    s_raw = scenes.tiny(seed=77, n_points=5000)
+    rng = np.random.default_rng(77)
+    s_raw.confidence[:] = rng.normal(0.0, 0.25, s_raw.confidence.shape).astype(np.float32)
+    s_raw.texture[:] = rng.uniform(-1.0, 1.0, s_raw.texture.shape).astype(np.float32)
+    s_raw.texture[:, :7] = 0.0  # |x| at 0: torch.abs passes no gradient there
+    scale = 10.0
+    s_act = copy.deepcopy(s_raw)
+    s_act.confidence[:] = oracle_lib.sigmoid(s_raw.confidence, scale).reshape(s_raw.confidence.shape)
+    s_act.texture[:] = np.abs(s_raw.texture)
+    index = rng.permutation(s_raw.n_points).astype(np.int32) if with_index else None
+    _, _, frames = oracle_frames(s_act, train=True, index=index)
+    ns, info, blend = gpu_render(s_raw, train=True, index=index, confidence_is_raw=True, confidence_scale=scale, texture_abs=True)
+    for t in (ns.texture.texture_raw, ns.texture.confidence_raw, ns.point_cloud_cuda.t_position):
+        t.requires_grad_(True)
+    outs = blend(info)
+    assert info.cache.last_status() == 0
+    C = s_raw.channels
+    loss, ref_tex, ref_conf = 0, 0, 0
+    for b, f in enumerate(frames):
+        nrec, pid, alpha = info.cache.debug_records(b, f.P)
+        onrec, opid, oalpha = f.records()
+        assert np.array_equal(nrec, onrec) and np.array_equal(pid, opid)
+        opyr = f.pyramid()
+        for l, o in enumerate(outs):
+            got = o[b].detach().cpu().numpy()
+            assert np.max(np.abs(got - opyr[l]) / np.maximum(np.abs(opyr[l]), 1e-3)) <= TOL_PYRAMID
+        g = scenes.target_gradient(s_raw, b)
+        for l, (w, h, base) in enumerate(f.layers):
+            loss = loss + (outs[l][b] * torch.from_numpy(g[C * base:C * (base + w * h)].reshape(C, h, w)).cuda()).sum()
+        r = f.backward(g)
+        ref_tex, ref_conf = ref_tex + r["texture"], ref_conf + r["confidence"]
+    loss.backward()
+    sg = s_act.confidence.reshape(-1).astype(np.float64)
+    ref_conf_raw = ref_conf.reshape(-1) * (scale * sg * (1.0 - sg))
+    ref_tex_raw = ref_tex * np.sign(s_raw.texture)
+    assert rel_err(ns.texture.confidence_raw.grad.reshape(-1).cpu().numpy(), ref_conf_raw) <= TOL_GRAD
+    assert rel_err(ns.texture.texture_raw.grad.cpu().numpy(), ref_tex_raw) <= TOL_GRAD
+    assert np.all(ns.texture.texture_raw.grad[:, :7].cpu().numpy() == 0)

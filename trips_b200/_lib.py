@@ -47,7 +47,7 @@ class TripsView(C.Structure):
 class TripsRenderParams(C.Structure):
     _fields_ = [("num_layers", C.c_int), ("k_keep", C.c_int), ("train", C.c_int), ("drop_out_points_by_radius", C.c_int),
                 ("drop_out_radius_threshold", C.c_float), ("viewer_only", C.c_int), ("stability_cutoff_value", C.c_float),
-                ("bg_uses_Tn", C.c_int)]
+                ("bg_uses_Tn", C.c_int), ("confidence_is_raw", C.c_int), ("confidence_scale", C.c_float), ("texture_abs", C.c_int)]
 
 
 class TripsGrads(C.Structure):

@@ -494,7 +494,9 @@ template <int C>
 __global__ __launch_bounds__(256) void unpack_point_kernel(const float* __restrict__ g_point, const float* __restrict__ g_conf_pt,
                                                            const uint32_t* __restrict__ rank, const int32_t* __restrict__ index, int N, int n_tex,
                                                            float4* __restrict__ g_points, float* __restrict__ g_size,
-                                                           float* __restrict__ g_texture, float* __restrict__ g_confidence)
+                                                           float* __restrict__ g_texture, float* __restrict__ g_confidence,
+                                                           const float* __restrict__ raw_texture, const float* __restrict__ raw_confidence,
+                                                           float confidence_scale)
 {
     constexpr int PS = egrad_stride(C);
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < (size_t)N; i += (size_t)gridDim.x * blockDim.x)
@@ -510,7 +512,27 @@ __global__ __launch_bounds__(256) void unpack_point_kernel(const float* __restri
             const float4 t4 = *reinterpret_cast<const float4*>(g_point + r * PS + 4 + c);
             gt[c] = t4.x, gt[c + 1] = t4.y, gt[c + 2] = t4.z, gt[c + 3] = t4.w;
         }
-        const float gc = g_conf_pt[r];
+        float gc = g_conf_pt[r];
+        // fused texture preparation: chain through sigmoid(scale * raw) and |raw| (raw_* are null when the caller passes
+        // activated tensors)
+        const int col = index ? index[i] : (int)i;
+        if ((unsigned)col < (unsigned)n_tex)
+        {
+            if (raw_confidence)
+            {
+                const float sg = tm_sigmoid(confidence_scale * raw_confidence[col]);
+                gc             = gc * (confidence_scale * (sg * (1.f - sg)));
+            }
+            if (raw_texture)
+            {
+#pragma unroll
+                for (int c = 0; c < C; ++c)
+                {
+                    const float w = raw_texture[(size_t)c * n_tex + col];
+                    gt[c]         = w > 0.f ? gt[c] : (w < 0.f ? -gt[c] : 0.f);
+                }
+            }
+        }
         if (!index)
         {
             if (g_texture)
@@ -551,7 +573,7 @@ __global__ void unpack_small_kernel(int C, int B, const CamConst* __restrict__ c
 }
 
 cudaError_t launch_unpack_grads(const ScenePtrs& sc, const CamConst* cams, int B, const FwdBuffers& fb, const BwdBuffers& bb,
-                                const TripsGrads& out, int sm_count, cudaStream_t st)
+                                const TripsGrads& out, const TripsRenderParams& pr, int sm_count, cudaStream_t st)
 {
     // the entry counts live on the device: the grid covers a fixed share of the worst case and threads stride
     {
@@ -598,8 +620,10 @@ cudaError_t launch_unpack_grads(const ScenePtrs& sc, const CamConst* cams, int B
         int blocks = max(1, (int)min((size_t)sm_count * 16, ((size_t)sc.N + 255) / 256));
 #define TRIPS_UNPACK_CASE(CC)                                                                                           \
     case CC:                                                                                                            \
-        unpack_point_kernel<CC><<<blocks, 256, 0, st>>>(bb.g_point, bb.g_conf_pt, fb.point_rank, sc.index, sc.N, sc.n_tex,              \
-                                                        (float4*)out.points, out.point_size, out.texture, out.confidence); \
+        unpack_point_kernel<CC><<<blocks, 256, 0, st>>>(bb.g_point, bb.g_conf_pt, fb.point_rank, sc.index, sc.N, sc.n_tex,   \
+                                                        (float4*)out.points, out.point_size, out.texture, out.confidence, \
+                                                        pr.texture_abs ? sc.texture : nullptr,                          \
+                                                        pr.confidence_is_raw ? sc.confidence : nullptr, pr.confidence_scale); \
         break;
         switch (sc.C)
         {

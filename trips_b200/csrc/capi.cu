@@ -485,7 +485,7 @@ int trips_backward(TripsContext* ctx, const TripsScene* scene, const float* cons
           launch_blend_backward(sp, (const CamConst*)ctx->cams.p, g, ctx->params, B, fb, bb, gin, cam_grads, ctx->sm_count, st));
     const int n_unpack = (N > 0 ? 2 : 0) + 1;
     STAGE(ctx, TRIPS_STAGE_UNPACK, n_unpack, st,
-          launch_unpack_grads(sp, (const CamConst*)ctx->cams.p, B, fb, bb, *grads, ctx->sm_count, st));
+          launch_unpack_grads(sp, (const CamConst*)ctx->cams.p, B, fb, bb, *grads, ctx->params, ctx->sm_count, st));
     return TRIPS_OK;
 }
 

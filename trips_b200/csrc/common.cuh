@@ -260,7 +260,7 @@ cudaError_t launch_blend_backward(const ScenePtrs& sc, const CamConst* cams, con
                                   int B, const FwdBuffers& fb, const BwdBuffers& bb, const ConstLayerPtrs& grad_in,
                                   bool want_cam_grads, int sm_count, cudaStream_t st);
 cudaError_t launch_unpack_grads(const ScenePtrs& sc, const CamConst* cams, int B, const FwdBuffers& fb, const BwdBuffers& bb,
-                                const TripsGrads& out, int sm_count, cudaStream_t st);
+                                const TripsGrads& out, const TripsRenderParams& pr, int sm_count, cudaStream_t st);
 cudaError_t launch_adam(const TripsAdamTensor* d_tensors, const int64_t* d_block_start, int n_tensors, int64_t total_blocks,
                         cudaStream_t st);
 cudaError_t launch_fused_reduce_adam(const float* const* grad_ptrs, float* const* param_ptrs, int world, int rank,

@@ -101,7 +101,12 @@ __device__ __forceinline__ Projected project_visible(const ScenePtrs& sc, const 
     if (pr.viewer_only)
     {
         // discard_point_for_confidence, RenderForward.cu:122-130
-        if ((unsigned)r.tex < (unsigned)sc.n_tex && __ldg(sc.confidence + r.tex) < pr.stability_cutoff_value) return r;
+        if ((unsigned)r.tex < (unsigned)sc.n_tex)
+        {
+            float c = __ldg(sc.confidence + r.tex);
+            if (pr.confidence_is_raw) c = tm_sigmoid(pr.confidence_scale * c);
+            if (c < pr.stability_cutoff_value) return r;
+        }
     }
     else if (pr.train && sc.dropout)
     {
@@ -292,7 +297,10 @@ __global__ __launch_bounds__(kBinThreads) void bin_scatter_kernel(ScenePtrs sc, 
         float conf = 0.f;
         const bool tex_ok = (unsigned)r.tex < (unsigned)sc.n_tex;
         if (tex_ok)
+        {
             conf = __ldg(sc.confidence + r.tex);
+            if (pr.confidence_is_raw) conf = tm_sigmoid(pr.confidence_scale * conf);  // PrepareConfidence, NeuralTexture.h:40-43
+        }
         else
             atomicOr(&fb.stats->status, TRIPS_DEV_BAD_TEXTURE_INDEX);  // the point is drawn with alpha 0
         const float4 p = __ldg(sc.position + i);
@@ -304,6 +312,11 @@ __global__ __launch_bounds__(kBinThreads) void bin_scatter_kernel(ScenePtrs sc, 
         float row_t[(C + 3) & ~3];
 #pragma unroll
         for (int c = 0; c < ((C + 3) & ~3); ++c) row_t[c] = (c < C && tex_ok) ? __ldg(sc.texture + (size_t)c * sc.n_tex + r.tex) : 0.f;
+        if (pr.texture_abs)  // PrepareTexture, NeuralTexture.h:45-57
+        {
+#pragma unroll
+            for (int c = 0; c < ((C + 3) & ~3); ++c) row_t[c] = fabsf(row_t[c]);
+        }
 #pragma unroll
         for (int c = 0; c < ((C + 3) & ~3); c += 4) e[1 + c / 4] = make_float4(row_t[c], row_t[c + 1], row_t[c + 2], row_t[c + 3]);
     }

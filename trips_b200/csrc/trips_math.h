@@ -107,6 +107,9 @@ TM_HD float tm_softplus_grad(float y)
     return z / (z + 1.0f);
 }
 
+// logistic function 1 / (1 + e^-x), the activation of the per-point confidence (NeuralTexture.h:40-43)
+TM_HD float tm_sigmoid(float x) { return 1.0f / (1.0f + tm_expf(-x)); }
+
 // Exact floor(log2(x)) and ceil(log2(x)) for finite normal x > 0, from the exponent / mantissa bits.
 // The reference takes floor / ceil of log2f(x) (RenderForward.cu:345, PointBlending.h:83-90); the two
 // agree except where log2f rounds a value a few ulp above a power of two down to that integer.

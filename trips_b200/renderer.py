@@ -54,6 +54,11 @@ class RenderParams:
     render_mode: int = 4  # TILED_BILINEAR_BLEND
     k_keep: int = 16  # PointRendererCache::max_pixels_per_list
     bg_uses_Tn: bool = False
+    # texture preparation fused into the rasterizer (NeuralTexture.h:40-57): the tensors handed to PointRender are the raw
+    # parameters, and the gradients are those of the raw parameters
+    confidence_is_raw: bool = False
+    confidence_scale: float = 10.0
+    texture_abs: bool = False
 
 
 @dataclass
@@ -141,7 +146,7 @@ class PointRendererCache:
         p = info.params
         return _lib.TripsRenderParams(info.num_layers, p.k_keep, int(info.train), int(p.drop_out_points_by_radius),
                                       p.drop_out_radius_threshold, int(p.viewer_only), p.stability_cutoff_value,
-                                      int(p.bg_uses_Tn))
+                                      int(p.bg_uses_Tn), int(p.confidence_is_raw), float(p.confidence_scale), int(p.texture_abs))
 
     # -- forward / backward -----------------------------------------------------------------------------------------
     def forward(self, info: NeuralRenderInfo, texture, background_color, points, intrinsics, confidence, point_size,
