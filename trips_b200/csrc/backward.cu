@@ -2,10 +2,12 @@
 // confidences, positions, point sizes, the background colour, the camera pose and the pinhole coefficients.
 //
 // Replaces BlendBackwardsBilinearTiled (src/lib/rendering/RenderBackward.cu:90-618).  Differences in structure:
-//   * half-warp per pixel, lane j = j-th kept fragment; the reference's O(K^2) inner loop
-//     (RenderBackward.cu:284-301) becomes a suffix sum over lanes;
-//   * gradients are accumulated in row-packed buffers ([n_tex,C] and [N,4] = xyz + size) with vector atomics,
-//     and transposed to the reference's layouts once per call (unpack_grads_kernel);
+//   * a warp per 8x4 pixel tile; the reference's O(K^2) inner loop (RenderBackward.cu:284-301) becomes a reverse
+//     running sum over the pixel's kept fragments;
+//   * fragments add image-space sums to a 32-byte row of their entry (one row per visible point and view, in screen
+//     order); the chain to position / size / pose is applied once per entry (entry_grad_finish_kernel), which adds to
+//     a 32-byte row per point (stored by spatial rank); one pass then writes the reference's layouts
+//     (unpack_point_kernel);
 //   * pixels are enumerated with the ceil-halved layer sizes of the forward pass (the reference halves with
 //     floor here, RenderBackward.cu:112-130, and thereby skips rows of odd-sized layers).
 #include "common.cuh"
@@ -397,7 +399,6 @@ __global__ __launch_bounds__(256) void entry_grad_finish_kernel(FwdBuffers fb, B
     const float fxc = cam.fx * cam.cfx;
     const unsigned long long first = fb.entry_base[b], n = fb.entry_base[b + 1] - first;
     const float4* head   = fb.ent_head + first * 2;
-    const float* tail    = fb.ent_tail + first * tail_stride(C);
     const float* egrad   = bb.egrad + first * GS;
     double acc[CAM_GRADS ? 11 : 1];
 #pragma unroll
@@ -408,13 +409,28 @@ __global__ __launch_bounds__(256) void entry_grad_finish_kernel(FwdBuffers fb, B
         const float* eg = egrad + i * GS;
         const float4 s4 = *reinterpret_cast<const float4*>(eg);      // sum J0 gbs, sum J1 gbs, sum bf conf lf' ga, sum bf lf ga
         const float4 e1 = head[2 * i + 1];  // pid z raw nl|rank
-        const float4 e2 = *reinterpret_cast<const float4*>(tail + i * tail_stride(C));  // x y z tex
+        const float4 e0 = head[2 * i];      // u v ps conf
         const int pid   = __float_as_int(e1.x);
         // row of the point: by spatial rank when the forward pass stored one (rows of a screen bin then share L2 lines)
         const size_t row = fb.point_rank ? (size_t)(__float_as_uint(e1.w) >> kRankShift) : (size_t)pid;
-        const int tex   = __float_as_int(e2.w);
-        float vx, vy, vz;
-        transform_point(cam, e2.x, e2.y, e2.z, vx, vy, vz);
+        // View-space position from the stored projection: (u, v) back through crop rotation, crop transform and the
+        // pinhole matrix gives the normalised coordinates, the stored depth scales them.  This spares the read of the
+        // entry's world position (a third of the kernel's DRAM traffic); the round trip costs a few 1e-7 relative,
+        // far inside the gradient tolerance.
+        const float vz = e1.y;
+        float vx, vy;
+        {
+            const float du = e0.x - cam.cenx, dv = e0.y - cam.ceny;
+            const float idet = 1.f / (cam.r00 * cam.r11 - cam.r01 * cam.r10);
+            const float jx = (cam.r11 * du - cam.r01 * dv) * idet + cam.cenx;
+            const float jy = (cam.r00 * dv - cam.r10 * du) * idet + cam.ceny;
+            const float iy = (jy - cam.ccy) / cam.cfy;
+            const float ix = (jx - cam.ccx - cam.cs * iy) / cam.cfx;
+            const float ny = (iy - cam.cy) / cam.fy;
+            const float nx = (ix - cam.cx - cam.s * ny) / cam.fx;
+            vx = nx * vz;
+            vy = ny * vz;
+        }
         if (vz > 0.f && (s4.x != 0.f || s4.y != 0.f || s4.z != 0.f))
         {
             const float iz  = 1.f / vz;
@@ -448,7 +464,8 @@ __global__ __launch_bounds__(256) void entry_grad_finish_kernel(FwdBuffers fb, B
                 acc[10] += (double)(ny * gk0);
             }
         }
-        if (tex < 0) continue;
+        // (an entry whose texture index is out of range was drawn with alpha 0: its sums are zero, and the unpack pass
+        // skips its column anyway)
         if (s4.w != 0.f) atomicAdd(bb.g_conf_pt + row, s4.w);
         float gt[(C + 3) & ~3];
         bool any = false;

@@ -271,6 +271,7 @@ int trips_forward(TripsContext* ctx, const TripsScene* scene, const TripsView* v
     if (scene->n_points < 0 || scene->n_tex < 1 || scene->n_images < 1 || scene->n_cameras < 1)
         return fail(ctx, TRIPS_ERR_INVALID_ARG, "bad scene sizes");
     if (scene->n_points > 0 && (!scene->position || !scene->point_size)) return fail(ctx, TRIPS_ERR_INVALID_ARG, "null point arrays");
+    if (!scene->index && scene->n_tex < scene->n_points) return fail(ctx, TRIPS_ERR_INVALID_ARG, "without an index the texture needs one column per point");
     if (!scene->texture || !scene->confidence || !scene->background || !scene->poses || !scene->intrinsics)
         return fail(ctx, TRIPS_ERR_INVALID_ARG, "null scene arrays");
     if (!scene->index && scene->n_tex < scene->n_points) return fail(ctx, TRIPS_ERR_INVALID_ARG, "identity index needs n_tex >= n_points");
