@@ -222,7 +222,8 @@ def _loss(frame, g):
 def test_backward_against_finite_differences(oracle_lib):
     """Descriptors and background enter linearly (exact differences); confidence and position are checked with the
     consistent background weight (bg_uses_Tn) on a one-layer render, where the reference's approximations
-     do not apply."""
+    (background weighted with the transmittance before the last kept fragment; position gradients of coarse layers not
+    scaled by 2^-l; the small-point factor's derivative 0.27591 ps) do not apply."""
     s = scenes.tiny(n_points=300, width=32, height=24, num_layers=1, n_views=1, seed=5, fx=40.0, size_range=(0.01, 0.05))
     s.confidence[:] = np.clip(s.confidence * 0.6 + 0.1, 0, 1)
     g = np.random.default_rng(3).normal(size=s.channels * 32 * 24).astype(np.float32)
