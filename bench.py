@@ -36,7 +36,7 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c3", choices=["c3", "c2", "c1", "tiny"])
+    ap.add_argument("--workload", default="c3", choices=["c3", "c2", "c1", "c4", "c5", "c5adv", "tiny"])
     ap.add_argument("--points", type=int, default=0, help="override the number of points (debugging)")
     ap.add_argument("--views-per-gpu", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -59,6 +59,12 @@ def make_workload(name, world, rank, points, views_per_gpu):
     elif name == "c2":
         vpg = views_per_gpu or 4
         s = scenes.config2(n_points=points or 2_000_000, n_views=vpg * world)
+    elif name == "c4":
+        vpg = views_per_gpu or 2
+        s = scenes.config4(n_points=points or 20_000_000, n_views=vpg * world)
+    elif name in ("c5", "c5adv"):
+        vpg = views_per_gpu or 8
+        s = scenes.config5(n_points=points or 10_000_000, n_views=vpg * world, adversarial=(name == "c5adv"))
     elif name == "c1":
         vpg = 1
         s = scenes.config1(n_points=points or 200_000)

@@ -115,6 +115,7 @@ typedef struct
     int64_t kept_fragments; /* Kf = sum over pixels of min(list length, k_keep) */
     int64_t pixels;         /* B * P */
     int64_t max_list_length;
+    int64_t culled_point_blocks; /* (view, block of 8192 consecutive points) pairs skipped by the bounding-box frustum test */
 } TripsStats;
 
 /* Context = PointRendererCache (src/lib/rendering/PointRenderer.h:120-232): owns all scratch memory and the

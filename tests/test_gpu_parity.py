@@ -39,6 +39,16 @@ def _variants():
     v["three_views_long_lists"] = (scenes.tiny(seed=23, n_points=20000, width=64, height=48, n_views=3), {}, None)
     # lists of several hundred fragments: exercises the streaming top-K path used for lists longer than 192
     v["very_long_lists"] = (scenes.tiny(seed=24, n_points=60000, width=40, height=30, n_views=1, num_layers=3), {}, None)
+    # a cloud stored in spatial order: blocks of 8192 consecutive points are compact, the ones beside the view are
+    # skipped as a whole by the bounding-box test (the test function checks that some were)
+    s = scenes.tiny(seed=30, n_points=50000, n_views=2)
+    s.position[:, 0] *= 6.0
+    order = np.argsort(s.position[:, 0], kind="stable")
+    s.position[:] = s.position[order]
+    s.point_size[:] = s.point_size[order]
+    s.texture[:] = s.texture[:, order]
+    s.confidence[:] = s.confidence.reshape(-1)[order].reshape(s.confidence.shape)
+    v["sorted_cloud_block_culling"] = (s, {}, None)
     return v
 
 
@@ -65,6 +75,7 @@ def test_forward_backward_parity(name, oracle_lib, cuda_lib):
     assert st["fragments"] == sum(f.F for f in frames)
     assert st["kept_fragments"] == sum(f.Kf for f in frames)
     assert st["visible_points"] == sum(f.V for f in frames)
+    assert (st["culled_point_blocks"] > 0) == (name == "sorted_cloud_block_culling")
 
     grad_flat = []
     for b, f in enumerate(frames):

@@ -57,7 +57,7 @@ class TripsGrads(C.Structure):
 
 class TripsStats(C.Structure):
     _fields_ = [("visible_points", C.c_int64), ("fragments", C.c_int64), ("kept_fragments", C.c_int64),
-                ("pixels", C.c_int64), ("max_list_length", C.c_int64)]
+                ("pixels", C.c_int64), ("max_list_length", C.c_int64), ("culled_point_blocks", C.c_int64)]
 
 
 class TripsAdamTensor(C.Structure):

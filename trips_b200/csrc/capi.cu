@@ -109,7 +109,7 @@ struct TripsContext
     int sm_count = 148;
     std::string error;
     // forward scratch
-    DevBuf views, cams, bin_count, bin_base, view_total, bin_cursor, entry_base, entries, counts, offsets, partial, view_base, frags, rec_n, records, stats, ticket, rank, rank_scratch, rank_temp, resize_scratch;
+    DevBuf views, cams, bin_count, bin_base, view_total, bin_cursor, entry_base, entries, counts, offsets, partial, view_base, frags, rec_n, records, stats, ticket, rank, rank_scratch, rank_temp, resize_scratch, block_box;
     // backward scratch
     DevBuf egrad, g_point, g_conf_pt, g_small;
     // adam
@@ -205,6 +205,7 @@ static FwdBuffers fwd_buffers(TripsContext* c)
     fb.stats      = (DevStats*)c->stats.p;
     fb.ticket     = (unsigned int*)c->ticket.p;
     fb.point_rank = c->rank_points >= 0 ? (const uint32_t*)c->rank.p : nullptr;
+    fb.block_box  = (const float*)c->block_box.p;
     return fb;
 }
 
@@ -253,7 +254,7 @@ void trips_context_destroy(TripsContext* c)
     if (!c) return;
     DevBuf* all[] = {&c->views, &c->cams, &c->bin_count, &c->bin_base, &c->view_total, &c->bin_cursor, &c->entry_base, &c->entries, &c->counts, &c->offsets,
                      &c->partial, &c->view_base, &c->frags, &c->rec_n, &c->records, &c->stats, &c->ticket, &c->egrad, &c->g_point,
-                     &c->g_conf_pt, &c->g_small, &c->adam_tab, &c->rank, &c->rank_scratch, &c->rank_temp, &c->resize_scratch};
+                     &c->g_conf_pt, &c->g_small, &c->adam_tab, &c->rank, &c->rank_scratch, &c->rank_temp, &c->resize_scratch, &c->block_box};
     for (DevBuf* b : all) free_buf(*b);
     c->timers.destroy();
     if (c->h_pinned) cudaFreeHost(c->h_pinned);
@@ -345,6 +346,7 @@ int trips_forward(TripsContext* ctx, const TripsScene* scene, const TripsView* v
     CU_CHECK(ctx, ensure(ctx->view_total, sizeof(uint32_t) * B));
     CU_CHECK(ctx, ensure(ctx->bin_cursor, sizeof(uint32_t) * (size_t)g.n_bins * B));
     CU_CHECK(ctx, ensure(ctx->entry_base, sizeof(unsigned long long) * (B + 1)));
+    CU_CHECK(ctx, ensure(ctx->block_box, sizeof(float) * 6 * ((N + 8191) / 8192 + 1)));
     // entries are sized for the worst case (every point visible in every view): no host round trip is needed to size them
     CU_CHECK(ctx, ensure(ctx->entries, sizeof(float) * ES * N * B + 16));
     ctx->entry_cap = (size_t)N * B;
@@ -438,6 +440,7 @@ int trips_forward(TripsContext* ctx, const TripsScene* scene, const TripsView* v
     ctx->host_stats.kept_fragments  = (int64_t)h_stats->kept;
     ctx->host_stats.pixels          = (int64_t)P * B;
     ctx->host_stats.max_list_length = (int64_t)h_stats->max_len;
+    ctx->host_stats.culled_point_blocks = (int64_t)h_stats->culled_blocks;
     ctx->have_forward          = true;
     return TRIPS_OK;
 }

@@ -65,6 +65,8 @@ struct DevStats
     unsigned long long kept;
     unsigned int max_len;
     unsigned int status;
+    unsigned int culled_blocks;  // (view, block of consecutive points) pairs skipped by the bounding-box test, counted once per pass
+    unsigned int pad;
 };
 
 // A visible point of one view ("entry"): everything the later stages need, gathered once and stored in screen-bin
@@ -101,6 +103,7 @@ struct FwdBuffers
     DevStats* stats;
     unsigned int* ticket;
     const uint32_t* point_rank;       // [N] spatial rank of every point, or nullptr: gradient rows are keyed by point id
+    const float* block_box;           // [ceil(N / 8192), 6] bounding boxes (min xyz, max xyz) of blocks of consecutive points
 };
 
 struct ScenePtrs

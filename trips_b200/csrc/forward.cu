@@ -132,9 +132,100 @@ __device__ __forceinline__ Projected project_visible(const ScenePtrs& sc, const 
 #endif
 constexpr int kBinThreads = TRIPS_BIN_THREADS;
 
+constexpr int kBinChunk = 8192;  // points per ticket of the binning kernels = points per bounding box
+
+// Bounding boxes of blocks of consecutive points and the conservative frustum test on them: the reference computes
+// such boxes per 10 240 points (NeuralPointCloudCuda.cpp:339-384) but never uses them.  Point clouds stored in a
+// spatially coherent order (scans, reconstructions) have compact blocks, and a block whose box lies outside a view
+// is skipped by both binning passes; for a cloud in random order every box spans the scene and nothing is skipped.
+// Boxes are recomputed by every forward pass (points move): one read of the positions.
+__global__ __launch_bounds__(256) void block_box_kernel(const float4* __restrict__ pos, int N, float* __restrict__ boxes)
+{
+    const int first = blockIdx.x * kBinChunk, last = min(N, first + kBinChunk);
+    float lo[3] = {3.0e38f, 3.0e38f, 3.0e38f}, hi[3] = {-3.0e38f, -3.0e38f, -3.0e38f};
+    bool bad = false;
+    for (int i = first + threadIdx.x; i < last; i += 256)
+    {
+        const float4 p = pos[i];
+        const float v[3] = {p.x, p.y, p.z};
+#pragma unroll
+        for (int k = 0; k < 3; ++k)
+        {
+            bad |= !(fabsf(v[k]) < 3.0e38f);  // NaN or infinite: the block is never skipped
+            lo[k] = fminf(lo[k], v[k]);
+            hi[k] = fmaxf(hi[k], v[k]);
+        }
+    }
+    __shared__ float s_lo[8][3], s_hi[8][3];
+    __shared__ int s_bad;
+    if (threadIdx.x == 0) s_bad = 0;
+    __syncthreads();
+    if (bad) s_bad = 1;
+#pragma unroll
+    for (int k = 0; k < 3; ++k)
+    {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+        {
+            lo[k] = fminf(lo[k], __shfl_xor_sync(kFull, lo[k], o));
+            hi[k] = fmaxf(hi[k], __shfl_xor_sync(kFull, hi[k], o));
+        }
+        if ((threadIdx.x & 31) == 0) s_lo[threadIdx.x >> 5][k] = lo[k], s_hi[threadIdx.x >> 5][k] = hi[k];
+    }
+    __syncthreads();
+    if (threadIdx.x < 3)
+    {
+        float a = s_lo[0][threadIdx.x], b = s_hi[0][threadIdx.x];
+        for (int w = 1; w < 8; ++w) a = fminf(a, s_lo[w][threadIdx.x]), b = fmaxf(b, s_hi[w][threadIdx.x]);
+        if (s_bad) a = -3.4e38f, b = 3.4e38f;
+        boxes[(size_t)blockIdx.x * 6 + threadIdx.x]     = a;
+        boxes[(size_t)blockIdx.x * 6 + 3 + threadIdx.x] = b;
+    }
+}
+
+// True when no point inside the box can pass the visibility test of project_visible for this view.  The image position
+// is an affine map of (x/z, y/z); multiplied by z > 0 every image border becomes a plane through the camera centre,
+// i.e. a linear function of the view-space position, and a box lies outside a plane when its 8 corners do.  The borders
+// are moved out by a margin of 2 pixels (+ 1e-3 of the depth), far more than the rounding difference between this
+// test and the per-point arithmetic.
+__device__ __forceinline__ bool box_outside_view(const CamConst& c, const Geom& g, const float* __restrict__ box)
+{
+    if (!(box[3] < 3.0e38f)) return false;
+    // u(nx, ny) = cu + au nx + bu ny, v likewise: evaluate the projection chain at three normalised positions
+    float u0, v0, u1, v1, u2, v2;
+    {
+        auto img = [&](float nx, float ny, float& u, float& v) {
+            const float ix = (c.fx * nx + c.s * ny) + c.cx, iy = c.fy * ny + c.cy;
+            const float jx = (c.cfx * ix + c.cs * iy) + c.ccx, jy = c.cfy * iy + c.ccy;
+            const float dx = jx - c.cenx, dy = jy - c.ceny;
+            u = (c.r00 * dx + c.r01 * dy) + c.cenx;
+            v = (c.r10 * dx + c.r11 * dy) + c.ceny;
+        };
+        img(0.f, 0.f, u0, v0);
+        img(1.f, 0.f, u1, v1);
+        img(0.f, 1.f, u2, v2);
+    }
+    const float au = u1 - u0, bu = u2 - u0, av = v1 - v0, bv = v2 - v0;
+    const float m = 2.f, wmax = (float)(g.W[0] - 1) + m, hmax = (float)(g.H[0] - 1) + m;
+    bool all_behind = true, all_left = true, all_right = true, all_up = true, all_down = true;
+#pragma unroll
+    for (int k = 0; k < 8; ++k)
+    {
+        float x, y, z;
+        transform_point(c, box[(k & 1) ? 3 : 0], box[(k & 2) ? 4 : 1], box[(k & 4) ? 5 : 2], x, y, z);
+        const float U = au * x + bu * y + u0 * z, V = av * x + bv * y + v0 * z;
+        const float slack = 1e-3f * fabsf(z) + 1e-6f * (fabsf(x) + fabsf(y));
+        all_behind &= z < -slack;
+        all_left &= (U + m * z) < -slack * (fabsf(au) + fabsf(bu) + fabsf(u0) + m);
+        all_right &= (wmax * z - U) < -slack * (fabsf(au) + fabsf(bu) + fabsf(u0) + wmax);
+        all_up &= (V + m * z) < -slack * (fabsf(av) + fabsf(bv) + fabsf(v0) + m);
+        all_down &= (hmax * z - V) < -slack * (fabsf(av) + fabsf(bv) + fabsf(v0) + hmax);
+    }
+    return all_behind || all_left || all_right || all_up || all_down;
+}
+
 // The binning kernels take chunks of the point cloud from a ticket counter, view after view, so that every SM is busy
 // until the last chunk whatever the number of resident blocks is (a static split left a partial last wave).
-constexpr int kBinChunk = 8192;  // points per ticket
 __device__ __forceinline__ bool next_point_chunk(unsigned* ticket, int N, int B, unsigned* s_ticket, int& b, int& first, int& last)
 {
     __syncthreads();
@@ -173,6 +264,11 @@ __global__ __launch_bounds__(kBinThreads) void bin_count_kernel(ScenePtrs sc, co
             if (threadIdx.x < sizeof(CamConst) / 4) ((int*)&cam)[threadIdx.x] = ((const int*)&cams[b])[threadIdx.x];
             __syncthreads();
             cur_b = b;
+        }
+        if (fb.block_box && box_outside_view(cam, g, fb.block_box + (size_t)(first / kBinChunk) * 6))  // uniform
+        {
+            if (threadIdx.x == 0) atomicAdd(&fb.stats->culled_blocks, 1u);
+            continue;
         }
         const size_t bN = (size_t)b * sc.N;
         const float fxc = cam.fx * cam.cfx;
@@ -273,6 +369,7 @@ __global__ __launch_bounds__(kBinThreads) void bin_scatter_kernel(ScenePtrs sc, 
         __syncthreads();
         cur_b = b;
     }
+    if (fb.block_box && box_outside_view(cam, g, fb.block_box + (size_t)(first / kBinChunk) * 6)) continue;  // uniform; the count pass skipped it too
     uint32_t* cursor = fb.bin_base + ((size_t)b * g.n_bins << kSubShift);  // next free entry of every (bin, tile) group
     const size_t bN  = (size_t)b * sc.N;
     const float fxc  = cam.fx * cam.cfx;
@@ -336,6 +433,7 @@ cudaError_t launch_bin_points(const ScenePtrs& sc, const CamConst* cams, const G
     if (e != cudaSuccess) return e;
     FwdBuffers f2 = fb;
     f2.ticket     = fb.ticket + 1;
+    if (sc.N > 0 && fb.block_box) block_box_kernel<<<(sc.N + kBinChunk - 1) / kBinChunk, 256, 0, st>>>(sc.position, sc.N, const_cast<float*>(fb.block_box));
     if (sc.N > 0) bin_count_kernel<<<grid, kBinThreads, 0, st>>>(sc, cams, g, pr, fb, B);
     bin_scan_kernel<<<B, 1024, 0, st>>>(fb.bin_count, fb.bin_base, fb.bin_cursor, n_keys, 1, fb.view_total, kSubShift);
     entry_base_kernel<<<1, 32, 0, st>>>(fb.view_total, B, fb.entry_base, fb.stats);
