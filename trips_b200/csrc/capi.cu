@@ -109,7 +109,7 @@ struct TripsContext
     int sm_count = 148;
     std::string error;
     // forward scratch
-    DevBuf views, cams, bin_count, bin_base, view_total, bin_cursor, entry_base, entries, counts, offsets, partial, view_base, frags, rec_n, records, stats, ticket, rank, rank_scratch, rank_temp, resize_scratch, block_box;
+    DevBuf views, cams, bin_count, bin_base, view_total, bin_cursor, entry_base, entries, counts, offsets, partial, view_base, frags, rec_n, records, stats, ticket, rank, rank_scratch, rank_temp, resize_scratch, block_box, block_skip;
     // backward scratch
     DevBuf egrad, g_point, g_conf_pt, g_small;
     // adam
@@ -206,6 +206,7 @@ static FwdBuffers fwd_buffers(TripsContext* c)
     fb.ticket     = (unsigned int*)c->ticket.p;
     fb.point_rank = c->rank_points >= 0 ? (const uint32_t*)c->rank.p : nullptr;
     fb.block_box  = (const float*)c->block_box.p;
+    fb.block_skip = (const uint8_t*)c->block_skip.p;
     return fb;
 }
 
@@ -254,7 +255,7 @@ void trips_context_destroy(TripsContext* c)
     if (!c) return;
     DevBuf* all[] = {&c->views, &c->cams, &c->bin_count, &c->bin_base, &c->view_total, &c->bin_cursor, &c->entry_base, &c->entries, &c->counts, &c->offsets,
                      &c->partial, &c->view_base, &c->frags, &c->rec_n, &c->records, &c->stats, &c->ticket, &c->egrad, &c->g_point,
-                     &c->g_conf_pt, &c->g_small, &c->adam_tab, &c->rank, &c->rank_scratch, &c->rank_temp, &c->resize_scratch, &c->block_box};
+                     &c->g_conf_pt, &c->g_small, &c->adam_tab, &c->rank, &c->rank_scratch, &c->rank_temp, &c->resize_scratch, &c->block_box, &c->block_skip};
     for (DevBuf* b : all) free_buf(*b);
     c->timers.destroy();
     if (c->h_pinned) cudaFreeHost(c->h_pinned);
@@ -347,6 +348,7 @@ int trips_forward(TripsContext* ctx, const TripsScene* scene, const TripsView* v
     CU_CHECK(ctx, ensure(ctx->bin_cursor, sizeof(uint32_t) * (size_t)g.n_bins * B));
     CU_CHECK(ctx, ensure(ctx->entry_base, sizeof(unsigned long long) * (B + 1)));
     CU_CHECK(ctx, ensure(ctx->block_box, sizeof(float) * 6 * ((N + 8191) / 8192 + 1)));
+    CU_CHECK(ctx, ensure(ctx->block_skip, (size_t)B * ((N + 8191) / 8192 + 1)));
     // entries are sized for the worst case (every point visible in every view): no host round trip is needed to size them
     CU_CHECK(ctx, ensure(ctx->entries, sizeof(float) * ES * N * B + 16));
     ctx->entry_cap = (size_t)N * B;
@@ -401,7 +403,7 @@ int trips_forward(TripsContext* ctx, const TripsScene* scene, const TripsView* v
     STAGE(ctx, TRIPS_STAGE_SETUP, 1, st,
           launch_setup_cams((const TripsView*)ctx->views.p, B, scene->poses, scene->n_images, scene->intrinsics,
                             scene->n_cameras, (CamConst*)ctx->cams.p, fb.stats, st));
-    STAGE(ctx, TRIPS_STAGE_BIN_POINTS, N > 0 ? 4 : 2, st, launch_bin_points(sp, (const CamConst*)ctx->cams.p, g, *params, B, fb, ctx->sm_count, st));
+    STAGE(ctx, TRIPS_STAGE_BIN_POINTS, N > 0 ? 6 : 2, st, launch_bin_points(sp, (const CamConst*)ctx->cams.p, g, *params, B, fb, ctx->sm_count, st));
     if (N > 0) STAGE(ctx, TRIPS_STAGE_COUNT, 1, st, launch_count(sp, g, B, fb, ctx->sm_count, st));
     {
         FwdBuffers fscan = fb;

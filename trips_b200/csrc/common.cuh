@@ -104,6 +104,7 @@ struct FwdBuffers
     unsigned int* ticket;
     const uint32_t* point_rank;       // [N] spatial rank of every point, or nullptr: gradient rows are keyed by point id
     const float* block_box;           // [ceil(N / 8192), 6] bounding boxes (min xyz, max xyz) of blocks of consecutive points
+    const uint8_t* block_skip;        // [B, ceil(N / 8192)] 1 = the block cannot hold a point visible in that view
 };
 
 struct ScenePtrs

@@ -224,6 +224,21 @@ __device__ __forceinline__ bool box_outside_view(const CamConst& c, const Geom& 
     return all_behind || all_left || all_right || all_up || all_down;
 }
 
+// skip[b * n_blocks + k] = 1 when block k of the point cloud cannot hold a point visible in view b.  A kernel of its
+// own: inside the binning kernels the test would cost their loops 30 registers.
+__global__ __launch_bounds__(128) void block_visibility_kernel(const CamConst* __restrict__ cams, const __grid_constant__ Geom g, int B,
+                                                               int n_blocks, const float* __restrict__ boxes, uint8_t* __restrict__ skip,
+                                                               DevStats* stats)
+{
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= B * n_blocks) return;
+    const int b = i / n_blocks, k = i - b * n_blocks;
+    const CamConst cam = cams[b];
+    const bool out = box_outside_view(cam, g, boxes + (size_t)k * 6);
+    skip[i] = out ? 1 : 0;
+    if (out) atomicAdd(&stats->culled_blocks, 1u);
+}
+
 // The binning kernels take chunks of the point cloud from a ticket counter, view after view, so that every SM is busy
 // until the last chunk whatever the number of resident blocks is (a static split left a partial last wave).
 __device__ __forceinline__ bool next_point_chunk(unsigned* ticket, int N, int B, unsigned* s_ticket, int& b, int& first, int& last)
@@ -265,11 +280,7 @@ __global__ __launch_bounds__(kBinThreads) void bin_count_kernel(ScenePtrs sc, co
             __syncthreads();
             cur_b = b;
         }
-        if (fb.block_box && box_outside_view(cam, g, fb.block_box + (size_t)(first / kBinChunk) * 6))  // uniform
-        {
-            if (threadIdx.x == 0) atomicAdd(&fb.stats->culled_blocks, 1u);
-            continue;
-        }
+        if (fb.block_skip && fb.block_skip[(size_t)b * ((sc.N + kBinChunk - 1) / kBinChunk) + first / kBinChunk]) continue;  // uniform
         const size_t bN = (size_t)b * sc.N;
         const float fxc = cam.fx * cam.cfx;
         uint32_t* hist  = fb.bin_count + ((size_t)b * g.n_bins << kSubShift);
@@ -369,7 +380,7 @@ __global__ __launch_bounds__(kBinThreads) void bin_scatter_kernel(ScenePtrs sc, 
         __syncthreads();
         cur_b = b;
     }
-    if (fb.block_box && box_outside_view(cam, g, fb.block_box + (size_t)(first / kBinChunk) * 6)) continue;  // uniform; the count pass skipped it too
+    if (fb.block_skip && fb.block_skip[(size_t)b * ((sc.N + kBinChunk - 1) / kBinChunk) + first / kBinChunk]) continue;  // uniform; the count pass skipped the block too
     uint32_t* cursor = fb.bin_base + ((size_t)b * g.n_bins << kSubShift);  // next free entry of every (bin, tile) group
     const size_t bN  = (size_t)b * sc.N;
     const float fxc  = cam.fx * cam.cfx;
@@ -433,7 +444,12 @@ cudaError_t launch_bin_points(const ScenePtrs& sc, const CamConst* cams, const G
     if (e != cudaSuccess) return e;
     FwdBuffers f2 = fb;
     f2.ticket     = fb.ticket + 1;
-    if (sc.N > 0 && fb.block_box) block_box_kernel<<<(sc.N + kBinChunk - 1) / kBinChunk, 256, 0, st>>>(sc.position, sc.N, const_cast<float*>(fb.block_box));
+    if (sc.N > 0 && fb.block_box && fb.block_skip)
+    {
+        const int nbk = (sc.N + kBinChunk - 1) / kBinChunk;
+        block_box_kernel<<<nbk, 256, 0, st>>>(sc.position, sc.N, const_cast<float*>(fb.block_box));
+        block_visibility_kernel<<<(B * nbk + 127) / 128, 128, 0, st>>>(cams, g, B, nbk, fb.block_box, const_cast<uint8_t*>(fb.block_skip), fb.stats);
+    }
     if (sc.N > 0) bin_count_kernel<<<grid, kBinThreads, 0, st>>>(sc, cams, g, pr, fb, B);
     bin_scan_kernel<<<B, 1024, 0, st>>>(fb.bin_count, fb.bin_base, fb.bin_cursor, n_keys, 1, fb.view_total, kSubShift);
     entry_base_kernel<<<1, 32, 0, st>>>(fb.view_total, B, fb.entry_base, fb.stats);
