@@ -92,6 +92,9 @@ struct Projected
     bool ok;
 };
 
+// ACT: the scene tensors may be raw parameters (fused texture preparation); compiled separately so that the common case
+// carries none of its code
+template <bool ACT>
 __device__ __forceinline__ Projected project_visible(const ScenePtrs& sc, const CamConst& cam, const Geom& g,
                                                      const TripsRenderParams& pr, size_t bN, int i, float fxc)
 {
@@ -104,7 +107,7 @@ __device__ __forceinline__ Projected project_visible(const ScenePtrs& sc, const 
         if ((unsigned)r.tex < (unsigned)sc.n_tex)
         {
             float c = __ldg(sc.confidence + r.tex);
-            if (pr.confidence_is_raw) c = tm_sigmoid(pr.confidence_scale * c);
+            if (ACT && pr.confidence_is_raw) c = tm_sigmoid(pr.confidence_scale * c);
             if (c < pr.stability_cutoff_value) return r;
         }
     }
@@ -266,6 +269,7 @@ __device__ __forceinline__ int bin_key(const Geom& g, float u, float v)
     return (bin << kSubShift) | (((py >> 2) & 7) << 2) | ((px >> 3) & 3);
 }
 
+template <bool ACT>
 __global__ __launch_bounds__(kBinThreads) void bin_count_kernel(ScenePtrs sc, const CamConst* __restrict__ cams,
                                                                 const __grid_constant__ Geom g, TripsRenderParams pr, FwdBuffers fb, int B)
 {
@@ -286,7 +290,7 @@ __global__ __launch_bounds__(kBinThreads) void bin_count_kernel(ScenePtrs sc, co
         uint32_t* hist  = fb.bin_count + ((size_t)b * g.n_bins << kSubShift);
         for (int i = first + threadIdx.x; i < last; i += blockDim.x)
         {
-            const Projected r = project_visible(sc, cam, g, pr, bN, i, fxc);
+            const Projected r = project_visible<ACT>(sc, cam, g, pr, bN, i, fxc);
             if (r.ok) atomicAdd(hist + bin_key(g, r.u, r.v), 1u);
         }
     }
@@ -364,7 +368,7 @@ __global__ void entry_base_kernel(const uint32_t* __restrict__ view_total, int B
     stats->visible = base;
 }
 
-template <int C>
+template <int C, bool ACT>
 __global__ __launch_bounds__(kBinThreads) void bin_scatter_kernel(ScenePtrs sc, const CamConst* __restrict__ cams,
                                                                   const __grid_constant__ Geom g, TripsRenderParams pr, FwdBuffers fb, int B)
 {
@@ -388,7 +392,7 @@ __global__ __launch_bounds__(kBinThreads) void bin_scatter_kernel(ScenePtrs sc, 
     float* tail      = fb.ent_tail + fb.entry_base[b] * TS;
     for (int i = first + threadIdx.x; i < last; i += blockDim.x)
     {
-        const Projected r = project_visible(sc, cam, g, pr, bN, i, fxc);
+        const Projected r = project_visible<ACT>(sc, cam, g, pr, bN, i, fxc);
         if (!r.ok) continue;
         const uint32_t slot = atomicAdd(cursor + bin_key(g, r.u, r.v), 1u);
         // layers 0..hi, stopping where the 2x2 footprint leaves the layer (RenderForward.cu:342-363)
@@ -407,7 +411,7 @@ __global__ __launch_bounds__(kBinThreads) void bin_scatter_kernel(ScenePtrs sc, 
         if (tex_ok)
         {
             conf = __ldg(sc.confidence + r.tex);
-            if (pr.confidence_is_raw) conf = tm_sigmoid(pr.confidence_scale * conf);  // PrepareConfidence, NeuralTexture.h:40-43
+            if (ACT && pr.confidence_is_raw) conf = tm_sigmoid(pr.confidence_scale * conf);  // PrepareConfidence, NeuralTexture.h:40-43
         }
         else
             atomicOr(&fb.stats->status, TRIPS_DEV_BAD_TEXTURE_INDEX);  // the point is drawn with alpha 0
@@ -420,7 +424,7 @@ __global__ __launch_bounds__(kBinThreads) void bin_scatter_kernel(ScenePtrs sc, 
         float row_t[(C + 3) & ~3];
 #pragma unroll
         for (int c = 0; c < ((C + 3) & ~3); ++c) row_t[c] = (c < C && tex_ok) ? __ldg(sc.texture + (size_t)c * sc.n_tex + r.tex) : 0.f;
-        if (pr.texture_abs)  // PrepareTexture, NeuralTexture.h:45-57
+        if (ACT && pr.texture_abs)  // PrepareTexture, NeuralTexture.h:45-57
         {
 #pragma unroll
             for (int c = 0; c < ((C + 3) & ~3); ++c) row_t[c] = fabsf(row_t[c]);
@@ -450,18 +454,50 @@ cudaError_t launch_bin_points(const ScenePtrs& sc, const CamConst* cams, const G
         block_box_kernel<<<nbk, 256, 0, st>>>(sc.position, sc.N, const_cast<float*>(fb.block_box));
         block_visibility_kernel<<<(B * nbk + 127) / 128, 128, 0, st>>>(cams, g, B, nbk, fb.block_box, const_cast<uint8_t*>(fb.block_skip), fb.stats);
     }
-    if (sc.N > 0) bin_count_kernel<<<grid, kBinThreads, 0, st>>>(sc, cams, g, pr, fb, B);
+    const bool act = pr.confidence_is_raw || pr.texture_abs;
+    if (sc.N > 0)
+    {
+        if (act)
+            bin_count_kernel<true><<<grid, kBinThreads, 0, st>>>(sc, cams, g, pr, fb, B);
+        else
+            bin_count_kernel<false><<<grid, kBinThreads, 0, st>>>(sc, cams, g, pr, fb, B);
+    }
     bin_scan_kernel<<<B, 1024, 0, st>>>(fb.bin_count, fb.bin_base, fb.bin_cursor, n_keys, 1, fb.view_total, kSubShift);
     entry_base_kernel<<<1, 32, 0, st>>>(fb.view_total, B, fb.entry_base, fb.stats);
     if (sc.N > 0)
     {
         switch (sc.C)
         {
-            case 3: bin_scatter_kernel<3><<<grid, kBinThreads, 0, st>>>(sc, cams, g, pr, f2, B); break;
-            case 4: bin_scatter_kernel<4><<<grid, kBinThreads, 0, st>>>(sc, cams, g, pr, f2, B); break;
-            case 6: bin_scatter_kernel<6><<<grid, kBinThreads, 0, st>>>(sc, cams, g, pr, f2, B); break;
-            case 8: bin_scatter_kernel<8><<<grid, kBinThreads, 0, st>>>(sc, cams, g, pr, f2, B); break;
-            case 16: bin_scatter_kernel<16><<<grid, kBinThreads, 0, st>>>(sc, cams, g, pr, f2, B); break;
+            case 3:
+                if (act)
+                    bin_scatter_kernel<3, true><<<grid, kBinThreads, 0, st>>>(sc, cams, g, pr, f2, B);
+                else
+                    bin_scatter_kernel<3, false><<<grid, kBinThreads, 0, st>>>(sc, cams, g, pr, f2, B);
+                break;
+            case 4:
+                if (act)
+                    bin_scatter_kernel<4, true><<<grid, kBinThreads, 0, st>>>(sc, cams, g, pr, f2, B);
+                else
+                    bin_scatter_kernel<4, false><<<grid, kBinThreads, 0, st>>>(sc, cams, g, pr, f2, B);
+                break;
+            case 6:
+                if (act)
+                    bin_scatter_kernel<6, true><<<grid, kBinThreads, 0, st>>>(sc, cams, g, pr, f2, B);
+                else
+                    bin_scatter_kernel<6, false><<<grid, kBinThreads, 0, st>>>(sc, cams, g, pr, f2, B);
+                break;
+            case 8:
+                if (act)
+                    bin_scatter_kernel<8, true><<<grid, kBinThreads, 0, st>>>(sc, cams, g, pr, f2, B);
+                else
+                    bin_scatter_kernel<8, false><<<grid, kBinThreads, 0, st>>>(sc, cams, g, pr, f2, B);
+                break;
+            case 16:
+                if (act)
+                    bin_scatter_kernel<16, true><<<grid, kBinThreads, 0, st>>>(sc, cams, g, pr, f2, B);
+                else
+                    bin_scatter_kernel<16, false><<<grid, kBinThreads, 0, st>>>(sc, cams, g, pr, f2, B);
+                break;
             default: return cudaErrorInvalidValue;
         }
     }
