@@ -248,7 +248,6 @@ cudaError_t launch_setup_cams(const TripsView* d_views, int B, const double* pos
                               int n_cameras, CamConst* cams, DevStats* stats, cudaStream_t st);
 cudaError_t launch_bin_points(const ScenePtrs& sc, const CamConst* cams, const Geom& g, const TripsRenderParams& pr, int B,
                               const FwdBuffers& fb, int sm_count, cudaStream_t st);
-int bin_blocks_per_view(int B, int sm_count);
 size_t resize_scratch_bytes(int64_t n_points);
 cudaError_t launch_resize_points(const int64_t* remove, int64_t n_remove, int64_t n_points, int64_t n_new, const TripsPointTensor* tensors,
                                  int n_tensors, void* scratch, DevStats* stats, int sm_count, cudaStream_t st);

@@ -77,13 +77,14 @@ cudaError_t launch_setup_cams(const TripsView* d_views, int B, const double* pos
 }
 
 // ------------------------------------------------------------------------------------------------------------
-// project + cull + layer select, bucket the visible points of every view by 32x32 screen bin, count fragments
+// project + cull + layer select, and sort the visible points of every view by (32x32 screen bin, 8x4 tile of the bin)
 //
-// Three kernels: (1) count visible points per (view, bin); (2) exclusive scan of the bin counts; (3) project again,
-// take a slot in the bin, write the point's 16-byte-aligned entry there and add 1 to the list length of every
-// pixel its 2x2 footprints touch, on each pyramid layer it is drawn into.  Replaces CountAndCollectTiled
-// (RenderForward.cu:168-366).  Projecting twice costs two coalesced reads of position + size per view and avoids
-// writing and re-reading a per-point record for all N points.
+// Kernels: bounding boxes of blocks of consecutive points and their visibility per view; (1) count the visible points
+// per (view, bin, tile) with one global counter each; (2) exclusive scan of the counters; (3) project again, take a slot
+// in the point's group and write its entry there (head and tail, 32 bytes each).  Replaces the projection part of
+// CountAndCollectTiled (RenderForward.cu:168-366); the list lengths are counted afterwards from the entries
+// (window_kernel<false>).  Projecting twice costs two coalesced reads of position + size per view and avoids writing
+// and re-reading a per-point record for all N points.
 // ------------------------------------------------------------------------------------------------------------
 struct Projected
 {
@@ -435,7 +436,6 @@ __global__ __launch_bounds__(kBinThreads) void bin_scatter_kernel(ScenePtrs sc, 
     }
 }
 
-int bin_blocks_per_view(int B, int sm_count) { return max(4, min(256, (TRIPS_BIN_BLOCKS_PER_SM * sm_count + B - 1) / max(B, 1))); }
 
 cudaError_t launch_bin_points(const ScenePtrs& sc, const CamConst* cams, const Geom& g, const TripsRenderParams& pr, int B,
                               const FwdBuffers& fb, int sm_count, cudaStream_t st)
