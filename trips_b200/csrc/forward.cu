@@ -1154,7 +1154,10 @@ __global__ __launch_bounds__(kSbThreads, (C <= 8 ? TRIPS_SB_MIN_BLOCKS : 1)) voi
                     const u64 mine  = ((u64)f.y << 32) | f.x;
                     const uint2* kp = reinterpret_cast<const uint2*>(frags + cur.seg_start);
                     int rank        = 0;
-#pragma unroll 4
+#ifndef TRIPS_RANK_UNROLL
+#define TRIPS_RANK_UNROLL 4
+#endif
+#pragma unroll TRIPS_RANK_UNROLL
                     for (uint32_t i = 0; i < cur.seg_cnt; ++i)
                     {
                         const uint2 o = kp[(size_t)i * 2];
@@ -1385,7 +1388,10 @@ cudaError_t launch_sort_blend(const ScenePtrs& sc, const Geom& g, const TripsRen
     const unsigned n_tiles = (unsigned)g.n_tiles * (unsigned)B;
     cudaError_t e          = cudaMemsetAsync(fb.ticket, 0, sizeof(unsigned), st);
     if (e != cudaSuccess) return e;
-    int blocks = (int)min((unsigned)(sm_count * 16), (n_tiles + kSbWarps - 1) / kSbWarps);
+#ifndef TRIPS_SB_BLOCKS_PER_SM
+#define TRIPS_SB_BLOCKS_PER_SM 16
+#endif
+    int blocks = (int)min((unsigned)(sm_count * TRIPS_SB_BLOCKS_PER_SM), (n_tiles + kSbWarps - 1) / kSbWarps);
     blocks     = max(blocks, 1);
     switch (sc.C)
     {
