@@ -980,6 +980,10 @@ constexpr int kSortedPad = 17;   // row pitch (entries) of the per-pixel sorted 
 #ifndef TRIPS_SB_THREADS
 #define TRIPS_SB_THREADS 128
 #endif
+#ifndef TRIPS_RANK_UNROLL
+#define TRIPS_RANK_UNROLL 4
+#endif
+constexpr int kRankUnroll = TRIPS_RANK_UNROLL;
 constexpr int kSbThreads = TRIPS_SB_THREADS;
 constexpr int kSbWarps   = kSbThreads / 32;
 
@@ -1154,10 +1158,7 @@ __global__ __launch_bounds__(kSbThreads, (C <= 8 ? TRIPS_SB_MIN_BLOCKS : 1)) voi
                     const u64 mine  = ((u64)f.y << 32) | f.x;
                     const uint2* kp = reinterpret_cast<const uint2*>(frags + cur.seg_start);
                     int rank        = 0;
-#ifndef TRIPS_RANK_UNROLL
-#define TRIPS_RANK_UNROLL 4
-#endif
-#pragma unroll TRIPS_RANK_UNROLL
+#pragma unroll kRankUnroll
                     for (uint32_t i = 0; i < cur.seg_cnt; ++i)
                     {
                         const uint2 o = kp[(size_t)i * 2];
