@@ -150,3 +150,30 @@ def test_bench_helpers():
     cs.proc = type("P", (), {"terminate": lambda self: None, "wait": lambda self, timeout=0: None})()
     out = cs.stop()
     assert out["sm_mhz"] == 1882.5 and out["reasons"] == ["sw_power_cap"] and out["sm_max_mhz"] == 1965
+
+
+def test_ctypes_structs_match_the_header_layout(tmp_path):
+    """Every struct of include/trips_b200.h as the C compiler lays it out (size and the offset of every field) against
+    the ctypes mirror in trips_b200/_lib.py: a field added on one side only would shift everything after it silently."""
+    import ctypes as C
+    import subprocess
+
+    from trips_b200 import _lib
+    structs = {"TripsScene": _lib.TripsScene, "TripsView": _lib.TripsView, "TripsRenderParams": _lib.TripsRenderParams,
+               "TripsGrads": _lib.TripsGrads, "TripsStats": _lib.TripsStats, "TripsAdamTensor": _lib.TripsAdamTensor,
+               "TripsAdamSegment": _lib.TripsAdamSegment, "TripsPointTensor": _lib.TripsPointTensor}
+    lines = ['#include <stdio.h>', '#include <stddef.h>', '#include "trips_b200.h"', 'int main(void) {']
+    for name, st in structs.items():
+        lines.append(f'  printf("{name} %zu\\n", sizeof({name}));')
+        for field, _ in st._fields_:
+            lines.append(f'  printf("{name}.{field} %zu\\n", offsetof({name}, {field}));')
+    lines += ['  return 0;', '}']
+    src = tmp_path / "layout.c"
+    src.write_text("\n".join(lines))
+    exe = tmp_path / "layout"
+    subprocess.run(["gcc", "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe)], check=True)
+    out = dict(l.split() for l in subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.splitlines())
+    for name, st in structs.items():
+        assert int(out[name]) == C.sizeof(st), name
+        for field, _ in st._fields_:
+            assert int(out[f"{name}.{field}"]) == getattr(st, field).offset, f"{name}.{field}"
