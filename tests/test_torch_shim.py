@@ -21,7 +21,7 @@ def test_shim_registers_class_and_operator(shim):
     info.add_image(96, 64, 0, 0, 0, [1.0, 1.0, 0.0, 0.0, 0.0], [1.0, 0.0, 0.0, 1.0])
     info.clear_images()
     assert info.last_status() == 0  # no context yet: nothing raised
-    assert hasattr(torch.ops.trips_b200, "blend_point_cloud")
+    assert hasattr(torch.ops.trips_b200, "blend_point_cloud") and hasattr(torch.ops.trips_b200, "adam_step")
     with pytest.raises(RuntimeError):
         info.add_image(96, 64, 0, 0, 0, [1.0], [1.0, 0.0, 0.0, 1.0])
 
@@ -73,3 +73,29 @@ def test_shim_matches_python_mirror(shim, cuda_lib):
     for k, v in ref_grad.items():
         scale = float(v.abs().max())
         assert float((got[k] - v).abs().max()) <= 1e-4 * max(scale, 1e-30), k
+
+
+@pytest.mark.gpu
+def test_shim_adam_step_matches_python_myadam(shim, cuda_lib):
+    torch = shim
+    from trips_b200.optim import MyAdam
+    from trips_b200.renderer import PointRendererCache
+    dev = torch.device("cuda")
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(11)
+    shapes = [(4, 3001), (1, 3001), (3001, 4), (3001, 1)]
+    ws = [torch.randn(s, device=dev, generator=gen) for s in shapes]
+    ref = [torch.nn.Parameter(w.clone()) for w in ws]
+    opt = MyAdam(ref, lr=1e-3, betas=(0.9, 0.999), cache=PointRendererCache(dev))
+    m = [torch.zeros_like(w) for w in ws]
+    v = [torch.zeros_like(w) for w in ws]
+    st = [torch.zeros(w.shape, dtype=torch.int32, device=dev) for w in ws]
+    for _ in range(3):
+        gs = [torch.randn(w.shape, device=dev, generator=gen) * (torch.rand(w.shape, device=dev, generator=gen) < 0.5) for w in ws]
+        for p, g in zip(ref, gs):
+            p.grad = g.clone()
+        opt.step()
+        torch.ops.trips_b200.adam_step(ws, gs, m, v, st, 1e-3, 0.9, 0.999, 1e-8)
+    for w, p in zip(ws, ref):
+        assert torch.equal(w, p.detach())  # the same kernel behind both host sides
+    assert int(st[0].max()) == 3 and int(st[0].min()) >= 0

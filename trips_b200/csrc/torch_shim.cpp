@@ -5,8 +5,8 @@
 // reference reaches its tensors through NeuralScene modules; here the info object holds the same tensors directly
 // (texture, background_color, t_position, poses_se3, intrinsics, confidence_value_of_point, t_point_size, t_index).
 // Tensors are flattened to device pointers and handed to trips_forward / trips_backward on the current CUDA stream;
-// nothing is computed in this file.  Registered as torch.classes.trips_b200.NeuralRenderInfo and
-// torch.ops.trips_b200.blend_point_cloud, which is how tests/ drive it.
+// nothing is computed in this file.  Registered as torch.classes.trips_b200.NeuralRenderInfo,
+// torch.ops.trips_b200.blend_point_cloud and torch.ops.trips_b200.adam_step (MyAdam::step), which is how tests/ drive it.
 #include <c10/cuda/CUDAStream.h>
 #include <torch/custom_class.h>
 #include <torch/torch.h>
@@ -209,6 +209,35 @@ std::vector<Tensor> BlendPointCloud(const c10::intrusive_ptr<NeuralRenderInfo>& 
                               info->t_point_size, torch::IValue(info));
 }
 
+// MyAdam::step over a list of parameter tensors (MyAdam.cu:164-345 launches adam_step once per tensor; here one launch
+// covers all of them).  State tensors are those MyAdam keeps per parameter: first_moments, second_moments (float32,
+// shape of the parameter) and param_steps (int32 here, int64 in the reference).  Updates weights and state in place.
+void AdamStep(std::vector<Tensor> weights, std::vector<Tensor> gradients, std::vector<Tensor> first_moments,
+              std::vector<Tensor> second_moments, std::vector<Tensor> steps, double lr, double beta1, double beta2, double eps)
+{
+    const size_t n = weights.size();
+    TORCH_CHECK(n > 0 && n <= TRIPS_ADAM_STATIC_MAX_TENSORS, "1 to ", TRIPS_ADAM_STATIC_MAX_TENSORS, " tensors per call");
+    TORCH_CHECK(gradients.size() == n && first_moments.size() == n && second_moments.size() == n && steps.size() == n,
+                "one gradient and one state triple per weight tensor");
+    std::vector<TripsAdamTensor> table(n);
+    for (size_t i = 0; i < n; ++i)
+    {
+        check_tensor(weights[i], torch::kFloat32, "weights");
+        check_tensor(gradients[i], torch::kFloat32, "gradients");
+        check_tensor(first_moments[i], torch::kFloat32, "first_moments");
+        check_tensor(second_moments[i], torch::kFloat32, "second_moments");
+        check_tensor(steps[i], torch::kInt32, "param_steps");
+        const int64_t k = weights[i].numel();
+        TORCH_CHECK(gradients[i].numel() == k && first_moments[i].numel() == k && second_moments[i].numel() == k && steps[i].numel() == k,
+                    "gradient and state must have the parameter's size");
+        table[i] = TripsAdamTensor{weights[i].data_ptr<float>(), gradients[i].data_ptr<float>(), first_moments[i].data_ptr<float>(),
+                                   second_moments[i].data_ptr<float>(), steps[i].data_ptr<int32_t>(), k, (float)lr, (float)beta1, (float)beta2,
+                                   (float)eps, 0.f, 0.f, 0.f, 0.f, 3.4028234663852886e38f};
+    }
+    const int st = trips_adam_step_static(table.data(), (int)n, c10::cuda::getCurrentCUDAStream().stream());
+    TORCH_CHECK(st == TRIPS_OK, "trips_adam_step_static: ", trips_status_string(st));
+}
+
 TORCH_LIBRARY(trips_b200, m)
 {
     m.class_<NeuralRenderInfo>("NeuralRenderInfo")
@@ -219,5 +248,8 @@ TORCH_LIBRARY(trips_b200, m)
         .def("set_params", &NeuralRenderInfo::set_params)
         .def("last_status", &NeuralRenderInfo::last_status);
     m.def("blend_point_cloud(__torch__.torch.classes.trips_b200.NeuralRenderInfo info, Tensor pose_tangents) -> Tensor[]", &BlendPointCloud);
+    m.def("adam_step(Tensor[] weights, Tensor[] gradients, Tensor[] first_moments, Tensor[] second_moments, Tensor[] steps, float lr, "
+          "float beta1, float beta2, float eps) -> ()",
+          &AdamStep);
 }
 }  // namespace trips_shim
