@@ -49,6 +49,22 @@ def _variants():
     s.texture[:] = s.texture[:, order]
     s.confidence[:] = s.confidence.reshape(-1)[order].reshape(s.confidence.shape)
     v["sorted_cloud_block_culling"] = (s, {}, None)
+    # seeded random corners of the parameter space: K = 1 / 4, L = 2 / 5 / 6 / 7, odd image sizes, texture index, drop-out
+    rr = np.random.default_rng(2024)
+    for i in range(8):
+        L = int(rr.choice([1, 2, 3, 5, 6, 7, 8]))
+        K = int(rr.choice([1, 4, 8, 16]))
+        C = int(rr.choice([3, 4, 6, 8, 16]))
+        w_, h_ = int(rr.integers(33, 130)), int(rr.integers(17, 90))
+        n = int(rr.integers(200, 12000))
+        hi = float(rr.choice([0.05, 0.4, 1.2]))
+        sc = scenes.tiny(seed=100 + i, n_points=n, width=w_, height=h_, num_layers=L, k_keep=K, n_views=int(rr.integers(1, 4)),
+                         channels=C, size_range=(2e-3, hi), fx=float(rr.choice([40.0, 90.0, 160.0])))
+        kw = {}
+        if rr.random() < 0.3:
+            kw = dict(drop_out_points_by_radius=True, drop_out_radius_threshold=float(rr.choice([1.0, 3.0])))
+        idx = rr.permutation(n).astype(np.int32) if rr.random() < 0.4 else None
+        v[f"rnd_{i}_L{L}_K{K}_C{C}_{w_}x{h_}"] = (sc, kw, idx)
     return v
 
 
