@@ -34,9 +34,10 @@ typedef enum
 /* Bits of the device status word (trips_last_status): conditions the reference would assert on. */
 #define TRIPS_DEV_BAD_TEXTURE_INDEX 1u /* RenderBackward.cu:217-218 */
 #define TRIPS_DEV_NONZERO_DISTORTION 2u /* distortion model not implemented: coefficients were ignored */
-#define TRIPS_DEV_FRAGMENT_OVERFLOW 4u /* a view's fragment count exceeded the list buffer */
+#define TRIPS_DEV_FRAGMENT_OVERFLOW 4u /* a view's fragments did not fit the list buffer (sized from the previous call): the view was rendered as background; the next call grows the buffer */
 #define TRIPS_DEV_BAD_FRAGMENT 8u /* a fragment referred to a point outside the view's visible set (internal error) */
 #define TRIPS_DEV_BAD_POINT_INDEX 16u /* trips_resize_points: a removal index is out of range or listed twice */
+#define TRIPS_DEV_ENTRY_OVERFLOW 32u /* a view's visible points did not fit the entry arrays (sized from the previous call): same handling as TRIPS_DEV_FRAGMENT_OVERFLOW */
 
 typedef struct TripsContext TripsContext;
 
@@ -212,15 +213,17 @@ int trips_resize_points(TripsContext* ctx, const int64_t* indices_to_remove, int
                         const TripsPointTensor* tensors, int n_tensors, void* stream);
 
 /* No counterpart in the reference.  Same update as trips_adam_step for callers that cannot allocate device
- * memory at the time of the step: code running while the application's own pool owns all free memory, hosts that
- * forbid cudaMalloc after start-up, or a step issued inside a stream capture.  The table describing the tensors,
- * which trips_adam_step keeps in cudaMalloc'ed context scratch, lives here in a fixed array inside the library's
- * device image, so the call performs no cudaMalloc / cudaFree and needs no TripsContext.
+ * memory at the time of the step: code running while the application's own pool owns all free memory, or hosts that
+ * forbid cudaMalloc after start-up.  The table describing the tensors, which trips_adam_step keeps in cudaMalloc'ed
+ * context scratch, lives here in a fixed array inside the library's device image, so the call performs no
+ * cudaMalloc / cudaFree and needs no TripsContext.
  * Limits and rules: at most TRIPS_ADAM_STATIC_MAX_TENSORS tensors per call (more returns TRIPS_ERR_TOO_LARGE); the
  * array costs about 6 KB on every GPU that loads the library, until the process exits; the first call on a device
  * looks up the array's device address (with that device current) and should be made before any stream capture;
- * all calls on a device share the one array, which is rewritten by each call, so two calls that may overlap on
- * the GPU (different streams without ordering) race on it and must be serialised by the caller. */
+ * the table is uploaded from the call's own stack frame, so a stream that is being captured is refused with
+ * TRIPS_ERR_UNSUPPORTED and nothing is enqueued; all calls on a device share the one array, which is rewritten by
+ * each call, so two calls that may overlap on the GPU (different streams without ordering) race on it and must be
+ * serialised by the caller. */
 #define TRIPS_ADAM_STATIC_MAX_TENSORS 64
 int trips_adam_step_static(const TripsAdamTensor* tensors, int n_tensors, void* stream);
 

@@ -71,6 +71,10 @@ def lib():
         L.or_sigmoid.restype = None
         L.or_sigmoid.argtypes = [C.c_void_p, C.c_float, C.c_void_p, C.c_longlong]
         L.or_set_threads.argtypes = [C.c_int]
+        L.or_layer_divergence.restype = None
+        L.or_layer_divergence.argtypes = [C.c_void_p, C.POINTER(OrScene), C.POINTER(OrView), C.POINTER(OrParams), C.c_void_p]
+        L.or_math_sweep.restype = None
+        L.or_math_sweep.argtypes = [C.c_uint32, C.POINTER(C.c_double), C.POINTER(C.c_double)]
         _lib = L
     return _lib
 
@@ -183,6 +187,21 @@ class Frame:
                           _ptr(out["texture"]), _ptr(out["confidence"]), _ptr(out["position"]), _ptr(out["point_size"]),
                           _ptr(out["background"]), _ptr(out["pose"]), _ptr(out["intrinsics"]))
         return out
+
+
+def layer_divergence(frame: "Frame") -> dict:
+    """How many visible points of the frame would pick other pyramid layers with the host libm (see trips_oracle.h)."""
+    out = np.zeros(6, np.int64)
+    lib().or_layer_divergence(frame._h, C.byref(frame.scene.struct), C.byref(frame.view), C.byref(frame.params), _ptr(out))
+    return dict(zip(("visible", "ps_gt_1", "ceil_log2_differs", "floor_log2_differs", "layers_differ_with_libm_softplus",
+                     "softplus_bits_differ"), (int(x) for x in out)))
+
+
+def math_sweep(stride: int = 64):
+    """(max ulp error of the reproducible exp, of the reproducible log) against double-precision libm."""
+    a, b = C.c_double(), C.c_double()
+    lib().or_math_sweep(int(stride), C.byref(a), C.byref(b))
+    return a.value, b.value
 
 
 def forward(scene: SceneArrays, view: OrView, params: OrParams) -> Frame:

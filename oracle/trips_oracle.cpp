@@ -276,12 +276,10 @@ OrFrame* or_forward(const OrScene* sc, const OrView* view, const OrParams* pr)
         int tex = sc->index ? sc->index[i] : i;
         if (pr->viewer_only)
         {
-            if (sc->confidence[tex] < pr->stability_cutoff_value) continue;  // discard_point_for_confidence
+            if (sc->confidence[tex] < pr->stability_cutoff_value) continue;  // discard_point_for_confidence, RenderForward.cu:122-130
         }
-        else if (pr->train && sc->dropout)
-        {
-            if (sc->dropout[i] == 1.f) continue;
-        }
+        // the drop-out mask applies in training whether or not viewer_only is set (second test at RenderForward.cu:236-240)
+        if (pr->train && sc->dropout && sc->dropout[i] == 1.f) continue;
         float s = tm_softplus(sc->point_size[i]);
         float u, v, z;
         project(cam, sc->position + (size_t)i * 4, u, v, z);
@@ -684,6 +682,91 @@ void or_adam(int64_t n, float* w, const float* g, float* m, float* v, int64_t* s
         if (clip != 0.f) nw = nw < -clip ? -clip : (clip < nw ? clip : nw);
         w[i] = nw;
     }
+}
+
+// ---- diagnostics for the parity report (no counterpart in the reference) ----
+// How often the exact-bits ceil(log2(ps)) used by both this oracle and the CUDA library differs from the reference's
+// expression ceil(log2f(ps)) (RenderForward.cu:345) evaluated with the host libm, and how often the number of pyramid
+// layers of a point would change if softplus were evaluated with libm's expf / logf instead of the reproducible
+// routines.  out[0] = visible points, out[1] = visible points with ps > 1, out[2] = points whose ceil(log2) differs,
+// out[3] = points whose floor(log2) differs, out[4] = points whose layer count (before the footprint test) differs
+// with a libm softplus, out[5] = points where tm_softplus and the libm softplus differ in any bit.
+void or_layer_divergence(const OrFrame* f, const OrScene* sc, const OrView* view, const OrParams* pr, int64_t* out)
+{
+    const Cam cam   = make_cam(view);
+    const float fxc = cam.fx * cam.cfx;
+    const int L     = pr->num_layers;
+    int64_t vis = 0, big = 0, dceil = 0, dfloor = 0, dlayers = 0, dsoft = 0;
+#pragma omp parallel for schedule(static) reduction(+ : vis, big, dceil, dfloor, dlayers, dsoft)
+    for (int i = 0; i < f->N; ++i)
+    {
+        const float z = f->depth[i];
+        if (!(z > 0.f)) continue;
+        ++vis;
+        const float ps = f->rec[(size_t)i * 4 + 2];
+        const float x  = sc->point_size[i];
+        const float sp_libm = x > 20.f ? x : std::log(1.f + std::exp(x));  // float overloads of libm
+        if (tm_float_to_bits(sp_libm) != tm_float_to_bits(tm_softplus(x))) ++dsoft;
+        const float ps_libm = fxc * sp_libm / z;
+        int hi = 0, hi_libm = 0;
+        if (ps > 1.f)
+        {
+            ++big;
+            const int c_bits = tm_ceil_log2(ps), c_libm = (int)std::ceil(std::log2(ps));
+            const int f_bits = tm_floor_log2(ps), f_libm = (int)std::floor(std::log2(ps));
+            if (c_bits != c_libm) ++dceil;
+            if (f_bits != f_libm) ++dfloor;
+            hi = std::min(c_bits, L - 1);
+        }
+        if (ps_libm > 1.f) hi_libm = std::min((int)std::ceil(std::log2(ps_libm)), L - 1);
+        if (hi != hi_libm) ++dlayers;
+    }
+    out[0] = vis;
+    out[1] = big;
+    out[2] = dceil;
+    out[3] = dfloor;
+    out[4] = dlayers;
+    out[5] = dsoft;
+}
+
+// Largest error, in units of the last place of the double-precision libm result rounded to float, of tm_expf over
+// [-87, 88] and of tm_logf over the positive normal floats, visiting every `stride`-th float.  This is the check of
+// the reproducible routines (shared with the CUDA library) against an independent implementation.
+void or_math_sweep(uint32_t stride, double* max_ulp_exp, double* max_ulp_log)
+{
+    if (stride == 0) stride = 1;
+    auto ulp_of = [](float r) {
+        uint32_t b = tm_float_to_bits(std::fabs(r));
+        float up   = tm_bits_to_float(b + 1);
+        return (double)up - (double)std::fabs(r);
+    };
+    double me = 0.0, ml = 0.0;
+    const uint32_t pos_hi = tm_float_to_bits(88.0f), neg_hi = tm_float_to_bits(-87.0f);
+#pragma omp parallel for schedule(static) reduction(max : me)
+    for (int64_t k = 0; k <= (int64_t)(pos_hi / stride); ++k)
+    {
+        const float x = tm_bits_to_float((uint32_t)k * stride);
+        const double ref = std::exp((double)x);
+        me = std::max(me, std::fabs((double)tm_expf(x) - ref) / ulp_of((float)ref));
+    }
+#pragma omp parallel for schedule(static) reduction(max : me)
+    for (int64_t k = 0; k <= (int64_t)((neg_hi - 0x80000000u) / stride); ++k)
+    {
+        const float x = tm_bits_to_float(0x80000000u + (uint32_t)k * stride);
+        const double ref = std::exp((double)x);
+        me = std::max(me, std::fabs((double)tm_expf(x) - ref) / ulp_of((float)ref));
+    }
+#pragma omp parallel for schedule(static) reduction(max : ml)
+    for (int64_t k = 0; k <= (int64_t)((0x7f7fffffu - 0x00800000u) / stride); ++k)
+    {
+        const float y = tm_bits_to_float(0x00800000u + (uint32_t)k * stride);
+        const double ref = std::log((double)y);
+        const float rf   = (float)ref;
+        const double u   = rf == 0.f ? 1.4e-45 : ulp_of(rf);
+        ml = std::max(ml, std::fabs((double)tm_logf(y) - ref) / std::max(u, 1e-45));
+    }
+    *max_ulp_exp = me;
+    *max_ulp_log = ml;
 }
 
 }  // extern "C"

@@ -89,6 +89,13 @@ float or_expf(float x);
 float or_logf(float x);
 void or_project(const OrView* view, const float* p3, float* u, float* v, float* z);
 
+/* diagnostics for the parity report: out[6] = visible points, visible with ps > 1, points whose exact-bits ceil(log2 ps)
+ * differs from ceil(log2f(ps)) of the host libm (RenderForward.cu:345), the same for floor, points whose layer count
+ * would change with a libm softplus, points whose softplus differs in any bit from the libm one */
+void or_layer_divergence(const OrFrame* f, const OrScene* scene, const OrView* view, const OrParams* params, int64_t* out);
+/* largest error (ulp of the float result) of the reproducible exp / log against double-precision libm, every stride-th float */
+void or_math_sweep(uint32_t stride, double* max_ulp_exp, double* max_ulp_log);
+
 #ifdef __cplusplus
 }
 #endif

@@ -294,8 +294,8 @@ def test_error_paths(cuda_lib):
 
 
 def test_config2_full_size_properties(cuda_lib):
-    """Config 2 in full (2 M points, 4 views 1280x720, 6 layers, K = 16), where the CPU oracle would take minutes:
-    size-independent properties instead of element-wise parity.  (1) the counters agree with one another; (2) every
+    """Config 2 in full (2 M points, 4 views 1280x720, 6 layers, K = 16): size-independent properties, in addition to the
+    element-wise comparison of test_gpu_fullsize.py.  (1) the counters agree with one another; (2) every
     kept list is sorted by (depth, point id) and has min(length, K) elements; (3) the forward pass is deterministic bit
     for bit although list slots are handed out by atomics; (4) the backward pass is linear in the incoming gradient;
     (5) a zero gradient gives zero gradients."""
@@ -402,3 +402,167 @@ def test_fused_texture_preparation(oracle_lib, cuda_lib, with_index):
     assert rel_err(ns.texture.confidence_raw.grad.reshape(-1).cpu().numpy(), ref_conf_raw) <= TOL_GRAD
     assert rel_err(ns.texture.texture_raw.grad.cpu().numpy(), ref_tex_raw) <= TOL_GRAD
     assert np.all(ns.texture.texture_raw.grad[:, :7].cpu().numpy() == 0)
+
+
+def _render_pair(s, okw, gkw, dropout=None, train=True):
+    """Oracle frames and GPU outputs of one scene with the given flags; dropout: [views, points] mask or None."""
+    import torch
+    frames = []
+    for v in range(s.n_views):
+        import oracle
+        sa = oracle.SceneArrays.from_scene(s, dropout=None if dropout is None else dropout[v])
+        p = oracle.make_params(s.num_layers, s.k_keep, train, **okw)
+        frames.append(oracle.forward(sa, oracle.make_view(s.width, s.height, s.poses[v], s.intrinsics[v]), p))
+    ns, info, blend = gpu_render(s, train=train, **gkw)
+    if dropout is not None:
+        info.cache.dropout_points = torch.from_numpy(np.ascontiguousarray(dropout, dtype=np.float32)).cuda()
+    return frames, ns, info, blend
+
+
+def _compare_forward(s, frames, info, outs, train=True):
+    for b, f in enumerate(frames):
+        depth, nl, _ = info.cache.debug_points(b, s.n_points)
+        odepth, onl, _ = f.points()
+        assert np.array_equal(depth.view(np.uint32), odepth.view(np.uint32)), "depth differs"
+        assert np.array_equal(nl, onl), "layer counts differ"
+        counts, offsets, frags = info.cache.debug_lists(b, f.P)
+        ocounts, ooffsets, ofrags = f.lists()
+        assert np.array_equal(counts, ocounts) and np.array_equal(offsets, ooffsets)
+        assert np.array_equal(sort_lists(counts, offsets, frags), ofrags), "fragment lists differ"
+        if train:
+            nrec, pid, alpha = info.cache.debug_records(b, f.P)
+            onrec, opid, oalpha = f.records()
+            assert np.array_equal(nrec, onrec) and np.array_equal(pid, opid)
+        for l, o in enumerate(f.pyramid()):
+            got = outs[l][b].detach().cpu().numpy()
+            assert np.max(np.abs(got - o) / np.maximum(np.abs(o), 1e-3)) <= TOL_PYRAMID
+
+
+def test_viewer_only_discards_unstable_points(oracle_lib, cuda_lib):
+    """viewer_only with a stability cut-off inside the range of the confidences: points below it are not drawn
+    (discard_point_for_confidence, RenderForward.cu:122-130, 224-229).  Inference render, as the viewer does."""
+    import torch
+    s = scenes.tiny(seed=41, n_points=6000)
+    cut = 0.45
+    assert 0.2 < float((s.confidence < cut).mean()) < 0.8
+    flags = dict(viewer_only=True, stability_cutoff_value=cut)
+    frames, ns, info, blend = _render_pair(s, flags, flags, train=False)
+    with torch.no_grad():
+        outs = blend(info)
+    assert info.cache.last_status() == 0
+    _compare_forward(s, frames, info, outs, train=False)
+    kept = s.confidence.reshape(-1) >= cut
+    for b, f in enumerate(frames):
+        depth, _, _ = info.cache.debug_points(b, s.n_points)
+        assert np.all(depth[~kept] == -1.0), "a point below the cut-off was drawn"
+        assert (depth[kept] > 0).any()
+
+
+def test_fixed_dropout_mask(oracle_lib, cuda_lib):
+    """A drop-out mask handed to both sides (RenderForward.cu:230-240: a point whose mask value is 1 is skipped in that
+    view, training only): forward intermediates bit for bit, gradients within tolerance, masked points get no gradient
+    from the views that dropped them."""
+    import torch
+    s = scenes.tiny(seed=42, n_points=5000, n_views=3)
+    rng = np.random.default_rng(42)
+    mask = (rng.random((s.n_views, s.n_points)) < 0.35).astype(np.float32)
+    frames, ns, info, blend = _render_pair(s, {}, {}, dropout=mask)
+    for t in (ns.texture.texture_raw, ns.texture.confidence_raw, ns.point_cloud_cuda.t_position, ns.point_cloud_cuda.t_point_size):
+        t.requires_grad_(True)
+    outs = blend(info)
+    assert info.cache.last_status() == 0
+    _compare_forward(s, frames, info, outs)
+    for b in range(s.n_views):
+        depth, _, _ = info.cache.debug_points(b, s.n_points)
+        assert np.all(depth[mask[b] == 1.0] == -1.0)
+    C = s.channels
+    loss, ref = 0, None
+    for b, f in enumerate(frames):
+        g = scenes.target_gradient(s, b)
+        for l, (w, h, base) in enumerate(f.layers):
+            loss = loss + (outs[l][b] * torch.from_numpy(g[C * base:C * (base + w * h)].reshape(C, h, w)).cuda()).sum()
+        r = f.backward(g)
+        ref = r if ref is None else {k: ref[k] + r[k] for k in r}
+    loss.backward()
+    got = dict(texture=ns.texture.texture_raw.grad, confidence=ns.texture.confidence_raw.grad.reshape(-1),
+               position=ns.point_cloud_cuda.t_position.grad, point_size=ns.point_cloud_cuda.t_point_size.grad.reshape(-1))
+    for k, g_ in got.items():
+        assert rel_err(g_.cpu().numpy(), ref[k]) <= TOL_GRAD, k
+    always = mask.min(axis=0) == 1.0  # dropped in every view
+    assert always.any()
+    assert np.all(ns.point_cloud_cuda.t_position.grad.cpu().numpy()[always] == 0)
+
+
+def test_normalize_grads_changes_nothing(cuda_lib):
+    """normalize_grads = true divides the point / pose / intrinsics gradients by hit counts that the reference
+    allocates as zeros and never increments (PointRenderer.cu:226-272; no kernel writes out_gradient_*_count), so its
+    `if (c > 0)` guard (PointRenderer.cu:1193-1230) never passes: the flag is accepted and the gradients are unchanged."""
+    import torch
+    s = scenes.tiny(seed=43, n_points=3000)
+    res = []
+    for flag in (False, True):
+        ns, info, blend = gpu_render(s, train=True, normalize_grads=flag)
+        ns.point_cloud_cuda.t_position.requires_grad_(True)
+        ns.poses.tangent_poses.requires_grad_(True)
+        outs = blend(info)
+        sum((o * o).sum() for o in outs).backward()
+        res.append((ns.point_cloud_cuda.t_position.grad.clone(), ns.poses.tangent_poses.grad.clone()))
+    # (gradients are sums of atomics in arbitrary order: compare within the gradient tolerance)
+    assert rel_err(res[1][0].cpu().numpy(), res[0][0].cpu().numpy()) <= TOL_GRAD
+    assert rel_err(res[1][1].cpu().numpy(), res[0][1].cpu().numpy()) <= TOL_GRAD
+
+
+def test_status_bits_survive_later_calls(cuda_lib):
+    """A device status bit raised by one call is still reported after later forward calls on the context; reading it
+    clears it.  (The reference would have asserted in the first call, RenderBackward.cu:217-218.)"""
+    import torch
+    from trips_b200 import _lib
+    s = scenes.tiny(seed=44, n_points=800)
+    bad = np.arange(s.n_points, dtype=np.int32)
+    bad[5] = s.n_points + 7  # texture column out of range
+    ns, info, blend = gpu_render(s, train=False, index=bad)
+    with torch.no_grad():
+        blend(info)
+        ns.point_cloud_cuda.t_index = torch.arange(s.n_points, dtype=torch.int32, device="cuda").reshape(-1, 1)
+        blend(info)  # a clean call afterwards must not erase the bit
+    assert info.cache.last_status() & _lib.DEV_BAD_TEXTURE_INDEX
+    assert info.cache.last_status() == 0
+
+
+def test_steady_state_sizing_and_overflow(oracle_lib, cuda_lib):
+    """Training calls with unchanged shapes size the entry and fragment buffers from the previous call (x 1.25) and do
+    not wait for their own counts.  (1) A repeated call renders the same bits as the first, sized call.  (2) When the
+    point cloud suddenly needs far more fragments than the buffers hold, the views that do not fit are rendered as
+    background, the status word says so, nothing is written out of bounds, and the next call - whose buffers were grown
+    from the reported need - is exact again."""
+    import torch
+    from trips_b200 import _lib
+    s = scenes.tiny(seed=45, n_points=8000, n_views=2, size_range=(5e-3, 0.02))
+    ns, info, blend = gpu_render(s, train=True)
+    with torch.no_grad():
+        first = [o.clone() for o in blend(info)]          # sized call (waits for its counts)
+        again = [o.clone() for o in blend(info)]          # steady state
+        for a, b_ in zip(first, again):
+            assert torch.equal(a, b_)
+        assert info.cache.last_status() == 0
+        f_small = info.cache.stats()["fragments"]
+        # the same points, four pyramid layers larger each: many times the fragments, same shapes
+        ns.point_cloud_cuda.t_point_size.data += 3.0
+        over = [o.clone() for o in blend(info)]
+        status = info.cache.last_status()
+        assert status & (_lib.DEV_FRAGMENT_OVERFLOW | _lib.DEV_ENTRY_OVERFLOW), "the overflow must be reported"
+        assert info.cache.stats()["fragments"] > 1.25 * f_small
+        bg = ns.texture.background_color.detach()
+        for o in over:  # views that did not fit show the background colour only
+            flat = o.permute(0, 2, 3, 1).reshape(o.shape[0], -1, o.shape[1])
+            empty = (flat == bg).all(dim=2).all(dim=1)
+            assert bool(empty.any())
+        exact = [o.clone() for o in blend(info)]          # buffers grown from the reported need
+        assert info.cache.last_status() == 0
+    s2 = scenes.tiny(seed=45, n_points=8000, n_views=2, size_range=(5e-3, 0.02))
+    s2.point_size[:] = s2.point_size + np.float32(3.0)
+    _, _, frames = oracle_frames(s2, train=True)
+    for b, f in enumerate(frames):
+        for l, o in enumerate(f.pyramid()):
+            got = exact[l][b].cpu().numpy()
+            assert np.max(np.abs(got - o) / np.maximum(np.abs(o), 1e-3)) <= TOL_PYRAMID

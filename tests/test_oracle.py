@@ -299,3 +299,11 @@ def test_oracle_reproduces_frozen_outputs(oracle_lib):
             np.testing.assert_allclose(b, a, rtol=1e-12, atol=0, err_msg=k)  # double accumulators, OpenMP order
         else:
             assert np.array_equal(a.view(np.uint8), b.view(np.uint8)), k
+
+
+def test_reproducible_exp_log_against_libm_sweep(oracle_lib):
+    """tm_expf / tm_logf (shared by the oracle and the CUDA library, and therefore not checked by comparing the two)
+    against double-precision libm over every 16th float of their domains: within 2 units of the last place."""
+    e_exp, e_log = oracle_lib.math_sweep(16)
+    assert e_exp <= 2.0, e_exp
+    assert e_log <= 2.0, e_log

@@ -21,13 +21,15 @@ def oracle_frames(s: scenes.Scene, train=None, views=None, **param_kw):
 
 
 def sort_lists(counts, offsets, frags):
-    """Sort every per-pixel list by its 64-bit key (list order is unspecified; the content is what must match)."""
-    out = frags.copy()
-    long_lists = np.nonzero(counts > 1)[0]
-    for p in long_lists:
-        a, b = offsets[p], offsets[p] + counts[p]
-        out[a:b] = np.sort(out[a:b])
-    return out
+    """Sort every per-pixel list by its 64-bit key (list order is unspecified; the content is what must match).
+    Vectorised: one stable sort by key, then one stable sort by the list a fragment belongs to."""
+    if frags.size == 0:
+        return frags.copy()
+    seg = np.repeat(np.arange(counts.size, dtype=np.int64), counts)
+    assert seg.size == frags.size, "list lengths do not add up to the number of fragments"
+    order = np.argsort(frags, kind="stable")
+    order = order[np.argsort(seg[order], kind="stable")]
+    return frags[order]
 
 
 def gpu_render(s: scenes.Scene, train=None, views=None, index=None, **render_kw):
@@ -56,3 +58,32 @@ def rel_err(a, b, floor=None):
     if floor is None:
         floor = max(1e-30, 1e-2 * np.abs(b).max())
     return float(np.max(np.abs(a - b) / np.maximum(np.abs(b), floor)))
+
+
+def strict_grad_report(a, b, rtol=1e-4):
+    """Element-wise view of a gradient comparison: the share of elements with |a - b| <= rtol |b| (elements where both
+    are exactly zero count as met), the worst absolute error in units of the tensor's largest magnitude, and the worst
+    relative error among the elements above 1e-3 of that magnitude."""
+    a = np.asarray(a, np.float64).reshape(-1)
+    b = np.asarray(b, np.float64).reshape(-1)
+    if b.size == 0:
+        return dict(share_strict=1.0, worst_abs_over_max=0.0, worst_rel_significant=0.0, n=0)
+    scale = max(np.abs(b).max(), 1e-300)
+    diff = np.abs(a - b)
+    met = diff <= rtol * np.abs(b)
+    sig = np.abs(b) > 1e-3 * scale
+    return dict(share_strict=float(met.mean()), worst_abs_over_max=float(diff.max() / scale),
+                worst_rel_significant=float((diff[sig] / np.abs(b[sig])).max()) if sig.any() else 0.0, n=int(b.size))
+
+
+def parity_report(name, record):
+    """Prints one JSON line per full-size parity case (visible with pytest -s / -rP) and, when TRIPS_PARITY_REPORT names
+    a file, appends it there."""
+    import json
+    import os
+    line = json.dumps({"case": name, **record})
+    print("PARITY " + line)
+    path = os.environ.get("TRIPS_PARITY_REPORT")
+    if path:
+        with open(path, "a") as fh:
+            fh.write(line + "\n")

@@ -30,6 +30,9 @@ ERR_TOO_LARGE = -6
 DEV_BAD_TEXTURE_INDEX = 1
 DEV_NONZERO_DISTORTION = 2
 DEV_FRAGMENT_OVERFLOW = 4
+DEV_BAD_FRAGMENT = 8
+DEV_BAD_POINT_INDEX = 16
+DEV_ENTRY_OVERFLOW = 32
 
 
 class TripsScene(C.Structure):

@@ -353,6 +353,23 @@ __global__ __launch_bounds__(kBwdThreads, (C <= 4 ? TRIPS_BWD_MIN_BLOCKS : 1)) v
     }
 }
 
+// The gradient rows of the entries the forward pass wrote start from zero.  Their number is known on the device only
+// (entry_base[B]): the host does not wait for the forward pass's counts.
+__global__ __launch_bounds__(256) void zero_entry_rows_kernel(float4* __restrict__ egrad, const unsigned long long* __restrict__ entry_base, int B,
+                                                              int row_f4)
+{
+    const unsigned long long n = entry_base[B] * (unsigned long long)row_f4;
+    const float4 z             = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (unsigned long long)gridDim.x * blockDim.x)
+        egrad[i] = z;
+}
+
+cudaError_t launch_zero_entry_rows(int C, int B, const FwdBuffers& fb, const BwdBuffers& bb, int sm_count, cudaStream_t st)
+{
+    zero_entry_rows_kernel<<<sm_count * 8, 256, 0, st>>>(reinterpret_cast<float4*>(bb.egrad), fb.entry_base, B, egrad_stride(C) / 4);
+    return cudaGetLastError();
+}
+
 cudaError_t launch_blend_backward(const ScenePtrs& sc, const CamConst* cams, const Geom& g, const TripsRenderParams& pr,
                                   int B, const FwdBuffers& fb, const BwdBuffers& bb, const ConstLayerPtrs& grad_in,
                                   bool want_cam_grads, int sm_count, cudaStream_t st)

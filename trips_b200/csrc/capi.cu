@@ -1,6 +1,7 @@
 // C ABI of libtrips_b200: context (scratch owner), forward, backward, fused Adam and the inspection calls.
 // The host logic here replaces PointRendererCache (src/lib/rendering/PointRenderer.cu:197-528) and the host
 // parts of RenderFast16 / BlendBackwardsBilinearFast / MyAdam::step.
+#include <algorithm>
 #include <cfloat>
 #include <cstdio>
 #include <cstring>
@@ -102,6 +103,12 @@ struct StageTimers
 };
 }  // namespace
 
+struct SizeKey
+{
+    int N, B, w, h, L, C, train;
+    bool operator==(const SizeKey& o) const { return N == o.N && B == o.B && w == o.w && h == o.h && L == o.L && C == o.C && train == o.train; }
+};
+
 struct TripsContext
 {
     StageTimers timers;
@@ -114,20 +121,24 @@ struct TripsContext
     DevBuf egrad, g_point, g_conf_pt, g_small;
     // adam
     DevBuf adam_tab;
-    // pinned host mirror: view_base[B+1] then DevStats
-    void* h_pinned      = nullptr;
-    size_t h_pinned_bytes = 0;
+    // pinned host mirror of DevStats and the event behind which it becomes valid when a call did not wait for it
+    void* h_pinned        = nullptr;
+    cudaEvent_t totals_ev = nullptr;
+    bool pending          = false;  // the totals of the last forward call have not been read yet
+    // sizes the last training call needed, and the shapes they belong to
+    SizeKey size_key{};
+    bool have_sizes                 = false;
+    unsigned long long need_entries = 0, need_frags = 0;
+    int entry_C                     = 0;  // channel count the entry arrays are laid out for
     // state of the last forward call
     bool have_forward = false;
     Geom geom{};
     TripsRenderParams params{};
     int B = 0, N = 0, n_tex = 0, C = 0;
     int nchunks = 0;
-    unsigned long long total_frags = 0;
     int rank_points = -1;                  // number of points the spatial ranks were computed for (-1: none yet)
     int rank_age    = 0;                   // training forward passes since then
     size_t entry_cap = 0;                  // entries the two entry arrays (head | tail, in this order) are laid out for
-    unsigned long long total_entries = 0;  // visible points summed over the views of the last forward call
     TripsStats host_stats{};
 };
 
@@ -210,6 +221,23 @@ static FwdBuffers fwd_buffers(TripsContext* c)
     return fb;
 }
 
+// DevStats is allocated once and zeroed then; afterwards only its counters are cleared per call.
+static cudaError_t ensure_stats(TripsContext* c, cudaStream_t st)
+{
+    if (c->stats.p) return cudaSuccess;
+    cudaError_t e = ensure(c->stats, sizeof(DevStats));
+    if (e != cudaSuccess) return e;
+    return cudaMemsetAsync(c->stats.p, 0, sizeof(DevStats), st);
+}
+
+static cudaError_t clear_counters(TripsContext* c, cudaStream_t st)
+{
+    static_assert(offsetof(DevStats, status) + sizeof(unsigned) == offsetof(DevStats, culled_blocks), "the counters lie on either side of the status word");
+    cudaError_t e = cudaMemsetAsync(c->stats.p, 0, offsetof(DevStats, status), st);
+    if (e != cudaSuccess) return e;
+    return cudaMemsetAsync((char*)c->stats.p + offsetof(DevStats, culled_blocks), 0, sizeof(unsigned int), st);
+}
+
 static bool valid_channels(int c) { return c == 3 || c == 4 || c == 6 || c == 8 || c == 16; }
 
 extern "C" {
@@ -259,86 +287,109 @@ void trips_context_destroy(TripsContext* c)
     for (DevBuf* b : all) free_buf(*b);
     c->timers.destroy();
     if (c->h_pinned) cudaFreeHost(c->h_pinned);
+    if (c->totals_ev) cudaEventDestroy(c->totals_ev);
     delete c;
 }
 
-int trips_forward(TripsContext* ctx, const TripsScene* scene, const TripsView* views, int n_views,
-                  const TripsRenderParams* params, float* const* out_layers, void* stream)
+// Geometry of the pyramid and of the tile / bin decompositions for a (w, h, L) image.
+static bool make_geom(int w, int h, int L, Geom& g)
 {
-    if (!ctx) return TRIPS_ERR_INVALID_ARG;
-    if (!scene || !views || !params || !out_layers || n_views < 1) return fail(ctx, TRIPS_ERR_INVALID_ARG, "null argument");
-    if (params->num_layers < 1 || params->num_layers > TRIPS_MAX_LAYERS) return fail(ctx, TRIPS_ERR_INVALID_ARG, "num_layers must be 1..8");
-    if (params->k_keep < 1 || params->k_keep > TRIPS_MAX_KEEP) return fail(ctx, TRIPS_ERR_INVALID_ARG, "k_keep must be 1..16");
-    if (!valid_channels(scene->channels)) return fail(ctx, TRIPS_ERR_INVALID_ARG, "channels must be 3, 4, 6, 8 or 16");
-    if (scene->n_points < 0 || scene->n_tex < 1 || scene->n_images < 1 || scene->n_cameras < 1)
-        return fail(ctx, TRIPS_ERR_INVALID_ARG, "bad scene sizes");
-    if (scene->n_points > 0 && (!scene->position || !scene->point_size)) return fail(ctx, TRIPS_ERR_INVALID_ARG, "null point arrays");
-    if (!scene->index && scene->n_tex < scene->n_points) return fail(ctx, TRIPS_ERR_INVALID_ARG, "without an index the texture needs one column per point");
-    if (!scene->texture || !scene->confidence || !scene->background || !scene->poses || !scene->intrinsics)
-        return fail(ctx, TRIPS_ERR_INVALID_ARG, "null scene arrays");
-    if (!scene->index && scene->n_tex < scene->n_points) return fail(ctx, TRIPS_ERR_INVALID_ARG, "identity index needs n_tex >= n_points");
-    const int w = views[0].w, h = views[0].h;
-    if (w < 2 || h < 2) return fail(ctx, TRIPS_ERR_INVALID_ARG, "image must be at least 2x2");
-    for (int b = 0; b < n_views; ++b)
+    g.L = L;
+    long long base = 0;
+    int lw = w, lh = h;
+    for (int l = 0; l < g.L; ++l)
     {
-        if (views[b].w != w || views[b].h != h) return fail(ctx, TRIPS_ERR_INVALID_ARG, "all views of a call must share (w, h)");
-        if (views[b].camera_model_type != 0) return fail(ctx, TRIPS_ERR_UNSUPPORTED, "only the pinhole camera model is implemented");
-        if (views[b].image_index < 0 || views[b].image_index >= scene->n_images || views[b].camera_index < 0 ||
-            views[b].camera_index >= scene->n_cameras)
-            return fail(ctx, TRIPS_ERR_INVALID_ARG, "view index out of range");
+        g.W[l]    = lw;
+        g.H[l]    = lh;
+        g.base[l] = (int)base;
+        base += (long long)lw * lh;
+        lw = (lw + 1) / 2;  // ceil halving, PointRenderer.cu:385-389
+        lh = (lh + 1) / 2;
     }
-    for (int l = 0; l < params->num_layers; ++l)
-        if (!out_layers[l]) return fail(ctx, TRIPS_ERR_INVALID_ARG, "null output layer");
-    cudaStream_t st = (cudaStream_t)stream;
-    ctx->have_forward = false;
+    for (int l = g.L; l <= TRIPS_MAX_LAYERS; ++l) g.base[l] = (int)base;
+    if (base > (1ll << 30)) return false;
+    g.P = (int)base;
+    static const int kRegTiles[5] = {0, 128, 160, 168, 170};
+    g.reg_layers = g.L < 4 ? g.L : 4;
+    g.reg_x      = (w + 63) / 64;
+    g.reg_tiles  = kRegTiles[g.reg_layers];
+    g.reg_total  = g.reg_x * ((h + 63) / 64) * g.reg_tiles;
+    int tb = g.reg_total;
+    for (int l = 0; l < TRIPS_MAX_LAYERS; ++l)
+    {
+        g.tile_base[l] = tb;
+        g.tiles_x[l]   = 1;
+        if (l >= g.reg_layers && l < g.L)
+        {
+            g.tiles_x[l] = (g.W[l] + kTileW - 1) / kTileW;
+            tb += g.tiles_x[l] * ((g.H[l] + kTileH - 1) / kTileH);
+        }
+    }
+    g.tile_base[TRIPS_MAX_LAYERS] = tb;
+    g.n_tiles = tb;
+    g.bins_x  = ((w - 1) >> kBinShift) + 1;
+    g.bins_y  = ((h - 1) >> kBinShift) + 1;
+    g.n_bins  = g.bins_x * g.bins_y;
+    return true;
+}
 
-    Geom g{};
-    g.L = params->num_layers;
+// The entry arrays (head | tail, in this order) re-laid out for at least `entries` entries.
+static cudaError_t ensure_entries(TripsContext* ctx, size_t entries, int C, double growth)
+{
+    const size_t ES = (size_t)entry_stride(C);
+    if (ctx->entries.p && ctx->entry_C == C && entries <= ctx->entry_cap) return cudaSuccess;
+    const size_t want = (size_t)((double)(entries > 0 ? entries : 1) * growth) + 1;
+    cudaError_t e = ensure(ctx->entries, sizeof(float) * ES * want + 16);
+    if (e != cudaSuccess)
     {
-        long long base = 0;
-        int lw = w, lh = h;
-        for (int l = 0; l < g.L; ++l)
-        {
-            g.W[l]    = lw;
-            g.H[l]    = lh;
-            g.base[l] = (int)base;
-            base += (long long)lw * lh;
-            lw = (lw + 1) / 2;  // ceil halving, PointRenderer.cu:385-389
-            lh = (lh + 1) / 2;
-        }
-        for (int l = g.L; l <= TRIPS_MAX_LAYERS; ++l) g.base[l] = (int)base;
-        if (base > (1ll << 30)) return fail(ctx, TRIPS_ERR_TOO_LARGE, "pyramid has more than 2^30 pixels");
-        g.P = (int)base;
-        static const int kRegTiles[5] = {0, 128, 160, 168, 170};
-        g.reg_layers = g.L < 4 ? g.L : 4;
-        g.reg_x      = (w + 63) / 64;
-        g.reg_tiles  = kRegTiles[g.reg_layers];
-        g.reg_total  = g.reg_x * ((h + 63) / 64) * g.reg_tiles;
-        int tb = g.reg_total;
-        for (int l = 0; l < TRIPS_MAX_LAYERS; ++l)
-        {
-            g.tile_base[l] = tb;
-            g.tiles_x[l]   = 1;
-            if (l >= g.reg_layers && l < g.L)
-            {
-                g.tiles_x[l] = (g.W[l] + kTileW - 1) / kTileW;
-                tb += g.tiles_x[l] * ((g.H[l] + kTileH - 1) / kTileH);
-            }
-        }
-        g.tile_base[TRIPS_MAX_LAYERS] = tb;
-        g.n_tiles = tb;
-        g.bins_x  = ((w - 1) >> kBinShift) + 1;
-        g.bins_y  = ((h - 1) >> kBinShift) + 1;
-        g.n_bins  = g.bins_x * g.bins_y;
+        ctx->entry_cap = 0;
+        return e;
     }
-    const int B       = n_views;
+    ctx->entry_cap = (ctx->entries.bytes - 16) / (sizeof(float) * ES);
+    ctx->entry_C   = C;
+    return cudaSuccess;
+}
+
+// Totals of a forward call whose sizes were not waited for (steady-state training): read them now, publish the
+// statistics, and grow the entry / fragment buffers if that call needed more than they hold (the call itself rendered
+// the views that did not fit as background and raised a status bit).
+static int resolve_pending(TripsContext* ctx)
+{
+    if (!ctx->pending) return TRIPS_OK;
+    ctx->pending = false;
+    CU_CHECK(ctx, cudaEventSynchronize(ctx->totals_ev));
+    const DevStats* hs = (const DevStats*)ctx->h_pinned;
+    ctx->need_entries  = hs->visible;
+    ctx->need_frags    = hs->frag_need;
+    ctx->host_stats.visible_points      = (int64_t)hs->visible;
+    ctx->host_stats.fragments           = (int64_t)hs->frag_need;
+    ctx->host_stats.kept_fragments      = (int64_t)hs->kept;
+    ctx->host_stats.max_list_length     = (int64_t)hs->max_len;
+    ctx->host_stats.culled_point_blocks = (int64_t)hs->culled_blocks;
+    return TRIPS_OK;
+}
+
+namespace
+{
+constexpr double kGrowth      = 1.25;  // head room of the entry / fragment buffers over the counted need
+constexpr int kEvalSubBatch   = 8;     // views rendered per pass when nothing has to be kept for a backward pass
+}  // namespace
+
+// One pass over `B` views (all views of a training call; up to kEvalSubBatch views of an inference call).
+//   wait_for_sizes = true : the entry and fragment buffers are sized from this pass's own counts, which costs two host
+//                           synchronisations (the reference synchronises 2 * num_layers times per view for the same
+//                           purpose, RenderForward.cu:1201-1208);
+//   wait_for_sizes = false: the buffers keep the capacity found by earlier calls (need x 1.25) and nothing is waited
+//                           for: the totals travel to pinned host memory behind an event that the next call reads.
+static int forward_views(TripsContext* ctx, const TripsScene* scene, const TripsView* views, int B, const TripsRenderParams* params,
+                         const Geom& g, float* const* out_layers, size_t out_view_offset, const float* dropout, cudaStream_t st,
+                         bool wait_for_sizes)
+{
     const size_t N    = (size_t)scene->n_points;
     const size_t P    = (size_t)g.P;
     const int C       = scene->channels;
     const int nchunks = (int)((P + kScanChunk - 1) / kScanChunk);
-    if (N * 4ull * g.L >= (1ull << 32)) return fail(ctx, TRIPS_ERR_TOO_LARGE, "a view could hold more than 2^32 fragments");
-    if ((unsigned long long)B * (unsigned long long)g.n_tiles >= (1ull << 32)) return fail(ctx, TRIPS_ERR_TOO_LARGE, "too many pixel tiles");
-    const size_t ES = (size_t)entry_stride(C);
+    const size_t n_box = (N + 8191) / 8192 + 1;
 
     CU_CHECK(ctx, ensure(ctx->views, sizeof(TripsView) * B));
     CU_CHECK(ctx, ensure(ctx->cams, sizeof(CamConst) * B));
@@ -347,16 +398,13 @@ int trips_forward(TripsContext* ctx, const TripsScene* scene, const TripsView* v
     CU_CHECK(ctx, ensure(ctx->view_total, sizeof(uint32_t) * B));
     CU_CHECK(ctx, ensure(ctx->bin_cursor, sizeof(uint32_t) * (size_t)g.n_bins * B));
     CU_CHECK(ctx, ensure(ctx->entry_base, sizeof(unsigned long long) * (B + 1)));
-    CU_CHECK(ctx, ensure(ctx->block_box, sizeof(float) * 6 * ((N + 8191) / 8192 + 1)));
-    CU_CHECK(ctx, ensure(ctx->block_skip, (size_t)B * ((N + 8191) / 8192 + 1)));
-    // entries are sized for the worst case (every point visible in every view): no host round trip is needed to size them
-    CU_CHECK(ctx, ensure(ctx->entries, sizeof(float) * ES * N * B + 16));
-    ctx->entry_cap = (size_t)N * B;
+    CU_CHECK(ctx, ensure(ctx->block_box, sizeof(float) * 6 * n_box));
+    CU_CHECK(ctx, ensure(ctx->block_skip, (size_t)B * n_box));
     CU_CHECK(ctx, ensure(ctx->counts, sizeof(uint32_t) * P * B));
     CU_CHECK(ctx, ensure(ctx->offsets, sizeof(uint32_t) * P * B));
     CU_CHECK(ctx, ensure(ctx->partial, sizeof(uint32_t) * (size_t)nchunks * B));
     CU_CHECK(ctx, ensure(ctx->view_base, sizeof(unsigned long long) * (B + 1)));
-    CU_CHECK(ctx, ensure(ctx->stats, sizeof(DevStats)));
+    CU_CHECK(ctx, ensure_stats(ctx, st));
     CU_CHECK(ctx, ensure(ctx->ticket, sizeof(unsigned) * (size_t)(B > 64 ? B : 64)));
     if (params->train)
     {
@@ -364,16 +412,16 @@ int trips_forward(TripsContext* ctx, const TripsScene* scene, const TripsView* v
         CU_CHECK(ctx, ensure(ctx->records, sizeof(uint2) * 16 * P * B));
     }
     if (ctx->frags.bytes == 0) CU_CHECK(ctx, ensure(ctx->frags, 16 * 1024 * 1024));
-    size_t pinned_need = sizeof(unsigned long long) * (B + 1) + sizeof(DevStats);
-    if (ctx->h_pinned_bytes < pinned_need)
+    if (!ctx->entries.p || ctx->entry_C != C) CU_CHECK(ctx, ensure_entries(ctx, 1024, C, 1.0));
+    if (!ctx->h_pinned)
     {
-        if (ctx->h_pinned) cudaFreeHost(ctx->h_pinned);
-        ctx->h_pinned = nullptr;
-        CU_CHECK(ctx, cudaMallocHost(&ctx->h_pinned, pinned_need * 2));
-        ctx->h_pinned_bytes = pinned_need * 2;
+        CU_CHECK(ctx, cudaMallocHost(&ctx->h_pinned, sizeof(DevStats)));
+        CU_CHECK(ctx, cudaEventCreateWithFlags(&ctx->totals_ev, cudaEventDisableTiming));
     }
+    DevStats* h_stats = (DevStats*)ctx->h_pinned;
 
-    ScenePtrs sp  = scene_ptrs(scene);
+    ScenePtrs sp = scene_ptrs(scene);
+    sp.dropout   = dropout;
     // Spatial ranks of the points (where their gradient rows live, rank.cu): training only; refreshed when the number
     // of points changes and every kRankRefresh forward passes, since points move slowly and a stale rank is still a
     // valid permutation.  Entries carry the rank, so the backward pass of this forward pass sees the same ranks.
@@ -396,54 +444,146 @@ int trips_forward(TripsContext* ctx, const TripsScene* scene, const TripsView* v
     else
         ctx->rank_points = -1;
     FwdBuffers fb = fwd_buffers(ctx);
-    CU_CHECK(ctx, cudaMemsetAsync(ctx->stats.p, 0, sizeof(DevStats), st));
+    // the counters start from zero; the status word keeps the bits raised by earlier calls until trips_last_status reads them
+    CU_CHECK(ctx, clear_counters(ctx, st));
     CU_CHECK(ctx, cudaMemsetAsync(ctx->counts.p, 0, sizeof(uint32_t) * P * B, st));
     // the view table comes from pageable host memory: the copy is staged before the call returns
     CU_CHECK(ctx, cudaMemcpyAsync(ctx->views.p, views, sizeof(TripsView) * B, cudaMemcpyHostToDevice, st));
     STAGE(ctx, TRIPS_STAGE_SETUP, 1, st,
           launch_setup_cams((const TripsView*)ctx->views.p, B, scene->poses, scene->n_images, scene->intrinsics,
                             scene->n_cameras, (CamConst*)ctx->cams.p, fb.stats, st));
-    STAGE(ctx, TRIPS_STAGE_BIN_POINTS, N > 0 ? 6 : 2, st, launch_bin_points(sp, (const CamConst*)ctx->cams.p, g, *params, B, fb, ctx->sm_count, st));
+    const CamConst* cams = (const CamConst*)ctx->cams.p;
+    STAGE(ctx, TRIPS_STAGE_BIN_POINTS, bin_count_launches((int)N, B), st,
+          launch_bin_count(sp, cams, g, *params, B, fb, wait_for_sizes ? ~0ull : (unsigned long long)ctx->entry_cap, ctx->sm_count, st));
+    if (wait_for_sizes)
+    {
+        CU_CHECK(ctx, cudaMemcpyAsync(h_stats, ctx->stats.p, sizeof(DevStats), cudaMemcpyDeviceToHost, st));
+        CU_CHECK(ctx, cudaStreamSynchronize(st));
+        CU_CHECK(ctx, ensure_entries(ctx, (size_t)h_stats->visible, C, kGrowth));
+        fb = fwd_buffers(ctx);
+    }
+    STAGE(ctx, TRIPS_STAGE_BIN_POINTS, bin_scatter_launches((int)N, B), st, launch_bin_scatter(sp, cams, g, *params, B, fb, ctx->sm_count, st));
     if (N > 0) STAGE(ctx, TRIPS_STAGE_COUNT, 1, st, launch_count(sp, g, B, fb, ctx->sm_count, st));
     {
         FwdBuffers fscan = fb;
-        fscan.frag_cap   = ~0ull;  // sizing pass: the list buffer is grown below, nothing can overflow yet
+        if (wait_for_sizes) fscan.frag_cap = ~0ull;  // sizing pass: the list buffer is grown below, nothing can overflow yet
         STAGE(ctx, TRIPS_STAGE_SCAN, 3, st, launch_scan(g, B, params->k_keep, fscan, nchunks, st));
     }
-    // The only host synchronisation of the forward pass: fragment totals of all views, to size the list buffer.
-    // (The reference synchronises 2 * num_layers times per view for the same purpose, RenderForward.cu:1201-1208.)
-    unsigned long long* h_base = (unsigned long long*)ctx->h_pinned;
-    DevStats* h_stats          = (DevStats*)(h_base + (B + 1));
-    CU_CHECK(ctx, cudaMemcpyAsync(h_base, ctx->view_base.p, sizeof(unsigned long long) * (B + 1), cudaMemcpyDeviceToHost, st));
     CU_CHECK(ctx, cudaMemcpyAsync(h_stats, ctx->stats.p, sizeof(DevStats), cudaMemcpyDeviceToHost, st));
-    CU_CHECK(ctx, cudaStreamSynchronize(st));
-    const unsigned long long total = h_base[B];
-    if (total * sizeof(uint4) > ctx->frags.bytes)
+    if (wait_for_sizes)
     {
-        CU_CHECK(ctx, ensure(ctx->frags, (size_t)total * sizeof(uint4), 1.25));
-        fb = fwd_buffers(ctx);
+        CU_CHECK(ctx, cudaStreamSynchronize(st));
+        if ((size_t)h_stats->frag_need * sizeof(uint4) > ctx->frags.bytes)
+        {
+            CU_CHECK(ctx, ensure(ctx->frags, (size_t)h_stats->frag_need * sizeof(uint4), kGrowth));
+            fb = fwd_buffers(ctx);
+        }
+        ctx->need_entries = h_stats->visible;
+        ctx->need_frags   = h_stats->frag_need;
+        ctx->host_stats.visible_points += (int64_t)h_stats->visible;
+        ctx->host_stats.fragments += (int64_t)h_stats->frag_need;
+        ctx->host_stats.kept_fragments += (int64_t)h_stats->kept;
+        ctx->host_stats.max_list_length = std::max<int64_t>(ctx->host_stats.max_list_length, (int64_t)h_stats->max_len);
+        ctx->host_stats.culled_point_blocks += (int64_t)h_stats->culled_blocks;
     }
-    ctx->total_frags   = total;
-    ctx->total_entries = h_stats->visible;
+    else
+    {
+        CU_CHECK(ctx, cudaEventRecord(ctx->totals_ev, st));
+        ctx->pending = true;
+    }
     if (N > 0) STAGE(ctx, TRIPS_STAGE_COLLECT, 1, st, launch_collect(sp, g, B, fb, ctx->sm_count, st));
     LayerPtrs out{};
-    for (int l = 0; l < g.L; ++l) out.p[l] = out_layers[l];
+    for (int l = 0; l < g.L; ++l) out.p[l] = out_layers[l] + out_view_offset * (size_t)C * g.W[l] * g.H[l];
     STAGE(ctx, TRIPS_STAGE_SORT_BLEND, 1, st, launch_sort_blend(sp, g, *params, B, fb, out, ctx->sm_count, st));
-
-    ctx->geom    = g;
-    ctx->params  = *params;
     ctx->B       = B;
-    ctx->N       = (int)N;
-    ctx->n_tex   = scene->n_tex;
-    ctx->C       = C;
     ctx->nchunks = nchunks;
-    ctx->host_stats.visible_points  = (int64_t)h_stats->visible;
-    ctx->host_stats.fragments       = (int64_t)total;
-    ctx->host_stats.kept_fragments  = (int64_t)h_stats->kept;
-    ctx->host_stats.pixels          = (int64_t)P * B;
-    ctx->host_stats.max_list_length = (int64_t)h_stats->max_len;
-    ctx->host_stats.culled_point_blocks = (int64_t)h_stats->culled_blocks;
-    ctx->have_forward          = true;
+    return TRIPS_OK;
+}
+
+int trips_forward(TripsContext* ctx, const TripsScene* scene, const TripsView* views, int n_views,
+                  const TripsRenderParams* params, float* const* out_layers, void* stream)
+{
+    if (!ctx) return TRIPS_ERR_INVALID_ARG;
+    if (!scene || !views || !params || !out_layers || n_views < 1) return fail(ctx, TRIPS_ERR_INVALID_ARG, "null argument");
+    if (params->num_layers < 1 || params->num_layers > TRIPS_MAX_LAYERS) return fail(ctx, TRIPS_ERR_INVALID_ARG, "num_layers must be 1..8");
+    if (params->k_keep < 1 || params->k_keep > TRIPS_MAX_KEEP) return fail(ctx, TRIPS_ERR_INVALID_ARG, "k_keep must be 1..16");
+    if (!valid_channels(scene->channels)) return fail(ctx, TRIPS_ERR_INVALID_ARG, "channels must be 3, 4, 6, 8 or 16");
+    if (scene->n_points < 0 || scene->n_tex < 1 || scene->n_images < 1 || scene->n_cameras < 1)
+        return fail(ctx, TRIPS_ERR_INVALID_ARG, "bad scene sizes");
+    if (scene->n_points > 0 && (!scene->position || !scene->point_size)) return fail(ctx, TRIPS_ERR_INVALID_ARG, "null point arrays");
+    if (!scene->texture || !scene->confidence || !scene->background || !scene->poses || !scene->intrinsics)
+        return fail(ctx, TRIPS_ERR_INVALID_ARG, "null scene arrays");
+    if (!scene->index && scene->n_tex < scene->n_points) return fail(ctx, TRIPS_ERR_INVALID_ARG, "identity index needs n_tex >= n_points");
+    const int w = views[0].w, h = views[0].h;
+    if (w < 2 || h < 2) return fail(ctx, TRIPS_ERR_INVALID_ARG, "image must be at least 2x2");
+    for (int b = 0; b < n_views; ++b)
+    {
+        if (views[b].w != w || views[b].h != h) return fail(ctx, TRIPS_ERR_INVALID_ARG, "all views of a call must share (w, h)");
+        if (views[b].camera_model_type != 0) return fail(ctx, TRIPS_ERR_UNSUPPORTED, "only the pinhole camera model is implemented");
+        if (views[b].image_index < 0 || views[b].image_index >= scene->n_images || views[b].camera_index < 0 ||
+            views[b].camera_index >= scene->n_cameras)
+            return fail(ctx, TRIPS_ERR_INVALID_ARG, "view index out of range");
+    }
+    for (int l = 0; l < params->num_layers; ++l)
+        if (!out_layers[l]) return fail(ctx, TRIPS_ERR_INVALID_ARG, "null output layer");
+    cudaStream_t st = (cudaStream_t)stream;
+    ctx->have_forward = false;
+    {
+        const int rs = resolve_pending(ctx);
+        if (rs != TRIPS_OK) return rs;
+    }
+    Geom g{};
+    if (!make_geom(w, h, params->num_layers, g)) return fail(ctx, TRIPS_ERR_TOO_LARGE, "pyramid has more than 2^30 pixels");
+    const int B    = n_views;
+    const size_t N = (size_t)scene->n_points;
+    if (N * 4ull * g.L >= (1ull << 32)) return fail(ctx, TRIPS_ERR_TOO_LARGE, "a view could hold more than 2^32 fragments");
+    if ((unsigned long long)B * (unsigned long long)g.n_tiles >= (1ull << 32)) return fail(ctx, TRIPS_ERR_TOO_LARGE, "too many pixel tiles");
+
+    const SizeKey key{scene->n_points, B, w, h, params->num_layers, scene->channels, params->train};
+    ctx->host_stats        = TripsStats{};
+    ctx->host_stats.pixels = (int64_t)g.P * B;
+    ctx->geom              = g;
+    ctx->params            = *params;
+    ctx->N                 = (int)N;
+    ctx->n_tex             = scene->n_tex;
+    ctx->C                 = scene->channels;
+    if (params->train)
+    {
+        // Steady state of a training loop: same shapes as the previous training call.  The buffers keep the capacity that
+        // call needed (x 1.25), grown here if its totals (read above, long after they were produced) say so.
+        bool steady = ctx->have_sizes && key == ctx->size_key;
+        if (steady)
+        {
+            if (ctx->need_entries > ctx->entry_cap)
+                steady = ensure_entries(ctx, (size_t)ctx->need_entries, scene->channels, kGrowth) == cudaSuccess;
+            if (steady && (size_t)ctx->need_frags * sizeof(uint4) > ctx->frags.bytes)
+                steady = ensure(ctx->frags, (size_t)ctx->need_frags * sizeof(uint4), kGrowth) == cudaSuccess;
+            (void)cudaGetLastError();
+        }
+        const int rc = forward_views(ctx, scene, views, B, params, g, out_layers, 0, scene->dropout, st, !steady);
+        if (rc != TRIPS_OK)
+        {
+            ctx->have_sizes = false;
+            return rc;
+        }
+        ctx->size_key   = key;
+        ctx->have_sizes = true;
+    }
+    else
+    {
+        // Nothing is kept for a backward pass: the views are rendered kEvalSubBatch at a time, so the scratch of a call
+        // with many views (a batch of 64 evaluation views) is that of kEvalSubBatch views.  The inspection calls then
+        // describe the last sub-batch.
+        ctx->have_sizes = false;
+        for (int b0 = 0; b0 < B; b0 += kEvalSubBatch)
+        {
+            const int nb = std::min(kEvalSubBatch, B - b0);
+            const int rc = forward_views(ctx, scene, views + b0, nb, params, g, out_layers, (size_t)b0,
+                                         nullptr, st, true);
+            if (rc != TRIPS_OK) return rc;
+        }
+    }
+    ctx->have_forward = true;
     return TRIPS_OK;
 }
 
@@ -463,7 +603,7 @@ int trips_backward(TripsContext* ctx, const TripsScene* scene, const float* cons
     const size_t N = (size_t)ctx->N;
 
     const size_t GS = (size_t)egrad_stride(C);
-    CU_CHECK(ctx, ensure(ctx->egrad, sizeof(float) * GS * (size_t)ctx->total_entries + 16, 1.25));
+    CU_CHECK(ctx, ensure(ctx->egrad, sizeof(float) * GS * ctx->entry_cap + 16));  // one row per entry the arrays can hold
     CU_CHECK(ctx, ensure(ctx->g_point, sizeof(float) * GS * N + 16));
     CU_CHECK(ctx, ensure(ctx->g_conf_pt, sizeof(float) * N + 16));
     const size_t small_bytes = sizeof(double) * (TRIPS_MAX_CHANNELS + (size_t)B * 11);
@@ -475,15 +615,20 @@ int trips_backward(TripsContext* ctx, const TripsScene* scene, const float* cons
     bb.g_bg         = (double*)ctx->g_small.p;
     bb.g_pose       = bb.g_bg + TRIPS_MAX_CHANNELS;
     bb.g_k          = bb.g_pose + (size_t)B * 6;
-    if (ctx->total_entries) CU_CHECK(ctx, cudaMemsetAsync(ctx->egrad.p, 0, sizeof(float) * GS * (size_t)ctx->total_entries, st));
-    if (N > 0) CU_CHECK(ctx, cudaMemsetAsync(ctx->g_point.p, 0, sizeof(float) * GS * N, st));
-    if (N > 0) CU_CHECK(ctx, cudaMemsetAsync(ctx->g_conf_pt.p, 0, sizeof(float) * N, st));
-    CU_CHECK(ctx, cudaMemsetAsync(ctx->g_small.p, 0, small_bytes, st));
-    if (grads->pose_tangent) CU_CHECK(ctx, cudaMemsetAsync(grads->pose_tangent, 0, sizeof(double) * 6 * scene->n_images, st));
-    if (grads->intrinsics) CU_CHECK(ctx, cudaMemsetAsync(grads->intrinsics, 0, sizeof(float) * 13 * scene->n_cameras, st));
-
     ScenePtrs sp  = scene_ptrs(scene);
     FwdBuffers fb = fwd_buffers(ctx);
+    // all accumulators start from zero (timed with the gradient bookkeeping of the unpack stage)
+    auto clear_accumulators = [&]() -> cudaError_t {
+        cudaError_t e = cudaSuccess;
+        if (N > 0 && e == cudaSuccess) e = cudaMemsetAsync(ctx->g_point.p, 0, sizeof(float) * GS * N, st);
+        if (N > 0 && e == cudaSuccess) e = cudaMemsetAsync(ctx->g_conf_pt.p, 0, sizeof(float) * N, st);
+        if (e == cudaSuccess) e = cudaMemsetAsync(ctx->g_small.p, 0, small_bytes, st);
+        if (grads->pose_tangent && e == cudaSuccess) e = cudaMemsetAsync(grads->pose_tangent, 0, sizeof(double) * 6 * scene->n_images, st);
+        if (grads->intrinsics && e == cudaSuccess) e = cudaMemsetAsync(grads->intrinsics, 0, sizeof(float) * 13 * scene->n_cameras, st);
+        if (N > 0 && e == cudaSuccess) e = launch_zero_entry_rows(C, B, fb, bb, ctx->sm_count, st);
+        return e;
+    };
+    STAGE(ctx, TRIPS_STAGE_UNPACK, N > 0 ? 1 : 0, st, clear_accumulators());
     ConstLayerPtrs gin{};
     for (int l = 0; l < g.L; ++l) gin.p[l] = grad_layers[l];
     const bool cam_grads = grads->pose_tangent || grads->intrinsics;
@@ -513,6 +658,10 @@ int trips_get_stats(TripsContext* ctx, TripsStats* out, void* stream)
     (void)stream;
     if (!ctx || !out) return TRIPS_ERR_INVALID_ARG;
     if (!ctx->have_forward) return fail(ctx, TRIPS_ERR_NO_FORWARD, "no forward pass");
+    {
+        const int rs = resolve_pending(ctx);  // waits for the totals of a call that did not wait for them itself
+        if (rs != TRIPS_OK) return rs;
+    }
     *out = ctx->host_stats;
     return TRIPS_OK;
 }
@@ -558,9 +707,8 @@ int trips_resize_points(TripsContext* ctx, const int64_t* indices_to_remove, int
         if ((n_new > 0 && !t.dst) || (n_points > n_remove && !t.src)) return fail(ctx, TRIPS_ERR_INVALID_ARG, "null tensor");
     }
     cudaStream_t st = (cudaStream_t)stream;
-    CU_CHECK(ctx, ensure(ctx->stats, sizeof(DevStats)));
+    CU_CHECK(ctx, ensure_stats(ctx, st));
     CU_CHECK(ctx, ensure(ctx->resize_scratch, resize_scratch_bytes(n_points)));
-    CU_CHECK(ctx, cudaMemsetAsync(ctx->stats.p, 0, sizeof(DevStats), st));
     STAGE(ctx, TRIPS_STAGE_RESIZE, 5, st,
           launch_resize_points(indices_to_remove, n_remove, n_points, n_new, tensors, n_tensors, ctx->resize_scratch.p, (DevStats*)ctx->stats.p,
                                ctx->sm_count, st));

@@ -61,8 +61,9 @@ struct ConstLayerPtrs
 // Device-side counters of one forward call.
 struct DevStats
 {
-    unsigned long long visible;
+    unsigned long long visible;    // visible points over all views (needed entries, whether or not they fitted)
     unsigned long long kept;
+    unsigned long long frag_need;  // fragments over all views (needed list slots, whether or not they fitted)
     unsigned int max_len;
     unsigned int status;
     unsigned int culled_blocks;  // (view, block of consecutive points) pairs skipped by the bounding-box test, counted once per pass
@@ -246,8 +247,12 @@ __device__ __forceinline__ void tile_pixel(const Geom& g, int tile, int lane, in
 // ---- launchers (forward.cu / backward.cu / adam.cu) ----
 cudaError_t launch_setup_cams(const TripsView* d_views, int B, const double* poses, int n_images, const float* intrinsics,
                               int n_cameras, CamConst* cams, DevStats* stats, cudaStream_t st);
-cudaError_t launch_bin_points(const ScenePtrs& sc, const CamConst* cams, const Geom& g, const TripsRenderParams& pr, int B,
-                              const FwdBuffers& fb, int sm_count, cudaStream_t st);
+cudaError_t launch_bin_count(const ScenePtrs& sc, const CamConst* cams, const Geom& g, const TripsRenderParams& pr, int B,
+                             const FwdBuffers& fb, unsigned long long entry_cap, int sm_count, cudaStream_t st);
+cudaError_t launch_bin_scatter(const ScenePtrs& sc, const CamConst* cams, const Geom& g, const TripsRenderParams& pr, int B,
+                               const FwdBuffers& fb, int sm_count, cudaStream_t st);
+int bin_count_launches(int N, int B);
+int bin_scatter_launches(int N, int B);
 size_t resize_scratch_bytes(int64_t n_points);
 cudaError_t launch_resize_points(const int64_t* remove, int64_t n_remove, int64_t n_points, int64_t n_new, const TripsPointTensor* tensors,
                                  int n_tensors, void* scratch, DevStats* stats, int sm_count, cudaStream_t st);
@@ -259,6 +264,7 @@ cudaError_t launch_count(const ScenePtrs& sc, const Geom& g, int B, const FwdBuf
 cudaError_t launch_collect(const ScenePtrs& sc, const Geom& g, int B, const FwdBuffers& fb, int sm_count, cudaStream_t st);
 cudaError_t launch_sort_blend(const ScenePtrs& sc, const Geom& g, const TripsRenderParams& pr, int B, const FwdBuffers& fb,
                               const LayerPtrs& out, int sm_count, cudaStream_t st);
+cudaError_t launch_zero_entry_rows(int C, int B, const FwdBuffers& fb, const BwdBuffers& bb, int sm_count, cudaStream_t st);
 cudaError_t launch_blend_backward(const ScenePtrs& sc, const CamConst* cams, const Geom& g, const TripsRenderParams& pr,
                                   int B, const FwdBuffers& fb, const BwdBuffers& bb, const ConstLayerPtrs& grad_in,
                                   bool want_cam_grads, int sm_count, cudaStream_t st);

@@ -83,60 +83,44 @@ cudaError_t launch_setup_cams(const TripsView* d_views, int B, const double* pos
 // per (view, bin, tile) with one global counter each; (2) exclusive scan of the counters; (3) project again, take a slot
 // in the point's group and write its entry there (head and tail, 32 bytes each).  Replaces the projection part of
 // CountAndCollectTiled (RenderForward.cu:168-366); the list lengths are counted afterwards from the entries
-// (window_kernel<false>).  Projecting twice costs two coalesced reads of position + size per view and avoids writing
-// and re-reading a per-point record for all N points.
+// (window_kernel<false>).  Both passes read every point ONCE per call and loop over the views with the point in
+// registers (the camera constants of up to kViewGroup views sit in shared memory): position, size and, in the scatter
+// pass, confidence, descriptor row and rank cost N reads per call instead of N x B, and softplus(size) is evaluated
+// once per point.  Projecting twice avoids writing and re-reading a per-point record for all N x B point-views.
 // ------------------------------------------------------------------------------------------------------------
 struct Projected
 {
     float u, v, z, ps, rad;
-    int tex;
     bool ok;
 };
 
-// ACT: the scene tensors may be raw parameters (fused texture preparation); compiled separately so that the common case
-// carries none of its code
-template <bool ACT>
-__device__ __forceinline__ Projected project_visible(const ScenePtrs& sc, const CamConst& cam, const Geom& g,
-                                                     const TripsRenderParams& pr, size_t bN, int i, float fxc)
+// Visibility test of one point in one view (RenderForward.cu:224-340).  `sp` caches softplus(raw) across the views of
+// the point: negative = not computed yet (softplus is never negative); only visible points pay for it.
+__device__ __forceinline__ Projected project_visible(const CamConst& cam, const Geom& g, const TripsRenderParams& pr, const float4& p,
+                                                     float raw, float& sp)
 {
     Projected r;
-    r.ok  = false;
-    r.tex = sc.index ? __ldg(sc.index + i) : i;
-    if (pr.viewer_only)
-    {
-        // discard_point_for_confidence, RenderForward.cu:122-130
-        if ((unsigned)r.tex < (unsigned)sc.n_tex)
-        {
-            float c = __ldg(sc.confidence + r.tex);
-            if (ACT && pr.confidence_is_raw) c = tm_sigmoid(pr.confidence_scale * c);
-            if (c < pr.stability_cutoff_value) return r;
-        }
-    }
-    else if (pr.train && sc.dropout)
-    {
-        if (__ldg(sc.dropout + bN + i) == 1.f) return r;
-    }
-    const float4 p  = __ldg(sc.position + i);
-    const float raw = __ldg(sc.point_size + i);
+    const float fxc = cam.fx * cam.cfx;
     project_point(cam, p.x, p.y, p.z, r.u, r.v, r.z);
     r.rad = fxc * p.w / r.z;
     r.ps  = 0.f;
     bool ok = !(r.z <= 0.f || r.u < 0.f || r.u >= (float)(g.W[0] - 1) || r.v < 0.f || r.v >= (float)(g.H[0] - 1));
     if (ok && pr.drop_out_points_by_radius && (float)(int)r.rad < pr.drop_out_radius_threshold) ok = false;
-    if (ok) r.ps = fxc * tm_softplus(raw) / r.z;  // only visible points pay for the softplus
+    if (ok)
+    {
+        if (sp < 0.f) sp = tm_softplus(raw);
+        r.ps = fxc * sp / r.z;
+    }
     r.ok = ok;
     return r;
 }
 
-#ifndef TRIPS_BIN_THREADS
-#define TRIPS_BIN_THREADS 256
-#endif
-#ifndef TRIPS_BIN_BLOCKS_PER_SM
-#define TRIPS_BIN_BLOCKS_PER_SM 8
-#endif
-constexpr int kBinThreads = TRIPS_BIN_THREADS;
-
-constexpr int kBinChunk = 8192;  // points per ticket of the binning kernels = points per bounding box
+constexpr int kBinThreads     = 256;
+constexpr int kBinBlocksPerSM = 8;
+constexpr int kBinChunk       = 8192;  // points per bounding box
+constexpr int kBinTicket      = 1024;  // points per work ticket of the binning kernels; a ticket lies inside one box
+constexpr int kViewGroup      = 16;    // views whose camera constants are in shared memory at a time (one launch per group)
+static_assert(kBinChunk % kBinTicket == 0, "a ticket must not straddle two bounding boxes");
 
 // Bounding boxes of blocks of consecutive points and the conservative frustum test on them: the reference computes
 // such boxes per 10 240 points (NeuralPointCloudCuda.cpp:339-384) but never uses them.  Point clouds stored in a
@@ -243,19 +227,26 @@ __global__ __launch_bounds__(128) void block_visibility_kernel(const CamConst* _
     if (out) atomicAdd(&stats->culled_blocks, 1u);
 }
 
-// The binning kernels take chunks of the point cloud from a ticket counter, view after view, so that every SM is busy
-// until the last chunk whatever the number of resident blocks is (a static split left a partial last wave).
-__device__ __forceinline__ bool next_point_chunk(unsigned* ticket, int N, int B, unsigned* s_ticket, int& b, int& first, int& last)
+// Work distribution of the binning kernels: tickets of kBinTicket consecutive points from one counter, so that every SM
+// is busy until the last ticket whatever the number of resident blocks is (a static split left a partial last wave).
+// Returns false when the cloud is exhausted; `skip` gets one bit per view of the group whose bounding-box test rules the
+// ticket's points out.
+__device__ __forceinline__ bool next_point_ticket(unsigned* ticket, int N, unsigned* s_ticket, const uint8_t* __restrict__ block_skip, int v0,
+                                                  int nv, int& first, int& last, unsigned& skip)
 {
     __syncthreads();
     if (threadIdx.x == 0) *s_ticket = atomicAdd(ticket, 1u);
     __syncthreads();
-    const unsigned t        = *s_ticket;
-    const unsigned per_view = ((unsigned)N + kBinChunk - 1) / kBinChunk;
-    if (t >= per_view * (unsigned)B) return false;
-    b     = (int)(t / per_view);
-    first = (int)((t - (unsigned)b * per_view) * kBinChunk);
-    last  = min(N, first + kBinChunk);
+    const unsigned t = *s_ticket;
+    if (t >= ((unsigned)N + kBinTicket - 1) / kBinTicket) return false;
+    first = (int)(t * kBinTicket);
+    last  = min(N, first + kBinTicket);
+    skip  = 0;
+    if (block_skip)
+    {
+        const int n_box = (N + kBinChunk - 1) / kBinChunk, box = first / kBinChunk;
+        for (int v = 0; v < nv; ++v) skip |= (unsigned)block_skip[(size_t)(v0 + v) * n_box + box] << v;  // uniform loads
+    }
     return true;
 }
 
@@ -270,29 +261,44 @@ __device__ __forceinline__ int bin_key(const Geom& g, float u, float v)
     return (bin << kSubShift) | (((py >> 2) & 7) << 2) | ((px >> 3) & 3);
 }
 
+// discard_point_for_confidence (RenderForward.cu:122-130): viewer only, points below the stability cut-off are not drawn
 template <bool ACT>
-__global__ __launch_bounds__(kBinThreads) void bin_count_kernel(ScenePtrs sc, const CamConst* __restrict__ cams,
-                                                                const __grid_constant__ Geom g, TripsRenderParams pr, FwdBuffers fb, int B)
+__device__ __forceinline__ bool discarded_for_confidence(const ScenePtrs& sc, const TripsRenderParams& pr, int tex)
 {
-    __shared__ CamConst cam;
+    if (!pr.viewer_only || (unsigned)tex >= (unsigned)sc.n_tex) return false;
+    float c = __ldg(sc.confidence + tex);
+    if (ACT && pr.confidence_is_raw) c = tm_sigmoid(pr.confidence_scale * c);
+    return c < pr.stability_cutoff_value;
+}
+
+// ACT: the scene tensors may be raw parameters (fused texture preparation); compiled separately so that the common case
+// carries none of its code.  One launch handles the views [v0, v0 + nv).
+template <bool ACT>
+__global__ __launch_bounds__(kBinThreads) void bin_count_kernel(ScenePtrs sc, const CamConst* __restrict__ cams, const __grid_constant__ Geom g,
+                                                                TripsRenderParams pr, FwdBuffers fb, int v0, int nv, unsigned* ticket)
+{
+    __shared__ CamConst s_cam[kViewGroup];
     __shared__ unsigned s_ticket;
-    int b, first, last, cur_b = -1;
-    while (next_point_chunk(fb.ticket, sc.N, B, &s_ticket, b, first, last))
+    for (int k = threadIdx.x; k < nv * (int)(sizeof(CamConst) / 4); k += kBinThreads) ((int*)s_cam)[k] = ((const int*)(cams + v0))[k];
+    const bool use_dropout = pr.train && sc.dropout;  // the mask applies with and without viewer_only (RenderForward.cu:224-240)
+    int first, last;
+    unsigned skip;
+    while (next_point_ticket(ticket, sc.N, &s_ticket, fb.block_skip, v0, nv, first, last, skip))
     {
-        if (b != cur_b)  // uniform
+        for (int i = first + threadIdx.x; i < last; i += kBinThreads)
         {
-            if (threadIdx.x < sizeof(CamConst) / 4) ((int*)&cam)[threadIdx.x] = ((const int*)&cams[b])[threadIdx.x];
-            __syncthreads();
-            cur_b = b;
-        }
-        if (fb.block_skip && fb.block_skip[(size_t)b * ((sc.N + kBinChunk - 1) / kBinChunk) + first / kBinChunk]) continue;  // uniform
-        const size_t bN = (size_t)b * sc.N;
-        const float fxc = cam.fx * cam.cfx;
-        uint32_t* hist  = fb.bin_count + ((size_t)b * g.n_bins << kSubShift);
-        for (int i = first + threadIdx.x; i < last; i += blockDim.x)
-        {
-            const Projected r = project_visible<ACT>(sc, cam, g, pr, bN, i, fxc);
-            if (r.ok) atomicAdd(hist + bin_key(g, r.u, r.v), 1u);
+            const int tex = sc.index ? __ldg(sc.index + i) : i;
+            if (discarded_for_confidence<ACT>(sc, pr, tex)) continue;
+            const float4 p  = __ldg(sc.position + i);
+            const float raw = __ldg(sc.point_size + i);
+            float sp        = -1.f;
+            for (int v = 0; v < nv; ++v)
+            {
+                if ((skip >> v) & 1u) continue;  // uniform
+                if (use_dropout && __ldg(sc.dropout + (size_t)(v0 + v) * sc.N + i) == 1.f) continue;
+                const Projected r = project_visible(s_cam[v], g, pr, p, raw, sp);
+                if (r.ok) atomicAdd(fb.bin_count + ((size_t)(v0 + v) * g.n_bins << kSubShift) + bin_key(g, r.u, r.v), 1u);
+            }
         }
     }
 }
@@ -355,99 +361,121 @@ __global__ __launch_bounds__(1024) void bin_scan_kernel(const uint32_t* __restri
     if (threadIdx.x == 0) view_total[b] = carry_s;
 }
 
-__global__ void entry_base_kernel(const uint32_t* __restrict__ view_total, int B, unsigned long long* __restrict__ entry_base,
-                                  DevStats* stats)
+// First entry of every view in the entry arrays.  A view whose entries do not fit the arrays (entry_cap entries: the
+// arrays are sized from the previous call's count, not for the worst case) gets none: it renders as background, the
+// status word says so and stats->visible still carries the number that was needed, so that the host grows the arrays.
+__global__ void entry_base_kernel(const uint32_t* __restrict__ view_total, int B, unsigned long long entry_cap,
+                                  unsigned long long* __restrict__ entry_base, DevStats* stats)
 {
     if (threadIdx.x != 0 || blockIdx.x != 0) return;
-    unsigned long long base = 0;
+    unsigned long long base = 0, need = 0;
     for (int b = 0; b < B; ++b)
     {
         entry_base[b] = base;
-        base += view_total[b];
+        need += view_total[b];
+        if (base + view_total[b] <= entry_cap)
+            base += view_total[b];
+        else
+            atomicOr(&stats->status, TRIPS_DEV_ENTRY_OVERFLOW);
     }
     entry_base[B]  = base;
-    stats->visible = base;
+    stats->visible = need;
 }
 
 template <int C, bool ACT>
-__global__ __launch_bounds__(kBinThreads) void bin_scatter_kernel(ScenePtrs sc, const CamConst* __restrict__ cams,
-                                                                  const __grid_constant__ Geom g, TripsRenderParams pr, FwdBuffers fb, int B)
+__global__ __launch_bounds__(kBinThreads) void bin_scatter_kernel(ScenePtrs sc, const CamConst* __restrict__ cams, const __grid_constant__ Geom g,
+                                                                  TripsRenderParams pr, FwdBuffers fb, int v0, int nv, unsigned* ticket)
 {
     constexpr int TS = tail_stride(C);
-    __shared__ CamConst cam;
+    constexpr int C4 = (C + 3) & ~3;
+    __shared__ CamConst s_cam[kViewGroup];
+    __shared__ unsigned long long s_ebase[kViewGroup + 1];
     __shared__ unsigned s_ticket;
-    int b, first, last, cur_b = -1;
-    while (next_point_chunk(fb.ticket, sc.N, B, &s_ticket, b, first, last))
+    for (int k = threadIdx.x; k < nv * (int)(sizeof(CamConst) / 4); k += kBinThreads) ((int*)s_cam)[k] = ((const int*)(cams + v0))[k];
+    if (threadIdx.x <= nv) s_ebase[threadIdx.x] = fb.entry_base[v0 + threadIdx.x];
+    __syncthreads();
+    unsigned no_room = 0;  // views without entries: nothing visible, or the view did not fit the entry arrays
+    for (int v = 0; v < nv; ++v) no_room |= (s_ebase[v + 1] == s_ebase[v] ? 1u : 0u) << v;
+    const bool use_dropout = pr.train && sc.dropout;
+    int first, last;
+    unsigned skip;
+    while (next_point_ticket(ticket, sc.N, &s_ticket, fb.block_skip, v0, nv, first, last, skip))
     {
-    if (b != cur_b)  // uniform
-    {
-        if (threadIdx.x < sizeof(CamConst) / 4) ((int*)&cam)[threadIdx.x] = ((const int*)&cams[b])[threadIdx.x];
-        __syncthreads();
-        cur_b = b;
-    }
-    if (fb.block_skip && fb.block_skip[(size_t)b * ((sc.N + kBinChunk - 1) / kBinChunk) + first / kBinChunk]) continue;  // uniform; the count pass skipped the block too
-    uint32_t* cursor = fb.bin_base + ((size_t)b * g.n_bins << kSubShift);  // next free entry of every (bin, tile) group
-    const size_t bN  = (size_t)b * sc.N;
-    const float fxc  = cam.fx * cam.cfx;
-    float4* head     = fb.ent_head + fb.entry_base[b] * 2;
-    float* tail      = fb.ent_tail + fb.entry_base[b] * TS;
-    for (int i = first + threadIdx.x; i < last; i += blockDim.x)
-    {
-        const Projected r = project_visible<ACT>(sc, cam, g, pr, bN, i, fxc);
-        if (!r.ok) continue;
-        const uint32_t slot = atomicAdd(cursor + bin_key(g, r.u, r.v), 1u);
-        // layers 0..hi, stopping where the 2x2 footprint leaves the layer (RenderForward.cu:342-363)
-        int hi = 0;
-        if (r.ps > 1.f) hi = min(tm_ceil_log2(r.ps), g.L - 1);
-        int layer = 0;
-        float x = r.u, y = r.v, rad = r.rad;
-        for (; layer < hi + 1; ++layer, x *= 0.5f, y *= 0.5f, rad *= 0.5f)
+        skip |= no_room;
+        for (int i = first + threadIdx.x; i < last; i += kBinThreads)
         {
-            const int px = __float2int_rd(x), py = __float2int_rd(y);
-            if (px < 0 || px >= g.W[layer] - 1 || py < 0 || py >= g.H[layer] - 1) break;
-            if (pr.drop_out_points_by_radius && (float)(int)rad < pr.drop_out_radius_threshold) break;
-        }
-        float conf = 0.f;
-        const bool tex_ok = (unsigned)r.tex < (unsigned)sc.n_tex;
-        if (tex_ok)
-        {
-            conf = __ldg(sc.confidence + r.tex);
-            if (ACT && pr.confidence_is_raw) conf = tm_sigmoid(pr.confidence_scale * conf);  // PrepareConfidence, NeuralTexture.h:40-43
-        }
-        else
-            atomicOr(&fb.stats->status, TRIPS_DEV_BAD_TEXTURE_INDEX);  // the point is drawn with alpha 0
-        const float4 p = __ldg(sc.position + i);
-        head[2 * (size_t)slot]     = make_float4(r.u, r.v, r.ps, conf);
-        const uint32_t rk          = fb.point_rank ? __ldg(fb.point_rank + i) : 0u;
-        head[2 * (size_t)slot + 1] = make_float4(__int_as_float(i), r.z, __ldg(sc.point_size + i), __uint_as_float((uint32_t)layer | (rk << kRankShift)));
-        float4* e = reinterpret_cast<float4*>(tail + (size_t)slot * TS);
-        e[0]      = make_float4(p.x, p.y, p.z, __int_as_float(tex_ok ? r.tex : -1));
-        float row_t[(C + 3) & ~3];
+            const int tex = sc.index ? __ldg(sc.index + i) : i;
+            if (discarded_for_confidence<ACT>(sc, pr, tex)) continue;
+            const float4 p  = __ldg(sc.position + i);
+            const float raw = __ldg(sc.point_size + i);
+            float sp        = -1.f;
+            // per-point data of the entry: fetched when the point turns out visible in a first view
+            bool fetched = false;
+            float conf   = 0.f;
+            uint32_t rk  = 0u;
+            float row_t[C4];
+            const bool tex_ok = (unsigned)tex < (unsigned)sc.n_tex;
+            for (int v = 0; v < nv; ++v)
+            {
+                if ((skip >> v) & 1u) continue;  // uniform
+                if (use_dropout && __ldg(sc.dropout + (size_t)(v0 + v) * sc.N + i) == 1.f) continue;
+                const Projected r = project_visible(s_cam[v], g, pr, p, raw, sp);
+                if (!r.ok) continue;
+                if (!fetched)
+                {
+                    fetched = true;
+                    if (tex_ok)
+                    {
+                        conf = __ldg(sc.confidence + tex);
+                        if (ACT && pr.confidence_is_raw) conf = tm_sigmoid(pr.confidence_scale * conf);  // PrepareConfidence, NeuralTexture.h:40-43
+                    }
+                    else
+                        atomicOr(&fb.stats->status, TRIPS_DEV_BAD_TEXTURE_INDEX);  // the point is drawn with alpha 0
 #pragma unroll
-        for (int c = 0; c < ((C + 3) & ~3); ++c) row_t[c] = (c < C && tex_ok) ? __ldg(sc.texture + (size_t)c * sc.n_tex + r.tex) : 0.f;
-        if (ACT && pr.texture_abs)  // PrepareTexture, NeuralTexture.h:45-57
-        {
+                    for (int c = 0; c < C4; ++c) row_t[c] = (c < C && tex_ok) ? __ldg(sc.texture + (size_t)c * sc.n_tex + tex) : 0.f;
+                    if (ACT && pr.texture_abs)  // PrepareTexture, NeuralTexture.h:45-57
+                    {
 #pragma unroll
-            for (int c = 0; c < ((C + 3) & ~3); ++c) row_t[c] = fabsf(row_t[c]);
+                        for (int c = 0; c < C4; ++c) row_t[c] = fabsf(row_t[c]);
+                    }
+                    rk = fb.point_rank ? __ldg(fb.point_rank + i) : 0u;
+                }
+                const uint32_t slot = atomicAdd(fb.bin_base + ((size_t)(v0 + v) * g.n_bins << kSubShift) + bin_key(g, r.u, r.v), 1u);
+                // layers 0..hi, stopping where the 2x2 footprint leaves the layer (RenderForward.cu:342-363)
+                int hi = 0;
+                if (r.ps > 1.f) hi = min(tm_ceil_log2(r.ps), g.L - 1);
+                int layer = 0;
+                float x = r.u, y = r.v, rad = r.rad;
+                for (; layer < hi + 1; ++layer, x *= 0.5f, y *= 0.5f, rad *= 0.5f)
+                {
+                    const int px = __float2int_rd(x), py = __float2int_rd(y);
+                    if (px < 0 || px >= g.W[layer] - 1 || py < 0 || py >= g.H[layer] - 1) break;
+                    if (pr.drop_out_points_by_radius && (float)(int)rad < pr.drop_out_radius_threshold) break;
+                }
+                float4* head = fb.ent_head + (s_ebase[v] + slot) * 2;
+                head[0]      = make_float4(r.u, r.v, r.ps, conf);
+                head[1]      = make_float4(__int_as_float(i), r.z, raw, __uint_as_float((uint32_t)layer | (rk << kRankShift)));
+                float4* e    = reinterpret_cast<float4*>(fb.ent_tail + (s_ebase[v] + slot) * TS);
+                e[0]         = make_float4(p.x, p.y, p.z, __int_as_float(tex_ok ? tex : -1));
+#pragma unroll
+                for (int c = 0; c < C4; c += 4) e[1 + c / 4] = make_float4(row_t[c], row_t[c + 1], row_t[c + 2], row_t[c + 3]);
+            }
         }
-#pragma unroll
-        for (int c = 0; c < ((C + 3) & ~3); c += 4) e[1 + c / 4] = make_float4(row_t[c], row_t[c + 1], row_t[c + 2], row_t[c + 3]);
-    }
     }
 }
 
-
-cudaError_t launch_bin_points(const ScenePtrs& sc, const CamConst* cams, const Geom& g, const TripsRenderParams& pr, int B,
-                              const FwdBuffers& fb, int sm_count, cudaStream_t st)
+// Count pass of the binning stage: bounding boxes, visible points per (view, bin, tile), their exclusive scan and the
+// first entry of every view.  After it fb.view_total / stats->visible say how many entries the scatter pass will write.
+cudaError_t launch_bin_count(const ScenePtrs& sc, const CamConst* cams, const Geom& g, const TripsRenderParams& pr, int B,
+                             const FwdBuffers& fb, unsigned long long entry_cap, int sm_count, cudaStream_t st)
 {
-    const int n_keys = g.n_bins << kSubShift;
-    const int grid   = sm_count * TRIPS_BIN_BLOCKS_PER_SM;
-    cudaError_t e    = cudaMemsetAsync(fb.bin_count, 0, sizeof(uint32_t) * (size_t)B * n_keys, st);
+    const int n_keys   = g.n_bins << kSubShift;
+    const int grid     = sm_count * kBinBlocksPerSM;
+    const int n_groups = (B + kViewGroup - 1) / kViewGroup;
+    cudaError_t e      = cudaMemsetAsync(fb.bin_count, 0, sizeof(uint32_t) * (size_t)B * n_keys, st);
     if (e != cudaSuccess) return e;
-    e = cudaMemsetAsync(fb.ticket, 0, 2 * sizeof(unsigned), st);  // one counter per pass
+    e = cudaMemsetAsync(fb.ticket, 0, 2 * n_groups * sizeof(unsigned), st);  // one counter per pass and view group
     if (e != cudaSuccess) return e;
-    FwdBuffers f2 = fb;
-    f2.ticket     = fb.ticket + 1;
     if (sc.N > 0 && fb.block_box && fb.block_skip)
     {
         const int nbk = (sc.N + kBinChunk - 1) / kBinChunk;
@@ -456,50 +484,51 @@ cudaError_t launch_bin_points(const ScenePtrs& sc, const CamConst* cams, const G
     }
     const bool act = pr.confidence_is_raw || pr.texture_abs;
     if (sc.N > 0)
-    {
-        if (act)
-            bin_count_kernel<true><<<grid, kBinThreads, 0, st>>>(sc, cams, g, pr, fb, B);
-        else
-            bin_count_kernel<false><<<grid, kBinThreads, 0, st>>>(sc, cams, g, pr, fb, B);
-    }
+        for (int gi = 0; gi < n_groups; ++gi)
+        {
+            const int v0 = gi * kViewGroup, nv = min(kViewGroup, B - v0);
+            if (act)
+                bin_count_kernel<true><<<grid, kBinThreads, 0, st>>>(sc, cams, g, pr, fb, v0, nv, fb.ticket + gi);
+            else
+                bin_count_kernel<false><<<grid, kBinThreads, 0, st>>>(sc, cams, g, pr, fb, v0, nv, fb.ticket + gi);
+        }
     bin_scan_kernel<<<B, 1024, 0, st>>>(fb.bin_count, fb.bin_base, fb.bin_cursor, n_keys, 1, fb.view_total, kSubShift);
-    entry_base_kernel<<<1, 32, 0, st>>>(fb.view_total, B, fb.entry_base, fb.stats);
-    if (sc.N > 0)
+    entry_base_kernel<<<1, 32, 0, st>>>(fb.view_total, B, entry_cap, fb.entry_base, fb.stats);
+    return cudaGetLastError();
+}
+
+int bin_count_launches(int N, int B) { return 2 + (N > 0 ? 2 + (B + kViewGroup - 1) / kViewGroup : 0); }
+int bin_scatter_launches(int N, int B) { return N > 0 ? (B + kViewGroup - 1) / kViewGroup : 0; }
+
+// Scatter pass of the binning stage: writes the entries (the arrays must hold fb.entry_base[B] entries).
+cudaError_t launch_bin_scatter(const ScenePtrs& sc, const CamConst* cams, const Geom& g, const TripsRenderParams& pr, int B,
+                               const FwdBuffers& fb, int sm_count, cudaStream_t st)
+{
+    if (sc.N <= 0) return cudaSuccess;
+    const int grid     = sm_count * kBinBlocksPerSM;
+    const int n_groups = (B + kViewGroup - 1) / kViewGroup;
+    const bool act     = pr.confidence_is_raw || pr.texture_abs;
+    for (int gi = 0; gi < n_groups; ++gi)
     {
+        const int v0 = gi * kViewGroup, nv = min(kViewGroup, B - v0);
+        unsigned* tk = fb.ticket + n_groups + gi;
+#define TRIPS_SCATTER_CASE(CC)                                                                                 \
+    case CC:                                                                                                   \
+        if (act)                                                                                               \
+            bin_scatter_kernel<CC, true><<<grid, kBinThreads, 0, st>>>(sc, cams, g, pr, fb, v0, nv, tk);      \
+        else                                                                                                   \
+            bin_scatter_kernel<CC, false><<<grid, kBinThreads, 0, st>>>(sc, cams, g, pr, fb, v0, nv, tk);     \
+        break;
         switch (sc.C)
         {
-            case 3:
-                if (act)
-                    bin_scatter_kernel<3, true><<<grid, kBinThreads, 0, st>>>(sc, cams, g, pr, f2, B);
-                else
-                    bin_scatter_kernel<3, false><<<grid, kBinThreads, 0, st>>>(sc, cams, g, pr, f2, B);
-                break;
-            case 4:
-                if (act)
-                    bin_scatter_kernel<4, true><<<grid, kBinThreads, 0, st>>>(sc, cams, g, pr, f2, B);
-                else
-                    bin_scatter_kernel<4, false><<<grid, kBinThreads, 0, st>>>(sc, cams, g, pr, f2, B);
-                break;
-            case 6:
-                if (act)
-                    bin_scatter_kernel<6, true><<<grid, kBinThreads, 0, st>>>(sc, cams, g, pr, f2, B);
-                else
-                    bin_scatter_kernel<6, false><<<grid, kBinThreads, 0, st>>>(sc, cams, g, pr, f2, B);
-                break;
-            case 8:
-                if (act)
-                    bin_scatter_kernel<8, true><<<grid, kBinThreads, 0, st>>>(sc, cams, g, pr, f2, B);
-                else
-                    bin_scatter_kernel<8, false><<<grid, kBinThreads, 0, st>>>(sc, cams, g, pr, f2, B);
-                break;
-            case 16:
-                if (act)
-                    bin_scatter_kernel<16, true><<<grid, kBinThreads, 0, st>>>(sc, cams, g, pr, f2, B);
-                else
-                    bin_scatter_kernel<16, false><<<grid, kBinThreads, 0, st>>>(sc, cams, g, pr, f2, B);
-                break;
+            TRIPS_SCATTER_CASE(3)
+            TRIPS_SCATTER_CASE(4)
+            TRIPS_SCATTER_CASE(6)
+            TRIPS_SCATTER_CASE(8)
+            TRIPS_SCATTER_CASE(16)
             default: return cudaErrorInvalidValue;
         }
+#undef TRIPS_SCATTER_CASE
     }
     return cudaGetLastError();
 }
@@ -571,7 +600,7 @@ __global__ __launch_bounds__(1024) void scan_partials_kernel(uint32_t* __restric
     __shared__ uint32_t sm[32];
     __shared__ uint32_t carry_s;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    unsigned long long base = 0;
+    unsigned long long base = 0, need = 0;
     for (int b = 0; b < B; ++b)
     {
         uint32_t* p = partial + (size_t)b * nchunks;
@@ -596,13 +625,22 @@ __global__ __launch_bounds__(1024) void scan_partials_kernel(uint32_t* __restric
         }
         if (threadIdx.x == 0)
         {
+            // a view that does not fit the list buffer (sized from the previous call) gets no fragments at all: the
+            // collect pass skips it and the blend treats its lists as empty
             view_base[b] = base;
-            base += carry_s;
-            if (base > frag_cap) atomicOr(&stats->status, TRIPS_DEV_FRAGMENT_OVERFLOW);
+            need += carry_s;
+            if (base + carry_s <= frag_cap)
+                base += carry_s;
+            else
+                atomicOr(&stats->status, TRIPS_DEV_FRAGMENT_OVERFLOW);
         }
         __syncthreads();
     }
-    if (threadIdx.x == 0) view_base[B] = base;
+    if (threadIdx.x == 0)
+    {
+        view_base[B]     = base;
+        stats->frag_need = need;
+    }
 }
 
 __global__ __launch_bounds__(256) void scan_apply_kernel(const uint32_t* __restrict__ counts, int P, int nchunks,
@@ -850,7 +888,7 @@ __global__ __launch_bounds__(kWinThreads, TRIPS_WIN_MIN_BLOCKS) void window_kern
     // where blocks cross over), which keeps the partially written list sectors of a view in L2 until they are complete
     for (int b = 0; b < B; ++b)
     {
-    if (COLLECT && fb.view_base[b + 1] > fb.frag_cap) continue;  // list buffer too small: the overflow status bit is already raised
+    if (COLLECT && fb.view_base[b + 1] == fb.view_base[b]) continue;  // no fragments, or the view did not fit the list buffer (status bit raised by the scan)
     uint32_t* pixel_ctr   = (COLLECT ? fb.offsets : fb.counts) + (size_t)b * g.P;
     uint4* frags          = fb.frags + fb.view_base[COLLECT ? b : 0];
     const uint32_t n_entry = (uint32_t)(fb.entry_base[b + 1] - fb.entry_base[b]);
@@ -1095,7 +1133,7 @@ __global__ __launch_bounds__(kSbThreads, (C <= 8 ? TRIPS_SB_MIN_BLOCKS : 1)) voi
         int layer, gx, gy, p;
         tile_pixel(g, tile, lane, layer, gx, gy, p);  // lane i owns one pixel of the tile
         uint32_t cnt = 0, start = 0;
-        if (p >= 0)
+        if (p >= 0 && fb.view_base[b + 1] != fb.view_base[b])  // (a view that did not fit the list buffer renders as background)
         {
             cnt   = fb.counts[bP + p];
             start = fb.offsets[bP + p] - cnt;  // offsets hold list ends after the collect pass

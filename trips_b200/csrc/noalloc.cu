@@ -3,10 +3,12 @@
 // trips_adam_step keeps the table that tells the kernel where every parameter tensor lives (pointers, sizes,
 // hyper-parameters, and the first thread block of each tensor) in context scratch that it cudaMallocs on first use
 // and regrows when more tensors arrive.  Some callers cannot tolerate that: an optimizer step issued while the
-// framework above holds every free byte in its own caching pool, a plugin whose host rules forbid cudaMalloc
-// after start-up, or a step recorded into a stream capture, where an allocation is not a capturable operation.
-// This variant places the same table in a fixed device array that is part of the loaded library image, so that a
-// call does no cudaMalloc, no cudaFree and no allocating library call; it needs no TripsContext either.
+// framework above holds every free byte in its own caching pool, or a plugin whose host rules forbid cudaMalloc
+// after start-up.  This variant places the same table in a fixed device array that is part of the loaded library
+// image, so that a call does no cudaMalloc, no cudaFree and no allocating library call; it needs no TripsContext
+// either.  The table is uploaded from this function's stack frame with every call, so the call belongs on a stream
+// that executes it now: a stream that is being captured is refused (TRIPS_ERR_UNSUPPORTED) before anything is
+// enqueued, because a recorded copy would read the dead stack frame when the graph is replayed.
 #include <mutex>
 
 #include "common.cuh"
@@ -40,6 +42,16 @@ extern "C" int trips_adam_step_static(const TripsAdamTensor* tensors, int n_tens
         (void)cudaGetLastError();
         return TRIPS_ERR_CUDA;
     }
+    cudaStream_t st = (cudaStream_t)stream;
+    {
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(st, &cap) != cudaSuccess)
+        {
+            (void)cudaGetLastError();
+            return TRIPS_ERR_CUDA;
+        }
+        if (cap != cudaStreamCaptureStatusNone) return TRIPS_ERR_UNSUPPORTED;  // host-only check, nothing was enqueued
+    }
     // Set-up, once per device and with that device current: ask the runtime where this device's copy of the
     // array lives.  The first call on a device should therefore come before any stream capture.
     void* table = nullptr;
@@ -69,7 +81,6 @@ extern "C" int trips_adam_step_static(const TripsAdamTensor* tensors, int n_tens
     }
     const int64_t total_blocks = host.block_start[n_tensors];
     if (total_blocks >= (1ll << 31)) return TRIPS_ERR_TOO_LARGE;
-    cudaStream_t st = (cudaStream_t)stream;
     // The whole table is rewritten by every call, so nothing of the previous call's contents is ever read.  The
     // source is pageable stack memory: the runtime stages it before cudaMemcpyAsync returns.
     unsigned char* dev = static_cast<unsigned char*>(table);

@@ -93,6 +93,9 @@ class PointRendererCache:
         self._h = h
         self._dropout = None
         self._keepalive = None
+        # [views, points] float32, 1 = the point is dropped in that view.  None: the mask is drawn per forward pass with
+        # probability RenderParams.dropout, as the reference does; set it to render with a mask of the caller's choosing.
+        self.dropout_points = None
 
     def close(self):
         if getattr(self, "_h", None):
@@ -108,6 +111,9 @@ class PointRendererCache:
     # -- helpers ------------------------------------------------------------------------------------------------
     @staticmethod
     def _check_live_path(p: RenderParams):
+        # normalize_grads is accepted and changes nothing, exactly as in the reference: NormalizeGradient divides by hit
+        # counts (PointRenderer.cu:1193-1230, call sites :1348-1412) that are allocated as zeros (:226-272) and that no
+        # kernel of the reference ever increments, so its `if (c > 0)` guard never passes.
         # RenderForward.cu:313-316 asserts the same; the legacy alternates are not implemented
         if not (p.use_layer_point_size and p.render_points_in_all_lower_resolutions) or p.combine_lists:
             raise _lib.TripsError(_lib.ERR_UNSUPPORTED, "only use_layer_point_size && render_points_in_all_lower_resolutions && !combine_lists")
@@ -157,7 +163,12 @@ class PointRendererCache:
         c = texture.shape[0]
         n = points.shape[0]
         dropout = None
-        if info.train and info.params.dropout > 0:
+        if info.train and self.dropout_points is not None:
+            # a mask handed in by the caller (the reference keeps the mask in PointRendererCache::dropout_points)
+            dropout = self.dropout_points
+            if dropout.shape != (B, n) or dropout.dtype != torch.float32 or not dropout.is_cuda or not dropout.is_contiguous():
+                raise ValueError("dropout_points must be a contiguous float32 CUDA tensor [views, points]")
+        elif info.train and info.params.dropout > 0:
             # PointRendererCache::InitializeData, PointRenderer.cu:518-523
             dropout = torch.empty((B, n), device=points.device, dtype=torch.float32).bernoulli_(info.params.dropout)
         self._dropout = dropout
