@@ -82,7 +82,7 @@ def build_torch_shim(force: bool = False) -> str:
     """Compile the libtorch host side (csrc/torch_shim.cpp: NeuralRenderInfo, PointRender, BlendPointCloud on top of
     the C ABI) with the host compiler and link it against libtrips_b200.so and libtorch."""
     build()
-    deps = [SHIM_SRC, os.path.join(HERE, "..", "include", "trips_b200.h"), __file__]
+    deps = [SHIM_SRC, os.path.join(CSRC, "torch_shim.h"), os.path.join(HERE, "..", "include", "trips_b200.h"), __file__]
     if not force and os.path.exists(SHIM) and all(os.path.getmtime(d) <= os.path.getmtime(SHIM) for d in deps):
         return SHIM
     import torch

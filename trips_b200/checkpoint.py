@@ -1,12 +1,13 @@
 """Checkpoints with the reference's file and tensor names.
 
 NeuralScene::SaveCheckpoint / LoadCheckpoint (src/lib/data/NeuralScene.cpp:533-628) write one libtorch archive per
-module: points.pth (t_position, t_point_size as parameters; t_index, t_original_color as buffers,
+module under the prefix <checkpoint_dir>/scene_<scene name>_ (NeuralScene.cpp:535,597): points.pth (t_position, t_point_size as parameters; t_index, t_original_color as buffers,
 NeuralPointCloudCuda.cpp:103-108), texture.pth (texture, background_color, confidence_value_of_point: the RAW
 tensors under the names of their activated versions, NeuralTexture.cpp:53-55), poses.pth (tangent_poses, poses_se3,
 NeuralStructure.cpp:34-35), intrinsics.pth (intrinsics, NeuralStructure.cpp:142).  A libtorch archive is a
 TorchScript module whose attributes carry those names, so it is written here by scripting a container module and read
-back with torch.jit.load: files written by either side load on the other.
+back with torch.jit.load.  tests/test_checkpoint.py compiles a small libtorch program that torch::load()s the files
+written here into modules registering the reference's names, and torch::save()s them back for this side to read.
 
 The reference cannot save optimizer state (MyAdam::save / load abort, MyAdam.cu:417-425); optimizer.pth holds the
 three state tensors of every parameter under "<parameter name>.first_moments|second_moments|param_steps".
@@ -53,18 +54,25 @@ def _state_names(scene) -> Dict[int, str]:
             id(tex.confidence_raw): "confidence_value_of_point", id(tex.background_color_raw): "background_color"}
 
 
-def SaveCheckpoint(scene, checkpoint_dir: str, optimizers=()):
-    """Writes points.pth, texture.pth, poses.pth, intrinsics.pth and, with optimizers, optimizer.pth."""
+def checkpoint_prefix(scene, checkpoint_dir: str, scene_name=None) -> str:
+    """<checkpoint_dir>/scene_<scene name>_ (NeuralScene.cpp:535,597); the name defaults to scene.scene_name."""
+    name = scene_name if scene_name is not None else getattr(scene, "scene_name", "scene")
+    return os.path.join(checkpoint_dir, f"scene_{name}_")
+
+
+def SaveCheckpoint(scene, checkpoint_dir: str, optimizers=(), scene_name=None):
+    """Writes <prefix>points.pth, texture.pth, poses.pth, intrinsics.pth and, with optimizers, optimizer.pth."""
     os.makedirs(checkpoint_dir, exist_ok=True)
+    checkpoint_dir = checkpoint_prefix(scene, checkpoint_dir, scene_name)
     pc, tex = scene.point_cloud_cuda, scene.texture
     p = {"t_position": pc.t_position}
     b = {"t_index": pc.t_index, "t_original_color": pc.t_original_color}
     (p if isinstance(pc.t_point_size, nn.Parameter) else b)["t_point_size"] = pc.t_point_size
-    _write(os.path.join(checkpoint_dir, POINTS), p, b)
-    _write(os.path.join(checkpoint_dir, TEXTURE), {"texture": tex.texture_raw, "background_color": tex.background_color_raw,
+    _write(checkpoint_dir + POINTS, p, b)
+    _write(checkpoint_dir + TEXTURE, {"texture": tex.texture_raw, "background_color": tex.background_color_raw,
                                                     "confidence_value_of_point": tex.confidence_raw}, {})
-    _write(os.path.join(checkpoint_dir, POSES), {"tangent_poses": scene.poses.tangent_poses}, {"poses_se3": scene.poses.poses_se3})
-    _write(os.path.join(checkpoint_dir, INTRINSICS), {"intrinsics": scene.intrinsics.intrinsics}, {})
+    _write(checkpoint_dir + POSES, {"tangent_poses": scene.poses.tangent_poses}, {"poses_se3": scene.poses.poses_se3})
+    _write(checkpoint_dir + INTRINSICS, {"intrinsics": scene.intrinsics.intrinsics}, {})
     names = _state_names(scene)
     state = {}
     for opt in optimizers:
@@ -75,19 +83,20 @@ def SaveCheckpoint(scene, checkpoint_dir: str, optimizers=()):
                     for k in ("first_moments", "second_moments", "param_steps"):
                         state[f"{names[id(q)]}.{k}".replace(".", "__")] = st[k]
     if state:
-        _write(os.path.join(checkpoint_dir, OPTIMIZER), {}, state)
+        _write(checkpoint_dir + OPTIMIZER, {}, state)
 
 
 @torch.no_grad()
-def LoadCheckpoint(scene, checkpoint_dir: str, optimizers=()):
-    """Loads whatever of the five files exists (as the reference does); tensors are replaced, so the number of points may
-    differ from the scene's current one.  Returns the list of files read."""
+def LoadCheckpoint(scene, checkpoint_dir: str, optimizers=(), scene_name=None):
+    """Loads whatever of the five files exists under the scene's prefix (as the reference does); tensors are replaced, so
+    the number of points may differ from the scene's current one.  Returns the list of files read (without the prefix)."""
     pc, tex = scene.point_cloud_cuda, scene.texture
+    prefix = checkpoint_prefix(scene, checkpoint_dir, scene_name)
     dev = pc.t_position.device
     read = []
 
     def have(name):
-        path = os.path.join(checkpoint_dir, name)
+        path = prefix + name
         if os.path.exists(path):
             read.append(name)
             return _read(path, dev)

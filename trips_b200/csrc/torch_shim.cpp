@@ -1,92 +1,89 @@
-// libtorch host side of the rasterizer: the reference's operator interface on top of the C ABI.
-//
-// Same names and argument order as the reference (src/lib/rendering/PointRenderer.h:23-53, RenderInfo.cpp:14-40):
-// NeuralRenderInfo (a torch custom class), PointRendererCache, torch::autograd::PointRender and BlendPointCloud.  The
-// reference reaches its tensors through NeuralScene modules; here the info object holds the same tensors directly
-// (texture, background_color, t_position, poses_se3, intrinsics, confidence_value_of_point, t_point_size, t_index).
-// Tensors are flattened to device pointers and handed to trips_forward / trips_backward on the current CUDA stream;
-// nothing is computed in this file.  Registered as torch.classes.trips_b200.NeuralRenderInfo,
-// torch.ops.trips_b200.blend_point_cloud and torch.ops.trips_b200.adam_step (MyAdam::step), which is how tests/ drive it.
+// libtorch host side of the rasterizer (see torch_shim.h): NeuralRenderInfo / PointRender / BlendPointCloud /
+// PointRenderModule / MyAdam and the parameter modules, all on top of the C ABI.  Also registered for Python as
+// torch.classes.trips_b200.{NeuralRenderInfo, PointRenderModule, MyAdam} and torch.ops.trips_b200.{blend_point_cloud,
+// adam_step}, which is how tests/ drive this file.
+#include "torch_shim.h"
+
 #include <c10/cuda/CUDAStream.h>
-#include <torch/custom_class.h>
-#include <torch/torch.h>
 
-#include <memory>
+#include <mutex>
 #include <stdexcept>
-#include <string>
-#include <vector>
 
-#include "trips_b200.h"
-
-namespace trips_shim
+namespace trips_b200
 {
-using torch::Tensor;
-
-// owns the C context, like PointRendererCache owns the reference's scratch tensors (PointRenderer.h:126-176)
-struct PointRendererCache
-{
-    TripsContext* handle = nullptr;
-    int device           = -1;
-    Tensor dropout_points;  // [B,N], training with dropout > 0 only (PointRenderer.cu:518-523)
-    ~PointRendererCache()
-    {
-        if (handle) trips_context_destroy(handle);
-    }
-    void ensure(int dev)
-    {
-        if (handle && dev == device) return;
-        if (handle) trips_context_destroy(handle);
-        handle = nullptr;
-        const int st = trips_context_create(&handle, dev);
-        if (st != TRIPS_OK) throw std::runtime_error(std::string("trips_context_create: ") + trips_status_string(st));
-        device = dev;
-    }
-};
-
 static void check(int st, TripsContext* ctx, const char* what)
 {
     if (st != TRIPS_OK) throw std::runtime_error(std::string(what) + ": " + trips_status_string(st) + " (" + trips_last_error(ctx) + ")");
 }
 
-struct NeuralRenderInfo : torch::CustomClassHolder
+// ------------------------------------------------------------------------------------------------------------
+// PointRendererCache, NeuralRenderInfo
+// ------------------------------------------------------------------------------------------------------------
+PointRendererCache::~PointRendererCache()
 {
-    // scene (NeuralScene: point_cloud_cuda, texture, poses, intrinsics)
-    Tensor texture, background_color, t_position, poses_se3, intrinsics, confidence_value_of_point, t_point_size, t_index;
-    std::vector<TripsView> images;  // ReducedImageInfo, SceneData.h:40-61
-    TripsRenderParams params{8, 16, 0, 0, 0.f, 0, 0.f, 0};
-    double dropout = 0.0;
-    int64_t num_layers = 8;
-    bool train         = false;
-    std::shared_ptr<PointRendererCache> cache = std::make_shared<PointRendererCache>();
+    if (handle) trips_context_destroy(handle);
+}
 
-    void set_scene(Tensor texture_, Tensor background_color_, Tensor t_position_, Tensor poses_se3_, Tensor intrinsics_,
-                   Tensor confidence_, Tensor t_point_size_, c10::optional<Tensor> t_index_)
-    {
-        texture = texture_, background_color = background_color_, t_position = t_position_, poses_se3 = poses_se3_;
-        intrinsics = intrinsics_, confidence_value_of_point = confidence_, t_point_size = t_point_size_;
-        t_index = t_index_.has_value() ? *t_index_ : Tensor();
-    }
-    void add_image(int64_t w, int64_t h, int64_t image_index, int64_t camera_index, int64_t camera_model_type,
-                   std::vector<double> crop_transform, std::vector<double> crop_rotation)
-    {
-        TORCH_CHECK(crop_transform.size() == 5 && crop_rotation.size() == 4, "crop_transform has 5, crop_rotation 4 values");
-        TripsView v{};
-        v.w = (int)w, v.h = (int)h, v.image_index = (int)image_index, v.camera_index = (int)camera_index;
-        v.camera_model_type = (int)camera_model_type;
-        for (int i = 0; i < 5; ++i) v.crop_transform[i] = (float)crop_transform[i];
-        for (int i = 0; i < 4; ++i) v.crop_rotation[i] = (float)crop_rotation[i];
-        images.push_back(v);
-    }
-    void clear_images() { images.clear(); }
-    void set_params(int64_t num_layers_, int64_t k_keep, bool train_, bool drop_out_points_by_radius, double drop_out_radius_threshold,
-                    bool viewer_only, double stability_cutoff_value, bool bg_uses_Tn, double dropout_)
-    {
-        num_layers = num_layers_, train = train_, dropout = dropout_;
-        params = TripsRenderParams{(int)num_layers_, (int)k_keep, train_ ? 1 : 0, drop_out_points_by_radius ? 1 : 0,
-                                   (float)drop_out_radius_threshold, viewer_only ? 1 : 0, (float)stability_cutoff_value, bg_uses_Tn ? 1 : 0};
-    }
-    int64_t last_status() { return cache->handle ? (int64_t)trips_last_status(cache->handle, c10::cuda::getCurrentCUDAStream().stream()) : 0; }
-};
+void PointRendererCache::ensure(int dev)
+{
+    if (handle && dev == device) return;
+    if (handle) trips_context_destroy(handle);
+    handle       = nullptr;
+    const int st = trips_context_create(&handle, dev);
+    if (st != TRIPS_OK) throw std::runtime_error(std::string("trips_context_create: ") + trips_status_string(st));
+    device = dev;
+}
+
+void NeuralRenderInfo::set_scene(Tensor texture_, Tensor background_color_, Tensor t_position_, Tensor poses_se3_,
+                                 c10::optional<Tensor> tangent_poses_, Tensor intrinsics_, Tensor confidence_, Tensor t_point_size_,
+                                 c10::optional<Tensor> t_index_)
+{
+    texture = texture_, background_color = background_color_, t_position = t_position_, poses_se3 = poses_se3_;
+    tangent_poses = tangent_poses_.has_value() ? *tangent_poses_ : Tensor();
+    intrinsics = intrinsics_, confidence_value_of_point = confidence_, t_point_size = t_point_size_;
+    t_index = t_index_.has_value() ? *t_index_ : Tensor();
+}
+
+void NeuralRenderInfo::add_image(int64_t w, int64_t h, int64_t image_index, int64_t camera_index, int64_t camera_model_type,
+                                 std::vector<double> crop_transform, std::vector<double> crop_rotation)
+{
+    TORCH_CHECK(crop_transform.size() == 5 && crop_rotation.size() == 4, "crop_transform has 5, crop_rotation 4 values");
+    TripsView v{};
+    v.w = (int)w, v.h = (int)h, v.image_index = (int)image_index, v.camera_index = (int)camera_index;
+    v.camera_model_type = (int)camera_model_type;
+    for (int i = 0; i < 5; ++i) v.crop_transform[i] = (float)crop_transform[i];
+    for (int i = 0; i < 4; ++i) v.crop_rotation[i] = (float)crop_rotation[i];
+    images.push_back(v);
+}
+
+void NeuralRenderInfo::clear_images() { images.clear(); }
+
+void NeuralRenderInfo::set_params(int64_t num_layers_, int64_t k_keep, bool train_, bool drop_out_points_by_radius,
+                                  double drop_out_radius_threshold, bool viewer_only, double stability_cutoff_value, bool bg_uses_Tn,
+                                  double dropout_)
+{
+    num_layers = num_layers_, train = train_, dropout = dropout_;
+    params.num_layers                = (int)num_layers_;
+    params.k_keep                    = (int)k_keep;
+    params.train                     = train_ ? 1 : 0;
+    params.drop_out_points_by_radius = drop_out_points_by_radius ? 1 : 0;
+    params.drop_out_radius_threshold = (float)drop_out_radius_threshold;
+    params.viewer_only               = viewer_only ? 1 : 0;
+    params.stability_cutoff_value    = (float)stability_cutoff_value;
+    params.bg_uses_Tn                = bg_uses_Tn ? 1 : 0;
+}
+
+void NeuralRenderInfo::set_texture_preparation(bool confidence_is_raw, double confidence_scale, bool texture_abs)
+{
+    params.confidence_is_raw = confidence_is_raw ? 1 : 0;
+    params.confidence_scale  = (float)confidence_scale;
+    params.texture_abs       = texture_abs ? 1 : 0;
+}
+
+int64_t NeuralRenderInfo::last_status()
+{
+    return cache->handle ? (int64_t)trips_last_status(cache->handle, c10::cuda::getCurrentCUDAStream().stream()) : 0;
+}
 
 static const float* fptr(const Tensor& t) { return t.defined() ? t.data_ptr<float>() : nullptr; }
 
@@ -201,22 +198,262 @@ class PointRender : public torch::autograd::Function<PointRender>
     }
 };
 
-// BlendPointCloud (RenderInfo.cpp:27-40)
-std::vector<Tensor> BlendPointCloud(const c10::intrusive_ptr<NeuralRenderInfo>& info, const Tensor& pose_tangents)
+std::vector<Tensor> BlendPointCloud(const c10::intrusive_ptr<NeuralRenderInfo>& info)
 {
-    return PointRender::apply(info->texture, info->background_color, info->t_position, pose_tangents, info->intrinsics,
+    TORCH_CHECK(info->texture.defined() && info->t_position.defined(), "NeuralRenderInfo has no scene");
+    const Tensor tangents = info->tangent_poses.defined() ? info->tangent_poses : torch::empty({0}, info->poses_se3.options());
+    return PointRender::apply(info->texture, info->background_color, info->t_position, tangents, info->intrinsics,
                               info->confidence_value_of_point, torch::empty({0}, info->t_position.options()) /* dynamic refinement: none */,
                               info->t_point_size, torch::IValue(info));
 }
 
-// MyAdam::step over a list of parameter tensors (MyAdam.cu:164-345 launches adam_step once per tensor; here one launch
-// covers all of them).  State tensors are those MyAdam keeps per parameter: first_moments, second_moments (float32,
-// shape of the parameter) and param_steps (int32 here, int64 in the reference).  Updates weights and state in place.
+PointRenderModuleImpl::PointRenderModuleImpl(int num_layers_) : num_layers(num_layers_), cache(std::make_shared<PointRendererCache>()) {}
+
+std::pair<std::vector<Tensor>, std::vector<Tensor>> PointRenderModuleImpl::forward(const c10::intrusive_ptr<NeuralRenderInfo>& nri)
+{
+    nri->cache      = cache;  // RenderModule.cpp:57
+    nri->num_layers = num_layers;
+    if (!is_training())  // RenderModule.cpp:27-35
+    {
+        nri->dropout = 0;
+        nri->train   = false;
+    }
+    else
+        nri->train = true;
+    auto images = BlendPointCloud(nri);
+    images.resize(num_layers);
+    return {images, {}};
+}
+
+// ------------------------------------------------------------------------------------------------------------
+// MyAdam
+// ------------------------------------------------------------------------------------------------------------
+MyAdam::MyAdam(std::vector<torch::optim::OptimizerParamGroup> param_groups, MyAdamOptions defaults)
+    : Optimizer(std::move(param_groups), std::make_unique<MyAdamOptions>(defaults))
+{
+    TORCH_CHECK(defaults.lr() >= 0, "Invalid learning rate: ", defaults.lr());
+    TORCH_CHECK(defaults.eps() >= 0, "Invalid epsilon value: ", defaults.eps());
+    auto betas = defaults.betas();
+    TORCH_CHECK(0 <= std::get<0>(betas) && std::get<0>(betas) < 1.0, "Invalid beta parameter at index 0: ", std::get<0>(betas));
+    TORCH_CHECK(0 <= std::get<1>(betas) && std::get<1>(betas) < 1.0, "Invalid beta parameter at index 1: ", std::get<1>(betas));
+    TORCH_CHECK(defaults.relative_weight_decay() >= 0, "Invalid relative_weight_decay value: ", defaults.relative_weight_decay());
+    TORCH_CHECK(defaults.absolute_weight_decay() >= 0, "Invalid absolute_weight_decay value: ", defaults.absolute_weight_decay());
+}
+
+MyAdam::MyAdam(std::vector<Tensor> params, MyAdamOptions defaults)
+    : MyAdam(std::vector<torch::optim::OptimizerParamGroup>{torch::optim::OptimizerParamGroup(std::move(params))}, defaults)
+{
+}
+
+MyAdam::~MyAdam()
+{
+    if (ctx_) trips_context_destroy(ctx_);
+}
+
+MyAdamParamState* MyAdam::state_of(const Tensor& p)
+{
+    auto it = state_.find(p.unsafeGetTensorImpl());
+    return it == state_.end() ? nullptr : static_cast<MyAdamParamState*>(it->second.get());
+}
+
+Tensor MyAdam::step(LossClosure closure)
+{
+    torch::NoGradGuard no_grad;
+    Tensor loss = {};
+    if (closure != nullptr)
+    {
+        at::AutoGradMode enable_grad(true);
+        loss = closure();
+    }
+    std::vector<TripsAdamTensor> table;
+    std::vector<Tensor> keep;  // contiguous gradients stay alive until the launch is enqueued
+    for (auto& group : param_groups_)
+    {
+        auto& options = static_cast<MyAdamOptions&>(group.options());
+        for (auto& p : group.params())
+        {
+            if (!p.grad().defined()) continue;
+            auto grad = p.grad();
+            TORCH_CHECK(!grad.is_sparse(), "Adam does not support sparse gradients");
+            TORCH_CHECK(p.scalar_type() == torch::kFloat32 && p.is_cuda() && p.is_contiguous(), "MyAdam takes contiguous float32 CUDA parameters");
+            if (device_ != p.get_device())
+            {
+                TORCH_CHECK(device_ < 0, "all parameters of one MyAdam must live on one device");
+                device_ = p.get_device();
+                check(trips_context_create(&ctx_, device_), nullptr, "trips_context_create");
+            }
+            MyAdamParamState* st = state_of(p);
+            if (!st)  // state initialisation, MyAdam.cu:184-200
+            {
+                auto state = std::make_unique<MyAdamParamState>();
+                state->param_steps(torch::zeros(p.sizes(), p.options().dtype(torch::kInt32)));
+                state->first_moments(torch::zeros_like(p, torch::MemoryFormat::Contiguous));
+                state->second_moments(torch::zeros_like(p, torch::MemoryFormat::Contiguous));
+                state->current_step(0);
+                st                                = state.get();
+                state_[p.unsafeGetTensorImpl()] = std::move(state);
+            }
+            st->current_step(st->current_step() + 1);
+            const float beta1 = (float)std::get<0>(options.betas()), beta2 = (float)std::get<1>(options.betas());
+            float lower = 0.f, upper = std::numeric_limits<float>::max();
+            if (options.adabound())  // MyAdam.cu:220-224
+            {
+                lower = 0.1f - 0.1f / ((1 - beta2) * (float)st->current_step() + 1);
+                upper = 0.1f + 0.1f / ((1 - beta2) * (float)st->current_step());
+            }
+            keep.push_back(grad.contiguous());
+            TORCH_CHECK(keep.back().scalar_type() == torch::kFloat32 && keep.back().numel() == p.numel(), "gradient must match the parameter");
+            table.push_back(TripsAdamTensor{p.data_ptr<float>(), keep.back().data_ptr<float>(), st->first_moments().data_ptr<float>(),
+                                            st->second_moments().data_ptr<float>(), st->param_steps().data_ptr<int32_t>(), p.numel(),
+                                            (float)options.lr(), beta1, beta2, (float)options.eps(), (float)options.relative_weight_decay(),
+                                            (float)options.absolute_weight_decay(), (float)options.weight_clipping_magnitude(), lower, upper});
+        }
+    }
+    if (!table.empty())
+        check(trips_adam_step(ctx_, table.data(), (int)table.size(), c10::cuda::getCurrentCUDAStream(device_).stream()), ctx_, "trips_adam_step");
+    return loss;
+}
+
+void MyAdam::save(torch::serialize::OutputArchive&) const { TORCH_CHECK(false, "MyAdam::save is not supported (as in the reference)"); }
+void MyAdam::load(torch::serialize::InputArchive&) { TORCH_CHECK(false, "MyAdam::load is not supported (as in the reference)"); }
+
+void MyAdam::shrinkInternalState(int param_group_index, Tensor indices_to_keep)
+{
+    TORCH_CHECK(param_group_index >= 0 && param_group_index < (int)param_groups_.size(), "param group out of range");
+    torch::NoGradGuard no_grad;
+    for (auto& p : param_groups_[param_group_index].params())
+    {
+        MyAdamParamState* st = state_of(p);
+        if (!st) continue;  // not created yet: initialised by the first step
+        auto shrink = [&](Tensor t) {
+            return t.index_select(t.dim() - 1, indices_to_keep.reshape({-1}).to(t.device()).to(torch::kLong)).contiguous();
+        };
+        st->first_moments(shrink(st->first_moments()));
+        st->second_moments(shrink(st->second_moments()));
+        st->param_steps(shrink(st->param_steps()));
+    }
+}
+
+void MyAdam::appendToInternalState(int param_group_index, int new_size)
+{
+    TORCH_CHECK(param_group_index >= 0 && param_group_index < (int)param_groups_.size(), "param group out of range");
+    torch::NoGradGuard no_grad;
+    for (auto& p : param_groups_[param_group_index].params())
+    {
+        MyAdamParamState* st = state_of(p);
+        if (!st) continue;
+        auto extend = [&](Tensor t) {
+            std::vector<int64_t> sizes(t.sizes().begin(), t.sizes().end());
+            sizes.back() = new_size - t.size(-1);
+            TORCH_CHECK(sizes.back() >= 0, "appendToInternalState cannot shrink");
+            return torch::cat({t, torch::zeros(sizes, t.options())}, -1).contiguous();
+        };
+        st->first_moments(extend(st->first_moments()));
+        st->second_moments(extend(st->second_moments()));
+        st->param_steps(extend(st->param_steps()));
+    }
+}
+
+void UpdateOptimLR(torch::optim::Optimizer* optimizer, double factor)
+{
+    for (auto& pg : optimizer->param_groups()) pg.options().set_lr(pg.options().get_lr() * factor);
+}
+
+// ------------------------------------------------------------------------------------------------------------
+// parameter modules (registered names = checkpoint format)
+// ------------------------------------------------------------------------------------------------------------
+NeuralPointCloudCudaImpl::NeuralPointCloudCudaImpl(Tensor position, Tensor point_size, Tensor index, Tensor original_color)
+{
+    t_position       = register_parameter("t_position", position);
+    t_index          = register_buffer("t_index", index);
+    t_original_color = register_buffer("t_original_color", original_color);
+    t_point_size     = register_parameter("t_point_size", point_size);
+}
+
+NeuralPointTextureImpl::NeuralPointTextureImpl(int num_channels, int num_points)
+{
+    texture_raw          = register_parameter("texture", torch::ones({num_channels, num_points}) * 0.5);
+    background_color_raw = register_parameter("background_color", torch::ones({num_channels}) * 0.25);
+    confidence_raw       = register_parameter("confidence_value_of_point", torch::ones({1, num_points}) * 0.5);
+}
+
+PoseModuleImpl::PoseModuleImpl(int num_images)
+{
+    tangent_poses = register_parameter("tangent_poses", torch::zeros({num_images, 6}, torch::kFloat64));
+    poses_se3     = register_buffer("poses_se3", torch::zeros({num_images, 8}, torch::kFloat64));
+}
+
+IntrinsicsModuleImpl::IntrinsicsModuleImpl(int num_cameras)
+{
+    intrinsics = register_parameter("intrinsics", torch::zeros({num_cameras, 13}));
+}
+
+// ------------------------------------------------------------------------------------------------------------
+// registration for Python (tests drive the C++ classes through these)
+// ------------------------------------------------------------------------------------------------------------
+namespace
+{
+struct PointRenderModuleHolder : torch::CustomClassHolder
+{
+    PointRenderModule module;
+    explicit PointRenderModuleHolder(int64_t num_layers) : module((int)num_layers) {}
+    void train(bool on) { module->train(on); }
+    std::vector<Tensor> forward(const c10::intrusive_ptr<NeuralRenderInfo>& nri) { return module->forward(nri).first; }
+};
+
+struct MyAdamHolder : torch::CustomClassHolder
+{
+    std::unique_ptr<MyAdam> opt;
+    void add_param_group(std::vector<Tensor> params, double lr, double beta1, double beta2, double eps, double relative_weight_decay,
+                         double absolute_weight_decay, double weight_clipping_magnitude, bool adabound)
+    {
+        MyAdamOptions o(lr);
+        o.betas(std::make_tuple(beta1, beta2)).eps(eps).relative_weight_decay(relative_weight_decay).absolute_weight_decay(absolute_weight_decay);
+        o.weight_clipping_magnitude(weight_clipping_magnitude).adabound(adabound);
+        torch::optim::OptimizerParamGroup g(std::move(params), std::make_unique<MyAdamOptions>(o));
+        if (!opt)
+            opt = std::make_unique<MyAdam>(std::vector<torch::optim::OptimizerParamGroup>{g}, o);
+        else
+            opt->add_param_group(g);
+    }
+    void step()
+    {
+        TORCH_CHECK(opt, "no param group");
+        opt->step();
+    }
+    void shrinkInternalState(int64_t group, Tensor keep) { opt->shrinkInternalState((int)group, keep); }
+    void appendToInternalState(int64_t group, int64_t new_size) { opt->appendToInternalState((int)group, (int)new_size); }
+    void scale_lr(double factor) { UpdateOptimLR(opt.get(), factor); }
+    // (first_moments, second_moments, param_steps) of parameter `index` of `group`; empty before its first step
+    std::vector<Tensor> state(int64_t group, int64_t index)
+    {
+        auto* st = opt->state_of(opt->param_groups().at(group).params().at(index));
+        if (!st) return {};
+        return {st->first_moments(), st->second_moments(), st->param_steps()};
+    }
+};
+
+// One context per device for the functional adam_step operator below.
+TripsContext* functional_context(int device)
+{
+    static std::mutex mu;
+    static TripsContext* ctx[64] = {};
+    std::lock_guard<std::mutex> lock(mu);
+    TORCH_CHECK(device >= 0 && device < 64, "device index out of range");
+    if (!ctx[device]) check(trips_context_create(&ctx[device], device), nullptr, "trips_context_create");
+    return ctx[device];
+}
+}  // namespace
+
+// MyAdam::step over explicit lists of tensors, for callers that keep the optimizer state themselves (MyAdam.cu:164-345
+// launches adam_step once per tensor; here one launch covers all of them).  State tensors: first_moments,
+// second_moments (float32, shape of the parameter) and param_steps (int32 here, int64 in the reference).  Runs through
+// trips_adam_step on a context the library keeps per device: calls on one device are ordered by their streams as usual.
 void AdamStep(std::vector<Tensor> weights, std::vector<Tensor> gradients, std::vector<Tensor> first_moments,
               std::vector<Tensor> second_moments, std::vector<Tensor> steps, double lr, double beta1, double beta2, double eps)
 {
     const size_t n = weights.size();
-    TORCH_CHECK(n > 0 && n <= TRIPS_ADAM_STATIC_MAX_TENSORS, "1 to ", TRIPS_ADAM_STATIC_MAX_TENSORS, " tensors per call");
+    TORCH_CHECK(n > 0, "no tensors");
     TORCH_CHECK(gradients.size() == n && first_moments.size() == n && second_moments.size() == n && steps.size() == n,
                 "one gradient and one state triple per weight tensor");
     std::vector<TripsAdamTensor> table(n);
@@ -234,8 +471,9 @@ void AdamStep(std::vector<Tensor> weights, std::vector<Tensor> gradients, std::v
                                    second_moments[i].data_ptr<float>(), steps[i].data_ptr<int32_t>(), k, (float)lr, (float)beta1, (float)beta2,
                                    (float)eps, 0.f, 0.f, 0.f, 0.f, 3.4028234663852886e38f};
     }
-    const int st = trips_adam_step_static(table.data(), (int)n, c10::cuda::getCurrentCUDAStream().stream());
-    TORCH_CHECK(st == TRIPS_OK, "trips_adam_step_static: ", trips_status_string(st));
+    const int device  = weights[0].get_device();
+    TripsContext* ctx = functional_context(device);
+    check(trips_adam_step(ctx, table.data(), (int)n, c10::cuda::getCurrentCUDAStream(device).stream()), ctx, "trips_adam_step");
 }
 
 TORCH_LIBRARY(trips_b200, m)
@@ -246,10 +484,23 @@ TORCH_LIBRARY(trips_b200, m)
         .def("add_image", &NeuralRenderInfo::add_image)
         .def("clear_images", &NeuralRenderInfo::clear_images)
         .def("set_params", &NeuralRenderInfo::set_params)
+        .def("set_texture_preparation", &NeuralRenderInfo::set_texture_preparation)
         .def("last_status", &NeuralRenderInfo::last_status);
-    m.def("blend_point_cloud(__torch__.torch.classes.trips_b200.NeuralRenderInfo info, Tensor pose_tangents) -> Tensor[]", &BlendPointCloud);
+    m.class_<PointRenderModuleHolder>("PointRenderModule")
+        .def(torch::init<int64_t>())
+        .def("train", &PointRenderModuleHolder::train)
+        .def("forward", &PointRenderModuleHolder::forward);
+    m.class_<MyAdamHolder>("MyAdam")
+        .def(torch::init<>())
+        .def("add_param_group", &MyAdamHolder::add_param_group)
+        .def("step", &MyAdamHolder::step)
+        .def("shrinkInternalState", &MyAdamHolder::shrinkInternalState)
+        .def("appendToInternalState", &MyAdamHolder::appendToInternalState)
+        .def("scale_lr", &MyAdamHolder::scale_lr)
+        .def("state", &MyAdamHolder::state);
+    m.def("blend_point_cloud(__torch__.torch.classes.trips_b200.NeuralRenderInfo info) -> Tensor[]", &BlendPointCloud);
     m.def("adam_step(Tensor[] weights, Tensor[] gradients, Tensor[] first_moments, Tensor[] second_moments, Tensor[] steps, float lr, "
           "float beta1, float beta2, float eps) -> ()",
           &AdamStep);
 }
-}  // namespace trips_shim
+}  // namespace trips_b200

@@ -143,6 +143,7 @@ class NeuralScene(nn.Module):
         self.poses = poses
         self.intrinsics = intrinsics
         self.dynamic_refinement_t = torch.zeros(1, device=point_cloud_cuda.t_position.device)  # dummy, NeuralScene.cpp
+        self.scene_name = "scene"  # SceneData::scene_name: part of the checkpoint file names (NeuralScene.cpp:535,597)
 
     @classmethod
     def from_synthetic(cls, s: Scene, device="cuda", confidence_is_activated: bool = True) -> "NeuralScene":
@@ -156,7 +157,9 @@ class NeuralScene(nn.Module):
             tex.background_color_raw.copy_(torch.from_numpy(s.background).to(dev))
         poses = PoseModule(torch.from_numpy(s.poses).to(dev))
         intr = IntrinsicsModule(torch.from_numpy(s.intrinsics).to(dev))
-        return cls(pc, tex, poses, intr)
+        ns = cls(pc, tex, poses, intr)
+        ns.scene_name = s.name
+        return ns
 
     # -- point removal / growth on the device (NeuralScene::RemovePoints / AddNewPoints, NeuralScene.cpp:1224-1431) ----
     def _point_tensors(self, optimizers=()):
