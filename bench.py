@@ -41,6 +41,10 @@ def parse_args():
     ap.add_argument("--views-per-gpu", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--render-only", action="store_true",
+                    help="step = inference render (train = 0) of the rank's views, no backward, no Adam: the render-only batch of "
+                         "BASELINE config 5 is `--workload c5 --render-only --views-per-gpu 64/N`")
+    ap.add_argument("--no-strong", action="store_true", help="N>1: skip the strong-scaling pass (8 views split over the ranks)")
     ap.add_argument("--cpu-views", type=int, default=12, help="views of the workload the CPU baseline renders")
     ap.add_argument("--op", default="step", choices=["step", "resize_points", "texture_prepare"],
                     help="'step' (default): the training-step benchmark; 'resize_points': removal of 10 % of the points over all "
@@ -153,6 +157,11 @@ def stage_bytes(stage, N, P, C, B, F, Kf):
         return RECORD_BYTES * Kf + 4 * C * P * B + 8 * (C + 5) * Kf
     if stage == "adam":
         return 36 * (N * (C + 1 + 4 + 1))
+    if stage == "unpack_grads":
+        # no term in the reference's formula (its backward kernel adds straight into the outputs); what the stage must move:
+        # per visible point and view one 32-byte gradient row cleared, read and its 32-byte entry head read, per point one row
+        # (4 + C4 + 1 floats) cleared, read and written out in the reference's layouts
+        return 0
     return 0
 
 
@@ -162,11 +171,11 @@ DRAM_BYTES_PER_UNIT = {"collect": (22.4, "F"), "sort_blend": (36.3, "F"), "blend
                        "bin_points": (95.9, "NB"), "adam": (347.9, "N")}
 
 
-def stage_traffic(stage, N, B, F, Kf):
+def stage_traffic(stage, N, B, F, Kf, V=0):
     if stage not in DRAM_BYTES_PER_UNIT:
         return None
     per, unit = DRAM_BYTES_PER_UNIT[stage]
-    return per * {"F": F, "Kf": Kf, "NB": N * B, "N": N}[unit]
+    return per * {"F": F, "Kf": Kf, "NB": N * B, "N": N, "V": V}[unit]
 
 
 def fused_adam_bytes(numel, world):
@@ -177,12 +186,12 @@ def fused_adam_bytes(numel, world):
 # ----------------------------------------------------------------------------------------------------------------
 # CPU arm: the oracle (restatement of the reference kernels) on the host cores
 # ----------------------------------------------------------------------------------------------------------------
-def cpu_views_per_second(s, views, repeats=1, with_adam=True):
-    """Forward + backward of `views` with the oracle; returns (views/s, seconds, fragments)."""
+def cpu_views_per_second(s, views, repeats=1, with_backward=True):
+    """Forward (+ backward) of `views` with the oracle; returns (views/s, seconds, fragments)."""
     import oracle
     from trips_b200 import scenes
     sa = oracle.SceneArrays.from_scene(s)
-    p = oracle.make_params(s.num_layers, s.k_keep, True)
+    p = oracle.make_params(s.num_layers, s.k_keep, with_backward)
     g = scenes.target_gradient(s, views[0])
     t0 = time.perf_counter()
     frags = 0
@@ -190,7 +199,8 @@ def cpu_views_per_second(s, views, repeats=1, with_adam=True):
     for _ in range(repeats):
         for v in views:
             f = oracle.forward(sa, oracle.make_view(s.width, s.height, s.poses[v], s.intrinsics[v]), p)
-            f.backward(g)
+            if with_backward:
+                f.backward(g)
             frags += f.F
             n += 1
             del f
@@ -198,8 +208,16 @@ def cpu_views_per_second(s, views, repeats=1, with_adam=True):
     return n / dt, dt, frags
 
 
+def workload_config(s, B, world):
+    """The keys that name the workload; both arms print the same ones."""
+    return {"workload": s.name, "points": s.n_points, "views_per_gpu": B, "global_views_per_step": B * world, "width": s.width,
+            "height": s.height, "layers": s.num_layers, "k_keep": s.k_keep, "channels": s.channels}
+
+
 def run_reference(args, rank):
-    """`--impl reference`: the CPU restatement timed on the host cores, one view of the workload per step."""
+    """`--impl reference`: the CPU restatement of the reference's kernels timed on the host cores, on the GPU arm's
+    configuration: one step = forward + backward of the rank-0 views of the workload and the Adam update of all point
+    parameters (oracle.adam, MyAdam.cu:41-88).  Under torchrun only rank 0 works."""
     if rank != 0:
         return
     import oracle
@@ -210,23 +228,38 @@ def run_reference(args, rank):
     sa = oracle.SceneArrays.from_scene(s)
     p = oracle.make_params(s.num_layers, s.k_keep, True)
     g = scenes.target_gradient(s, 0)
+    # parameters in the reference's tensors; gradients are summed over the views in double and handed to Adam in float
+    weights = {"texture": sa.texture.reshape(-1), "confidence": sa.confidence.reshape(-1), "position": sa.position.reshape(-1),
+               "point_size": sa.point_size.reshape(-1)}
+    state = {k: (np.zeros_like(w), np.zeros_like(w), np.zeros(w.size, np.int64)) for k, w in weights.items()}
     times = []
     for it in range(args.warmup + args.steps):
-        v = my_views[it % len(my_views)]
         t0 = time.perf_counter()
-        f = oracle.forward(sa, oracle.make_view(s.width, s.height, s.poses[v], s.intrinsics[v]), p)
-        f.backward(g)
+        total = None
+        for v in my_views:
+            f = oracle.forward(sa, oracle.make_view(s.width, s.height, s.poses[v], s.intrinsics[v]), p)
+            r = f.backward(g)
+            del f
+            if total is None:
+                total = r
+            else:
+                for k in weights:
+                    total[k] += r[k]
+        for k, w in weights.items():
+            m, v2, st = state[k]
+            oracle.adam(w, np.ascontiguousarray(total[k].reshape(-1), dtype=np.float32), m, v2, st, lr=1e-3)
         dt = time.perf_counter() - t0
-        del f
         if it >= args.warmup:
             times.append(dt)
     ms = 1000.0 * float(np.mean(times))
-    value = 1000.0 / ms
-    sample = f"1 view of {s.name} per step (forward + backward, no Adam), {args.steps} steps"
+    value = len(my_views) * 1000.0 / ms
+    sample = f"{len(my_views)} view(s) of {s.name} per step: forward + backward + Adam over all point parameters, {args.steps} steps"
+    cfg = workload_config(s, len(my_views), 1)
+    cfg["parallelism"] = f"OpenMP on {cores} host cores"
     emit({
         "impl": "reference", "metric": METRIC, "value": value, "unit": "views/s", "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "f32", "data": "synthetic", "config": {"workload": s.name, "views_per_step": 1, "points": s.n_points},
+        "dtype": "f32", "data": "synthetic", "config": cfg,
         "cpu_baseline": {"value": value, "unit": "views/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "views/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -322,6 +355,13 @@ def run_ours(args, rank, world, local_rank):
             dist.barrier()
         torch.cuda.synchronize()
 
+    if args.render_only:
+        info.train = False
+
+        def step_resident():  # noqa: F811 - the render-only step replaces the training step
+            with torch.no_grad():
+                return cache.forward(info, *scene_args())
+
     for _ in range(max(args.warmup, 3)):
         step_resident()
     barrier()
@@ -359,7 +399,37 @@ def run_ours(args, rank, world, local_rank):
 
     # ---- end to end: targets come from pinned host memory, loss goes back to the host, every step ----
     e2e = None
-    if not args.no_e2e:
+    if not args.no_e2e and args.render_only:
+        # the step's inputs are the camera poses of its views (pinned host memory), its result is the image pyramid of
+        # every view, copied back to pinned host memory; the host waits for the images every step
+        poses_host = ns.poses.poses_se3.detach().cpu().pin_memory()
+        host_out = [torch.empty((B, C, h, w)).pin_memory() for (w, h) in sizes]
+        d2h = sum(x.numel() * 4 for x in host_out)
+
+        def step_e2e_render():
+            ns.poses.poses_se3.copy_(poses_host, non_blocking=True)
+            outs = step_resident()
+            for h_, o in zip(host_out, outs):
+                h_.copy_(o, non_blocking=True)
+            torch.cuda.current_stream(dev).synchronize()
+
+        for _ in range(2):
+            step_e2e_render()
+        barrier()
+        t0 = time.perf_counter()
+        e0.record()
+        for _ in range(args.steps):
+            step_e2e_render()
+        e1.record()
+        barrier()
+        wall = (time.perf_counter() - t0) * 1000.0
+        te = torch.tensor([max(e0.elapsed_time(e1), 0.0)], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(te, op=dist.ReduceOp.MAX)
+        ms_e_step = float(te.item()) / args.steps
+        e2e = {"value": world * B / (ms_e_step / 1000.0), "unit": "views/s", "h2d_bytes_per_step": int(poses_host.numel() * 8),
+               "d2h_bytes_per_step": int(d2h), "ms_per_step": ms_e_step, "wall_ms_per_step": wall / args.steps}
+    elif not args.no_e2e:
         rng = np.random.Generator(np.random.Philox(4242 + rank))
         host_t = [torch.from_numpy(rng.random((B, C, h, w), dtype=np.float32)).pin_memory() for (w, h) in sizes]
         dev_t = [[torch.empty_like(x, device=dev) for x in host_t] for _ in range(2)]
@@ -414,6 +484,46 @@ def run_ours(args, rank, world, local_rank):
         e2e = {"value": world * B / (ms_e_step / 1000.0), "unit": "views/s", "h2d_bytes_per_step": int(h2d),
                "d2h_bytes_per_step": 8, "ms_per_step": ms_e_step, "wall_ms_per_step": wall / args.steps}
 
+    # ---- N > 1: the split BASELINE config 3 names (a global batch of 8 views, 8 / N per rank), strong scaling ----
+    strong = None
+    if world > 1 and not args.render_only and not args.no_strong and args.workload == "c3" and 8 % world == 0 and B >= 8 // world:
+        sb = 8 // world
+        info_s = NeuralRenderInfo(scene=ns, images=images_for(s, my_views[:sb]), params=info.params, num_layers=L, train=True, cache=cache)
+        grads_s = [g[:sb].contiguous() for g in grads_in]
+
+        def step_strong():
+            cache.forward(info_s, *scene_args())
+            cache.backward(grads_s, *scene_args(), out=gout)
+            reduce_and_update()
+
+        for _ in range(max(args.warmup, 3)):
+            step_strong()
+        barrier()
+        e0.record()
+        for _ in range(args.steps):
+            step_strong()
+        e1.record()
+        barrier()
+        ts = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+        dist.all_reduce(ts, op=dist.ReduceOp.MAX)
+        ms_s = float(ts.item()) / args.steps
+        strong = {"scaling": "strong", "global_views_per_step": 8, "views_per_gpu": sb, "ms_per_step": ms_s, "value": 8.0 / (ms_s * 1e-3),
+                  "unit": "views/s", "note": "the same 6 M-point scene, 8 views per step split over the ranks, gradient sum + Adam every step"}
+
+    # ---- N > 1: every rank must hold the same parameters after the same number of steps ----
+    replicas_equal = None
+    if world > 1 and not args.render_only:
+        digest = []
+        for p_ in params:
+            v = p_.detach().reshape(-1).view(torch.int32).to(torch.int64)
+            w_ = (torch.arange(v.numel(), device=dev, dtype=torch.int64) % 65521) + 1
+            digest += [v.sum(), (v * w_).sum()]
+        mine = torch.stack(digest)
+        allr = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(allr, mine)
+        replicas_equal = all(bool(torch.equal(allr[0], x)) for x in allr[1:])
+    status_after = cache.last_status()
+
     if rank != 0:
         if world > 1:
             dist.barrier()
@@ -431,7 +541,9 @@ def run_ours(args, rank, world, local_rank):
             # a stage may be timed in several spans per step (the unpack stage: clearing the accumulators before the
             # backward kernel, finishing them after it): the figure is the stage's time per step
             per_stage[name] = {"ms_per_launch": ms / args.steps, "launches": int(launches)}
-    step_stages = ("bin_points", "count", "scan", "collect", "sort_blend", "blend_backward", "adam", "fused_reduce_adam")
+    step_stages = ("bin_points", "count", "scan", "collect", "sort_blend", "blend_backward", "unpack_grads", "adam", "fused_reduce_adam")
+    if args.render_only:
+        step_stages = ("bin_points", "count", "scan", "collect", "sort_blend")
 
     def bytes_of(k):
         if k == "fused_reduce_adam":
@@ -448,8 +560,20 @@ def run_ours(args, rank, world, local_rank):
         v["alg_gb"] = b_ / 1e9
         v["gbs"] = (b_ / (v["ms_per_launch"] * 1e-3) / 1e9) if b_ else None
     total_alg = sum(bytes_of(k) for k in step_stages)
+    V = stats["visible_points"]
+    dom_traffic = stage_traffic(dom, N, B, F, Kf, V)
+    total_traffic = sum(stage_traffic(k, N, B, F, Kf, V) or 0 for k in per_stage if k in step_stages)
+    for k, v in per_stage.items():
+        t_ = stage_traffic(k, N, B, F, Kf, V)
+        v["dram_gb"] = t_ / 1e9 if t_ else None
+        v["traffic_over_alg"] = (t_ / bytes_of(k)) if (t_ and bytes_of(k)) else None
     roofline = {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "peak_kind": peak_kind, "traffic": stage_traffic(dom, N, B, F, Kf),
+                "peak_kind": peak_kind, "traffic": dom_traffic,
+                # the same kernel on measured DRAM bytes: much of its algorithmic traffic (gradient read-modify-writes) stays in L2
+                "frac_dram": (dom_traffic / (per_stage[dom]["ms_per_launch"] * 1e-3) / 1e9 / peak) if dom_traffic else None,
+                # the whole step against the HBM roofline: algorithmic bytes of all stages / step time, and the same on measured DRAM bytes
+                "step_frac": total_alg / (ms_step * 1e-3) / 1e9 / peak,
+                "step_frac_dram": (total_traffic / (ms_step * 1e-3) / 1e9 / peak) if total_traffic else None,
                 "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum per unit of work (profiles/rasterizer_kernels_c3_full_dram_traffic.md) x units of this run",
                 "alg_bytes_per_launch": dom_bytes,
                 "step_alg_bytes": total_alg, "step_gbs": total_alg / (ms_step * 1e-3) / 1e9, "stages": per_stage}
@@ -459,22 +583,28 @@ def run_ours(args, rank, world, local_rank):
         import oracle
         oracle.build()
         oracle.use_all_cores()
-        vps, secs, cfr = cpu_views_per_second(s, [my_views[i % B] for i in range(args.cpu_views)])
+        vps, secs, cfr = cpu_views_per_second(s, [my_views[i % B] for i in range(args.cpu_views)], with_backward=not args.render_only)
+        what = "forward only" if args.render_only else "forward + backward"
         cpu = {"value": vps, "unit": "views/s", "cores": oracle.max_threads(), "kind": "port",
-               "sample": f"{args.cpu_views} view(s) of {s.name}, forward + backward with the OpenMP oracle ({secs:.1f} s)"}
+               "sample": f"{args.cpu_views} view(s) of {s.name}, {what} with the OpenMP oracle ({secs:.1f} s)"}
 
     out = {
         "metric": METRIC, "value": value, "unit": "views/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
         "ms_per_step": ms_step, "ms_per_view": ms_step / B, "step_ms": step_stats, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": {"workload": s.name, "points": N, "views_per_gpu": B, "global_views_per_step": B * world, "width": s.width,
-                   "height": s.height, "layers": L, "k_keep": s.k_keep, "channels": C, "parallelism": f"view-dp{world}", "collective": collective,
+        "config": {**workload_config(s, B, world), "parallelism": f"view-dp{world}", "collective": collective,
+                   "step": "render only (train = 0)" if args.render_only else "forward + backward + gradient sum + Adam",
                    "l2_policy": "inputs (>2 GB touched per step) larger than the 126 MB L2; no explicit flush",
                    "fragments_per_step": int(F), "kept_fragments_per_step": int(Kf), "visible_points_per_step": int(stats["visible_points"]),
                    "max_list_length": int(stats["max_list_length"]), "fragments_per_s": F * world / (ms_step * 1e-3),
                    "backward_atomic_floats_per_s": (C + 5) * Kf / (per_stage["blend_backward"]["ms_per_launch"] * 1e-3) if "blend_backward" in per_stage else None},
         "e2e": e2e, "gpu_launches": int(launches_total), "roofline": roofline, "cpu_baseline": cpu, "clocks": clocks,
+        "device_status_after_run": int(status_after),
     }
+    if strong is not None:
+        out["strong"] = strong
+    if replicas_equal is not None:
+        out["replicas_equal"] = replicas_equal
     emit(out)
     if world > 1:
         dist.barrier()

@@ -23,7 +23,7 @@ pytestmark = pytest.mark.gpu
 
 TOL_PYRAMID = 1e-5
 TOL_GRAD = 1e-4
-STRICT_SHARE_MIN = 0.5
+STRICT_SHARE_MIN = 0.999  # measured: 0.9995 to 0.99999 over all cases and tensors
 
 # name -> (scene factory, views compared)
 CASES = {
@@ -131,9 +131,9 @@ def test_full_size_parity(name, oracle_lib, cuda_lib):
         e = rel_err(a, ref[k])
         grads[k] = dict(rel_err=e, **strict_grad_report(a, ref[k]))
         assert e <= TOL_GRAD, f"grad {k}: rel err {e}"
-        # element-wise: no element is off by more than 1e-5 of the tensor's scale, and most meet a strict 1e-4 (the others
+        # element-wise: no element is off by more than 1e-6 of the tensor's scale, and most meet a strict 1e-4 (the others
         # are sums of terms of both signs that cancel to near zero; fp32 atomics add them in arbitrary order)
-        assert grads[k]["worst_abs_over_max"] <= 1e-5, (k, grads[k])
+        assert grads[k]["worst_abs_over_max"] <= 1e-6, (k, grads[k])  # measured: 1e-7 to 3e-7
         assert grads[k]["share_strict"] >= STRICT_SHARE_MIN, (k, grads[k])
     assert np.all(ns.point_cloud_cuda.t_position.grad[:, 3].cpu().numpy() == 0)
     gpose = ns.poses.tangent_poses.grad.cpu().numpy()

@@ -537,7 +537,8 @@ def test_steady_state_sizing_and_overflow(oracle_lib, cuda_lib):
     from the reported need - is exact again."""
     import torch
     from trips_b200 import _lib
-    s = scenes.tiny(seed=45, n_points=8000, n_views=2, size_range=(5e-3, 0.02))
+    # (enough fragments to exceed the list buffer's initial 16 MB: the buffers are then sized from the counts)
+    s = scenes.tiny(seed=45, n_points=200000, n_views=2, width=160, height=120, size_range=(5e-3, 0.02))
     ns, info, blend = gpu_render(s, train=True)
     with torch.no_grad():
         first = [o.clone() for o in blend(info)]          # sized call (waits for its counts)
@@ -546,6 +547,7 @@ def test_steady_state_sizing_and_overflow(oracle_lib, cuda_lib):
             assert torch.equal(a, b_)
         assert info.cache.last_status() == 0
         f_small = info.cache.stats()["fragments"]
+        assert f_small * 16 > 16 * 1024 * 1024
         # the same points, four pyramid layers larger each: many times the fragments, same shapes
         ns.point_cloud_cuda.t_point_size.data += 3.0
         over = [o.clone() for o in blend(info)]
@@ -559,7 +561,7 @@ def test_steady_state_sizing_and_overflow(oracle_lib, cuda_lib):
             assert bool(empty.any())
         exact = [o.clone() for o in blend(info)]          # buffers grown from the reported need
         assert info.cache.last_status() == 0
-    s2 = scenes.tiny(seed=45, n_points=8000, n_views=2, size_range=(5e-3, 0.02))
+    s2 = scenes.tiny(seed=45, n_points=200000, n_views=2, width=160, height=120, size_range=(5e-3, 0.02))
     s2.point_size[:] = s2.point_size + np.float32(3.0)
     _, _, frames = oracle_frames(s2, train=True)
     for b, f in enumerate(frames):

@@ -139,6 +139,9 @@ __device__ __forceinline__ void fused_element(const TripsAdamSegment& sg, float&
     adam_element(t, w, g, m, v, step, cache);
 }
 
+// W: compile-time bound of the number of ranks (2, 4, 8 or 16), so that the gradient loads of all ranks are issued
+// before the first one is used (one round trip over NVLink per vector instead of `world` in a row).
+template <int W>
 __global__ __launch_bounds__(256) void fused_reduce_adam_kernel(const __grid_constant__ FusedArgs a, float* __restrict__ m_state,
                                                                 float* __restrict__ v_state, int32_t* __restrict__ steps)
 {
@@ -156,12 +159,14 @@ __global__ __launch_bounds__(256) void fused_reduce_adam_kernel(const __grid_con
     for (int64_t q = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; q < n_vec; q += (int64_t)gridDim.x * blockDim.x)
     {
         const int64_t i = lo4 + 4 * q;
-        float4 g = *reinterpret_cast<const float4*>(a.grad[0] + i);
-        for (int r = 1; r < a.world; ++r)
-        {
-            const float4 o = *reinterpret_cast<const float4*>(a.grad[r] + i);
-            g.x += o.x, g.y += o.y, g.z += o.z, g.w += o.w;
-        }
+        float4 part[W];
+#pragma unroll
+        for (int r = 0; r < W; ++r)
+            part[r] = r < a.world ? *reinterpret_cast<const float4*>(a.grad[r] + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        float4 g = part[0];  // summed in rank order on every rank: all replicas see the same bits
+#pragma unroll
+        for (int r = 1; r < W; ++r)
+            if (r < a.world) g.x += part[r].x, g.y += part[r].y, g.z += part[r].z, g.w += part[r].w;
         if (g.x == 0.f && g.y == 0.f && g.z == 0.f && g.w == 0.f) continue;  // unseen on every rank: nothing moves anywhere
         const int64_t j = i - a.lo;  // the optimizer state is stored for the owned slice only
         float4 w = *reinterpret_cast<const float4*>(a.param[a.rank] + i);
@@ -212,7 +217,14 @@ cudaError_t launch_fused_reduce_adam(const float* const* grad_ptrs, float* const
     a.world = world, a.rank = rank, a.n_seg = n_seg, a.lo = lo, a.hi = hi;
     const int64_t n_vec = (hi - lo + 3) / 4;
     const int blocks    = (int)max((int64_t)1, min((int64_t)sm_count * 8, (n_vec + 255) / 256));
-    fused_reduce_adam_kernel<<<blocks, 256, 0, st>>>(a, m_state, v_state, steps);
+    if (world <= 2)
+        fused_reduce_adam_kernel<2><<<blocks, 256, 0, st>>>(a, m_state, v_state, steps);
+    else if (world <= 4)
+        fused_reduce_adam_kernel<4><<<blocks, 256, 0, st>>>(a, m_state, v_state, steps);
+    else if (world <= 8)
+        fused_reduce_adam_kernel<8><<<blocks, 256, 0, st>>>(a, m_state, v_state, steps);
+    else
+        fused_reduce_adam_kernel<16><<<blocks, 256, 0, st>>>(a, m_state, v_state, steps);
     return cudaGetLastError();
 }
 

@@ -115,10 +115,23 @@ __device__ __forceinline__ Projected project_visible(const CamConst& cam, const 
     return r;
 }
 
+#ifndef TRIPS_STORE_256
+#define TRIPS_STORE_256 1
+#endif
+#ifndef TRIPS_SCATTER_MIN_BLOCKS
+#define TRIPS_SCATTER_MIN_BLOCKS 3  // measured on config 3: 1.46 ms unbounded (95 registers), 1.34 ms at 3 blocks (85), 1.36 ms at 4 (64)
+#endif
+#ifndef TRIPS_SCATTER_SWEEP
+#define TRIPS_SCATTER_SWEEP 4
+#endif
+#ifndef TRIPS_BIN_TICKET
+#define TRIPS_BIN_TICKET 1024
+#endif
 constexpr int kBinThreads     = 256;
 constexpr int kBinBlocksPerSM = 8;
 constexpr int kBinChunk       = 8192;  // points per bounding box
-constexpr int kBinTicket      = 1024;  // points per work ticket of the binning kernels; a ticket lies inside one box
+constexpr int kBinTicket      = TRIPS_BIN_TICKET;
+constexpr int kSweep          = TRIPS_SCATTER_SWEEP;  // views whose entry slots a thread requests before it waits for any of them  // points per work ticket of the binning kernels; a ticket lies inside one box
 constexpr int kViewGroup      = 16;    // views whose camera constants are in shared memory at a time (one launch per group)
 static_assert(kBinChunk % kBinTicket == 0, "a ticket must not straddle two bounding boxes");
 
@@ -382,8 +395,22 @@ __global__ void entry_base_kernel(const uint32_t* __restrict__ view_total, int B
     stats->visible = need;
 }
 
+// One 32-byte store (sm_100 has 256-bit global stores) for the two float4 halves of a 32-byte-aligned record: half the
+// store instructions of the entry scatter, each covering a whole sector.
+__device__ __forceinline__ void store_entry_head(float4* dst, const float4& a, const float4& b)
+{
+#if TRIPS_STORE_256
+    asm volatile("st.global.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst), "f"(a.x), "f"(a.y), "f"(a.z), "f"(a.w), "f"(b.x), "f"(b.y),
+                 "f"(b.z), "f"(b.w)
+                 : "memory");
+#else
+    dst[0] = a;
+    dst[1] = b;
+#endif
+}
+
 template <int C, bool ACT>
-__global__ __launch_bounds__(kBinThreads) void bin_scatter_kernel(ScenePtrs sc, const CamConst* __restrict__ cams, const __grid_constant__ Geom g,
+__global__ __launch_bounds__(kBinThreads, TRIPS_SCATTER_MIN_BLOCKS) void bin_scatter_kernel(ScenePtrs sc, const CamConst* __restrict__ cams, const __grid_constant__ Geom g,
                                                                   TripsRenderParams pr, FwdBuffers fb, int v0, int nv, unsigned* ticket)
 {
     constexpr int TS = tail_stride(C);
@@ -415,12 +442,27 @@ __global__ __launch_bounds__(kBinThreads) void bin_scatter_kernel(ScenePtrs sc, 
             uint32_t rk  = 0u;
             float row_t[C4];
             const bool tex_ok = (unsigned)tex < (unsigned)sc.n_tex;
-            for (int v = 0; v < nv; ++v)
+            // Views are handled kSweep at a time in two sweeps: the first projects and takes the entry slots (up to kSweep
+            // returning atomics in flight per thread instead of one), the second projects again (the same arithmetic,
+            // hence the same bits) and writes the entries.  Waiting for each slot before the next projection made the
+            // kernel latency-bound.
+            for (int vb = 0; vb < nv; vb += kSweep)
             {
-                if ((skip >> v) & 1u) continue;  // uniform
-                if (use_dropout && __ldg(sc.dropout + (size_t)(v0 + v) * sc.N + i) == 1.f) continue;
-                const Projected r = project_visible(s_cam[v], g, pr, p, raw, sp);
-                if (!r.ok) continue;
+                uint32_t slot[kSweep];
+                unsigned vis = 0;
+#pragma unroll
+                for (int j = 0; j < kSweep; ++j)
+                {
+                    const int v = vb + j;
+                    slot[j]     = 0;
+                    if (v >= nv || ((skip >> v) & 1u)) continue;  // uniform
+                    if (use_dropout && __ldg(sc.dropout + (size_t)(v0 + v) * sc.N + i) == 1.f) continue;
+                    const Projected r = project_visible(s_cam[v], g, pr, p, raw, sp);
+                    if (!r.ok) continue;
+                    vis |= 1u << j;
+                    slot[j] = atomicAdd(fb.bin_base + ((size_t)(v0 + v) * g.n_bins << kSubShift) + bin_key(g, r.u, r.v), 1u);
+                }
+                if (!vis) continue;
                 if (!fetched)
                 {
                     fetched = true;
@@ -440,25 +482,37 @@ __global__ __launch_bounds__(kBinThreads) void bin_scatter_kernel(ScenePtrs sc, 
                     }
                     rk = fb.point_rank ? __ldg(fb.point_rank + i) : 0u;
                 }
-                const uint32_t slot = atomicAdd(fb.bin_base + ((size_t)(v0 + v) * g.n_bins << kSubShift) + bin_key(g, r.u, r.v), 1u);
-                // layers 0..hi, stopping where the 2x2 footprint leaves the layer (RenderForward.cu:342-363)
-                int hi = 0;
-                if (r.ps > 1.f) hi = min(tm_ceil_log2(r.ps), g.L - 1);
-                int layer = 0;
-                float x = r.u, y = r.v, rad = r.rad;
-                for (; layer < hi + 1; ++layer, x *= 0.5f, y *= 0.5f, rad *= 0.5f)
-                {
-                    const int px = __float2int_rd(x), py = __float2int_rd(y);
-                    if (px < 0 || px >= g.W[layer] - 1 || py < 0 || py >= g.H[layer] - 1) break;
-                    if (pr.drop_out_points_by_radius && (float)(int)rad < pr.drop_out_radius_threshold) break;
-                }
-                float4* head = fb.ent_head + (s_ebase[v] + slot) * 2;
-                head[0]      = make_float4(r.u, r.v, r.ps, conf);
-                head[1]      = make_float4(__int_as_float(i), r.z, raw, __uint_as_float((uint32_t)layer | (rk << kRankShift)));
-                float4* e    = reinterpret_cast<float4*>(fb.ent_tail + (s_ebase[v] + slot) * TS);
-                e[0]         = make_float4(p.x, p.y, p.z, __int_as_float(tex_ok ? tex : -1));
 #pragma unroll
-                for (int c = 0; c < C4; c += 4) e[1 + c / 4] = make_float4(row_t[c], row_t[c + 1], row_t[c + 2], row_t[c + 3]);
+                for (int j = 0; j < kSweep; ++j)
+                {
+                    if (!((vis >> j) & 1u)) continue;
+                    const int v       = vb + j;
+                    const Projected r = project_visible(s_cam[v], g, pr, p, raw, sp);
+                    // layers 0..hi, stopping where the 2x2 footprint leaves the layer (RenderForward.cu:342-363)
+                    int hi = 0;
+                    if (r.ps > 1.f) hi = min(tm_ceil_log2(r.ps), g.L - 1);
+                    int layer = 0;
+                    float x = r.u, y = r.v, rad = r.rad;
+                    for (; layer < hi + 1; ++layer, x *= 0.5f, y *= 0.5f, rad *= 0.5f)
+                    {
+                        const int px = __float2int_rd(x), py = __float2int_rd(y);
+                        if (px < 0 || px >= g.W[layer] - 1 || py < 0 || py >= g.H[layer] - 1) break;
+                        if (pr.drop_out_points_by_radius && (float)(int)rad < pr.drop_out_radius_threshold) break;
+                    }
+                    const unsigned long long at = s_ebase[v] + slot[j];
+                    store_entry_head(fb.ent_head + at * 2, make_float4(r.u, r.v, r.ps, conf),
+                                     make_float4(__int_as_float(i), r.z, raw, __uint_as_float((uint32_t)layer | (rk << kRankShift))));
+                    float4* e = reinterpret_cast<float4*>(fb.ent_tail + at * TS);
+                    if constexpr (C4 == 4)
+                        store_entry_head(e, make_float4(p.x, p.y, p.z, __int_as_float(tex_ok ? tex : -1)),
+                                         make_float4(row_t[0], row_t[1], row_t[2], row_t[3]));
+                    else
+                    {
+                        e[0] = make_float4(p.x, p.y, p.z, __int_as_float(tex_ok ? tex : -1));
+#pragma unroll
+                        for (int c = 0; c < C4; c += 4) e[1 + c / 4] = make_float4(row_t[c], row_t[c + 1], row_t[c + 2], row_t[c + 3]);
+                    }
+                }
             }
         }
     }
