@@ -116,7 +116,7 @@ struct TripsContext
     int sm_count = 148;
     std::string error;
     // forward scratch
-    DevBuf views, cams, bin_count, bin_base, view_total, bin_cursor, entry_base, entries, counts, offsets, partial, view_base, frags, rec_n, records, stats, ticket, rank, rank_scratch, rank_temp, resize_scratch, block_box, block_skip;
+    DevBuf heavy, views, cams, bin_count, bin_base, view_total, bin_cursor, entry_base, entries, counts, offsets, partial, view_base, frags, rec_n, records, stats, ticket, rank, rank_scratch, rank_temp, resize_scratch, block_box, block_skip;
     // backward scratch
     DevBuf egrad, g_point, g_conf_pt, g_small;
     // adam
@@ -130,6 +130,7 @@ struct TripsContext
     bool have_sizes                 = false;
     unsigned long long need_entries = 0, need_frags = 0;
     int entry_C                     = 0;  // channel count the entry arrays are laid out for
+    bool crowded                    = false;  // the point cloud crowds into few screen tiles: use the aggregating binning kernels
     // state of the last forward call
     bool have_forward = false;
     Geom geom{};
@@ -218,6 +219,7 @@ static FwdBuffers fwd_buffers(TripsContext* c)
     fb.point_rank = c->rank_points >= 0 ? (const uint32_t*)c->rank.p : nullptr;
     fb.block_box  = (const float*)c->block_box.p;
     fb.block_skip = (const uint8_t*)c->block_skip.p;
+    fb.heavy      = (uint2*)c->heavy.p;
     return fb;
 }
 
@@ -281,7 +283,7 @@ int trips_context_create(TripsContext** out, int device)
 void trips_context_destroy(TripsContext* c)
 {
     if (!c) return;
-    DevBuf* all[] = {&c->views, &c->cams, &c->bin_count, &c->bin_base, &c->view_total, &c->bin_cursor, &c->entry_base, &c->entries, &c->counts, &c->offsets,
+    DevBuf* all[] = {&c->heavy, &c->views, &c->cams, &c->bin_count, &c->bin_base, &c->view_total, &c->bin_cursor, &c->entry_base, &c->entries, &c->counts, &c->offsets,
                      &c->partial, &c->view_base, &c->frags, &c->rec_n, &c->records, &c->stats, &c->ticket, &c->egrad, &c->g_point,
                      &c->g_conf_pt, &c->g_small, &c->adam_tab, &c->rank, &c->rank_scratch, &c->rank_temp, &c->resize_scratch, &c->block_box, &c->block_skip};
     for (DevBuf* b : all) free_buf(*b);
@@ -361,6 +363,7 @@ static int resolve_pending(TripsContext* ctx)
     const DevStats* hs = (const DevStats*)ctx->h_pinned;
     ctx->need_entries  = hs->visible;
     ctx->need_frags    = hs->frag_need;
+    ctx->crowded       = hs->max_key >= kHotKey;
     ctx->host_stats.visible_points      = (int64_t)hs->visible;
     ctx->host_stats.fragments           = (int64_t)hs->frag_need;
     ctx->host_stats.kept_fragments      = (int64_t)hs->kept;
@@ -400,6 +403,7 @@ static int forward_views(TripsContext* ctx, const TripsScene* scene, const Trips
     CU_CHECK(ctx, ensure(ctx->entry_base, sizeof(unsigned long long) * (B + 1)));
     CU_CHECK(ctx, ensure(ctx->block_box, sizeof(float) * 6 * n_box));
     CU_CHECK(ctx, ensure(ctx->block_skip, (size_t)B * n_box));
+    CU_CHECK(ctx, ensure(ctx->heavy, sizeof(uint2) * (size_t)kHeavyCap));
     CU_CHECK(ctx, ensure(ctx->counts, sizeof(uint32_t) * P * B));
     CU_CHECK(ctx, ensure(ctx->offsets, sizeof(uint32_t) * P * B));
     CU_CHECK(ctx, ensure(ctx->partial, sizeof(uint32_t) * (size_t)nchunks * B));
@@ -453,16 +457,18 @@ static int forward_views(TripsContext* ctx, const TripsScene* scene, const Trips
           launch_setup_cams((const TripsView*)ctx->views.p, B, scene->poses, scene->n_images, scene->intrinsics,
                             scene->n_cameras, (CamConst*)ctx->cams.p, fb.stats, st));
     const CamConst* cams = (const CamConst*)ctx->cams.p;
+    // crowded: the last call that reported back saw more than kHotKey visible points in one (view, bin, tile) group
     STAGE(ctx, TRIPS_STAGE_BIN_POINTS, bin_count_launches((int)N, B), st,
-          launch_bin_count(sp, cams, g, *params, B, fb, wait_for_sizes ? ~0ull : (unsigned long long)ctx->entry_cap, ctx->sm_count, st));
+          launch_bin_count(sp, cams, g, *params, B, fb, wait_for_sizes ? ~0ull : (unsigned long long)ctx->entry_cap, ctx->crowded, ctx->sm_count, st));
     if (wait_for_sizes)
     {
         CU_CHECK(ctx, cudaMemcpyAsync(h_stats, ctx->stats.p, sizeof(DevStats), cudaMemcpyDeviceToHost, st));
         CU_CHECK(ctx, cudaStreamSynchronize(st));
         CU_CHECK(ctx, ensure_entries(ctx, (size_t)h_stats->visible, C, kGrowth));
-        fb = fwd_buffers(ctx);
+        ctx->crowded = h_stats->max_key >= kHotKey;  // this call's own count pass already knows
+        fb           = fwd_buffers(ctx);
     }
-    STAGE(ctx, TRIPS_STAGE_BIN_POINTS, bin_scatter_launches((int)N, B), st, launch_bin_scatter(sp, cams, g, *params, B, fb, ctx->sm_count, st));
+    STAGE(ctx, TRIPS_STAGE_BIN_POINTS, bin_scatter_launches((int)N, B), st, launch_bin_scatter(sp, cams, g, *params, B, fb, ctx->crowded, ctx->sm_count, st));
     if (N > 0) STAGE(ctx, TRIPS_STAGE_COUNT, 1, st, launch_count(sp, g, B, fb, ctx->sm_count, st));
     {
         FwdBuffers fscan = fb;
@@ -494,7 +500,10 @@ static int forward_views(TripsContext* ctx, const TripsScene* scene, const Trips
     if (N > 0) STAGE(ctx, TRIPS_STAGE_COLLECT, 1, st, launch_collect(sp, g, B, fb, ctx->sm_count, st));
     LayerPtrs out{};
     for (int l = 0; l < g.L; ++l) out.p[l] = out_layers[l] + out_view_offset * (size_t)C * g.W[l] * g.H[l];
-    STAGE(ctx, TRIPS_STAGE_SORT_BLEND, 1, st, launch_sort_blend(sp, g, *params, B, fb, out, ctx->sm_count, st));
+    STAGE(ctx, TRIPS_STAGE_SORT_BLEND, 2, st, [&]() -> cudaError_t {
+        cudaError_t e = launch_heavy_topk(g, B, fb, ctx->sm_count, st);
+        return e != cudaSuccess ? e : launch_sort_blend(sp, g, *params, B, fb, out, ctx->sm_count, st);
+    }());
     ctx->B       = B;
     ctx->nchunks = nchunks;
     return TRIPS_OK;

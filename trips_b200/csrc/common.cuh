@@ -15,6 +15,8 @@ constexpr int kTileW      = 8;   // one warp renders / differentiates an 8x4 pix
 constexpr int kTileH      = 4;
 constexpr int kRankShift  = 4;   // entry head: number of layers in the low 4 bits, spatial rank above
 constexpr int kMaxRankedPoints = 1 << 28;
+constexpr int kHeavyList  = 512;      // lists longer than this get their 16 nearest fragments moved to the front by a block of their own
+constexpr int kHeavyCap   = 1 << 16;  // such lists per call the pre-selection handles; beyond that the blend walks them itself
 
 // Pyramid geometry shared by all views of a call.
 struct Geom
@@ -65,9 +67,11 @@ struct DevStats
     unsigned long long kept;
     unsigned long long frag_need;  // fragments over all views (needed list slots, whether or not they fitted)
     unsigned int max_len;
+    unsigned int n_heavy;          // pixels whose list is longer than kHeavyList (they are pre-selected before the blend)
+    unsigned int max_key;          // largest number of visible points in one (view, screen bin, tile) group
+    unsigned int pad0;
     unsigned int status;
     unsigned int culled_blocks;  // (view, block of consecutive points) pairs skipped by the bounding-box test, counted once per pass
-    unsigned int pad;
 };
 
 // A visible point of one view ("entry"): everything the later stages need, gathered once and stored in screen-bin
@@ -106,6 +110,7 @@ struct FwdBuffers
     const uint32_t* point_rank;       // [N] spatial rank of every point, or nullptr: gradient rows are keyed by point id
     const float* block_box;           // [ceil(N / 8192), 6] bounding boxes (min xyz, max xyz) of blocks of consecutive points
     const uint8_t* block_skip;        // [B, ceil(N / 8192)] 1 = the block cannot hold a point visible in that view
+    uint2* heavy;                     // [kHeavyCap] (view, pixel) of the lists longer than kHeavyList
 };
 
 struct ScenePtrs
@@ -248,9 +253,10 @@ __device__ __forceinline__ void tile_pixel(const Geom& g, int tile, int lane, in
 cudaError_t launch_setup_cams(const TripsView* d_views, int B, const double* poses, int n_images, const float* intrinsics,
                               int n_cameras, CamConst* cams, DevStats* stats, cudaStream_t st);
 cudaError_t launch_bin_count(const ScenePtrs& sc, const CamConst* cams, const Geom& g, const TripsRenderParams& pr, int B,
-                             const FwdBuffers& fb, unsigned long long entry_cap, int sm_count, cudaStream_t st);
+                             const FwdBuffers& fb, unsigned long long entry_cap, bool hot, int sm_count, cudaStream_t st);
 cudaError_t launch_bin_scatter(const ScenePtrs& sc, const CamConst* cams, const Geom& g, const TripsRenderParams& pr, int B,
-                               const FwdBuffers& fb, int sm_count, cudaStream_t st);
+                               const FwdBuffers& fb, bool hot, int sm_count, cudaStream_t st);
+constexpr unsigned kHotKey = 4096;  // visible points in one (view, bin, tile) group beyond which the binning passes aggregate in shared memory
 int bin_count_launches(int N, int B);
 int bin_scatter_launches(int N, int B);
 size_t resize_scratch_bytes(int64_t n_points);
@@ -262,6 +268,7 @@ cudaError_t launch_point_rank(const float4* position, int N, unsigned* scratch, 
 cudaError_t launch_scan(const Geom& g, int B, int k_keep, const FwdBuffers& fb, int nchunks, cudaStream_t st);
 cudaError_t launch_count(const ScenePtrs& sc, const Geom& g, int B, const FwdBuffers& fb, int sm_count, cudaStream_t st);
 cudaError_t launch_collect(const ScenePtrs& sc, const Geom& g, int B, const FwdBuffers& fb, int sm_count, cudaStream_t st);
+cudaError_t launch_heavy_topk(const Geom& g, int B, const FwdBuffers& fb, int sm_count, cudaStream_t st);
 cudaError_t launch_sort_blend(const ScenePtrs& sc, const Geom& g, const TripsRenderParams& pr, int B, const FwdBuffers& fb,
                               const LayerPtrs& out, int sm_count, cudaStream_t st);
 cudaError_t launch_zero_entry_rows(int C, int B, const FwdBuffers& fb, const BwdBuffers& bb, int sm_count, cudaStream_t st);

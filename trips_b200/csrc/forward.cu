@@ -320,7 +320,7 @@ __global__ __launch_bounds__(kBinThreads) void bin_count_kernel(ScenePtrs sc, co
 // (block, bin) pair, ordered by bin first and block second; view_total[b] = visible points of the view
 __global__ __launch_bounds__(1024) void bin_scan_kernel(const uint32_t* __restrict__ rows_in, uint32_t* __restrict__ rows_out,
                                                         uint32_t* __restrict__ bin_first, int n_bins, int n_blocks,
-                                                        uint32_t* __restrict__ view_total, int first_shift)
+                                                        uint32_t* __restrict__ view_total, int first_shift, DevStats* stats)
 {
     __shared__ uint32_t sm[32];
     __shared__ uint32_t carry_s;
@@ -337,6 +337,7 @@ __global__ __launch_bounds__(1024) void bin_scan_kernel(const uint32_t* __restri
         uint32_t v  = 0;  // visible points of bin i (sum over blocks)
         if (i < n_bins)
             for (int k = 0; k < n_blocks; ++k) v += r[(size_t)k * n_bins + i];
+        if (v >= kHotKey) atomicMax(&stats->max_key, v);  // crowded group: the next call uses the aggregating binning kernels
         uint32_t inc = v;
 #pragma unroll
         for (int k = 1; k < 32; k <<= 1)
@@ -409,12 +410,75 @@ __device__ __forceinline__ void store_entry_head(float4* dst, const float4& a, c
 #endif
 }
 
+// What an entry carries of its point besides the projection: fetched once per point, when it turns out visible in a view.
+template <int C>
+struct PointRow
+{
+    static constexpr int C4 = (C + 3) & ~3;
+    bool fetched = false, tex_ok = false;
+    int tex      = 0;
+    float conf   = 0.f;
+    uint32_t rk  = 0u;
+    float row[C4];
+};
+
+template <int C, bool ACT>
+__device__ __forceinline__ void fetch_point_row(const ScenePtrs& sc, const TripsRenderParams& pr, const FwdBuffers& fb, int i, PointRow<C>& d)
+{
+    if (d.fetched) return;
+    d.fetched = true;
+    if (d.tex_ok)
+    {
+        d.conf = __ldg(sc.confidence + d.tex);
+        if (ACT && pr.confidence_is_raw) d.conf = tm_sigmoid(pr.confidence_scale * d.conf);  // PrepareConfidence, NeuralTexture.h:40-43
+    }
+    else
+        atomicOr(&fb.stats->status, TRIPS_DEV_BAD_TEXTURE_INDEX);  // the point is drawn with alpha 0
+#pragma unroll
+    for (int c = 0; c < PointRow<C>::C4; ++c) d.row[c] = (c < C && d.tex_ok) ? __ldg(sc.texture + (size_t)c * sc.n_tex + d.tex) : 0.f;
+    if (ACT && pr.texture_abs)  // PrepareTexture, NeuralTexture.h:45-57
+    {
+#pragma unroll
+        for (int c = 0; c < PointRow<C>::C4; ++c) d.row[c] = fabsf(d.row[c]);
+    }
+    d.rk = fb.point_rank ? __ldg(fb.point_rank + i) : 0u;
+}
+
+// Writes entry `at` (index into the entry arrays) of point i as projected by `r`.
+template <int C>
+__device__ __forceinline__ void write_entry(const FwdBuffers& fb, const Geom& g, const TripsRenderParams& pr, unsigned long long at, int i,
+                                            const float4& p, float raw, const Projected& r, const PointRow<C>& d)
+{
+    constexpr int TS = tail_stride(C);
+    constexpr int C4 = PointRow<C>::C4;
+    // layers 0..hi, stopping where the 2x2 footprint leaves the layer (RenderForward.cu:342-363)
+    int hi = 0;
+    if (r.ps > 1.f) hi = min(tm_ceil_log2(r.ps), g.L - 1);
+    int layer = 0;
+    float x = r.u, y = r.v, rad = r.rad;
+    for (; layer < hi + 1; ++layer, x *= 0.5f, y *= 0.5f, rad *= 0.5f)
+    {
+        const int px = __float2int_rd(x), py = __float2int_rd(y);
+        if (px < 0 || px >= g.W[layer] - 1 || py < 0 || py >= g.H[layer] - 1) break;
+        if (pr.drop_out_points_by_radius && (float)(int)rad < pr.drop_out_radius_threshold) break;
+    }
+    store_entry_head(fb.ent_head + at * 2, make_float4(r.u, r.v, r.ps, d.conf),
+                     make_float4(__int_as_float(i), r.z, raw, __uint_as_float((uint32_t)layer | (d.rk << kRankShift))));
+    float4* e = reinterpret_cast<float4*>(fb.ent_tail + at * TS);
+    if constexpr (C4 == 4)
+        store_entry_head(e, make_float4(p.x, p.y, p.z, __int_as_float(d.tex_ok ? d.tex : -1)), make_float4(d.row[0], d.row[1], d.row[2], d.row[3]));
+    else
+    {
+        e[0] = make_float4(p.x, p.y, p.z, __int_as_float(d.tex_ok ? d.tex : -1));
+#pragma unroll
+        for (int c = 0; c < C4; c += 4) e[1 + c / 4] = make_float4(d.row[c], d.row[c + 1], d.row[c + 2], d.row[c + 3]);
+    }
+}
+
 template <int C, bool ACT>
 __global__ __launch_bounds__(kBinThreads, TRIPS_SCATTER_MIN_BLOCKS) void bin_scatter_kernel(ScenePtrs sc, const CamConst* __restrict__ cams, const __grid_constant__ Geom g,
                                                                   TripsRenderParams pr, FwdBuffers fb, int v0, int nv, unsigned* ticket)
 {
-    constexpr int TS = tail_stride(C);
-    constexpr int C4 = (C + 3) & ~3;
     __shared__ CamConst s_cam[kViewGroup];
     __shared__ unsigned long long s_ebase[kViewGroup + 1];
     __shared__ unsigned s_ticket;
@@ -431,17 +495,13 @@ __global__ __launch_bounds__(kBinThreads, TRIPS_SCATTER_MIN_BLOCKS) void bin_sca
         skip |= no_room;
         for (int i = first + threadIdx.x; i < last; i += kBinThreads)
         {
-            const int tex = sc.index ? __ldg(sc.index + i) : i;
-            if (discarded_for_confidence<ACT>(sc, pr, tex)) continue;
+            PointRow<C> d;
+            d.tex    = sc.index ? __ldg(sc.index + i) : i;
+            d.tex_ok = (unsigned)d.tex < (unsigned)sc.n_tex;
+            if (discarded_for_confidence<ACT>(sc, pr, d.tex)) continue;
             const float4 p  = __ldg(sc.position + i);
             const float raw = __ldg(sc.point_size + i);
             float sp        = -1.f;
-            // per-point data of the entry: fetched when the point turns out visible in a first view
-            bool fetched = false;
-            float conf   = 0.f;
-            uint32_t rk  = 0u;
-            float row_t[C4];
-            const bool tex_ok = (unsigned)tex < (unsigned)sc.n_tex;
             // Views are handled kSweep at a time in two sweeps: the first projects and takes the entry slots (up to kSweep
             // returning atomics in flight per thread instead of one), the second projects again (the same arithmetic,
             // hence the same bits) and writes the entries.  Waiting for each slot before the next projection made the
@@ -463,56 +523,187 @@ __global__ __launch_bounds__(kBinThreads, TRIPS_SCATTER_MIN_BLOCKS) void bin_sca
                     slot[j] = atomicAdd(fb.bin_base + ((size_t)(v0 + v) * g.n_bins << kSubShift) + bin_key(g, r.u, r.v), 1u);
                 }
                 if (!vis) continue;
-                if (!fetched)
-                {
-                    fetched = true;
-                    if (tex_ok)
-                    {
-                        conf = __ldg(sc.confidence + tex);
-                        if (ACT && pr.confidence_is_raw) conf = tm_sigmoid(pr.confidence_scale * conf);  // PrepareConfidence, NeuralTexture.h:40-43
-                    }
-                    else
-                        atomicOr(&fb.stats->status, TRIPS_DEV_BAD_TEXTURE_INDEX);  // the point is drawn with alpha 0
-#pragma unroll
-                    for (int c = 0; c < C4; ++c) row_t[c] = (c < C && tex_ok) ? __ldg(sc.texture + (size_t)c * sc.n_tex + tex) : 0.f;
-                    if (ACT && pr.texture_abs)  // PrepareTexture, NeuralTexture.h:45-57
-                    {
-#pragma unroll
-                        for (int c = 0; c < C4; ++c) row_t[c] = fabsf(row_t[c]);
-                    }
-                    rk = fb.point_rank ? __ldg(fb.point_rank + i) : 0u;
-                }
+                fetch_point_row<C, ACT>(sc, pr, fb, i, d);
 #pragma unroll
                 for (int j = 0; j < kSweep; ++j)
                 {
                     if (!((vis >> j) & 1u)) continue;
                     const int v       = vb + j;
                     const Projected r = project_visible(s_cam[v], g, pr, p, raw, sp);
-                    // layers 0..hi, stopping where the 2x2 footprint leaves the layer (RenderForward.cu:342-363)
-                    int hi = 0;
-                    if (r.ps > 1.f) hi = min(tm_ceil_log2(r.ps), g.L - 1);
-                    int layer = 0;
-                    float x = r.u, y = r.v, rad = r.rad;
-                    for (; layer < hi + 1; ++layer, x *= 0.5f, y *= 0.5f, rad *= 0.5f)
-                    {
-                        const int px = __float2int_rd(x), py = __float2int_rd(y);
-                        if (px < 0 || px >= g.W[layer] - 1 || py < 0 || py >= g.H[layer] - 1) break;
-                        if (pr.drop_out_points_by_radius && (float)(int)rad < pr.drop_out_radius_threshold) break;
-                    }
-                    const unsigned long long at = s_ebase[v] + slot[j];
-                    store_entry_head(fb.ent_head + at * 2, make_float4(r.u, r.v, r.ps, conf),
-                                     make_float4(__int_as_float(i), r.z, raw, __uint_as_float((uint32_t)layer | (rk << kRankShift))));
-                    float4* e = reinterpret_cast<float4*>(fb.ent_tail + at * TS);
-                    if constexpr (C4 == 4)
-                        store_entry_head(e, make_float4(p.x, p.y, p.z, __int_as_float(tex_ok ? tex : -1)),
-                                         make_float4(row_t[0], row_t[1], row_t[2], row_t[3]));
-                    else
-                    {
-                        e[0] = make_float4(p.x, p.y, p.z, __int_as_float(tex_ok ? tex : -1));
-#pragma unroll
-                        for (int c = 0; c < C4; c += 4) e[1 + c / 4] = make_float4(row_t[c], row_t[c + 1], row_t[c + 2], row_t[c + 3]);
-                    }
+                    write_entry<C>(fb, g, pr, s_ebase[v] + slot[j], i, p, raw, r, d);
                 }
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------------------
+// The same two passes for point clouds that crowd into a few screen tiles (a distant or tiny object: millions of points
+// in a 64x64-pixel window).  There the per-(bin, tile) counters above become a handful of addresses that every thread
+// of the machine updates, and same-address atomics are served one after the other.  These variants aggregate in shared
+// memory first: a block takes a ticket of kHotTicket points, counts its visible point-views per key in a small hash
+// table (linear probing, at most four probes; a key that finds no slot simply uses the global counter directly), and
+// touches the global counter of every key it met once per ticket.  In the scatter pass that one returning atomic
+// reserves a range of the key's entries for the whole ticket, and the slots inside the range come from the table.
+// The host selects these variants when the previous call (or, in a sized call, this call's own count pass) saw more
+// than kHotKey visible points in one (view, bin, tile) group; ordinary scenes never do and run the kernels above.
+// ------------------------------------------------------------------------------------------------------------
+constexpr int kHotTicket        = 2048;
+constexpr int kHotSlots         = 2048;
+constexpr uint32_t kHotEmpty    = 0xffffffffu;
+
+__device__ __forceinline__ uint32_t hot_hash(uint32_t key) { return (key * 2654435761u) >> 21; }  // 11 bits
+
+__device__ __forceinline__ int hot_find_or_insert(uint32_t* tag, uint32_t key)
+{
+    const uint32_t h = hot_hash(key);
+#pragma unroll
+    for (int probe = 0; probe < 4; ++probe)
+    {
+        const uint32_t s   = (h + probe) & (kHotSlots - 1);
+        const uint32_t old = atomicCAS(tag + s, kHotEmpty, key);
+        if (old == kHotEmpty || old == key) return (int)s;
+    }
+    return -1;
+}
+
+__device__ __forceinline__ int hot_find(const uint32_t* tag, uint32_t key)
+{
+    const uint32_t h = hot_hash(key);
+#pragma unroll
+    for (int probe = 0; probe < 4; ++probe)
+    {
+        const uint32_t s = (h + probe) & (kHotSlots - 1);
+        const uint32_t t = tag[s];
+        if (t == key) return (int)s;
+        if (t == kHotEmpty) return -1;
+    }
+    return -1;
+}
+
+__device__ __forceinline__ bool next_hot_ticket(unsigned* ticket, int N, unsigned* s_ticket, int& first, int& last)
+{
+    __syncthreads();
+    if (threadIdx.x == 0) *s_ticket = atomicAdd(ticket, 1u);
+    __syncthreads();
+    const unsigned t = *s_ticket;
+    if (t >= ((unsigned)N + kHotTicket - 1) / kHotTicket) return false;
+    first = (int)(t * kHotTicket);
+    last  = min(N, first + kHotTicket);
+    return true;
+}
+
+template <bool ACT>
+__global__ __launch_bounds__(kBinThreads) void bin_count_hot_kernel(ScenePtrs sc, const CamConst* __restrict__ cams, const __grid_constant__ Geom g,
+                                                                    TripsRenderParams pr, FwdBuffers fb, int v0, int nv, unsigned* ticket)
+{
+    __shared__ CamConst s_cam[kViewGroup];
+    __shared__ uint32_t s_tag[kHotSlots], s_cnt[kHotSlots];
+    __shared__ unsigned s_ticket;
+    for (int k = threadIdx.x; k < nv * (int)(sizeof(CamConst) / 4); k += kBinThreads) ((int*)s_cam)[k] = ((const int*)(cams + v0))[k];
+    const bool use_dropout = pr.train && sc.dropout;
+    const uint32_t n_keys  = (uint32_t)g.n_bins << kSubShift;
+    uint32_t* counters     = fb.bin_count + (size_t)v0 * n_keys;  // counter of (view v0 + v, key) at [v * n_keys + key]
+    int first, last;
+    while (next_hot_ticket(ticket, sc.N, &s_ticket, first, last))
+    {
+        for (int k = threadIdx.x; k < kHotSlots; k += kBinThreads) s_tag[k] = kHotEmpty, s_cnt[k] = 0u;
+        __syncthreads();
+        for (int i = first + threadIdx.x; i < last; i += kBinThreads)
+        {
+            const int tex = sc.index ? __ldg(sc.index + i) : i;
+            if (discarded_for_confidence<ACT>(sc, pr, tex)) continue;
+            const float4 p  = __ldg(sc.position + i);
+            const float raw = __ldg(sc.point_size + i);
+            float sp        = -1.f;
+            for (int v = 0; v < nv; ++v)
+            {
+                if (use_dropout && __ldg(sc.dropout + (size_t)(v0 + v) * sc.N + i) == 1.f) continue;
+                const Projected r = project_visible(s_cam[v], g, pr, p, raw, sp);
+                if (!r.ok) continue;
+                const uint32_t key = (uint32_t)v * n_keys + (uint32_t)bin_key(g, r.u, r.v);
+                const int s        = hot_find_or_insert(s_tag, key);
+                if (s >= 0)
+                    atomicAdd(s_cnt + s, 1u);
+                else
+                    atomicAdd(counters + key, 1u);
+            }
+        }
+        __syncthreads();
+        for (int k = threadIdx.x; k < kHotSlots; k += kBinThreads)
+            if (s_tag[k] != kHotEmpty) atomicAdd(counters + s_tag[k], s_cnt[k]);
+    }
+}
+
+template <int C, bool ACT>
+__global__ __launch_bounds__(kBinThreads) void bin_scatter_hot_kernel(ScenePtrs sc, const CamConst* __restrict__ cams, const __grid_constant__ Geom g,
+                                                                      TripsRenderParams pr, FwdBuffers fb, int v0, int nv, unsigned* ticket)
+{
+    __shared__ CamConst s_cam[kViewGroup];
+    __shared__ unsigned long long s_ebase[kViewGroup + 1];
+    __shared__ uint32_t s_tag[kHotSlots], s_cnt[kHotSlots], s_base[kHotSlots];
+    __shared__ unsigned s_ticket;
+    for (int k = threadIdx.x; k < nv * (int)(sizeof(CamConst) / 4); k += kBinThreads) ((int*)s_cam)[k] = ((const int*)(cams + v0))[k];
+    if (threadIdx.x <= nv) s_ebase[threadIdx.x] = fb.entry_base[v0 + threadIdx.x];
+    __syncthreads();
+    unsigned no_room = 0;  // views without entries: nothing visible, or the view did not fit the entry arrays
+    for (int v = 0; v < nv; ++v) no_room |= (s_ebase[v + 1] == s_ebase[v] ? 1u : 0u) << v;
+    const bool use_dropout = pr.train && sc.dropout;
+    const uint32_t n_keys  = (uint32_t)g.n_bins << kSubShift;
+    uint32_t* cursors      = fb.bin_base + (size_t)v0 * n_keys;
+    int first, last;
+    while (next_hot_ticket(ticket, sc.N, &s_ticket, first, last))
+    {
+        for (int k = threadIdx.x; k < kHotSlots; k += kBinThreads) s_tag[k] = kHotEmpty, s_cnt[k] = 0u;
+        __syncthreads();
+        // ---- the ticket's visible point-views per key ----
+        for (int i = first + threadIdx.x; i < last; i += kBinThreads)
+        {
+            const int tex = sc.index ? __ldg(sc.index + i) : i;
+            if (discarded_for_confidence<ACT>(sc, pr, tex)) continue;
+            const float4 p  = __ldg(sc.position + i);
+            const float raw = __ldg(sc.point_size + i);
+            float sp        = -1.f;
+            for (int v = 0; v < nv; ++v)
+            {
+                if ((no_room >> v) & 1u) continue;  // uniform
+                if (use_dropout && __ldg(sc.dropout + (size_t)(v0 + v) * sc.N + i) == 1.f) continue;
+                const Projected r = project_visible(s_cam[v], g, pr, p, raw, sp);
+                if (!r.ok) continue;
+                const int s = hot_find_or_insert(s_tag, (uint32_t)v * n_keys + (uint32_t)bin_key(g, r.u, r.v));
+                if (s >= 0) atomicAdd(s_cnt + s, 1u);
+            }
+        }
+        __syncthreads();
+        // ---- one returning atomic per key reserves the ticket's range of that key's entries ----
+        for (int k = threadIdx.x; k < kHotSlots; k += kBinThreads)
+            if (s_tag[k] != kHotEmpty)
+            {
+                s_base[k] = atomicAdd(cursors + s_tag[k], s_cnt[k]);
+                s_cnt[k]  = 0u;
+            }
+        __syncthreads();
+        // ---- the same point-views again (the same arithmetic, hence the same keys): slots from the table, entries out ----
+        for (int i = first + threadIdx.x; i < last; i += kBinThreads)
+        {
+            PointRow<C> d;
+            d.tex    = sc.index ? __ldg(sc.index + i) : i;
+            d.tex_ok = (unsigned)d.tex < (unsigned)sc.n_tex;
+            if (discarded_for_confidence<ACT>(sc, pr, d.tex)) continue;
+            const float4 p  = __ldg(sc.position + i);
+            const float raw = __ldg(sc.point_size + i);
+            float sp        = -1.f;
+            for (int v = 0; v < nv; ++v)
+            {
+                if ((no_room >> v) & 1u) continue;  // uniform
+                if (use_dropout && __ldg(sc.dropout + (size_t)(v0 + v) * sc.N + i) == 1.f) continue;
+                const Projected r = project_visible(s_cam[v], g, pr, p, raw, sp);
+                if (!r.ok) continue;
+                fetch_point_row<C, ACT>(sc, pr, fb, i, d);
+                const uint32_t key  = (uint32_t)v * n_keys + (uint32_t)bin_key(g, r.u, r.v);
+                const int s         = hot_find(s_tag, key);
+                const uint32_t slot = s >= 0 ? s_base[s] + atomicAdd(s_cnt + s, 1u) : atomicAdd(cursors + key, 1u);
+                write_entry<C>(fb, g, pr, s_ebase[v] + slot, i, p, raw, r, d);
             }
         }
     }
@@ -521,7 +712,7 @@ __global__ __launch_bounds__(kBinThreads, TRIPS_SCATTER_MIN_BLOCKS) void bin_sca
 // Count pass of the binning stage: bounding boxes, visible points per (view, bin, tile), their exclusive scan and the
 // first entry of every view.  After it fb.view_total / stats->visible say how many entries the scatter pass will write.
 cudaError_t launch_bin_count(const ScenePtrs& sc, const CamConst* cams, const Geom& g, const TripsRenderParams& pr, int B,
-                             const FwdBuffers& fb, unsigned long long entry_cap, int sm_count, cudaStream_t st)
+                             const FwdBuffers& fb, unsigned long long entry_cap, bool hot, int sm_count, cudaStream_t st)
 {
     const int n_keys   = g.n_bins << kSubShift;
     const int grid     = sm_count * kBinBlocksPerSM;
@@ -541,12 +732,16 @@ cudaError_t launch_bin_count(const ScenePtrs& sc, const CamConst* cams, const Ge
         for (int gi = 0; gi < n_groups; ++gi)
         {
             const int v0 = gi * kViewGroup, nv = min(kViewGroup, B - v0);
-            if (act)
+            if (hot && act)
+                bin_count_hot_kernel<true><<<grid, kBinThreads, 0, st>>>(sc, cams, g, pr, fb, v0, nv, fb.ticket + gi);
+            else if (hot)
+                bin_count_hot_kernel<false><<<grid, kBinThreads, 0, st>>>(sc, cams, g, pr, fb, v0, nv, fb.ticket + gi);
+            else if (act)
                 bin_count_kernel<true><<<grid, kBinThreads, 0, st>>>(sc, cams, g, pr, fb, v0, nv, fb.ticket + gi);
             else
                 bin_count_kernel<false><<<grid, kBinThreads, 0, st>>>(sc, cams, g, pr, fb, v0, nv, fb.ticket + gi);
         }
-    bin_scan_kernel<<<B, 1024, 0, st>>>(fb.bin_count, fb.bin_base, fb.bin_cursor, n_keys, 1, fb.view_total, kSubShift);
+    bin_scan_kernel<<<B, 1024, 0, st>>>(fb.bin_count, fb.bin_base, fb.bin_cursor, n_keys, 1, fb.view_total, kSubShift, fb.stats);
     entry_base_kernel<<<1, 32, 0, st>>>(fb.view_total, B, entry_cap, fb.entry_base, fb.stats);
     return cudaGetLastError();
 }
@@ -556,7 +751,7 @@ int bin_scatter_launches(int N, int B) { return N > 0 ? (B + kViewGroup - 1) / k
 
 // Scatter pass of the binning stage: writes the entries (the arrays must hold fb.entry_base[B] entries).
 cudaError_t launch_bin_scatter(const ScenePtrs& sc, const CamConst* cams, const Geom& g, const TripsRenderParams& pr, int B,
-                               const FwdBuffers& fb, int sm_count, cudaStream_t st)
+                               const FwdBuffers& fb, bool hot, int sm_count, cudaStream_t st)
 {
     if (sc.N <= 0) return cudaSuccess;
     const int grid     = sm_count * kBinBlocksPerSM;
@@ -566,12 +761,16 @@ cudaError_t launch_bin_scatter(const ScenePtrs& sc, const CamConst* cams, const 
     {
         const int v0 = gi * kViewGroup, nv = min(kViewGroup, B - v0);
         unsigned* tk = fb.ticket + n_groups + gi;
-#define TRIPS_SCATTER_CASE(CC)                                                                                 \
-    case CC:                                                                                                   \
-        if (act)                                                                                               \
-            bin_scatter_kernel<CC, true><<<grid, kBinThreads, 0, st>>>(sc, cams, g, pr, fb, v0, nv, tk);      \
-        else                                                                                                   \
-            bin_scatter_kernel<CC, false><<<grid, kBinThreads, 0, st>>>(sc, cams, g, pr, fb, v0, nv, tk);     \
+#define TRIPS_SCATTER_CASE(CC)                                                                                    \
+    case CC:                                                                                                      \
+        if (hot && act)                                                                                           \
+            bin_scatter_hot_kernel<CC, true><<<grid, kBinThreads, 0, st>>>(sc, cams, g, pr, fb, v0, nv, tk);     \
+        else if (hot)                                                                                             \
+            bin_scatter_hot_kernel<CC, false><<<grid, kBinThreads, 0, st>>>(sc, cams, g, pr, fb, v0, nv, tk);    \
+        else if (act)                                                                                             \
+            bin_scatter_kernel<CC, true><<<grid, kBinThreads, 0, st>>>(sc, cams, g, pr, fb, v0, nv, tk);         \
+        else                                                                                                      \
+            bin_scatter_kernel<CC, false><<<grid, kBinThreads, 0, st>>>(sc, cams, g, pr, fb, v0, nv, tk);        \
         break;
         switch (sc.C)
         {
@@ -617,7 +816,7 @@ __device__ __forceinline__ uint32_t block_excl_scan_256(uint32_t v, uint32_t* sm
 }
 
 __global__ __launch_bounds__(256) void scan_reduce_kernel(const uint32_t* __restrict__ counts, int P, int nchunks, int k_keep,
-                                                          uint32_t* __restrict__ partial, DevStats* stats)
+                                                          uint32_t* __restrict__ partial, DevStats* stats, uint2* __restrict__ heavy)
 {
     __shared__ uint32_t sm[8];
     const int b           = blockIdx.y;
@@ -632,6 +831,11 @@ __global__ __launch_bounds__(256) void scan_reduce_kernel(const uint32_t* __rest
         sum += v;
         kept += min(v, (uint32_t)k_keep);
         mx = max(mx, v);
+        if (v > (uint32_t)kHeavyList)  // a list worth a block of its own (heavy_topk_kernel); rare
+        {
+            const unsigned slot = atomicAdd(&stats->n_heavy, 1u);
+            if (slot < (unsigned)kHeavyCap) heavy[slot] = make_uint2((unsigned)b, (unsigned)i);
+        }
     }
     uint32_t total;
     block_excl_scan_256(sum, sm, total);
@@ -727,7 +931,7 @@ __global__ __launch_bounds__(256) void scan_apply_kernel(const uint32_t* __restr
 
 cudaError_t launch_scan(const Geom& g, int B, int k_keep, const FwdBuffers& fb, int nchunks, cudaStream_t st)
 {
-    scan_reduce_kernel<<<dim3(nchunks, B), 256, 0, st>>>(fb.counts, g.P, nchunks, k_keep, fb.partial, fb.stats);
+    scan_reduce_kernel<<<dim3(nchunks, B), 256, 0, st>>>(fb.counts, g.P, nchunks, k_keep, fb.partial, fb.stats, fb.heavy);
     scan_partials_kernel<<<1, 1024, 0, st>>>(fb.partial, nchunks, B, fb.view_base, fb.frag_cap, fb.stats);
     scan_apply_kernel<<<dim3(nchunks, B), 256, 0, st>>>(fb.counts, g.P, nchunks, fb.partial, fb.offsets);
     return cudaGetLastError();
@@ -1072,6 +1276,9 @@ constexpr int kSortedPad = 17;   // row pitch (entries) of the per-pixel sorted 
 #ifndef TRIPS_SB_THREADS
 #define TRIPS_SB_THREADS 128
 #endif
+#ifndef TRIPS_SB_SHUFFLE_RANK
+#define TRIPS_SB_SHUFFLE_RANK 1
+#endif
 #ifndef TRIPS_RANK_UNROLL
 #define TRIPS_RANK_UNROLL 4
 #endif
@@ -1119,6 +1326,118 @@ __device__ __forceinline__ KeyVal bitonic_merge16(KeyVal v, int j)
 #pragma unroll
     for (int s = 8; s > 0; s >>= 1) v = cmpx(v, s, (j & s) == 0);
     return v;
+}
+
+// Merges a chunk of up to 16 fragments (one per lane of a half-warp, unsorted, kInfKey = absent) into the ascending
+// top-16 `v` the half-warp keeps.  Both half-warps of a warp must call this together (full-mask shuffles).
+__device__ __forceinline__ void topk_merge16(KeyVal& v, KeyVal nk, int j, int hbase)
+{
+    const u64 cur_max = __shfl_sync(kFull, v.key, hbase | 15);
+    if (__ballot_sync(kFull, nk.key < cur_max) == 0) return;  // nothing nearer in either half
+    nk = bitonic_sort16(nk, j);
+    KeyVal rev;
+    rev.key   = __shfl_sync(kFull, nk.key, hbase | (15 - j));
+    rev.alpha = __shfl_sync(kFull, nk.alpha, hbase | (15 - j));
+    rev.eidx  = __shfl_sync(kFull, nk.eidx, hbase | (15 - j));
+    if (rev.key < v.key) v = rev;
+    v = bitonic_merge16(v, j);
+}
+
+// Pre-selection of very long lists.  A pixel list of thousands of fragments (many points projected into a few pixels)
+// would keep one half-warp of the blend kernel busy on its own while the rest of the machine idles.  Here a block of
+// 256 threads takes one such list: its 16 half-warps each select the 16 nearest fragments of a sixteenth of the list
+// (the streaming bitonic top-16 of the blend kernel), one half-warp merges the 256 candidates, and the 16 winners are
+// moved to the front of the list in depth order by swapping them with the fragments that were there - the list stays
+// the same set of fragments.  The blend kernel then reads only the first 16 entries of every list longer than
+// kHeavyList.  Lists are found by the scan (scan_reduce_kernel); with more than kHeavyCap of them nothing is done here
+// and the blend kernel, which sees the same counter, walks them itself.
+__global__ __launch_bounds__(256) void heavy_topk_kernel(const __grid_constant__ Geom g, FwdBuffers fb, int B)
+{
+    __shared__ u64 s_key[16][16];
+    __shared__ uint32_t s_pos[16][16];
+    __shared__ uint32_t s_vac[16];
+    const unsigned n_heavy = fb.stats->n_heavy;
+    if (n_heavy == 0 || n_heavy > (unsigned)kHeavyCap) return;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, j = lane & 15, hbase = lane & 16, hw = threadIdx.x >> 4;
+    for (unsigned h = blockIdx.x; h < n_heavy; h += gridDim.x)
+    {
+        const uint2 e = fb.heavy[h];
+        const int b   = (int)e.x;
+        if (b >= B || fb.view_base[b + 1] == fb.view_base[b]) continue;  // uniform: the view did not fit the list buffer
+        const size_t bP    = (size_t)b * g.P;
+        const uint32_t cnt = fb.counts[bP + e.y];
+        uint4* list        = fb.frags + fb.view_base[b] + (fb.offsets[bP + e.y] - cnt);  // offsets hold list ends after the collect pass
+        const uint32_t n_chunks = (cnt + 15) / 16, per = (n_chunks + 15) / 16;
+        const uint32_t c0 = hw * per, c1 = min(n_chunks, c0 + per);
+        KeyVal v;
+        v.key = kInfKey, v.alpha = 0u, v.eidx = 0u;
+        for (uint32_t k0 = 0; k0 < per; k0 += 4)  // the same trip count for all half-warps; four chunks of keys in flight per lane
+        {
+            KeyVal nk[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+            {
+                const uint32_t k = k0 + q, idx = (c0 + k) * 16 + j;
+                nk[q].key = kInfKey, nk[q].alpha = 0u, nk[q].eidx = 0u;
+                if (k < per && c0 + k < c1 && idx < cnt)
+                {
+                    const uint2 kk = *reinterpret_cast<const uint2*>(list + idx);
+                    nk[q].key      = ((u64)kk.y << 32) | kk.x;
+                    nk[q].alpha    = idx;  // the payload is the fragment's position in the list
+                }
+            }
+#pragma unroll
+            for (int q = 0; q < 4; ++q) topk_merge16(v, nk[q], j, hbase);
+        }
+        s_key[hw][j] = v.key;
+        s_pos[hw][j] = v.alpha;
+        __syncthreads();
+        if (warp == 0)
+        {
+            KeyVal w;
+            w.key = kInfKey, w.alpha = 0u, w.eidx = 0u;
+            for (int k = 0; k < 16; k += 2)  // each half of warp 0 merges eight of the sixteen candidate lists
+            {
+                const int src = k + (hbase >> 4);
+                KeyVal nk;
+                nk.key = s_key[src][j], nk.alpha = s_pos[src][j], nk.eidx = 0u;
+                topk_merge16(w, nk, j, hbase);
+            }
+            {
+                KeyVal nk;  // the upper half's result goes into the lower half's
+                nk.key   = __shfl_sync(kFull, w.key, 16 | j);
+                nk.alpha = __shfl_sync(kFull, w.alpha, 16 | j);
+                nk.eidx  = 0u;
+                if (hbase) nk.key = kInfKey;
+                topk_merge16(w, nk, j, hbase);
+            }
+            // lanes 0..15 hold the 16 nearest fragments in depth order (cnt > kHeavyList >= 16: all present); swap them to the front
+            const bool act    = lane < 16;
+            const uint32_t wp = w.alpha;
+            uint4 winner = make_uint4(0u, 0u, 0u, 0u), front = winner;
+            if (act)
+            {
+                winner = list[wp];
+                front  = list[j];
+            }
+            bool front_is_winner = false;
+            for (int k = 0; k < 16; ++k) front_is_winner |= (__shfl_sync(kFull, wp, k) == (uint32_t)j);
+            const bool displaced = act && !front_is_winner;  // a fragment that has to leave the front
+            const bool vacated   = act && wp >= 16u;         // a winner's old place outside the front
+            const unsigned m_d = __ballot_sync(kFull, displaced) & 0xffffu, m_v = __ballot_sync(kFull, vacated) & 0xffffu;
+            if (vacated) s_vac[__popc(m_v & ((1u << j) - 1u))] = wp;
+            __syncwarp();  // every lane holds its two fragments in registers before anything is stored
+            if (displaced) list[s_vac[__popc(m_d & ((1u << j) - 1u))]] = front;
+            if (act) list[j] = winner;
+        }
+        __syncthreads();
+    }
+}
+
+cudaError_t launch_heavy_topk(const Geom& g, int B, const FwdBuffers& fb, int sm_count, cudaStream_t st)
+{
+    heavy_topk_kernel<<<sm_count * 6, 256, 0, st>>>(g, fb, B);
+    return cudaGetLastError();
 }
 
 // A sorted entry in shared memory is (alpha, descriptor row[C]) when the row fits the shared-memory budget (C <= 4:
@@ -1170,6 +1489,7 @@ __global__ __launch_bounds__(kSbThreads, (C <= 8 ? TRIPS_SB_MIN_BLOCKS : 1)) voi
 #pragma unroll
     for (int c = 0; c < C; ++c) bg[c] = __ldg(sc.background + c);
 
+    const bool preselected = fb.stats->n_heavy <= (unsigned)kHeavyCap;  // heavy_topk_kernel handled every long list
     unsigned next_ticket = 0;
     if (lane == 0) next_ticket = atomicAdd(fb.ticket, 1u);
     for (;;)
@@ -1186,12 +1506,14 @@ __global__ __launch_bounds__(kSbThreads, (C <= 8 ? TRIPS_SB_MIN_BLOCKS : 1)) voi
         const uint32_t n_entry = (uint32_t)(fb.entry_base[b + 1] - fb.entry_base[b]);
         int layer, gx, gy, p;
         tile_pixel(g, tile, lane, layer, gx, gy, p);  // lane i owns one pixel of the tile
-        uint32_t cnt = 0, start = 0;
+        uint32_t cnt_all = 0, start = 0;
         if (p >= 0 && fb.view_base[b + 1] != fb.view_base[b])  // (a view that did not fit the list buffer renders as background)
         {
-            cnt   = fb.counts[bP + p];
-            start = fb.offsets[bP + p] - cnt;  // offsets hold list ends after the collect pass
+            cnt_all = fb.counts[bP + p];
+            start   = fb.offsets[bP + p] - cnt_all;  // offsets hold list ends after the collect pass
         }
+        // of a pre-selected list (heavy_topk_kernel) only the front matters: its 16 nearest fragments in depth order
+        const uint32_t cnt = (preselected && cnt_all > (uint32_t)kHeavyList) ? 16u : cnt_all;
         uint32_t incl = cnt;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1)
@@ -1232,6 +1554,67 @@ __global__ __launch_bounds__(kSbThreads, (C <= 8 ? TRIPS_SB_MIN_BLOCKS : 1)) voi
                 L.seg_p     = __shfl_sync(kFull, p, seg);
                 return L;
             };
+#if TRIPS_SB_SHUFFLE_RANK
+            // Rounds of whole lists: a round takes the lists of consecutive pixels as long as they fit 32 lanes (every
+            // list has at most kRankMax = 32 fragments here), so the fragments of one pixel always sit in neighbouring
+            // lanes of one round and a fragment finds its rank by reading the keys of its list from those lanes with
+            // shuffles.  Reading the keys from the list in memory instead cost one gather over several 128-byte lines
+            // per key and lane, and it was the load/store unit's line rate that bounded this kernel.
+            static_assert(kRankMax <= 32, "a list ranked by shuffles must fit one round of 32 lanes");
+            struct Round
+            {
+                uint32_t base, total;  // fragments of the tile before this round, fragments in it
+                int end_px;            // first pixel (lane) of the next round
+            };
+            auto plan = [&](int first_px) {
+                Round r;
+                r.base              = __shfl_sync(kFull, rel_start, first_px & 31);
+                const unsigned fits = __ballot_sync(kFull, lane >= first_px && incl - r.base <= 32u);  // a run of lanes from first_px on
+                r.end_px            = first_px + __popc(fits);
+                r.total             = __shfl_sync(kFull, incl, (r.end_px - 1) & 31) - r.base;
+                return r;
+            };
+            Round rn     = plan(0);
+            Loc nxt      = locate(rn.base + lane);
+            uint4 f_next = make_uint4(kFull, kFull, 0u, 0u);
+            if ((uint32_t)lane < rn.total) f_next = frags[nxt.seg_start + nxt.idx];
+            for (;;)
+            {
+                const Round rc   = rn;
+                const Loc cur    = nxt;
+                const uint4 f    = f_next;
+                const bool valid = (uint32_t)lane < rc.total;
+                const bool more  = rc.end_px < 32 && rc.base + rc.total < tile_total;  // uniform
+                if (more)
+                {
+                    rn     = plan(rc.end_px);
+                    nxt    = locate(rn.base + lane);
+                    f_next = make_uint4(kFull, kFull, 0u, 0u);
+                    if ((uint32_t)lane < rn.total) f_next = frags[nxt.seg_start + nxt.idx];
+                }
+                const int lane0   = (int)(rc.base + lane - cur.idx - rc.base);  // lane of the first fragment of this fragment's list
+                const int longest = __reduce_max_sync(kFull, valid ? (int)cur.seg_cnt : 0);
+                const u64 mine    = ((u64)f.y << 32) | f.x;
+                int rank          = 0;
+                for (int i = 0; i < longest; ++i)
+                {
+                    const int src     = max(0, min(lane0 + i, 31));
+                    const uint32_t oy = __shfl_sync(kFull, f.y, src), ox = __shfl_sync(kFull, f.x, src);
+                    if (i < (int)cur.seg_cnt) rank += ((((u64)oy << 32) | ox) < mine) ? 1 : 0;
+                }
+                if (valid)
+                {
+                    if (f.w >= n_entry)
+                        atomicOr(&fb.stats->status, TRIPS_DEV_BAD_FRAGMENT);  // corrupted list: skip instead of gathering out of bounds
+                    else if (rank < K)
+                    {
+                        sb_store_entry<C>(sorted + (cur.seg * kSortedPad + rank) * E, entries, f.w, f.z);
+                        if (pr.train) fb.records[(bP + cur.seg_p) * 16 + rank] = make_uint2(f.w, f.z);
+                    }
+                }
+                if (!more) break;
+            }
+#else
             Loc nxt      = locate(lane);
             uint4 f_next = make_uint4(0u, 0u, 0u, 0u);
             if (lane < tile_total) f_next = frags[nxt.seg_start + nxt.idx];
@@ -1265,6 +1648,7 @@ __global__ __launch_bounds__(kSbThreads, (C <= 8 ? TRIPS_SB_MIN_BLOCKS : 1)) voi
                     }
                 }
             }
+#endif
         }
         else
         {
@@ -1304,15 +1688,7 @@ __global__ __launch_bounds__(kSbThreads, (C <= 8 ? TRIPS_SB_MIN_BLOCKS : 1)) voi
                         nk.alpha      = f.z;
                         nk.eidx       = f.w;
                     }
-                    const u64 cur_max = __shfl_sync(kFull, v.key, hbase | 15);
-                    if (__ballot_sync(kFull, nk.key < cur_max) == 0) continue;  // nothing nearer in either half
-                    nk = bitonic_sort16(nk, j);
-                    KeyVal rev;
-                    rev.key   = __shfl_sync(kFull, nk.key, hbase | (15 - j));
-                    rev.alpha = __shfl_sync(kFull, nk.alpha, hbase | (15 - j));
-                    rev.eidx  = __shfl_sync(kFull, nk.eidx, hbase | (15 - j));
-                    if (rev.key < v.key) v = rev;
-                    v = bitonic_merge16(v, j);
+                    topk_merge16(v, nk, j, hbase);
                 }
                 if (j < min((int)cnt_s, K))
                 {
