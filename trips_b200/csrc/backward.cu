@@ -59,15 +59,11 @@ constexpr int kBwdWarps   = kBwdThreads / 32;
 // What bounds the kernel (ncu): about 50 % of the issue slots and 48 % of the load/store unit's line rate are in use
 // at 16-20 resident warps per SM; DRAM is at 20-30 %.  Hence the care for lines per instruction (entries ordered by
 // tile, paired atomics, coalesced staging) and for instructions per fragment (fragment table, no shuffle searches).
-#ifndef TRIPS_BWD_BLOCKS_PER_SM
-#define TRIPS_BWD_BLOCKS_PER_SM 12
-#endif
+constexpr int kBwdBlocksPerSM = 12;  // grid size of the persistent kernel, in blocks per SM
 // measured: 5 resident blocks (96 registers) 3.59 ms, 4 blocks (108) 3.63 ms, 6 blocks (80) 3.76 ms
-#ifndef TRIPS_BWD_MIN_BLOCKS
-#define TRIPS_BWD_MIN_BLOCKS 5
-#endif
+constexpr int kBwdMinBlocks = 5;
 template <int C>
-__global__ __launch_bounds__(kBwdThreads, (C <= 4 ? TRIPS_BWD_MIN_BLOCKS : 1)) void blend_backward_kernel(ScenePtrs sc, const CamConst* __restrict__ cams,
+__global__ __launch_bounds__(kBwdThreads, (C <= 4 ? kBwdMinBlocks : 1)) void blend_backward_kernel(ScenePtrs sc, const CamConst* __restrict__ cams,
                                                                      const __grid_constant__ Geom g, TripsRenderParams pr, int B,
                                                                      FwdBuffers fb, BwdBuffers bb,
                                                                      const __grid_constant__ ConstLayerPtrs grad_in)
@@ -376,7 +372,7 @@ cudaError_t launch_blend_backward(const ScenePtrs& sc, const CamConst* cams, con
 {
     cudaError_t e = cudaMemsetAsync(fb.ticket, 0, sizeof(unsigned), st);
     if (e != cudaSuccess) return e;
-    const int grid = (int)max(1u, min((unsigned)(sm_count * TRIPS_BWD_BLOCKS_PER_SM), ((unsigned)g.n_tiles * (unsigned)B + kBwdWarps - 1) / kBwdWarps));
+    const int grid = (int)max(1u, min((unsigned)(sm_count * kBwdBlocksPerSM), ((unsigned)g.n_tiles * (unsigned)B + kBwdWarps - 1) / kBwdWarps));
 #define TRIPS_BWD_CASE(CC)                                                                                         \
     case CC:                                                                                                       \
         blend_backward_kernel<CC><<<grid, kBwdThreads, 0, st>>>(sc, cams, g, pr, B, fb, bb, grad_in);             \

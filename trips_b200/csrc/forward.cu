@@ -115,23 +115,12 @@ __device__ __forceinline__ Projected project_visible(const CamConst& cam, const 
     return r;
 }
 
-#ifndef TRIPS_STORE_256
-#define TRIPS_STORE_256 1
-#endif
-#ifndef TRIPS_SCATTER_MIN_BLOCKS
-#define TRIPS_SCATTER_MIN_BLOCKS 3  // measured on config 3: 1.46 ms unbounded (95 registers), 1.34 ms at 3 blocks (85), 1.36 ms at 4 (64)
-#endif
-#ifndef TRIPS_SCATTER_SWEEP
-#define TRIPS_SCATTER_SWEEP 4
-#endif
-#ifndef TRIPS_BIN_TICKET
-#define TRIPS_BIN_TICKET 1024
-#endif
 constexpr int kBinThreads     = 256;
 constexpr int kBinBlocksPerSM = 8;
+constexpr int kScatterMinBlocks = 3;   // measured on config 3: 1.46 ms unbounded (95 registers), 1.34 ms at 3 resident blocks (85), 1.36 ms at 4 (64)
 constexpr int kBinChunk       = 8192;  // points per bounding box
-constexpr int kBinTicket      = TRIPS_BIN_TICKET;
-constexpr int kSweep          = TRIPS_SCATTER_SWEEP;  // views whose entry slots a thread requests before it waits for any of them  // points per work ticket of the binning kernels; a ticket lies inside one box
+constexpr int kBinTicket      = 1024;
+constexpr int kSweep          = 4;      // views whose entry slots a thread requests before it waits for any of them  // points per work ticket of the binning kernels; a ticket lies inside one box
 constexpr int kViewGroup      = 16;    // views whose camera constants are in shared memory at a time (one launch per group)
 static_assert(kBinChunk % kBinTicket == 0, "a ticket must not straddle two bounding boxes");
 
@@ -400,14 +389,14 @@ __global__ void entry_base_kernel(const uint32_t* __restrict__ view_total, int B
 // store instructions of the entry scatter, each covering a whole sector.
 __device__ __forceinline__ void store_entry_head(float4* dst, const float4& a, const float4& b)
 {
-#if TRIPS_STORE_256
-    asm volatile("st.global.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst), "f"(a.x), "f"(a.y), "f"(a.z), "f"(a.w), "f"(b.x), "f"(b.y),
-                 "f"(b.z), "f"(b.w)
+    // Entries of one screen tile are written by many point blocks at different times.  Keeping the written lines in L2 for as
+    // long as it will hold them lets neighbouring 32-byte sectors meet in one line before it goes to DRAM (measured: the
+    // scatter pass 3 % faster than with the default policy, evict_first no different from the default).
+    uint64_t policy;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(policy));
+    asm volatile("st.global.L2::cache_hint.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8}, %9;" ::"l"(dst), "f"(a.x), "f"(a.y), "f"(a.z), "f"(a.w), "f"(b.x), "f"(b.y),
+                 "f"(b.z), "f"(b.w), "l"(policy)
                  : "memory");
-#else
-    dst[0] = a;
-    dst[1] = b;
-#endif
 }
 
 // What an entry carries of its point besides the projection: fetched once per point, when it turns out visible in a view.
@@ -476,7 +465,7 @@ __device__ __forceinline__ void write_entry(const FwdBuffers& fb, const Geom& g,
 }
 
 template <int C, bool ACT>
-__global__ __launch_bounds__(kBinThreads, TRIPS_SCATTER_MIN_BLOCKS) void bin_scatter_kernel(ScenePtrs sc, const CamConst* __restrict__ cams, const __grid_constant__ Geom g,
+__global__ __launch_bounds__(kBinThreads, kScatterMinBlocks) void bin_scatter_kernel(ScenePtrs sc, const CamConst* __restrict__ cams, const __grid_constant__ Geom g,
                                                                   TripsRenderParams pr, FwdBuffers fb, int v0, int nv, unsigned* ticket)
 {
     __shared__ CamConst s_cam[kViewGroup];
@@ -954,21 +943,11 @@ cudaError_t launch_scan(const Geom& g, int B, int k_keep, const FwdBuffers& fb, 
 // in the operation order of FastSortFusedNew (RenderForward.cu:882-899) is computed here, where every thread holds
 // a whole point, and travels with the fragment.
 // ------------------------------------------------------------------------------------------------------------
-#ifndef TRIPS_WIN_CHUNK
-#define TRIPS_WIN_CHUNK 4096
-#endif
-#ifndef TRIPS_WIN_THREADS
-#define TRIPS_WIN_THREADS 256
-#endif
-#ifndef TRIPS_WIN_BLOCKS_PER_SM
-#define TRIPS_WIN_BLOCKS_PER_SM 8
-#endif
-#ifndef TRIPS_WIN_CHUNK_COLLECT
-#define TRIPS_WIN_CHUNK_COLLECT 1024
-#endif
-constexpr int kWinChunkCount   = TRIPS_WIN_CHUNK;          // entries per block ticket, counting pass
-constexpr int kWinChunkCollect = TRIPS_WIN_CHUNK_COLLECT;  // and collecting pass: the lists a chunk writes to must stay in L2 until complete (measured with tile-ordered entries: 256 1.80 ms, 512 1.46 ms, 1024 1.35 ms, 2048 1.47 ms)
-constexpr int kWinThreads = TRIPS_WIN_THREADS;
+constexpr int kWinChunkCount   = 4096;  // entries per block ticket, counting pass
+constexpr int kWinChunkCollect = 1024;  // and collecting pass: the lists a chunk writes to must stay in L2 until complete (measured with tile-ordered entries: 256 1.80 ms, 512 1.46 ms, 1024 1.35 ms, 2048 1.47 ms)
+constexpr int kWinThreads    = 256;
+constexpr int kWinBlocksPerSM = 8;  // grid size of the window kernels, in blocks per SM
+constexpr int kWinMinBlocks  = 5;  // resident blocks the register allocation leaves room for
 constexpr int kWinMax     = 34 * 34 + 18 * 18 + 10 * 10 + 6 * 6 + 4 * 4 + 3 * 3 * 3;  // 1659 window pixels over 8 layers
 
 // Window of a bin: on layer l it starts at ((32 bx) >> l, (32 by) >> l) and is win_w(l) pixels wide; the counters of
@@ -1108,34 +1087,22 @@ __device__ __forceinline__ void for_each_footprint(const float4* __restrict__ he
     }
 }
 
-#ifndef TRIPS_FRAG_EVICT_LAST
-#define TRIPS_FRAG_EVICT_LAST 1
-#endif
 
 // 16-byte store that asks L2 to keep the line: a pixel's list is written 16 bytes at a time by many threads, and a
 // sector that leaves L2 half written costs a read-modify-write in DRAM.
 __device__ __forceinline__ void store_frag(uint4* p, const uint4& v, uint64_t policy)
 {
-#if TRIPS_FRAG_EVICT_LAST
     asm volatile("st.global.L2::cache_hint.v4.b32 [%0], {%1, %2, %3, %4}, %5;" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w), "l"(policy) : "memory");
-#else
-    *p = v;
-#endif
 }
 __device__ __forceinline__ uint64_t evict_last_policy()
 {
     uint64_t policy = 0;
-#if TRIPS_FRAG_EVICT_LAST
     asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(policy));
-#endif
     return policy;
 }
 
-#ifndef TRIPS_WIN_MIN_BLOCKS
-#define TRIPS_WIN_MIN_BLOCKS 5
-#endif
 template <bool COLLECT>
-__global__ __launch_bounds__(kWinThreads, TRIPS_WIN_MIN_BLOCKS) void window_kernel(const __grid_constant__ Geom g, FwdBuffers fb, int B)
+__global__ __launch_bounds__(kWinThreads, kWinMinBlocks) void window_kernel(const __grid_constant__ Geom g, FwdBuffers fb, int B)
 {
     __shared__ uint32_t s_cnt[kWinMax];
     __shared__ uint32_t s_base[COLLECT ? kWinMax : 1];
@@ -1235,7 +1202,7 @@ cudaError_t launch_count(const ScenePtrs& sc, const Geom& g, int B, const FwdBuf
 {
     cudaError_t e = cudaMemsetAsync(fb.ticket, 0, sizeof(unsigned) * B, st);
     if (e != cudaSuccess) return e;
-    window_kernel<false><<<sm_count * TRIPS_WIN_BLOCKS_PER_SM, kWinThreads, 0, st>>>(g, fb, B);
+    window_kernel<false><<<sm_count * kWinBlocksPerSM, kWinThreads, 0, st>>>(g, fb, B);
     return cudaGetLastError();
 }
 
@@ -1243,7 +1210,7 @@ cudaError_t launch_collect(const ScenePtrs& sc, const Geom& g, int B, const FwdB
 {
     cudaError_t e = cudaMemsetAsync(fb.ticket, 0, sizeof(unsigned) * B, st);
     if (e != cudaSuccess) return e;
-    window_kernel<true><<<sm_count * TRIPS_WIN_BLOCKS_PER_SM, kWinThreads, 0, st>>>(g, fb, B);
+    window_kernel<true><<<sm_count * kWinBlocksPerSM, kWinThreads, 0, st>>>(g, fb, B);
     return cudaGetLastError();
 }
 
@@ -1262,28 +1229,11 @@ cudaError_t launch_collect(const ScenePtrs& sc, const Geom& g, int B, const FwdB
 // ------------------------------------------------------------------------------------------------------------
 typedef unsigned long long u64;
 constexpr u64 kInfKey    = 0xffffffffffffffffull;
-#ifndef TRIPS_SB_RING
-#define TRIPS_SB_RING 2
-#endif
-#ifndef TRIPS_RANK_MAX
-#define TRIPS_RANK_MAX 32  // measured: 16 3.12 ms, 24 3.03, 32 3.02, 48 3.08, 64 3.15
-#endif
-constexpr int kRankMax   = TRIPS_RANK_MAX;  // longest list ranked by counting; longer lists use the streaming path
+constexpr int kSbRing    = 2;    // descriptor rows requested ahead of their use in the blend loop (C <= 4)
+constexpr int kRankMax   = 32;   // longest list ranked by counting; longer lists use the streaming path (measured: 16 3.12 ms, 24 3.03, 32 3.02, 48 3.08, 64 3.15)
 constexpr int kSortedPad = 17;   // row pitch (entries) of the per-pixel sorted lists in shared memory
-#ifndef TRIPS_SB_STAGE_MAX_C
-#define TRIPS_SB_STAGE_MAX_C 0
-#endif
-#ifndef TRIPS_SB_THREADS
-#define TRIPS_SB_THREADS 128
-#endif
-#ifndef TRIPS_SB_SHUFFLE_RANK
-#define TRIPS_SB_SHUFFLE_RANK 1
-#endif
-#ifndef TRIPS_RANK_UNROLL
-#define TRIPS_RANK_UNROLL 4
-#endif
-constexpr int kRankUnroll = TRIPS_RANK_UNROLL;
-constexpr int kSbThreads = TRIPS_SB_THREADS;
+constexpr int kSbStageMaxC = 0;  // widest descriptor whose rows are staged in shared memory by phase A (0: none; staging cost more L1 than it saved)
+constexpr int kSbThreads = 128;
 constexpr int kSbWarps   = kSbThreads / 32;
 
 struct KeyVal
@@ -1446,7 +1396,7 @@ cudaError_t launch_heavy_topk(const Geom& g, int B, const FwdBuffers& fb, int sm
 template <int C>
 struct SbEntry
 {
-    static constexpr bool kStaged = (C <= TRIPS_SB_STAGE_MAX_C);
+    static constexpr bool kStaged = (C <= kSbStageMaxC);
     static constexpr int kFloats  = kStaged ? (1 + C) : 2;
 };
 
@@ -1470,11 +1420,9 @@ __device__ __forceinline__ void sb_store_entry(float* dst, const float* entries,
 }
 
 // measured: 7 resident blocks (72 registers) 3.18 ms, 6 blocks (80) 3.46 ms, 5 blocks 3.83 ms, 8 blocks (64, spills) 3.76 ms
-#ifndef TRIPS_SB_MIN_BLOCKS
-#define TRIPS_SB_MIN_BLOCKS 7
-#endif
+constexpr int kSbMinBlocks = 7;
 template <int C>
-__global__ __launch_bounds__(kSbThreads, (C <= 8 ? TRIPS_SB_MIN_BLOCKS : 1)) void sort_blend_kernel(ScenePtrs sc, const __grid_constant__ Geom g, TripsRenderParams pr,
+__global__ __launch_bounds__(kSbThreads, (C <= 8 ? kSbMinBlocks : 1)) void sort_blend_kernel(ScenePtrs sc, const __grid_constant__ Geom g, TripsRenderParams pr,
                                                                 int B, FwdBuffers fb, const __grid_constant__ LayerPtrs out,
                                                                 unsigned n_tiles_total)
 {
@@ -1554,7 +1502,6 @@ __global__ __launch_bounds__(kSbThreads, (C <= 8 ? TRIPS_SB_MIN_BLOCKS : 1)) voi
                 L.seg_p     = __shfl_sync(kFull, p, seg);
                 return L;
             };
-#if TRIPS_SB_SHUFFLE_RANK
             // Rounds of whole lists: a round takes the lists of consecutive pixels as long as they fit 32 lanes (every
             // list has at most kRankMax = 32 fragments here), so the fragments of one pixel always sit in neighbouring
             // lanes of one round and a fragment finds its rank by reading the keys of its list from those lanes with
@@ -1614,41 +1561,6 @@ __global__ __launch_bounds__(kSbThreads, (C <= 8 ? TRIPS_SB_MIN_BLOCKS : 1)) voi
                 }
                 if (!more) break;
             }
-#else
-            Loc nxt      = locate(lane);
-            uint4 f_next = make_uint4(0u, 0u, 0u, 0u);
-            if (lane < tile_total) f_next = frags[nxt.seg_start + nxt.idx];
-            for (uint32_t t0 = 0; t0 < tile_total; t0 += 32)
-            {
-                const Loc cur    = nxt;
-                const uint4 f    = f_next;
-                const bool valid = t0 + lane < tile_total;
-                if (t0 + 32 < tile_total)
-                {
-                    nxt = locate(t0 + 32 + lane);
-                    if (t0 + 32 + lane < tile_total) f_next = frags[nxt.seg_start + nxt.idx];
-                }
-                if (valid)
-                {
-                    const u64 mine  = ((u64)f.y << 32) | f.x;
-                    const uint2* kp = reinterpret_cast<const uint2*>(frags + cur.seg_start);
-                    int rank        = 0;
-#pragma unroll kRankUnroll
-                    for (uint32_t i = 0; i < cur.seg_cnt; ++i)
-                    {
-                        const uint2 o = kp[(size_t)i * 2];
-                        rank += ((((u64)o.y << 32) | o.x) < mine) ? 1 : 0;
-                    }
-                    if (f.w >= n_entry)
-                        atomicOr(&fb.stats->status, TRIPS_DEV_BAD_FRAGMENT);  // corrupted list: skip instead of gathering out of bounds
-                    else if (rank < K)
-                    {
-                        sb_store_entry<C>(sorted + (cur.seg * kSortedPad + rank) * E, entries, f.w, f.z);
-                        if (pr.train) fb.records[(bP + cur.seg_p) * 16 + rank] = make_uint2(f.w, f.z);
-                    }
-                }
-            }
-#endif
         }
         else
         {
@@ -1720,7 +1632,7 @@ __global__ __launch_bounds__(kSbThreads, (C <= 8 ? TRIPS_SB_MIN_BLOCKS : 1)) voi
         const float* my_sorted = sorted + lane * kSortedPad * E;
         // descriptor rows are requested kRing entries ahead of their use (the gathers are independent of the recurrence)
         constexpr int kRows = (C + 3) / 4;
-        constexpr int kRing = SbEntry<C>::kStaged ? 1 : (C <= 4 ? TRIPS_SB_RING : (C <= 8 ? 2 : 1));
+        constexpr int kRing = SbEntry<C>::kStaged ? 1 : (C <= 4 ? kSbRing : (C <= 8 ? 2 : 1));
         float4 ring[kRing][kRows];
         auto fetch_row = [&](int j, float4 (&dst)[kRows]) {
             if (!SbEntry<C>::kStaged && j < n)
@@ -1857,10 +1769,7 @@ cudaError_t launch_sort_blend(const ScenePtrs& sc, const Geom& g, const TripsRen
     const unsigned n_tiles = (unsigned)g.n_tiles * (unsigned)B;
     cudaError_t e          = cudaMemsetAsync(fb.ticket, 0, sizeof(unsigned), st);
     if (e != cudaSuccess) return e;
-#ifndef TRIPS_SB_BLOCKS_PER_SM
-#define TRIPS_SB_BLOCKS_PER_SM 16
-#endif
-    int blocks = (int)min((unsigned)(sm_count * TRIPS_SB_BLOCKS_PER_SM), (n_tiles + kSbWarps - 1) / kSbWarps);
+    int blocks = (int)min((unsigned)(sm_count * 16), (n_tiles + kSbWarps - 1) / kSbWarps);
     blocks     = max(blocks, 1);
     switch (sc.C)
     {
