@@ -49,9 +49,10 @@ def parse_args():
     ap.add_argument("--op", default="step", choices=["step", "resize_points", "texture_prepare"],
                     help="'step' (default): the training-step benchmark; 'resize_points': removal of 10 % of the points over all "
                          "per-point tensors and the Adam state (trips_resize_points) against the numpy restatement")
-    ap.add_argument("--collective", default="auto", choices=["auto", "fused", "nccl"],
+    ap.add_argument("--collective", default="auto", choices=["auto", "fused", "fused-peer", "nccl"],
                     help="N>1: 'fused' = one kernel sums the gradients over peer memory, applies Adam and broadcasts; "
-                         "'nccl' = all-reduce then Adam; 'auto' = fused when symmetric memory can be set up")
+                         "(through NVSwitch multicast addresses when the allocation has them, 'fused-peer' = over peer pointers "
+                         "only); 'nccl' = all-reduce then Adam; 'auto' = fused when symmetric memory can be set up")
     return ap.parse_args()
 
 
@@ -304,13 +305,15 @@ def run_ours(args, rank, world, local_rank):
     params = [tex.texture_raw, tex.confidence_raw, pc.t_position, pc.t_point_size, tex.background_color_raw]
     keys = ("texture", "confidence", "points", "point_size", "background")
     fused, collective = None, "none"
-    if world > 1 and args.collective in ("auto", "fused"):
+    if world > 1 and args.collective in ("auto", "fused", "fused-peer"):
         from trips_b200.dist import FusedPointOptimizer
         ok = torch.ones(1, device=dev)
         try:
-            fused = FusedPointOptimizer(list(zip(keys, params)), cache, lr=1e-3, betas=(0.9, 0.999))
+            # NVSwitch multicast (multimem) when the symmetric-memory allocation has a multicast address, peer pointers otherwise
+            fused = FusedPointOptimizer(list(zip(keys, params)), cache, lr=1e-3, betas=(0.9, 0.999),
+                                        multicast=False if args.collective == "fused-peer" else None)
         except Exception as e:  # noqa: BLE001 - symmetric memory is optional plumbing; the NCCL path is always there
-            if args.collective == "fused":
+            if args.collective in ("fused", "fused-peer"):
                 raise
             print(f"[bench] rank {rank}: symmetric memory unavailable ({type(e).__name__}: {e}); using NCCL all-reduce", file=sys.stderr)
             ok.zero_()
@@ -318,7 +321,9 @@ def run_ours(args, rank, world, local_rank):
         if ok.item() == 0:
             fused = None
     if fused is not None:
-        gout, collective = fused.grad_views, "fused peer-memory reduce + Adam + broadcast (trips_fused_reduce_adam)"
+        gout = fused.grad_views
+        collective = ("fused multimem reduce + Adam + multicast store (trips_fused_reduce_adam_multicast)" if fused.mode == "multimem"
+                      else "fused peer-memory reduce + Adam + broadcast (trips_fused_reduce_adam)")
         opt, flat = None, fused.grad_flat
     else:
         layout = FlatGradLayout(N, N, C)
@@ -483,6 +488,11 @@ def run_ours(args, rank, world, local_rank):
         ms_e_step = float(te.item()) / args.steps
         e2e = {"value": world * B / (ms_e_step / 1000.0), "unit": "views/s", "h2d_bytes_per_step": int(h2d),
                "d2h_bytes_per_step": 8, "ms_per_step": ms_e_step, "wall_ms_per_step": wall / args.steps}
+        # host link: the copy of the next step's targets runs beside the kernels of this step; what it takes of the host
+        # memory system grows with the number of ranks copying at once (every GPU of these machines reports NUMA node 0,
+        # so there is no closer node to allocate the pinned buffers on)
+        e2e["host_link"] = {"h2d_gb_per_s_per_gpu": h2d / (ms_e_step * 1e6), "h2d_gb_per_s_all_gpus": world * h2d / (ms_e_step * 1e6),
+                            "ms_over_device_step": ms_e_step - ms_step}
 
     # ---- N > 1: the split BASELINE config 3 names (a global batch of 8 views, 8 / N per rank), strong scaling ----
     strong = None

@@ -93,6 +93,14 @@ typedef struct
     int confidence_is_raw;           /* 1: confidence = sigmoid(confidence_scale * raw) */
     float confidence_scale;          /* 10 + narrowing factor */
     int texture_abs;                 /* 1: descriptor = |raw| */
+    /* The flags whose non-default values select the reference's second forward pipeline (PointRenderer.cu:730-731:
+     * CountTiled, CollectTiled2[Pointsize], FastSortAndBlendWPrep2WarpSharedWork, RenderForward.cu:1401-3674).  The
+     * reference's defaults are 1, 1, 0, 0 (Settings.h); a zero-initialised struct does NOT hold the defaults. */
+    int use_layer_point_size;                   /* 0: a point is written to every layer, alpha carries no layer factor */
+    int render_points_in_all_lower_resolutions; /* 0: only the two layers around log2(size) are written (RenderForward.cu:2291-2393) */
+    int combine_lists;                          /* 1: a pixel also draws from the lists of the pixels above it on the coarser layers (RenderForward.cu:3232-3242) */
+    int saturated_alpha_accumulation;           /* forward: second pipeline only (RenderForward.cu:3524-3548; compiled out of the
+                                                   first, :908-935); backward: always (RenderBackward.cu:227-259) */
 } TripsRenderParams;
 
 /* Gradient outputs of BlendPointCloudBackward (src/lib/rendering/PointRenderer.cu:1423-1426).
@@ -187,6 +195,16 @@ typedef struct
 int trips_fused_reduce_adam(TripsContext* ctx, const float* const* grad_ptrs, float* const* param_ptrs, int world, int rank,
                             const TripsAdamSegment* segments, int n_segments, int64_t lo, int64_t hi, float* first_moments,
                             float* second_moments, int32_t* steps, void* stream);
+
+/* The same step through NVSwitch multicast addresses (multimem.ld_reduce / multimem.st): grad_multicast and
+ * param_multicast are the multicast mappings of the flat gradient buffers and of the flat parameter replicas of all
+ * ranks (e.g. the multicast_ptr of a symmetric-memory allocation), param_local is this rank's replica.  Half the
+ * NVLink bytes of trips_fused_reduce_adam.  The switch sums in an order of its own: weights equal
+ * trips_fused_reduce_adam's bit for bit with two ranks only; replicas are identical with any number of ranks.
+ * lo and hi must be multiples of 4 elements.  Ordering as for trips_fused_reduce_adam: the kernel waits on nothing. */
+int trips_fused_reduce_adam_multicast(TripsContext* ctx, const float* grad_multicast, float* param_multicast, const float* param_local,
+                                      const TripsAdamSegment* segments, int n_segments, int64_t lo, int64_t hi, float* first_moments,
+                                      float* second_moments, int32_t* steps, void* stream);
 
 /* One per-point tensor of the scene or of the optimizer state for trips_resize_points. */
 typedef struct

@@ -38,7 +38,8 @@ class OrView(C.Structure):
 class OrParams(C.Structure):
     _fields_ = [("num_layers", C.c_int), ("k_keep", C.c_int), ("train", C.c_int), ("drop_out_points_by_radius", C.c_int),
                 ("drop_out_radius_threshold", C.c_float), ("viewer_only", C.c_int), ("stability_cutoff_value", C.c_float),
-                ("bg_uses_Tn", C.c_int)]
+                ("bg_uses_Tn", C.c_int), ("use_layer_point_size", C.c_int), ("render_points_in_all_lower_resolutions", C.c_int),
+                ("combine_lists", C.c_int), ("saturated_alpha_accumulation", C.c_int)]
 
 
 def lib():
@@ -56,6 +57,7 @@ def lib():
         L.or_layer_size.argtypes = [C.c_void_p, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_int64)]
         L.or_get_points.argtypes = [C.c_void_p] + [C.c_void_p] * 3
         L.or_get_lists.argtypes = [C.c_void_p] + [C.c_void_p] * 3
+        L.or_get_first_layer.argtypes = [C.c_void_p, C.c_void_p]
         L.or_get_pyramid.argtypes = [C.c_void_p, C.c_void_p]
         L.or_get_records.argtypes = [C.c_void_p] + [C.c_void_p] * 3
         L.or_backward.argtypes = [C.c_void_p, C.POINTER(OrScene), C.POINTER(OrView), C.POINTER(OrParams)] + [C.c_void_p] * 8
@@ -84,9 +86,11 @@ def _ptr(a):
 
 
 def make_params(num_layers, k_keep, train, drop_out_points_by_radius=False, drop_out_radius_threshold=0.6,
-                viewer_only=False, stability_cutoff_value=10000.0, bg_uses_Tn=False) -> OrParams:
+                viewer_only=False, stability_cutoff_value=10000.0, bg_uses_Tn=False, use_layer_point_size=True,
+                render_points_in_all_lower_resolutions=True, combine_lists=False, saturated_alpha_accumulation=False) -> OrParams:
     return OrParams(num_layers, k_keep, int(train), int(drop_out_points_by_radius), drop_out_radius_threshold,
-                    int(viewer_only), stability_cutoff_value, int(bg_uses_Tn))
+                    int(viewer_only), stability_cutoff_value, int(bg_uses_Tn), int(use_layer_point_size),
+                    int(render_points_in_all_lower_resolutions), int(combine_lists), int(saturated_alpha_accumulation))
 
 
 def make_view(w, h, pose8, intr13, crop_transform=(1, 1, 0, 0, 0), crop_rotation=(1, 0, 0, 1)) -> OrView:
@@ -150,6 +154,11 @@ class Frame:
         rec = np.empty((n, 4), np.float32)
         lib().or_get_points(self._h, _ptr(depth), _ptr(nl), _ptr(rec))
         return depth, nl, rec
+
+    def first_layer(self):
+        first = np.empty(self.scene.n, np.int32)
+        lib().or_get_first_layer(self._h, _ptr(first))
+        return first
 
     def lists(self):
         counts = np.empty(self.P, np.int32)

@@ -182,7 +182,8 @@ struct OrFrame
     int64_t base[kMaxLayers + 1];
     int64_t P = 0, F = 0, Kf = 0, V = 0;
     std::vector<float> depth;
-    std::vector<int32_t> nlayers;
+    std::vector<int32_t> nlayers;  // layers the point is written to ...
+    std::vector<int32_t> first;    // ... starting with this one
     std::vector<float> rec;  // [N,4]
     std::vector<int32_t> counts;
     std::vector<int64_t> offsets;
@@ -262,6 +263,14 @@ OrFrame* or_forward(const OrScene* sc, const OrView* view, const OrParams* pr)
     const Cam cam = make_cam(view);
     f->depth.assign(N, -1.f);
     f->nlayers.assign(N, 0);
+    f->first.assign(N, 0);
+    // The reference has two forward pipelines (PointRenderer.cu:730-731).  The second one (CountTiled,
+    // CollectTiled2[Pointsize], FastSortAndBlendWPrep2WarpSharedWork: RenderForward.cu:1401-3674) runs when one of
+    // these three flags differs from its default; it differs from the first in the layers a point is written to, in
+    // the radius test (float instead of int), in the way the bilinear weight is evaluated, in combine_lists and in the
+    // saturated accumulation.
+    const bool second = !(pr->use_layer_point_size && pr->render_points_in_all_lower_resolutions && !pr->combine_lists);
+    const bool strict = pr->use_layer_point_size && !pr->render_points_in_all_lower_resolutions;
     f->rec.assign((size_t)N * 4, 0.f);
     f->counts.assign(f->P, 0);
 
@@ -286,7 +295,8 @@ OrFrame* or_forward(const OrScene* sc, const OrView* view, const OrParams* pr)
         float radius_px = fxc * sc->position[(size_t)i * 4 + 3] / z;
         float ps        = fxc * s / z;
         auto dropped    = [&](float rad) {
-            return pr->drop_out_points_by_radius && (float)(int)rad < pr->drop_out_radius_threshold;
+            // first pipeline: the test takes an int (RenderForward.cu:212-218); second: the float (RenderForward.cu:1527-1531)
+            return pr->drop_out_points_by_radius && (second ? rad : (float)(int)rad) < pr->drop_out_radius_threshold;
         };
         if (z <= 0.f || u < 0.f || u >= (float)(f->W[0] - 1) || v < 0.f || v >= (float)(f->H[0] - 1)) continue;
         if (dropped(radius_px)) continue;
@@ -295,10 +305,20 @@ OrFrame* or_forward(const OrScene* sc, const OrView* view, const OrParams* pr)
         f->rec[(size_t)i * 4 + 1] = v;
         f->rec[(size_t)i * 4 + 2] = ps;
         f->rec[(size_t)i * 4 + 3] = tm_bits_to_float((uint32_t)tex);
-        int hi = 0;
-        if (ps > 1.f) hi = std::min(tm_ceil_log2(ps), L - 1);
-        int layer = 0;
-        float x = u, y = v, rad = radius_px;
+        int lo = 0, hi = 0;
+        if (!pr->use_layer_point_size)
+            hi = L - 1;  // every layer (RenderForward.cu:1611-1631)
+        else if (ps > 1.f)
+        {
+            lo = std::min(tm_floor_log2(ps), L - 1);
+            hi = std::min(tm_ceil_log2(ps), L - 1);
+        }
+        // layers first .. last, stopping where the 2x2 footprint leaves the layer; the strict write starts at the layer
+        // below log2(size) and has at most two layers (RenderForward.cu:1555-1583, 2291-2393)
+        const int first = strict ? lo : 0;
+        const float sc0 = 1.f / (float)(1 << first);  // powf(0.5f, lo): exact
+        int layer = first;
+        float x = u * sc0, y = v * sc0, rad = radius_px * sc0;
         for (; layer < hi + 1; ++layer, x *= 0.5f, y *= 0.5f, rad *= 0.5f)
         {
             int px = (int)std::floor(x), py = (int)std::floor(y);
@@ -310,7 +330,8 @@ OrFrame* or_forward(const OrScene* sc, const OrView* view, const OrParams* pr)
                 counts[pix]++;
             }
         }
-        f->nlayers[i] = layer;
+        f->first[i]   = first;
+        f->nlayers[i] = layer - first;
         visible++;
     }
     f->V = visible;
@@ -337,8 +358,9 @@ OrFrame* or_forward(const OrScene* sc, const OrView* view, const OrParams* pr)
             float z = f->depth[i];
             if (!(z > 0.f)) continue;
             uint64_t key = ((uint64_t)tm_float_to_bits(z) << 32) | (uint32_t)i;
-            float x = f->rec[(size_t)i * 4 + 0], y = f->rec[(size_t)i * 4 + 1];
-            for (int layer = 0; layer < f->nlayers[i]; ++layer, x *= 0.5f, y *= 0.5f)
+            const float sc0 = 1.f / (float)(1 << f->first[i]);
+            float x = f->rec[(size_t)i * 4 + 0] * sc0, y = f->rec[(size_t)i * 4 + 1] * sc0;
+            for (int layer = f->first[i]; layer < f->first[i] + f->nlayers[i]; ++layer, x *= 0.5f, y *= 0.5f)
             {
                 int px = (int)std::floor(x), py = (int)std::floor(y);
                 for (int k = 0; k < 4; ++k)
@@ -376,32 +398,79 @@ OrFrame* or_forward(const OrScene* sc, const OrView* view, const OrParams* pr)
         while (p >= f->base[layer + 1]) ++layer;
         int64_t t = p - f->base[layer];
         int gx = (int)(t % f->W[layer]), gy = (int)(t / f->W[layer]);
+        // the nearest K fragments of the pixel's list; with combine_lists also of the lists of the pixels above it on the
+        // coarser layers (RenderForward.cu:3232-3242; a point written to several layers then appears several times)
+        uint64_t keys[kMaxKeep];
         int n = std::min(counts[p], K);
-        kept += n;
+        kept += n;  // the statistic counts the pixel's own list, also with combine_lists
+        for (int j = 0; j < n; ++j) keys[j] = f->frags[f->offsets[p] + j];
+        if (pr->combine_lists)
+        {
+            std::vector<uint64_t> cand(f->frags.begin() + f->offsets[p], f->frags.begin() + f->offsets[p] + counts[p]);
+            int x = gx / 2, y = gy / 2;
+            for (int l2 = layer + 1; l2 < L; ++l2, x /= 2, y /= 2)
+            {
+                int64_t q = f->base[l2] + (int64_t)y * f->W[l2] + x;
+                cand.insert(cand.end(), f->frags.begin() + f->offsets[q], f->frags.begin() + f->offsets[q] + counts[q]);
+            }
+            std::sort(cand.begin(), cand.end());
+            n = (int)std::min<size_t>(cand.size(), (size_t)K);
+            for (int j = 0; j < n; ++j) keys[j] = cand[j];
+        }
         float alpha[kMaxKeep], T[kMaxKeep];
         float contrib[kMaxKeep][16];
         int tex[kMaxKeep], pid[kMaxKeep];
         const float fac = 1.f / (float)(1 << layer);
         for (int j = 0; j < n; ++j)
         {
-            uint64_t key = f->frags[f->offsets[p] + j];
+            uint64_t key = keys[j];
             int i        = (int)(uint32_t)(key & 0xffffffffu);
             pid[j]       = i;
             float u = f->rec[(size_t)i * 4 + 0], v = f->rec[(size_t)i * 4 + 1], ps = f->rec[(size_t)i * 4 + 2];
             tex[j]   = (int)tm_float_to_bits(f->rec[(size_t)i * 4 + 3]);
             float ux = u * fac, uy = v * fac;
-            float b  = (1.f - std::fabs(ux - (float)gx)) * (1.f - std::fabs(uy - (float)gy));
+            float b;
+            if (second)
+            {
+                // compute_blending_fac + blend_fac_index (RenderForward.cu:3493-3496, PointBlending.h:216-263): the weight of
+                // the corner the pixel is, from the sub-pixel position.  A coordinate that is exactly an integer gets the
+                // weight 0 on both of its pixels here; the first pipeline's closed form gives 1 and 0.
+                float sx = ux - std::floor(ux), sy = uy - std::floor(uy);
+                int q    = ((float)gx < ux ? 0 : 1) + ((float)gy < uy ? 0 : 2);
+                b        = ((q & 1) ? sx : (1.f - sx)) * ((q & 2) ? sy : (1.f - sy));
+            }
+            else
+                b = (1.f - std::fabs(ux - (float)gx)) * (1.f - std::fabs(uy - (float)gy));
             if (std::fabs(ux - (float)gx) > 1.f || std::fabs(uy - (float)gy) > 1.f) b = 0.f;
             float a = b * sc->confidence[tex[j]];
-            a *= layer_factor(ps, layer, L, nullptr);
+            if (pr->use_layer_point_size) a *= layer_factor(ps, layer, L, nullptr);
             alpha[j] = a;
         }
-        // transmittance chain: T_j = T_{j-1} * (1 - alpha_{j-1}); reported as 0 below the cut-off
         float run = 1.f;
-        for (int j = 0; j < n; ++j)
+        if (second && pr->saturated_alpha_accumulation)
         {
-            if (j > 0) run = run * (1.f - alpha[j - 1]);
-            T[j] = (j == 0 || run >= kAlphaCut) ? run : 0.f;
+            // RenderForward.cu:3524-3548 as written: the weight of a fragment is 1 while the alphas before it and its own sum
+            // to less than 1, and saturate(1) / (alpha + 1e-9) (in double) for the fragment that crosses 1: its own lane's
+            // alpha_dest is still the initial 1 when it is read there.  Below the cut-off: 0.
+            for (int j = 0; j < n; ++j)
+            {
+                if (j > 0) run = run - alpha[j - 1];
+                if (j == 0)
+                    T[j] = 1.f;
+                else if (run >= kAlphaCut)
+                    T[j] = (run - alpha[j] > 0.f) ? 1.f : (float)(1.0 / ((double)alpha[j] + 1e-9));
+                else
+                    T[j] = 0.f;
+            }
+        }
+        else
+        {
+            // transmittance chain: T_j = T_{j-1} * (1 - alpha_{j-1}); reported as 0 below the cut-off
+            for (int j = 0; j < n; ++j)
+            {
+                if (j > 0) run = run * (1.f - alpha[j - 1]);
+                T[j] = (j == 0 || run >= kAlphaCut) ? run : 0.f;
+            }
         }
         for (int j = 0; j < kMaxKeep; ++j)
             for (int c = 0; c < C; ++c) contrib[j][c] = (j < n) ? T[j] * alpha[j] * sc->texture[(size_t)c * sc->n_tex + tex[j]] : 0.f;
@@ -412,7 +481,7 @@ OrFrame* or_forward(const OrScene* sc, const OrView* view, const OrParams* pr)
         float wb;
         if (n == 0)
             wb = 1.f;  // the reference reads a neighbouring lane here; defined as pure background
-        else if (pr->bg_uses_Tn)
+        else if (pr->bg_uses_Tn && !second)  // (an option of the first pipeline only)
         {
             float tn = run * (1.f - alpha[n - 1]);
             wb       = (T[n - 1] >= kAlphaCut && tn >= kAlphaCut) ? tn : 0.f;
@@ -461,6 +530,7 @@ void or_get_points(const OrFrame* f, float* depth, int32_t* nlayers, float* rec)
     if (nlayers) memcpy(nlayers, f->nlayers.data(), sizeof(int32_t) * f->N);
     if (rec) memcpy(rec, f->rec.data(), sizeof(float) * 4 * f->N);
 }
+void or_get_first_layer(const OrFrame* f, int32_t* first) { memcpy(first, f->first.data(), sizeof(int32_t) * f->N); }
 void or_get_lists(const OrFrame* f, int32_t* counts, int64_t* offsets, uint64_t* frags)
 {
     if (counts) memcpy(counts, f->counts.data(), sizeof(int32_t) * f->P);
@@ -529,6 +599,42 @@ void or_backward(const OrFrame* f, const OrScene* sc, const OrView* view, const 
                 float colors[16];
                 for (int c = 0; c < C; ++c) colors[c] = fg ? sc->texture[(size_t)c * sc->n_tex + tex] : sc->background[c];
                 float g_alpha = 0.f;
+                if (pr->saturated_alpha_accumulation)
+                {
+                    // RenderBackward.cu:227-259 as written
+                    const float sat = std::fmin(std::fmax(alpha_dest, 0.f), 1.f);
+                    float alpha_TA  = ((alpha_dest - alpha_val) > 0.f) ? alpha_val : sat;
+                    for (int c = 0; c < C; ++c)
+                    {
+                        float g = alpha_TA * g_in[c];
+                        if (fg)
+                        {
+#pragma omp atomic
+                            g_texture[(size_t)c * sc->n_tex + tex] += (double)g;
+                        }
+                        else
+                            bg_local[c] += (double)g;
+                        g_alpha += colors[c] * g_in[c];
+                    }
+                    if (fg) conf_grad[idx] += g_alpha;
+                    if ((alpha_dest - alpha_val) < 0.f && alpha_dest > 0.f)
+                    {
+                        // the fragment that fills the pixel: its own gradient is dropped and the sum of its colours (not
+                        // weighted by the incoming gradient) is taken from every fragment before it.  (The reference
+                        // writes conf_gradients[idx] also for the background step after 16 records, one past the array.)
+                        if (idx < kMaxKeep) conf_grad[idx] = 0.f;
+                        for (int j = 0; j < idx; ++j)
+                        {
+                            float g_iter = 0.f;
+                            for (int c = 0; c < C; ++c) g_iter += colors[c];
+                            conf_grad[j] -= g_iter;
+                        }
+                    }
+                    alpha_dest = std::fmin(std::fmax(alpha_dest - alpha_val, 0.f), 1.f);
+                    if (!fg) break;
+                    ++idx;
+                    continue;
+                }
                 for (int c = 0; c < C; ++c)
                 {
                     float g = alpha_dest * alpha_val * g_in[c];
@@ -580,7 +686,9 @@ void or_backward(const OrFrame* f, const OrScene* sc, const OrView* view, const 
                     for (int k = 0; k < 4; ++k) bf[k] *= 0.f;
                 float conf = sc->confidence[tex];
                 float lf_grad = 0.f;
-                float lf      = layer_factor(ps, layer, L, &lf_grad);
+                // (the reference applies the factor whenever the size gradient is requested, RenderBackward.cu:366-372; without
+                // use_layer_point_size its forward pass stored no size to evaluate it with: no factor and no size gradient)
+                float lf      = pr->use_layer_point_size ? layer_factor(ps, layer, L, &lf_grad) : 1.f;
                 float g_conf  = bf[q] * lf * ga;
 #pragma omp atomic
                 g_confidence[tex] += (double)g_conf;
@@ -657,7 +765,6 @@ void or_backward(const OrFrame* f, const OrScene* sc, const OrView* view, const 
         for (int k = 0; k < 6; ++k) g_pose[k] += pose_acc[k];
     if (g_intrinsics)
         for (int k = 0; k < 5; ++k) g_intrinsics[k] += k_acc[k];
-    (void)pr;
 }
 
 // ---- A5: Adam (adam_step, MyAdam.cu:41-88) ----

@@ -49,6 +49,13 @@ typedef struct
     int viewer_only;
     float stability_cutoff_value;
     int bg_uses_Tn; /* 0 = reference behaviour (weight before the last kept fragment) */
+    /* The flags that select the reference's second forward pipeline (PointRenderer.cu:730-731: CountTiled,
+     * CollectTiled2[Pointsize], FastSortAndBlendWPrep2WarpSharedWork) when they differ from 1, 1, 0. */
+    int use_layer_point_size;                   /* 0: every layer is written, no layer factor */
+    int render_points_in_all_lower_resolutions; /* 0: only the two layers around log2(size) are written */
+    int combine_lists;                          /* 1: a pixel also draws from the lists of the coarser layers above it */
+    int saturated_alpha_accumulation;           /* forward: second pipeline only (RenderForward.cu:3524-3548; compiled out
+                                                   of the first, :908-935); backward: always (RenderBackward.cu:227-259) */
 } OrParams;
 
 typedef struct OrFrame OrFrame; /* all intermediates of one rendered view */
@@ -68,6 +75,7 @@ void or_layer_size(const OrFrame* f, int layer, int* w, int* h, int64_t* base);
 
 /* copy-outs; every pointer may be NULL */
 void or_get_points(const OrFrame* f, float* depth /*[N]*/, int32_t* nlayers /*[N]*/, float* rec /*[N,4] u v ps texidx-bits*/);
+void or_get_first_layer(const OrFrame* f, int32_t* first /*[N] first layer each point is written to*/);
 void or_get_lists(const OrFrame* f, int32_t* counts /*[P]*/, int64_t* offsets /*[P]*/, uint64_t* frags /*[F]*/);
 void or_get_pyramid(const OrFrame* f, float* out /*[sum_l C*H_l*W_l], layer-major, channel-planar*/);
 void or_get_records(const OrFrame* f, int32_t* nrec /*[P]*/, int32_t* rec_pid /*[P,16]*/, float* rec_alpha /*[P,16]*/);

@@ -55,6 +55,28 @@ def _variants():
     s.position[h:2 * h] = s.position[:h]
     s.point_size[h:2 * h] = s.point_size[:h]
     v["duplicate_points_depth_ties"] = (s, {}, None)
+    # ---- the reference's second forward pipeline (PointRenderer.cu:730-731), selected by its non-default flags ----
+    strict = dict(render_points_in_all_lower_resolutions=False)
+    v["second_strict_L8_odd_97x65"] = (scenes.tiny(num_layers=8, width=97, height=65, seed=41, size_range=(5e-3, 1.5)), dict(strict), None)
+    v["second_combine_lists"] = (scenes.tiny(seed=42, size_range=(5e-3, 0.4)), dict(combine_lists=True), None)
+    v["second_combine_strict_L6"] = (scenes.tiny(num_layers=6, seed=43, width=120, height=80, size_range=(5e-3, 1.0)),
+                                     dict(strict, combine_lists=True), None)
+    v["second_no_layer_point_size_L5"] = (scenes.tiny(seed=44, num_layers=5), dict(use_layer_point_size=False), None)
+    s = scenes.tiny(seed=45, n_points=6000, size_range=(0.05, 0.6))
+    s.confidence[:] = np.minimum(1.0, s.confidence * 3.0)  # alphas that sum past 1 within a few fragments
+    v["second_saturated_accumulation"] = (s, dict(combine_lists=True, saturated_alpha_accumulation=True), None)
+    s = scenes.tiny(seed=46, n_points=6000, size_range=(0.05, 0.6), channels=8)
+    s.confidence[:] = np.minimum(1.0, s.confidence * 3.0)
+    v["second_saturated_strict_C8_index"] = (s, dict(strict, saturated_alpha_accumulation=True),
+                                             np.random.default_rng(9).permutation(s.n_points).astype(np.int32))
+    # on the first pipeline the flag changes the backward pass only (its forward branch is compiled out, RenderForward.cu:908-935)
+    s = scenes.tiny(seed=47, n_points=6000, size_range=(0.05, 0.6))
+    s.confidence[:] = np.minimum(1.0, s.confidence * 3.0)
+    v["first_pipeline_saturated_backward"] = (s, dict(saturated_alpha_accumulation=True), None)
+    v["second_strict_drop_radius"] = (scenes.tiny(seed=48, size_range=(5e-3, 0.8)),
+                                      dict(strict, drop_out_points_by_radius=True, drop_out_radius_threshold=2.0), None)
+    v["second_combine_three_views_long_lists"] = (scenes.tiny(seed=49, n_points=20000, width=64, height=48, n_views=3),
+                                                  dict(combine_lists=True), None)
     # seeded random corners of the parameter space: K = 1 / 4, L = 2 / 5 / 6 / 7, odd image sizes, texture index, drop-out
     rr = np.random.default_rng(2024)
     for i in range(8):

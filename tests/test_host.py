@@ -49,19 +49,20 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
         _lib.lib()
 
 
-def test_renderer_needs_cuda_and_rejects_legacy_flags():
+def test_renderer_needs_cuda_and_rejects_unsupported_flags():
     import torch
     from trips_b200 import TripsError
     from trips_b200.renderer import PointRendererCache, RenderParams
     if not torch.cuda.is_available():
         with pytest.raises(RuntimeError, match="no CPU fallback"):
             PointRendererCache()
-    for kw in (dict(use_layer_point_size=False), dict(render_points_in_all_lower_resolutions=False), dict(combine_lists=True),
-               dict(saturated_alpha_accumulation=True), dict(check_normal=True)):
-        with pytest.raises(TripsError) as e:
-            PointRendererCache._check_live_path(RenderParams(**kw))
-        assert e.value.status == -4
-    PointRendererCache._check_live_path(RenderParams())
+    with pytest.raises(TripsError) as e:
+        PointRendererCache._check_live_path(RenderParams(check_normal=True))
+    assert e.value.status == -4
+    # the flags of the reference's second forward pipeline are accepted
+    for kw in (dict(), dict(use_layer_point_size=False), dict(render_points_in_all_lower_resolutions=False), dict(combine_lists=True),
+               dict(saturated_alpha_accumulation=True)):
+        PointRendererCache._check_live_path(RenderParams(**kw))
 
 
 def test_layer_sizes_are_ceil_halved():

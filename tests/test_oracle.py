@@ -167,6 +167,128 @@ def test_blend_closed_forms(oracle_lib):
         assert nrec[p] == 1 and pid[p, 1] == -1
 
 
+# ---- the reference's second forward pipeline (non-default flags; RenderForward.cu:1401-3674) ----
+def test_strict_two_layer_write(oracle_lib):
+    # fx = 1, raw = 24 (softplus passes it through): size_px = 24 / z.  512 x 512 image, central point.
+    L = 8
+    for z, first, layers in ((24.0, 0, 1), (8.0, 1, 2), (6.0, 2, 1), (4.8, 2, 2), (0.1, 7, 1)):
+        # size 1 -> {0}; 3 -> {1, 2}; 4 -> {2}; 5 -> {2, 3}; 240 -> {7} (both ends clamp to the coarsest layer)
+        f, _ = render([(0, 0, z)], [24.0], np.ones((4, 1)), [0.5], w=512, h=512, fx=1.0, L=L,
+                      render_points_in_all_lower_resolutions=False)
+        assert (f.first_layer()[0], f.points()[1][0]) == (first, layers), z
+        counts, _, _ = f.lists()
+        per_layer = [int(counts[b:b + w * h].sum()) for (w, h, b) in f.layers]
+        assert per_layer == [4 if first <= l < first + layers else 0 for l in range(L)]
+    # the default pipeline writes the same point to every layer up to the upper one
+    f, _ = render([(0, 0, 4.8)], [24.0], np.ones((4, 1)), [0.5], w=512, h=512, fx=1.0, L=L)
+    assert (f.first_layer()[0], f.points()[1][0]) == (0, 4)
+    # a footprint that leaves the lower layer drops the point from both layers; one that leaves only the upper keeps the lower
+    f, _ = render([(29.0, 0, 1.0)], [3.0], np.ones((4, 1)), [0.5], w=64, h=64, fx=1.0, L=6,
+                  render_points_in_all_lower_resolutions=False)  # u = 61, size 3: layers 1, 2; u_1 = 30.5 ok, u_2 = 15.25 -> 15 >= 15
+    assert (f.first_layer()[0], f.points()[1][0]) == (1, 1)
+    # without use_layer_point_size every layer is written and the alpha carries no layer factor
+    f, _ = render([(0.25, 0.5, 1.0)], [24.0], np.ones((4, 1)), [0.5], w=512, h=512, fx=1.0, L=4, use_layer_point_size=False)
+    assert (f.first_layer()[0], f.points()[1][0]) == (0, 4)
+    nrec, pid, alpha = f.records()
+    w1, h1, b1 = f.layers[1]
+    p = b1 + 128 * w1 + 128  # u = 256.25 / 2 = 128.125, v = 256.5 / 2 = 128.25
+    assert nrec[p] == 1 and alpha[p, 0] == np.float32(0.875 * 0.75 * 0.5)
+
+
+def test_second_pipeline_bilinear_weight_at_integer_coordinates(oracle_lib):
+    # u = 12 exactly: the first pipeline gives pixel 12 the weight (1 - 0) and pixel 13 the weight 0; the second evaluates
+    # the corner weights from the sub-pixel position and picks the corner by comparison, which gives 0 to both
+    fx, z = 100.0, 2.0
+    x, y = (12 - 32) * z / fx, (7.5 - 24) * z / fx
+    raw = float(scenes.inverse_softplus(np.array([1.0 * z / fx]))[0])
+    f1, _ = render([(x, y, z)], [raw], np.ones((4, 1)), [0.8], fx=fx)
+    f2, _ = render([(x, y, z)], [raw], np.ones((4, 1)), [0.8], fx=fx, combine_lists=True)
+    assert f1.points()[2][0, 0] == 12.0
+    a1, a2 = f1.records()[2], f2.records()[2]
+    p = 7 * 64 + 12
+    assert a1[p, 0] > 0.39 and a1[p + 1, 0] == 0.0
+    assert a2[p, 0] == 0.0 and a2[p + 1, 0] == 0.0
+
+
+def test_combine_lists_known_answer(oracle_lib):
+    # Point A (size 0.5 px, layer 0 only) and point B (size 3 px: layers 0, 1, 2) on a 64 x 64 image, 3 layers.  The pixel
+    # (10, 20) of layer 0 then holds A and B from its own list and B again from the lists of (5, 10) on layer 1 and
+    # (2, 5) on layer 2; all three copies of B carry the alpha of layer 0.
+    fx = 100.0
+    za, zb = 2.0, 3.0
+    A = ((10.25 - 32) * za / fx, (20.5 - 32) * za / fx, za)
+    B = ((10.5 - 32) * zb / fx, (20.25 - 32) * zb / fx, zb)
+    raws = [float(scenes.inverse_softplus(np.array([0.5 * za / fx]))[0]), float(scenes.inverse_softplus(np.array([3.0 * zb / fx]))[0])]
+    tex = np.array([[0.2, 0.9], [0.4, 0.7], [0.6, 0.5], [0.8, 0.3]], np.float32)
+    bg = np.array([0.25, 0.5, 0.75, 1.0], np.float32)
+    f, _ = render([A, B], raws, tex, [0.8, 0.6], w=64, h=64, fx=fx, L=3, bg=bg, combine_lists=True)
+    nrec, pid, alpha = f.records()
+    p = 20 * 64 + 10
+    assert nrec[p] == 4 and list(pid[p, :4]) == [0, 1, 1, 1]
+    ps = f.points()[2][:, 2]
+    aA = np.float32(0.75 * 0.5 * 0.8) * (np.float32(0.75) * np.float32(math.exp(ps[0] - 1)) + np.float32(0.25))
+    aB = np.float32(0.5 * 0.75 * 0.6)  # layer 0 is below the layers of a 3 px point: factor 1
+    np.testing.assert_allclose(alpha[p, :4], [aA, aB, aB, aB], rtol=1e-6)
+    T = [1.0, 1 - aA, (1 - aA) * (1 - aB), (1 - aA) * (1 - aB) ** 2]
+    expect = T[0] * aA * tex[:, 0] + sum(T[k] * aB * tex[:, 1] for k in (1, 2, 3)) + bg * T[3]
+    np.testing.assert_allclose(f.pyramid()[0][:, 20, 10], expect, rtol=3e-5)
+    # the coarsest layer has nothing above it: its pixel holds B once
+    w2, h2, b2 = f.layers[2]
+    q = b2 + 5 * w2 + 2
+    assert nrec[q] == 1 and pid[q, 0] == 1
+    # a coarse-layer fragment that is more than a pixel away on the fine layer is kept in the list with alpha 0
+    q0 = 21 * 64 + 8  # (8, 21) on layer 0 -> (4, 10) on layer 1, where B's footprint (5.25, 10.125) -> pixels 5..6 is absent; (2, 5) on layer 2 holds B
+    assert nrec[q0] == 1 and pid[q0, 0] == 1 and alpha[q0, 0] == 0.0
+    np.testing.assert_allclose(f.pyramid()[0][:, 21, 8], bg, rtol=1e-6)
+
+
+def test_saturated_accumulation_known_answer(oracle_lib):
+    # three fragments with alphas 0.5, 0.4, 0.3 on one pixel centre (integer coordinates are avoided: the second pipeline
+    # gives them the weight 0): u = 12.5, v = 7.5 -> four pixels with bilinear weight 0.25 each; size 1 px -> factor 1
+    fx = 100.0
+    zs = (2.0, 3.0, 4.0)
+    pts = [((12.5 - 32) * z / fx, (7.5 - 24) * z / fx, z) for z in zs]
+    raws = [float(scenes.inverse_softplus(np.array([1.0 * z / fx]))[0]) for z in zs]
+    tex = np.array([[0.2, 0.9, 0.1], [0.4, 0.7, 0.2], [0.6, 0.5, 0.3], [0.8, 0.3, 0.4]], np.float32)
+    bg = np.array([0.25, 0.5, 0.75, 1.0], np.float32)
+    conf = [1.0, 1.0, 1.0]
+    # bilinear 0.25 would make all alphas 0.25: scale with the texture-free knob we have, the confidence
+    conf = [2.0, 1.6, 1.2]  # alphas 0.5, 0.4, 0.3
+    f, _ = render(pts, raws, tex, conf, fx=fx, bg=bg, combine_lists=True, saturated_alpha_accumulation=True)
+    nrec, pid, alpha = f.records()
+    p = 7 * 64 + 12
+    ps = f.points()[2][:, 2]
+    a = [np.float32(0.25 * c) * (np.float32(0.75) * np.float32(math.exp(s - 1)) + np.float32(0.25)) for c, s in zip(conf, ps)]
+    np.testing.assert_allclose(alpha[p, :3], a, rtol=1e-6)
+    assert nrec[p] == 3
+    # weights: 1 (first), 1 (0.5 + 0.4 < 1), then the crossing fragment: 1 / (alpha + 1e-9); background sees the last weight
+    w = [1.0, 1.0, 1.0 / (float(a[2]) + 1e-9)]
+    expect = sum(w[k] * a[k] * tex[:, k] for k in range(3)) + bg * w[2]
+    np.testing.assert_allclose(f.pyramid()[0][:, 7, 12], expect, rtol=3e-5)
+    # backward as written (RenderBackward.cu:227-259): texture gradients weighted by alpha, alpha, and the remainder;
+    # the crossing fragment's own alpha gradient is dropped and the sum of its colours is taken from the ones before it
+    g = np.zeros(4 * f.P, np.float32)
+    gin = np.array([0.3, -0.2, 0.5, 0.1], np.float32)
+    for c in range(4):
+        g[c * 64 * 48 + p] = gin[c]
+    out = f.backward(g)
+    rest = 1.0 - float(a[0]) - float(a[1])
+    np.testing.assert_allclose(out["texture"][:, 0], float(a[0]) * gin, rtol=1e-5)
+    np.testing.assert_allclose(out["texture"][:, 1], float(a[1]) * gin, rtol=1e-5)
+    np.testing.assert_allclose(out["texture"][:, 2], rest * gin, rtol=1e-4)
+    assert np.all(out["background"] == 0.0)  # nothing is left for the background
+    s2 = float(tex[:, 2].sum())
+    lf = [float(x) / (0.25 * c) for x, c in zip(a, conf)]
+    # (that colour sum is not weighted by the incoming gradient: the three other pixels of the footprint, whose incoming
+    # gradient is zero, subtract it as well)
+    expect_conf = [0.25 * lf[0] * (float(tex[:, 0] @ gin) - 4 * s2), 0.25 * lf[1] * (float(tex[:, 1] @ gin) - 4 * s2), 0.0]
+    np.testing.assert_allclose(out["confidence"], expect_conf, rtol=1e-4, atol=1e-7)
+    # on the first pipeline the forward pass ignores the flag (its branch is compiled out, RenderForward.cu:908-935)
+    f1, _ = render(pts, raws, tex, conf, fx=fx, bg=bg, saturated_alpha_accumulation=True)
+    f0, _ = render(pts, raws, tex, conf, fx=fx, bg=bg)
+    assert np.array_equal(f1.pyramid_flat(), f0.pyramid_flat())
+
+
 def test_top_k_keeps_the_nearest_with_index_ties(oracle_lib):
     # 40 points on one pixel centre, several at identical depth: kept = 16 smallest (depth, id)
     rng = np.random.default_rng(0)

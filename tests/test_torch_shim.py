@@ -24,6 +24,7 @@ def test_shim_registers_class_and_operator(shim):
     assert info.last_status() == 0  # no context yet: nothing raised
     assert hasattr(torch.ops.trips_b200, "blend_point_cloud") and hasattr(torch.ops.trips_b200, "adam_step")
     info.set_texture_preparation(True, 10.0, True)
+    info.set_pipeline_flags(True, False, True, False)
     assert torch.classes.trips_b200.PointRenderModule(4) is not None
     opt = torch.classes.trips_b200.MyAdam()
     with pytest.raises(RuntimeError):
@@ -32,8 +33,11 @@ def test_shim_registers_class_and_operator(shim):
         info.add_image(96, 64, 0, 0, 0, [1.0], [1.0, 0.0, 0.0, 1.0])
 
 
+# (use_layer_point_size, render_points_in_all_lower_resolutions, combine_lists, saturated_alpha_accumulation): the
+# reference's defaults, and a combination that selects its second forward pipeline
 @pytest.mark.gpu
-def test_shim_matches_python_mirror(shim, cuda_lib):
+@pytest.mark.parametrize("flags", [(True, True, False, False), (True, False, True, True)], ids=["first_pipeline", "second_pipeline"])
+def test_shim_matches_python_mirror(shim, cuda_lib, flags):
     torch = shim
     from trips_b200 import scenes
     from trips_b200.modules import NeuralScene, images_for
@@ -48,8 +52,10 @@ def test_shim_matches_python_mirror(shim, cuda_lib):
 
     # Python mirror
     ns = NeuralScene.from_synthetic(s, device=dev)
-    info = NeuralRenderInfo(scene=ns, images=images_for(s, [0, 1]), params=RenderParams(num_texture_channels=s.channels, k_keep=s.k_keep),
-                            num_layers=s.num_layers, train=True, cache=PointRendererCache(dev))
+    params = RenderParams(num_texture_channels=s.channels, k_keep=s.k_keep, use_layer_point_size=flags[0],
+                          render_points_in_all_lower_resolutions=flags[1], combine_lists=flags[2], saturated_alpha_accumulation=flags[3])
+    info = NeuralRenderInfo(scene=ns, images=images_for(s, [0, 1]), params=params, num_layers=s.num_layers, train=True,
+                            cache=PointRendererCache(dev))
     outs = BlendPointCloud(info)
     gen = torch.Generator(device=dev)
     gen.manual_seed(3)
@@ -68,6 +74,7 @@ def test_shim_matches_python_mirror(shim, cuda_lib):
         cinfo.add_image(im.w, im.h, im.image_index, im.camera_index, im.camera_model_type, [float(x) for x in im.crop_transform],
                         [float(x) for x in im.crop_rotation])
     cinfo.set_params(s.num_layers, s.k_keep, True, False, 0.0, False, 0.0, False, 0.0)
+    cinfo.set_pipeline_flags(*flags)
     couts = torch.ops.trips_b200.blend_point_cloud(cinfo)  # BlendPointCloud(NeuralRenderInfo*), RenderInfo.cpp:27
     assert cinfo.last_status() == 0
     assert len(couts) == len(ref_out)

@@ -50,7 +50,9 @@ class TripsView(C.Structure):
 class TripsRenderParams(C.Structure):
     _fields_ = [("num_layers", C.c_int), ("k_keep", C.c_int), ("train", C.c_int), ("drop_out_points_by_radius", C.c_int),
                 ("drop_out_radius_threshold", C.c_float), ("viewer_only", C.c_int), ("stability_cutoff_value", C.c_float),
-                ("bg_uses_Tn", C.c_int), ("confidence_is_raw", C.c_int), ("confidence_scale", C.c_float), ("texture_abs", C.c_int)]
+                ("bg_uses_Tn", C.c_int), ("confidence_is_raw", C.c_int), ("confidence_scale", C.c_float), ("texture_abs", C.c_int),
+                ("use_layer_point_size", C.c_int), ("render_points_in_all_lower_resolutions", C.c_int), ("combine_lists", C.c_int),
+                ("saturated_alpha_accumulation", C.c_int)]
 
 
 class TripsGrads(C.Structure):
@@ -97,6 +99,8 @@ SYMBOLS = {
     "trips_fused_reduce_adam": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.c_int, C.c_int,
                                           C.POINTER(TripsAdamSegment), C.c_int, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p,
                                           C.c_void_p, C.c_void_p]),
+    "trips_fused_reduce_adam_multicast": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(TripsAdamSegment), C.c_int,
+                                                    C.c_int64, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "trips_resize_points": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.POINTER(TripsPointTensor), C.c_int, C.c_void_p]),
     "trips_adam_step_static": (C.c_int, [C.POINTER(TripsAdamTensor), C.c_int, C.c_void_p]),
     "trips_enable_stage_timers": (C.c_int, [C.c_void_p, C.c_int]),

@@ -18,7 +18,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libtrips_b200.so")
-SOURCES = ["forward.cu", "backward.cu", "adam.cu", "rank.cu", "resize.cu", "capi.cu", "noalloc.cu"]
+SOURCES = ["forward.cu", "second.cu", "backward.cu", "adam.cu", "rank.cu", "resize.cu", "capi.cu", "noalloc.cu"]
 HEADERS = ["common.cuh", "trips_math.h", os.path.join("..", "..", "include", "trips_b200.h")]
 
 NVCC_FLAGS = [

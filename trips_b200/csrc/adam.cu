@@ -228,6 +228,110 @@ cudaError_t launch_fused_reduce_adam(const float* const* grad_ptrs, float* const
     return cudaGetLastError();
 }
 
+// ------------------------------------------------------------------------------------------------------------
+// The same step through NVSwitch multicast addresses (multimem): the gradient buffers of all ranks are bound to one
+// multicast object and so are the parameter replicas.  A rank fetches its slice of the gradient with
+// multimem.ld_reduce (the switch reads the 16 bytes from every GPU and returns their sum) and writes the new weights
+// with multimem.st (one store, delivered to every replica).  Per GPU and direction the links then carry the slice
+// once per peer for the reduction plus once for the broadcast, half of what the peer-pointer kernel above moves
+// (which also sends every new weight to each peer separately and receives each peer's partial gradients separately);
+// with 8 ranks that kernel sits at the link bandwidth.  The switch adds in an order of its own, so weights equal the
+// peer-pointer kernel's bit for bit only with two ranks; every replica receives the owner's bits, so replicas stay
+// identical with any number of ranks.  Ordering is the caller's, as above; the kernel waits on nothing.
+// ------------------------------------------------------------------------------------------------------------
+struct McArgs
+{
+    const float* grad_mc;   // multicast address of the flat gradient buffers
+    float* param_mc;        // multicast address of the flat parameter replicas
+    const float* param;     // this rank's replica
+    TripsAdamSegment seg[TRIPS_MAX_SEGMENTS];
+    int n_seg;
+    int64_t lo, hi;
+};
+
+__device__ __forceinline__ float4 multimem_sum4(const float* mc)
+{
+    float4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                 : "l"(mc)
+                 : "memory");
+    return v;
+}
+__device__ __forceinline__ void multimem_store4(float* mc, const float4& v)
+{
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
+
+__global__ __launch_bounds__(256) void fused_multicast_adam_kernel(const __grid_constant__ McArgs a, float* __restrict__ m_state,
+                                                                   float* __restrict__ v_state, int32_t* __restrict__ steps)
+{
+    // [lo, hi) is a whole number of 16-byte vectors (checked by the host)
+    const int64_t n_vec = (a.hi - a.lo) >> 2;
+    auto segment_of = [&](int64_t i) {
+        int k = 0;
+        for (int s = 1; s < a.n_seg; ++s)
+            if (i >= a.seg[s].offset) k = s;
+        return k;
+    };
+    LrCache cache;
+    int cache_seg = -1;
+    // kMcUnroll reductions per thread are in flight before the first is used: a multimem.ld_reduce is a round trip through
+    // the switch to every GPU, several times the latency of a peer load
+    constexpr int kMcUnroll = 4;
+    const int64_t stride    = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t q0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; q0 < n_vec; q0 += stride * kMcUnroll)
+    {
+        float4 gs[kMcUnroll];
+#pragma unroll
+        for (int u = 0; u < kMcUnroll; ++u)
+            gs[u] = (q0 + u * stride < n_vec) ? multimem_sum4(a.grad_mc + a.lo + 4 * (q0 + u * stride)) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int u = 0; u < kMcUnroll; ++u)
+        {
+            const int64_t q = q0 + u * stride;
+            if (q >= n_vec) break;
+            const int64_t i = a.lo + 4 * q;
+            const float4 g  = gs[u];
+            if (g.x == 0.f && g.y == 0.f && g.z == 0.f && g.w == 0.f) continue;  // unseen on every rank: nothing moves anywhere
+            const int64_t j = i - a.lo;
+            const float4 w  = *reinterpret_cast<const float4*>(a.param + i);
+            float gg[4]     = {g.x, g.y, g.z, g.w};
+            float ww[4]     = {w.x, w.y, w.z, w.w};
+            float mm[4], vv[4];
+            int ss[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) mm[k] = m_state[j + k], vv[k] = v_state[j + k], ss[k] = steps[j + k];
+            const int s0 = segment_of(i), s3 = segment_of(i + 3);
+            if (s0 != s3 || s0 != cache_seg) cache.step = -1;  // the cached learning rate belongs to one segment
+            cache_seg = s3;
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+            {
+                if (k > 0 && s0 != s3) cache.step = -1;
+                fused_element(a.seg[s0 == s3 ? s0 : segment_of(i + k)], ww[k], gg[k], mm[k], vv[k], ss[k], cache);
+            }
+#pragma unroll
+            for (int k = 0; k < 4; ++k) m_state[j + k] = mm[k], v_state[j + k] = vv[k], steps[j + k] = ss[k];
+            multimem_store4(a.param_mc + i, make_float4(ww[0], ww[1], ww[2], ww[3]));
+        }
+    }
+}
+
+cudaError_t launch_fused_multicast_adam(const float* grad_mc, float* param_mc, const float* param, const TripsAdamSegment* segs, int n_seg,
+                                        int64_t lo, int64_t hi, float* m_state, float* v_state, int32_t* steps, int sm_count, cudaStream_t st)
+{
+    if (hi <= lo) return cudaSuccess;
+    McArgs a{};
+    a.grad_mc = grad_mc, a.param_mc = param_mc, a.param = param;
+    for (int s = 0; s < n_seg; ++s) a.seg[s] = segs[s];
+    a.n_seg = n_seg, a.lo = lo, a.hi = hi;
+    const int64_t n_vec = (hi - lo) / 4;
+    const int blocks    = (int)max((int64_t)1, min((int64_t)sm_count * 8, (n_vec + 255) / 256));
+    fused_multicast_adam_kernel<<<blocks, 256, 0, st>>>(a, m_state, v_state, steps);
+    return cudaGetLastError();
+}
+
 // L1 loss against a target pyramid and its gradient, all layers in one launch (benchmark helper).
 __global__ __launch_bounds__(256) void l1_loss_kernel(const __grid_constant__ L1Args a, int64_t total, float inv_total,
                                                       double* __restrict__ loss_out)

@@ -62,7 +62,9 @@ constexpr int kBwdWarps   = kBwdThreads / 32;
 constexpr int kBwdBlocksPerSM = 12;  // grid size of the persistent kernel, in blocks per SM
 // measured: 5 resident blocks (96 registers) 3.59 ms, 4 blocks (108) 3.63 ms, 6 blocks (80) 3.76 ms
 constexpr int kBwdMinBlocks = 5;
-template <int C>
+// SAT: saturated_alpha_accumulation as the reference's backward pass has it (RenderBackward.cu:227-259); a separate
+// instantiation, so that the common case carries none of its code or registers.
+template <int C, bool SAT>
 __global__ __launch_bounds__(kBwdThreads, (C <= 4 ? kBwdMinBlocks : 1)) void blend_backward_kernel(ScenePtrs sc, const CamConst* __restrict__ cams,
                                                                      const __grid_constant__ Geom g, TripsRenderParams pr, int B,
                                                                      FwdBuffers fb, BwdBuffers bb,
@@ -72,6 +74,7 @@ __global__ __launch_bounds__(kBwdThreads, (C <= 4 ? kBwdMinBlocks : 1)) void ble
     constexpr int GS = egrad_stride(C);
     __shared__ float s_g[kBwdWarps][C][32];
     __shared__ float s_d[kBwdWarps][32 * kPad];   // G_j, then dA_j = G_j T_j, finally d_j
+    __shared__ float s_sum[SAT ? kBwdWarps : 1][SAT ? 32 * kPad : 1];  // SAT: sum of the descriptor channels of fragment j
     __shared__ uint16_t s_map[kBwdWarps][32 * 16];
     __shared__ uint2 s_rec[kBwdWarps][32 * kPad]; // the tile's records: (entry index, alpha_j bits; after phase 1: w_j = T_j * alpha_j)
     const int lane = threadIdx.x & 31;
@@ -210,6 +213,20 @@ __global__ __launch_bounds__(kBwdThreads, (C <= 4 ? kBwdMinBlocks : 1)) void ble
                         if (c + 3 < C) G += v4.w * s_g[warp][c + 3][seg];
                     }
                     s_d[warp][j] = G;
+                    if constexpr (SAT)
+                    {
+                        float S = 0.f;
+#pragma unroll
+                        for (int c = 0; c < C; c += 4)
+                        {
+                            const float4 v4 = row[c / 4];
+                            S += v4.x;
+                            if (c + 1 < C) S += v4.y;
+                            if (c + 2 < C) S += v4.z;
+                            if (c + 3 < C) S += v4.w;
+                        }
+                        s_sum[warp][j] = S;
+                    }
                 }
             }
         }
@@ -218,6 +235,56 @@ __global__ __launch_bounds__(kBwdThreads, (C <= 4 ? kBwdMinBlocks : 1)) void ble
         // ---- phase 1 (lane = pixel), forward: T_j, dA_j = G_j T_j, w_j = T_j a_j.  The alphas move to registers (the
         //      reverse sweep needs them again) and w_j takes their place in shared memory. ----
         float run = 1.f;
+        if constexpr (SAT)
+        {
+            // RenderBackward.cu:227-259 as written.  alpha_dest starts at 1 and loses every alpha; a fragment's texture
+            // gradient is weighted by its alpha while alpha_dest - alpha > 0, else by what is left (the fragment that
+            // fills the pixel).  d_j starts as G_j = <colour_j, g>; the filling fragment's own d is dropped and the sum
+            // of its colour channels (not weighted by g) is taken from every fragment before it.  After the filling
+            // fragment alpha_dest is 0 and the replay ends, so this happens at most once per pixel, possibly for the
+            // background step (colour = background, alpha = 1).
+            float* my_sum = s_sum[warp] + lane * kPad;
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+            {
+                if (j >= m_max) continue;  // uniform
+                if (j < m && run < kAlphaCut)
+                {
+                    // the replay ends where alpha_dest falls below the cut-off (RenderBackward.cu:308); records behind that
+                    // point exist when the forward pass blended by transmittance, which falls more slowly
+                    my_rec[j].y = 0u;
+                    my_d[j]     = 0.f;
+                }
+                else if (j < m)
+                {
+                    const float a    = __uint_as_float(my_rec[j].y);
+                    const bool fill  = (run - a) < 0.f && run > 0.f;
+                    my_rec[j].y      = __float_as_uint((run - a) > 0.f ? a : __saturatef(run));
+                    if (fill)
+                    {
+                        const float S = my_sum[j];
+                        my_d[j]       = 0.f;
+                        for (int i = 0; i < j; ++i) my_d[i] -= S;
+                    }
+                    run = __saturatef(run - a);
+                }
+            }
+            if (p >= 0 && run >= kAlphaCut)
+            {
+                // background step: alpha 1, weight saturate(alpha_dest); it fills the pixel whenever alpha_dest < 1
+                float S = 0.f;
+#pragma unroll
+                for (int c = 0; c < C; ++c)
+                {
+                    acc_bg[c] += (double)(((run - 1.f) > 0.f ? 1.f : __saturatef(run)) * gin[c]);
+                    S += bg[c];
+                }
+                if ((run - 1.f) < 0.f && run > 0.f)
+                    for (int i = 0; i < m; ++i) my_d[i] -= S;
+            }
+        }
+        else
+        {
         float al[16];
 #pragma unroll
         for (int j = 0; j < 16; ++j)
@@ -256,6 +323,7 @@ __global__ __launch_bounds__(kBwdThreads, (C <= 4 ? kBwdMinBlocks : 1)) void ble
                 my_d[j]         = dA - R * dem;
                 R += dA * a;
             }
+        }
         }
         __syncwarp();
 
@@ -302,7 +370,8 @@ __global__ __launch_bounds__(kBwdThreads, (C <= 4 ? kBwdMinBlocks : 1)) void ble
                 const float J1 = (q & 2) ? ((q & 1) ? sx : (1.f - sx)) : ((q & 1) ? -sx : (sx - 1.f));
                 if (fabsf(ux - (float)gx_s) > 1.f || fabsf(uy - (float)gy_s) > 1.f) bf *= 0.f;
                 float lf_grad   = 0.f;
-                const float lf  = layer_factor<true>(ps, layer_s, g.L, &lf_grad);
+                // (without use_layer_point_size the forward pass applied no layer factor: none here, and no size gradient)
+                const float lf  = pr.use_layer_point_size ? layer_factor<true>(ps, layer_s, g.L, &lf_grad) : 1.f;
                 const float gbs = conf * lf * ga;  // dLoss / d(bilinear weight) (RenderBackward.cu:385)
                 // image-space sums of the entry: the chain to position / size / pose is linear in them and is applied
                 // once per entry by entry_grad_finish_kernel
@@ -375,7 +444,10 @@ cudaError_t launch_blend_backward(const ScenePtrs& sc, const CamConst* cams, con
     const int grid = (int)max(1u, min((unsigned)(sm_count * kBwdBlocksPerSM), ((unsigned)g.n_tiles * (unsigned)B + kBwdWarps - 1) / kBwdWarps));
 #define TRIPS_BWD_CASE(CC)                                                                                         \
     case CC:                                                                                                       \
-        blend_backward_kernel<CC><<<grid, kBwdThreads, 0, st>>>(sc, cams, g, pr, B, fb, bb, grad_in);             \
+        if (pr.saturated_alpha_accumulation)                                                                       \
+            blend_backward_kernel<CC, true><<<grid, kBwdThreads, 0, st>>>(sc, cams, g, pr, B, fb, bb, grad_in);   \
+        else                                                                                                       \
+            blend_backward_kernel<CC, false><<<grid, kBwdThreads, 0, st>>>(sc, cams, g, pr, B, fb, bb, grad_in);  \
         break;
     switch (sc.C)
     {

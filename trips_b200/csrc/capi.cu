@@ -106,7 +106,11 @@ struct StageTimers
 struct SizeKey
 {
     int N, B, w, h, L, C, train;
-    bool operator==(const SizeKey& o) const { return N == o.N && B == o.B && w == o.w && h == o.h && L == o.L && C == o.C && train == o.train; }
+    int layer_rule;  // which layers a point is written to (use_layer_point_size, render_points_in_all_lower_resolutions): changes the fragment count
+    bool operator==(const SizeKey& o) const
+    {
+        return N == o.N && B == o.B && w == o.w && h == o.h && L == o.L && C == o.C && train == o.train && layer_rule == o.layer_rule;
+    }
 };
 
 struct TripsContext
@@ -469,7 +473,7 @@ static int forward_views(TripsContext* ctx, const TripsScene* scene, const Trips
         fb           = fwd_buffers(ctx);
     }
     STAGE(ctx, TRIPS_STAGE_BIN_POINTS, bin_scatter_launches((int)N, B), st, launch_bin_scatter(sp, cams, g, *params, B, fb, ctx->crowded, ctx->sm_count, st));
-    if (N > 0) STAGE(ctx, TRIPS_STAGE_COUNT, 1, st, launch_count(sp, g, B, fb, ctx->sm_count, st));
+    if (N > 0) STAGE(ctx, TRIPS_STAGE_COUNT, 1, st, launch_count(sp, g, B, fb, strict_layers(*params), ctx->sm_count, st));
     {
         FwdBuffers fscan = fb;
         if (wait_for_sizes) fscan.frag_cap = ~0ull;  // sizing pass: the list buffer is grown below, nothing can overflow yet
@@ -497,13 +501,16 @@ static int forward_views(TripsContext* ctx, const TripsScene* scene, const Trips
         CU_CHECK(ctx, cudaEventRecord(ctx->totals_ev, st));
         ctx->pending = true;
     }
-    if (N > 0) STAGE(ctx, TRIPS_STAGE_COLLECT, 1, st, launch_collect(sp, g, B, fb, ctx->sm_count, st));
+    if (N > 0) STAGE(ctx, TRIPS_STAGE_COLLECT, 1, st, launch_collect(sp, g, B, fb, strict_layers(*params), ctx->sm_count, st));
     LayerPtrs out{};
     for (int l = 0; l < g.L; ++l) out.p[l] = out_layers[l] + out_view_offset * (size_t)C * g.W[l] * g.H[l];
-    STAGE(ctx, TRIPS_STAGE_SORT_BLEND, 2, st, [&]() -> cudaError_t {
-        cudaError_t e = launch_heavy_topk(g, B, fb, ctx->sm_count, st);
-        return e != cudaSuccess ? e : launch_sort_blend(sp, g, *params, B, fb, out, ctx->sm_count, st);
-    }());
+    if (second_pipeline(*params))
+        STAGE(ctx, TRIPS_STAGE_SORT_BLEND, 1, st, launch_second_blend(sp, g, *params, B, fb, out, ctx->sm_count, st));
+    else
+        STAGE(ctx, TRIPS_STAGE_SORT_BLEND, 2, st, [&]() -> cudaError_t {
+            cudaError_t e = launch_heavy_topk(g, B, fb, ctx->sm_count, st);
+            return e != cudaSuccess ? e : launch_sort_blend(sp, g, *params, B, fb, out, ctx->sm_count, st);
+        }());
     ctx->B       = B;
     ctx->nchunks = nchunks;
     return TRIPS_OK;
@@ -548,7 +555,8 @@ int trips_forward(TripsContext* ctx, const TripsScene* scene, const TripsView* v
     if (N * 4ull * g.L >= (1ull << 32)) return fail(ctx, TRIPS_ERR_TOO_LARGE, "a view could hold more than 2^32 fragments");
     if ((unsigned long long)B * (unsigned long long)g.n_tiles >= (1ull << 32)) return fail(ctx, TRIPS_ERR_TOO_LARGE, "too many pixel tiles");
 
-    const SizeKey key{scene->n_points, B, w, h, params->num_layers, scene->channels, params->train};
+    const SizeKey key{scene->n_points, B, w, h, params->num_layers, scene->channels, params->train,
+                      (params->use_layer_point_size ? 1 : 0) | (params->render_points_in_all_lower_resolutions ? 2 : 0)};
     ctx->host_stats        = TripsStats{};
     ctx->host_stats.pixels = (int64_t)g.P * B;
     ctx->geom              = g;
@@ -744,6 +752,26 @@ int trips_fused_reduce_adam(TripsContext* ctx, const float* const* grad_ptrs, fl
     STAGE(ctx, TRIPS_STAGE_FUSED_ADAM, hi > lo ? 1 : 0, st,
           launch_fused_reduce_adam(grad_ptrs, param_ptrs, world, rank, segments, n_segments, lo, hi, first_moments, second_moments,
                                    steps, ctx->sm_count, st));
+    return TRIPS_OK;
+}
+
+int trips_fused_reduce_adam_multicast(TripsContext* ctx, const float* grad_multicast, float* param_multicast, const float* param_local,
+                                      const TripsAdamSegment* segments, int n_segments, int64_t lo, int64_t hi, float* first_moments,
+                                      float* second_moments, int32_t* steps, void* stream)
+{
+    if (!ctx) return TRIPS_ERR_INVALID_ARG;
+    if (!grad_multicast || !param_multicast || !param_local || !segments) return fail(ctx, TRIPS_ERR_INVALID_ARG, "null argument");
+    if (n_segments < 1 || n_segments > TRIPS_MAX_SEGMENTS || segments[0].offset != 0) return fail(ctx, TRIPS_ERR_INVALID_ARG, "bad segment table");
+    for (int s = 1; s < n_segments; ++s)
+        if (segments[s].offset <= segments[s - 1].offset) return fail(ctx, TRIPS_ERR_INVALID_ARG, "segments must be sorted by offset");
+    if (lo < 0 || hi < lo || ((lo | hi) & 3)) return fail(ctx, TRIPS_ERR_INVALID_ARG, "the slice must start and end on a multiple of 4 elements");
+    if (((uintptr_t)grad_multicast | (uintptr_t)param_multicast | (uintptr_t)param_local) & 15)
+        return fail(ctx, TRIPS_ERR_INVALID_ARG, "flat buffers must be 16-byte aligned");
+    if (hi > lo && (!first_moments || !second_moments || !steps)) return fail(ctx, TRIPS_ERR_INVALID_ARG, "null optimizer state");
+    cudaStream_t st = (cudaStream_t)stream;
+    STAGE(ctx, TRIPS_STAGE_FUSED_ADAM, hi > lo ? 1 : 0, st,
+          launch_fused_multicast_adam(grad_multicast, param_multicast, param_local, segments, n_segments, lo, hi, first_moments,
+                                      second_moments, steps, ctx->sm_count, st));
     return TRIPS_OK;
 }
 

@@ -135,6 +135,18 @@ struct BwdBuffers
     double* g_k;          // [B,5]
 };
 
+// The reference has two forward pipelines (PointRenderer.cu:730-731): the second (CountTiled, CollectTiled2[Pointsize],
+// FastSortAndBlendWPrep2WarpSharedWork, RenderForward.cu:1401-3674) runs when one of these flags differs from its
+// default.  strict_layers: a point is written to the two layers around log2(size) only (RenderForward.cu:2291-2393).
+__host__ __device__ inline bool second_pipeline(const TripsRenderParams& pr)
+{
+    return !(pr.use_layer_point_size && pr.render_points_in_all_lower_resolutions && !pr.combine_lists);
+}
+__host__ __device__ inline bool strict_layers(const TripsRenderParams& pr)
+{
+    return pr.use_layer_point_size && !pr.render_points_in_all_lower_resolutions;
+}
+
 // ---- device helpers (op order mirrors the CPU oracle; compiled with -fmad=false) ----
 
 __device__ __forceinline__ void transform_point(const CamConst& V, float px, float py, float pz, float& ox, float& oy,
@@ -266,8 +278,12 @@ size_t rank_temp_bytes(int N);
 cudaError_t launch_point_rank(const float4* position, int N, unsigned* scratch, void* temp, size_t temp_bytes, unsigned* rank,
                               int sm_count, cudaStream_t st);
 cudaError_t launch_scan(const Geom& g, int B, int k_keep, const FwdBuffers& fb, int nchunks, cudaStream_t st);
-cudaError_t launch_count(const ScenePtrs& sc, const Geom& g, int B, const FwdBuffers& fb, int sm_count, cudaStream_t st);
-cudaError_t launch_collect(const ScenePtrs& sc, const Geom& g, int B, const FwdBuffers& fb, int sm_count, cudaStream_t st);
+// strict: an entry's layers start at the layer below log2(size) instead of layer 0 (strict_layers above)
+cudaError_t launch_count(const ScenePtrs& sc, const Geom& g, int B, const FwdBuffers& fb, bool strict, int sm_count, cudaStream_t st);
+cudaError_t launch_collect(const ScenePtrs& sc, const Geom& g, int B, const FwdBuffers& fb, bool strict, int sm_count, cudaStream_t st);
+// top-K + blend by the rules of the reference's second forward pipeline (one thread per pixel)
+cudaError_t launch_second_blend(const ScenePtrs& sc, const Geom& g, const TripsRenderParams& pr, int B, const FwdBuffers& fb,
+                                const LayerPtrs& out, int sm_count, cudaStream_t st);
 cudaError_t launch_heavy_topk(const Geom& g, int B, const FwdBuffers& fb, int sm_count, cudaStream_t st);
 cudaError_t launch_sort_blend(const ScenePtrs& sc, const Geom& g, const TripsRenderParams& pr, int B, const FwdBuffers& fb,
                               const LayerPtrs& out, int sm_count, cudaStream_t st);
@@ -282,6 +298,8 @@ cudaError_t launch_adam(const TripsAdamTensor* d_tensors, const int64_t* d_block
 cudaError_t launch_fused_reduce_adam(const float* const* grad_ptrs, float* const* param_ptrs, int world, int rank,
                                      const TripsAdamSegment* segs, int n_seg, int64_t lo, int64_t hi, float* m_state,
                                      float* v_state, int32_t* steps, int sm_count, cudaStream_t st);
+cudaError_t launch_fused_multicast_adam(const float* grad_mc, float* param_mc, const float* param, const TripsAdamSegment* segs, int n_seg,
+                                        int64_t lo, int64_t hi, float* m_state, float* v_state, int32_t* steps, int sm_count, cudaStream_t st);
 struct L1Args
 {
     const float* out[TRIPS_MAX_LAYERS];

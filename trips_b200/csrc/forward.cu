@@ -105,7 +105,8 @@ __device__ __forceinline__ Projected project_visible(const CamConst& cam, const 
     r.rad = fxc * p.w / r.z;
     r.ps  = 0.f;
     bool ok = !(r.z <= 0.f || r.u < 0.f || r.u >= (float)(g.W[0] - 1) || r.v < 0.f || r.v >= (float)(g.H[0] - 1));
-    if (ok && pr.drop_out_points_by_radius && (float)(int)r.rad < pr.drop_out_radius_threshold) ok = false;
+    // the first pipeline's test takes an int (RenderForward.cu:212-218), the second's the float (RenderForward.cu:1527-1531)
+    if (ok && pr.drop_out_points_by_radius && (second_pipeline(pr) ? r.rad : (float)(int)r.rad) < pr.drop_out_radius_threshold) ok = false;
     if (ok)
     {
         if (sp < 0.f) sp = tm_softplus(raw);
@@ -440,19 +441,30 @@ __device__ __forceinline__ void write_entry(const FwdBuffers& fb, const Geom& g,
 {
     constexpr int TS = tail_stride(C);
     constexpr int C4 = PointRow<C>::C4;
-    // layers 0..hi, stopping where the 2x2 footprint leaves the layer (RenderForward.cu:342-363)
-    int hi = 0;
-    if (r.ps > 1.f) hi = min(tm_ceil_log2(r.ps), g.L - 1);
-    int layer = 0;
-    float x = r.u, y = r.v, rad = r.rad;
+    // layers first..hi, stopping where the 2x2 footprint leaves the layer (RenderForward.cu:342-363).  first = 0 except for
+    // the strict write of the second pipeline, which starts at the layer below log2(size) (RenderForward.cu:2291-2393);
+    // without use_layer_point_size every layer is written (RenderForward.cu:1611-1631).  The entry stores the NUMBER of
+    // layers; the first layer of a strict entry is recomputed from its size where needed (strict_first_layer).
+    int hi = 0, first = 0;
+    if (!pr.use_layer_point_size)
+        hi = g.L - 1;
+    else if (r.ps > 1.f)
+    {
+        hi = min(tm_ceil_log2(r.ps), g.L - 1);
+        if (!pr.render_points_in_all_lower_resolutions) first = min(tm_floor_log2(r.ps), g.L - 1);
+    }
+    const bool second = second_pipeline(pr);
+    const float sc0   = __int_as_float((127 - first) << 23);  // 2^-first
+    int layer = first;
+    float x = r.u * sc0, y = r.v * sc0, rad = r.rad * sc0;
     for (; layer < hi + 1; ++layer, x *= 0.5f, y *= 0.5f, rad *= 0.5f)
     {
         const int px = __float2int_rd(x), py = __float2int_rd(y);
         if (px < 0 || px >= g.W[layer] - 1 || py < 0 || py >= g.H[layer] - 1) break;
-        if (pr.drop_out_points_by_radius && (float)(int)rad < pr.drop_out_radius_threshold) break;
+        if (pr.drop_out_points_by_radius && (second ? rad : (float)(int)rad) < pr.drop_out_radius_threshold) break;
     }
     store_entry_head(fb.ent_head + at * 2, make_float4(r.u, r.v, r.ps, d.conf),
-                     make_float4(__int_as_float(i), r.z, raw, __uint_as_float((uint32_t)layer | (d.rk << kRankShift))));
+                     make_float4(__int_as_float(i), r.z, raw, __uint_as_float((uint32_t)(layer - first) | (d.rk << kRankShift))));
     float4* e = reinterpret_cast<float4*>(fb.ent_tail + at * TS);
     if constexpr (C4 == 4)
         store_entry_head(e, make_float4(p.x, p.y, p.z, __int_as_float(d.tex_ok ? d.tex : -1)), make_float4(d.row[0], d.row[1], d.row[2], d.row[3]));
@@ -1026,8 +1038,11 @@ __device__ __forceinline__ bool next_chunk(const FwdBuffers& fb, const Geom& g, 
 // position on that layer.  A warp takes 32 entries at a time: layer 0 directly (every entry has it), the higher layers
 // through a per-warp queue of (lane, layer) items that all 32 lanes drain together, so that an entry with many layers
 // does not hold up the 31 other lanes.  WITH_E1 = false: body only needs x, y, layer.
-template <bool WITH_E1, class Body>
-__device__ __forceinline__ void for_each_footprint(const float4* __restrict__ head, uint32_t lo, uint32_t hi, uint8_t* queue, Body&& body)
+// First layer of an entry written by the strict two-layer rule: the layer below log2(size), as write_entry computed it.
+__device__ __forceinline__ int strict_first_layer(float ps, int L) { return ps > 1.f ? min(tm_floor_log2(ps), L - 1) : 0; }
+
+template <bool WITH_E1, bool STRICT, class Body>
+__device__ __forceinline__ void for_each_footprint(const float4* __restrict__ head, uint32_t lo, uint32_t hi, uint8_t* queue, int L, Body&& body)
 {
     const int lane = threadIdx.x & 31;
     uint32_t base  = lo + (threadIdx.x & ~31);
@@ -1047,7 +1062,15 @@ __device__ __forceinline__ void for_each_footprint(const float4* __restrict__ he
             e0n = head[2 * (size_t)(ei + kWinThreads)];
             e1n = head[2 * (size_t)(ei + kWinThreads) + 1];
         }
-        if (nl > 0) body(e0, e1, e0.x, e0.y, 0, ei);
+        int first = 0;
+        if constexpr (STRICT)
+        {
+            first = strict_first_layer(e0.z, L);
+            const float sc = __int_as_float((127 - first) << 23);
+            if (nl > 0) body(e0, e1, e0.x * sc, e0.y * sc, first, ei);
+        }
+        else if (nl > 0)
+            body(e0, e1, e0.x, e0.y, 0, ei);
         const int extra = max(nl - 1, 0);
         int incl = extra;
 #pragma unroll
@@ -1059,7 +1082,7 @@ __device__ __forceinline__ void for_each_footprint(const float4* __restrict__ he
         const int total = __shfl_sync(kFull, incl, 31);
         if (total == 0) continue;  // uniform
         int pos = incl - extra;
-        for (int l = 1; l < nl; ++l) queue[pos++] = (uint8_t)(lane | (l << 5));
+        for (int l = 1; l < nl; ++l) queue[pos++] = (uint8_t)(lane | ((first + l) << 5));
         __syncwarp();
         for (int i0 = 0; i0 < total; i0 += 32)
         {
@@ -1101,7 +1124,7 @@ __device__ __forceinline__ uint64_t evict_last_policy()
     return policy;
 }
 
-template <bool COLLECT>
+template <bool COLLECT, bool STRICT>
 __global__ __launch_bounds__(kWinThreads, kWinMinBlocks) void window_kernel(const __grid_constant__ Geom g, FwdBuffers fb, int B)
 {
     __shared__ uint32_t s_cnt[kWinMax];
@@ -1133,7 +1156,7 @@ __global__ __launch_bounds__(kWinThreads, kWinMinBlocks) void window_kernel(cons
             for (int i = threadIdx.x; i < n_win; i += kWinThreads) s_cnt[i] = 0;
             __syncthreads();
             // ---- fragments per window pixel ----
-            for_each_footprint<false>(head, lo, hi, s_queue[threadIdx.x >> 5],
+            for_each_footprint<false, STRICT>(head, lo, hi, s_queue[threadIdx.x >> 5], g.L,
                                       [&](const float4&, const float4&, float x, float y, int layer, uint32_t) {
                                           const int ww = win_w(layer);
                                           uint32_t* c  = s_cnt + win_off(layer) + (__float2int_rd(y) - w.y0(layer)) * ww + (__float2int_rd(x) - w.x0(layer));
@@ -1163,7 +1186,7 @@ __global__ __launch_bounds__(kWinThreads, kWinMinBlocks) void window_kernel(cons
             if (COLLECT)
             {
                 // ---- slots inside the reserved ranges; alpha and the fragment itself ----
-                for_each_footprint<true>(head, lo, hi, s_queue[threadIdx.x >> 5],
+                for_each_footprint<true, STRICT>(head, lo, hi, s_queue[threadIdx.x >> 5], g.L,
                                          [&](const float4& e0, const float4& e1, float x, float y, int layer, uint32_t ei) {
                                              // x, y equal (u, v) * 2^-layer exactly (power-of-two scaling)
                                              const float conf   = e0.w;
@@ -1198,19 +1221,25 @@ __global__ __launch_bounds__(kWinThreads, kWinMinBlocks) void window_kernel(cons
     }
 }
 
-cudaError_t launch_count(const ScenePtrs& sc, const Geom& g, int B, const FwdBuffers& fb, int sm_count, cudaStream_t st)
+cudaError_t launch_count(const ScenePtrs& sc, const Geom& g, int B, const FwdBuffers& fb, bool strict, int sm_count, cudaStream_t st)
 {
     cudaError_t e = cudaMemsetAsync(fb.ticket, 0, sizeof(unsigned) * B, st);
     if (e != cudaSuccess) return e;
-    window_kernel<false><<<sm_count * kWinBlocksPerSM, kWinThreads, 0, st>>>(g, fb, B);
+    if (strict)
+        window_kernel<false, true><<<sm_count * kWinBlocksPerSM, kWinThreads, 0, st>>>(g, fb, B);
+    else
+        window_kernel<false, false><<<sm_count * kWinBlocksPerSM, kWinThreads, 0, st>>>(g, fb, B);
     return cudaGetLastError();
 }
 
-cudaError_t launch_collect(const ScenePtrs& sc, const Geom& g, int B, const FwdBuffers& fb, int sm_count, cudaStream_t st)
+cudaError_t launch_collect(const ScenePtrs& sc, const Geom& g, int B, const FwdBuffers& fb, bool strict, int sm_count, cudaStream_t st)
 {
     cudaError_t e = cudaMemsetAsync(fb.ticket, 0, sizeof(unsigned) * B, st);
     if (e != cudaSuccess) return e;
-    window_kernel<true><<<sm_count * kWinBlocksPerSM, kWinThreads, 0, st>>>(g, fb, B);
+    if (strict)
+        window_kernel<true, true><<<sm_count * kWinBlocksPerSM, kWinThreads, 0, st>>>(g, fb, B);
+    else
+        window_kernel<true, false><<<sm_count * kWinBlocksPerSM, kWinThreads, 0, st>>>(g, fb, B);
     return cudaGetLastError();
 }
 

@@ -80,6 +80,15 @@ void NeuralRenderInfo::set_texture_preparation(bool confidence_is_raw, double co
     params.texture_abs       = texture_abs ? 1 : 0;
 }
 
+void NeuralRenderInfo::set_pipeline_flags(bool use_layer_point_size, bool render_points_in_all_lower_resolutions, bool combine_lists,
+                                          bool saturated_alpha_accumulation)
+{
+    params.use_layer_point_size                   = use_layer_point_size ? 1 : 0;
+    params.render_points_in_all_lower_resolutions = render_points_in_all_lower_resolutions ? 1 : 0;
+    params.combine_lists                          = combine_lists ? 1 : 0;
+    params.saturated_alpha_accumulation           = saturated_alpha_accumulation ? 1 : 0;
+}
+
 int64_t NeuralRenderInfo::last_status()
 {
     return cache->handle ? (int64_t)trips_last_status(cache->handle, c10::cuda::getCurrentCUDAStream().stream()) : 0;
@@ -485,6 +494,7 @@ TORCH_LIBRARY(trips_b200, m)
         .def("clear_images", &NeuralRenderInfo::clear_images)
         .def("set_params", &NeuralRenderInfo::set_params)
         .def("set_texture_preparation", &NeuralRenderInfo::set_texture_preparation)
+        .def("set_pipeline_flags", &NeuralRenderInfo::set_pipeline_flags)
         .def("last_status", &NeuralRenderInfo::last_status);
     m.class_<PointRenderModuleHolder>("PointRenderModule")
         .def(torch::init<int64_t>())

@@ -79,9 +79,13 @@ class FusedPointOptimizer:
     more than one rank both buffers are symmetric-memory allocations, so every rank holds peer pointers to all of
     them.  `step()` = barrier, trips_fused_reduce_adam on this rank's slice, barrier.  Update semantics are MyAdam's
     (src/lib/models/MyAdam.cu:41-88) evaluated after the sum, i.e. those of a single process that saw all views.
-    The optimizer state exists only for the owned slice."""
+    The optimizer state exists only for the owned slice.
 
-    def __init__(self, named_params, cache, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, lrs=None, group=None):
+    multicast: when the symmetric-memory allocations come with NVSwitch multicast addresses, the step runs
+    trips_fused_reduce_adam_multicast instead (the switch sums the gradients and replicates the new weights: half the
+    NVLink bytes).  None = use it when available, False = never, True = require it.  `self.mode` says which one runs."""
+
+    def __init__(self, named_params, cache, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, lrs=None, group=None, multicast=None):
         import ctypes as C
 
         import torch
@@ -106,6 +110,8 @@ class FusedPointOptimizer:
             self.handles = (hp, hg)
             self.param_ptrs = [int(x) for x in hp.buffer_ptrs]
             self.grad_ptrs = [int(x) for x in hg.buffer_ptrs]
+            self.param_mc = int(getattr(hp, "multicast_ptr", 0) or 0)
+            self.grad_mc = int(getattr(hg, "multicast_ptr", 0) or 0)
         else:
             self.param_flat = torch.empty(self.numel, dtype=torch.float32, device=dev)
             self.grad_flat = torch.empty(self.numel, dtype=torch.float32, device=dev)
@@ -134,6 +140,16 @@ class FusedPointOptimizer:
         self.steps = torch.zeros(n_own, dtype=torch.int32, device=dev)
         self._gp = (C.c_void_p * self.world)(*self.grad_ptrs)
         self._pp = (C.c_void_p * self.world)(*self.param_ptrs)
+        have_mc = self.world > 1 and bool(getattr(self, "param_mc", 0)) and bool(getattr(self, "grad_mc", 0))
+        if multicast and not have_mc:
+            raise RuntimeError("FusedPointOptimizer: multicast=True, but the symmetric-memory allocations have no multicast address")
+        self.mode = "multimem" if (have_mc and multicast is not False) else "peer"
+        # all ranks must run the same kernel (a rank without a multicast address would otherwise read stale replicas)
+        if self.world > 1:
+            flag = torch.tensor([1 if self.mode == "multimem" else 0], device=dev, dtype=torch.int32)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
+            if int(flag.item()) == 0:
+                self.mode = "peer"
 
     def barrier(self):
         if self.handles is not None:
@@ -144,7 +160,13 @@ class FusedPointOptimizer:
         C, _lib, torch = self._C, self._lib, self.torch
         self.barrier()  # all gradients are complete and visible
         stream = C.c_void_p(torch.cuda.current_stream(self.param_flat.device).cuda_stream)
-        _lib.check(_lib.lib().trips_fused_reduce_adam(self.cache._h, self._gp, self._pp, self.world, self.rank, self.segments,
-                                                     len(self.segments), self.lo, self.hi, self.first_moments.data_ptr(),
-                                                     self.second_moments.data_ptr(), self.steps.data_ptr(), stream), self.cache._h)
+        if self.mode == "multimem":
+            _lib.check(_lib.lib().trips_fused_reduce_adam_multicast(
+                self.cache._h, C.c_void_p(self.grad_mc), C.c_void_p(self.param_mc), C.c_void_p(self.param_flat.data_ptr()), self.segments,
+                len(self.segments), self.lo, self.hi, self.first_moments.data_ptr(), self.second_moments.data_ptr(),
+                self.steps.data_ptr(), stream), self.cache._h)
+        else:
+            _lib.check(_lib.lib().trips_fused_reduce_adam(self.cache._h, self._gp, self._pp, self.world, self.rank, self.segments,
+                                                         len(self.segments), self.lo, self.hi, self.first_moments.data_ptr(),
+                                                         self.second_moments.data_ptr(), self.steps.data_ptr(), stream), self.cache._h)
         self.barrier()  # every replica holds the new parameters before anybody renders again

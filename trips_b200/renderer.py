@@ -114,11 +114,11 @@ class PointRendererCache:
         # normalize_grads is accepted and changes nothing, exactly as in the reference: NormalizeGradient divides by hit
         # counts (PointRenderer.cu:1193-1230, call sites :1348-1412) that are allocated as zeros (:226-272) and that no
         # kernel of the reference ever increments, so its `if (c > 0)` guard never passes.
-        # RenderForward.cu:313-316 asserts the same; the legacy alternates are not implemented
-        if not (p.use_layer_point_size and p.render_points_in_all_lower_resolutions) or p.combine_lists:
-            raise _lib.TripsError(_lib.ERR_UNSUPPORTED, "only use_layer_point_size && render_points_in_all_lower_resolutions && !combine_lists")
-        if p.saturated_alpha_accumulation or p.check_normal:
-            raise _lib.TripsError(_lib.ERR_UNSUPPORTED, "saturated_alpha_accumulation / check_normal")
+        # use_layer_point_size, render_points_in_all_lower_resolutions and combine_lists select the reference's second forward
+        # pipeline when they differ from their defaults (PointRenderer.cu:730-731); the library follows its rules then.
+        # Normals are not part of the point cloud handed to the tiled renderer (GetPointWoNormal, RenderForward.cu:260).
+        if p.check_normal:
+            raise _lib.TripsError(_lib.ERR_UNSUPPORTED, "check_normal")
 
     def _scene_struct(self, texture, background_color, points, intrinsics, confidence, point_size, index, poses, dropout):
         n = points.shape[0]
@@ -152,7 +152,9 @@ class PointRendererCache:
         p = info.params
         return _lib.TripsRenderParams(info.num_layers, p.k_keep, int(info.train), int(p.drop_out_points_by_radius),
                                       p.drop_out_radius_threshold, int(p.viewer_only), p.stability_cutoff_value,
-                                      int(p.bg_uses_Tn), int(p.confidence_is_raw), float(p.confidence_scale), int(p.texture_abs))
+                                      int(p.bg_uses_Tn), int(p.confidence_is_raw), float(p.confidence_scale), int(p.texture_abs),
+                                      int(p.use_layer_point_size), int(p.render_points_in_all_lower_resolutions), int(p.combine_lists),
+                                      int(p.saturated_alpha_accumulation))
 
     # -- forward / backward -----------------------------------------------------------------------------------------
     def forward(self, info: NeuralRenderInfo, texture, background_color, points, intrinsics, confidence, point_size,
