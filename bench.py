@@ -49,10 +49,10 @@ def parse_args():
     ap.add_argument("--op", default="step", choices=["step", "resize_points", "texture_prepare"],
                     help="'step' (default): the training-step benchmark; 'resize_points': removal of 10 % of the points over all "
                          "per-point tensors and the Adam state (trips_resize_points) against the numpy restatement")
-    ap.add_argument("--collective", default="auto", choices=["auto", "fused", "fused-peer", "nccl"],
+    ap.add_argument("--collective", default="auto", choices=["auto", "fused", "fused-peer", "fused-multimem", "nccl"],
                     help="N>1: 'fused' = one kernel sums the gradients over peer memory, applies Adam and broadcasts; "
-                         "(through NVSwitch multicast addresses when the allocation has them, 'fused-peer' = over peer pointers "
-                         "only); 'nccl' = all-reduce then Adam; 'auto' = fused when symmetric memory can be set up")
+                         "(over peer pointers, from 8 ranks on through NVSwitch multicast addresses; 'fused-peer' / 'fused-multimem' "
+                         "force one of the two); 'nccl' = all-reduce then Adam; 'auto' = fused when symmetric memory can be set up")
     return ap.parse_args()
 
 
@@ -142,8 +142,8 @@ def measured_peak():
     return 6650.0, "fallback"
 
 
-def stage_bytes(stage, N, P, C, B, F, Kf):
-    """Algorithmic bytes of one launch of a stage over B views (F, Kf are totals over those views)."""
+def stage_bytes(stage, N, P, C, B, F, Kf, V=0):
+    """Algorithmic bytes of one launch of a stage over B views (F, Kf, V are totals over those views)."""
     if stage == "bin_points":
         return 24 * N * B
     if stage == "count":
@@ -162,21 +162,26 @@ def stage_bytes(stage, N, P, C, B, F, Kf):
         # no term in the reference's formula (its backward kernel adds straight into the outputs); what the stage must move:
         # per visible point and view one 32-byte gradient row cleared, read and its 32-byte entry head read, per point one row
         # (4 + C4 + 1 floats) cleared, read and written out in the reference's layouts
-        return 0
+        c4 = (C + 3) // 4 * 4
+        return 96 * V + (2 * 4 * (5 + c4) + 4 * (4 + 1 + C + 1)) * N
     return 0
 
 
-# DRAM bytes (read + write) per unit of work, from the single-pass ncu capture of the full workload summarised in
-# profiles/rasterizer_kernels_c3_full_dram_traffic.md; traffic grows in proportion to the unit count
-DRAM_BYTES_PER_UNIT = {"collect": (22.4, "F"), "sort_blend": (36.3, "F"), "blend_backward": (42.7, "Kf"), "count": (5.5, "F"),
-                       "bin_points": (95.9, "NB"), "adam": (347.9, "N")}
+# DRAM bytes (read + write) per unit of work, from the ncu captures summarised under profiles/: the tile kernels, the
+# gradient finish / unpack kernels and Adam from one view of config 3 (rasterizer_kernels_c3_6Mpts_1view_ncu_sections.md:
+# same list density and the same N as the benchmark), the binning kernels, which read every point once for all views of a
+# call, from a quarter of the points with all 8 views (binning_adam_kernels_1.5Mpts_8views_ncu_sections.md).
+# Traffic grows in proportion to the unit count.  Units: F fragments, Kf kept fragments, NB points x views, V entries
+# (visible points over all views), N points.
+DRAM_BYTES_PER_UNIT = {"count": [(5.2, "F")], "collect": [(19.7, "F")], "sort_blend": [(35.5, "F")], "blend_backward": [(41.4, "Kf")],
+                       "bin_points": [(43.1, "NB")], "unpack_grads": [(23.5 + 126.4, "V"), (196.8, "N")], "adam": [(337.3, "N")]}
 
 
 def stage_traffic(stage, N, B, F, Kf, V=0):
     if stage not in DRAM_BYTES_PER_UNIT:
         return None
-    per, unit = DRAM_BYTES_PER_UNIT[stage]
-    return per * {"F": F, "Kf": Kf, "NB": N * B, "N": N, "V": V}[unit]
+    units = {"F": F, "Kf": Kf, "NB": N * B, "N": N, "V": V}
+    return sum(per * units[unit] for per, unit in DRAM_BYTES_PER_UNIT[stage])
 
 
 def fused_adam_bytes(numel, world):
@@ -305,15 +310,15 @@ def run_ours(args, rank, world, local_rank):
     params = [tex.texture_raw, tex.confidence_raw, pc.t_position, pc.t_point_size, tex.background_color_raw]
     keys = ("texture", "confidence", "points", "point_size", "background")
     fused, collective = None, "none"
-    if world > 1 and args.collective in ("auto", "fused", "fused-peer"):
+    if world > 1 and args.collective in ("auto", "fused", "fused-peer", "fused-multimem"):
         from trips_b200.dist import FusedPointOptimizer
         ok = torch.ones(1, device=dev)
         try:
             # NVSwitch multicast (multimem) when the symmetric-memory allocation has a multicast address, peer pointers otherwise
             fused = FusedPointOptimizer(list(zip(keys, params)), cache, lr=1e-3, betas=(0.9, 0.999),
-                                        multicast=False if args.collective == "fused-peer" else None)
+                                        multicast={"fused-peer": False, "fused-multimem": True}.get(args.collective))
         except Exception as e:  # noqa: BLE001 - symmetric memory is optional plumbing; the NCCL path is always there
-            if args.collective in ("fused", "fused-peer"):
+            if args.collective in ("fused", "fused-peer", "fused-multimem"):
                 raise
             print(f"[bench] rank {rank}: symmetric memory unavailable ({type(e).__name__}: {e}); using NCCL all-reduce", file=sys.stderr)
             ok.zero_()
@@ -560,7 +565,7 @@ def run_ours(args, rank, world, local_rank):
             return fused_adam_bytes(fused.numel, world) if fused is not None else 0
         if k == "adam" and fused is not None:
             return 0
-        return stage_bytes(k, N, P, C, B, F, Kf)
+        return stage_bytes(k, N, P, C, B, F, Kf, stats["visible_points"])
 
     dom = max((k for k in per_stage if k in step_stages), key=lambda k: per_stage[k]["ms_per_launch"])
     dom_bytes = bytes_of(dom)
@@ -584,7 +589,7 @@ def run_ours(args, rank, world, local_rank):
                 # the whole step against the HBM roofline: algorithmic bytes of all stages / step time, and the same on measured DRAM bytes
                 "step_frac": total_alg / (ms_step * 1e-3) / 1e9 / peak,
                 "step_frac_dram": (total_traffic / (ms_step * 1e-3) / 1e9 / peak) if total_traffic else None,
-                "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum per unit of work (profiles/rasterizer_kernels_c3_full_dram_traffic.md) x units of this run",
+                "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum per unit of work (profiles/rasterizer_kernels_c3_6Mpts_1view_ncu_sections.md, binning_adam_kernels_1.5Mpts_8views_ncu_sections.md) x units of this run",
                 "alg_bytes_per_launch": dom_bytes,
                 "step_alg_bytes": total_alg, "step_gbs": total_alg / (ms_step * 1e-3) / 1e9, "stages": per_stage}
 

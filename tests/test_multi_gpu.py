@@ -53,7 +53,14 @@ def _worker(rank, world, port, out_dir, multicast):
     params = [tex.texture_raw, tex.confidence_raw, pc.t_position, pc.t_point_size, tex.background_color_raw]
     keys = ("texture", "confidence", "points", "point_size", "background")
     start = [p.detach().clone() for p in params]
-    fused = FusedPointOptimizer(list(zip(keys, params)), cache, lr=1e-3, betas=(0.9, 0.999), multicast=multicast)
+    try:
+        fused = FusedPointOptimizer(list(zip(keys, params)), cache, lr=1e-3, betas=(0.9, 0.999), multicast=multicast)
+    except RuntimeError as exc:  # multicast required but not available: the same on every rank
+        with open(os.path.join(out_dir, f"rank{rank}.txt"), "w") as f:
+            f.write(f"SKIP: {exc}\n")
+        dist.barrier()
+        dist.destroy_process_group()
+        return
     ref = [torch.nn.Parameter(p.detach().clone()) for p in params]
     ref_opt = MyAdam(ref, lr=1e-3, betas=(0.9, 0.999), cache=PointRendererCache(dev))
     gen = torch.Generator(device=dev)
@@ -100,7 +107,7 @@ def _worker(rank, world, port, out_dir, multicast):
 
 
 @pytest.mark.timeout(600)
-@pytest.mark.parametrize("multicast", [False, None], ids=["peer_pointers", "multimem"])
+@pytest.mark.parametrize("multicast", [False, True], ids=["peer_pointers", "multimem"])
 def test_fused_reduce_adam_on_two_gpus(cuda_lib, tmp_path, multicast):
     import torch
     if torch.cuda.device_count() < 2:
@@ -117,8 +124,6 @@ def test_fused_reduce_adam_on_two_gpus(cuda_lib, tmp_path, multicast):
         assert p.exitcode == 0
     results = [(tmp_path / f"rank{r}.txt").read_text().strip() for r in range(2)]
     print("FUSED", results)
-    for res in results:
-        assert res.startswith("ok "), res
-    if multicast is None and results[0] != "ok multimem":
-        pytest.skip("the symmetric-memory allocation has no multicast address on this machine: the peer-pointer kernel ran")
-    assert results[0] == results[1] == ("ok multimem" if multicast is None else "ok peer")
+    if multicast and all("no multicast address" in res for res in results):
+        pytest.skip("the symmetric-memory allocations have no multicast address on this machine")
+    assert results[0] == results[1] == ("ok multimem" if multicast else "ok peer"), results
