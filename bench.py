@@ -51,8 +51,8 @@ def parse_args():
                          "per-point tensors and the Adam state (trips_resize_points) against the numpy restatement")
     ap.add_argument("--collective", default="auto", choices=["auto", "fused", "fused-peer", "fused-multimem", "nccl"],
                     help="N>1: 'fused' = one kernel sums the gradients over peer memory, applies Adam and broadcasts; "
-                         "(over peer pointers, from 8 ranks on through NVSwitch multicast addresses; 'fused-peer' / 'fused-multimem' "
-                         "force one of the two); 'nccl' = all-reduce then Adam; 'auto' = fused when symmetric memory can be set up")
+                         "(over peer pointers; 'fused-multimem' = through NVSwitch multicast addresses); 'nccl' = all-reduce then "
+                         "Adam; 'auto' = fused over peer pointers when symmetric memory can be set up")
     return ap.parse_args()
 
 
@@ -314,7 +314,6 @@ def run_ours(args, rank, world, local_rank):
         from trips_b200.dist import FusedPointOptimizer
         ok = torch.ones(1, device=dev)
         try:
-            # NVSwitch multicast (multimem) when the symmetric-memory allocation has a multicast address, peer pointers otherwise
             fused = FusedPointOptimizer(list(zip(keys, params)), cache, lr=1e-3, betas=(0.9, 0.999),
                                         multicast={"fused-peer": False, "fused-multimem": True}.get(args.collective))
         except Exception as e:  # noqa: BLE001 - symmetric memory is optional plumbing; the NCCL path is always there

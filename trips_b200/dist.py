@@ -81,16 +81,14 @@ class FusedPointOptimizer:
     (src/lib/models/MyAdam.cu:41-88) evaluated after the sum, i.e. those of a single process that saw all views.
     The optimizer state exists only for the owned slice.
 
-    multicast: when the symmetric-memory allocations come with NVSwitch multicast addresses, the step runs
-    trips_fused_reduce_adam_multicast instead (the switch sums the gradients and replicates the new weights: half the
-    NVLink bytes in the busier direction at 8 ranks).  Every GPU sends ALL of its gradient buffer into the switch for
-    the reduction, whatever the number of ranks, while over peer pointers it serves (world - 1) / world of it and
-    sends the new weights of its slice world - 1 times: measured on config 3 (360 MB of parameters) the multicast
-    kernel takes 0.65 / 0.56 ms at 2 / 4 ranks against 0.37 / 0.51 ms over peer pointers, and the curves cross
-    between 4 and 8 ranks.  multicast: None = multicast from 8 ranks on when available, False = never,
-    True = require it.  `self.mode` says which kernel runs."""
-
-    MULTICAST_FROM_WORLD = 8
+    multicast: when the symmetric-memory allocations come with NVSwitch multicast addresses, the step can run
+    trips_fused_reduce_adam_multicast instead (the switch sums the gradients and replicates the new weights).  There
+    every GPU sends ALL of its gradient buffer into the switch for the reduction, whatever the number of ranks, while
+    over peer pointers it serves (world - 1) / world of it and sends the new weights of its slice world - 1 times.
+    Measured on config 3 (360 MB of parameters): 0.65 / 0.56 ms at 2 / 4 ranks through multicast against 0.37 / 0.51
+    ms over peer pointers; by the byte counts the curves cross between 4 and 8 ranks.  multicast: None or False = peer
+    pointers, True = multicast (an error where the allocation has no multicast address).  `self.mode` says which
+    kernel runs."""
 
     def __init__(self, named_params, cache, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, lrs=None, group=None, multicast=None):
         import ctypes as C
@@ -150,7 +148,7 @@ class FusedPointOptimizer:
         have_mc = self.world > 1 and bool(getattr(self, "param_mc", 0)) and bool(getattr(self, "grad_mc", 0))
         if multicast and not have_mc:
             raise RuntimeError("FusedPointOptimizer: multicast=True, but the symmetric-memory allocations have no multicast address")
-        self.mode = "multimem" if have_mc and (multicast or (multicast is None and self.world >= self.MULTICAST_FROM_WORLD)) else "peer"
+        self.mode = "multimem" if (have_mc and multicast) else "peer"
         # all ranks must run the same kernel (a rank without a multicast address would otherwise read stale replicas)
         if self.world > 1:
             flag = torch.tensor([1 if self.mode == "multimem" else 0], device=dev, dtype=torch.int32)
