@@ -25,25 +25,31 @@ TOL_PYRAMID = 1e-5
 TOL_GRAD = 1e-4
 STRICT_SHARE_MIN = 0.999  # measured: 0.9995 to 0.99999 over all cases and tensors
 
-# name -> (scene factory, views compared)
+# name -> (scene factory, views compared, render flags)
 CASES = {
-    "config2_2M_720p_all_4_views": (lambda: scenes.config2(), [0, 1, 2, 3]),
-    "config3_6M_1080p_views_0_5": (lambda: scenes.config3(), [0, 5]),
-    "config4_20M_1440p_view_1": (lambda: scenes.config4(n_views=4), [1]),
-    "config5_10M_1080p_random_view_3": (lambda: scenes.config5(n_views=8), [3]),
+    "config2_2M_720p_all_4_views": (lambda: scenes.config2(), [0, 1, 2, 3], {}),
+    "config3_6M_1080p_views_0_5": (lambda: scenes.config3(), [0, 5], {}),
+    "config4_20M_1440p_view_1": (lambda: scenes.config4(n_views=4), [1], {}),
+    "config5_10M_1080p_random_view_3": (lambda: scenes.config5(n_views=8), [3], {}),
     # every point inside a 64x64 pixel window: lists of several thousand fragments, all through the streaming top-K
-    "config5_adversarial_1M_64x64px": (lambda: scenes.config5(n_points=1_000_000, n_views=1, adversarial=True), [0]),
+    "config5_adversarial_1M_64x64px": (lambda: scenes.config5(n_points=1_000_000, n_views=1, adversarial=True), [0], {}),
+    # the reference's second forward pipeline (PointRenderer.cu:730-731) on a benchmark-sized view: strict two-layer
+    # write, lists combined over the coarser layers.  (Saturated accumulation is covered by the small variants: its
+    # backward rule subtracts colour sums that do not depend on the incoming gradient, so its gradients are differences
+    # of large numbers and meet the 1e-4 bar but not the element-wise bounds reported here.)
+    "config3_6M_1080p_view_2_second_pipeline": (lambda: scenes.config3(), [2],
+                                                dict(render_points_in_all_lower_resolutions=False, combine_lists=True)),
 }
 
 
 @pytest.mark.parametrize("name", list(CASES))
 def test_full_size_parity(name, oracle_lib, cuda_lib):
     import torch
-    make, views = CASES[name]
+    make, views, flags = CASES[name]
     s = make()
     oracle_lib.use_all_cores()
     C = s.channels
-    ns, info, blend = gpu_render(s, train=True, views=views)
+    ns, info, blend = gpu_render(s, train=True, views=views, **flags)
     for t in (ns.texture.texture_raw, ns.texture.confidence_raw, ns.texture.background_color_raw,
               ns.point_cloud_cuda.t_position, ns.point_cloud_cuda.t_point_size):
         t.requires_grad_(True)
@@ -60,7 +66,7 @@ def test_full_size_parity(name, oracle_lib, cuda_lib):
     ref = None
     tot = dict(F=0, Kf=0, V=0)
     for b, v in enumerate(views):
-        sa, op, frames = oracle_frames(s, train=True, views=[v])
+        sa, op, frames = oracle_frames(s, train=True, views=[v], **flags)
         f = frames[0]
         tot["F"] += f.F
         tot["Kf"] += f.Kf
@@ -133,7 +139,9 @@ def test_full_size_parity(name, oracle_lib, cuda_lib):
         assert e <= TOL_GRAD, f"grad {k}: rel err {e}"
         # element-wise: no element is off by more than 1e-6 of the tensor's scale, and most meet a strict 1e-4 (the others
         # are sums of terms of both signs that cancel to near zero; fp32 atomics add them in arbitrary order)
-        assert grads[k]["worst_abs_over_max"] <= 1e-6, (k, grads[k])  # measured: 1e-7 to 3e-7
+        # measured: 1e-7 to 3e-7; with combine_lists up to 1.9e-6 (fragments of coarser lists that lie more than a pixel away
+        # enter the position gradient with alpha 0 but a non-zero Jacobian, RenderBackward.cu:353-390: more terms cancel)
+        assert grads[k]["worst_abs_over_max"] <= (5e-6 if flags.get("combine_lists") else 1e-6), (k, grads[k])
         assert grads[k]["share_strict"] >= STRICT_SHARE_MIN, (k, grads[k])
     assert np.all(ns.point_cloud_cuda.t_position.grad[:, 3].cpu().numpy() == 0)
     gpose = ns.poses.tangent_poses.grad.cpu().numpy()
