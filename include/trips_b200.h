@@ -33,7 +33,7 @@ typedef enum
 
 /* Bits of the device status word (trips_last_status): conditions the reference would assert on. */
 #define TRIPS_DEV_BAD_TEXTURE_INDEX 1u /* RenderBackward.cu:217-218 */
-#define TRIPS_DEV_NONZERO_DISTORTION 2u /* distortion model not implemented: coefficients were ignored */
+#define TRIPS_DEV_NONZERO_DISTORTION 2u /* non-zero distortion coefficients while TripsRenderParams.distortion = 0: they were ignored */
 #define TRIPS_DEV_FRAGMENT_OVERFLOW 4u /* a view's fragments did not fit the list buffer (sized from the previous call): the view was rendered as background; the next call grows the buffer */
 #define TRIPS_DEV_BAD_FRAGMENT 8u /* a fragment referred to a point outside the view's visible set (internal error) */
 #define TRIPS_DEV_BAD_POINT_INDEX 16u /* trips_resize_points: a removal index is out of range or listed twice */
@@ -60,7 +60,7 @@ typedef struct
     const float* dropout;     /* [B,N] 1 = point dropped in that view (training only); NULL = none */
     const double* poses;      /* [n_images,8] world->view: quaternion x,y,z,w, translation x,y,z, pad */
     int n_images;
-    const float* intrinsics;  /* [n_cameras,13] fx fy cx cy s + 8 distortion coefficients (must be 0) */
+    const float* intrinsics;  /* [n_cameras,13] fx fy cx cy s + 8 distortion coefficients k1 k2 k3 k4 k5 k6 p1 p2 */
     int n_cameras;
 } TripsScene;
 
@@ -101,6 +101,13 @@ typedef struct
     int combine_lists;                          /* 1: a pixel also draws from the lists of the pixels above it on the coarser layers (RenderForward.cu:3232-3242) */
     int saturated_alpha_accumulation;           /* forward: second pipeline only (RenderForward.cu:3524-3548; compiled out of the
                                                    first, :908-935); backward: always (RenderBackward.cu:227-259) */
+    /* Lens distortion of ProjectPointPinholeWoNormal / ProjectPointPinholeBackward (PointRendererHelper.h:232-253,
+     * 434-494): the 8-coefficient rational model with tangential terms of saiga's distortNormalizedPoint,
+     * x' = x (1 + k1 r2 + k2 r4 + k3 r6) / (1 + k4 r2 + k5 r4 + k6 r6) + 2 p1 x y + p2 (r2 + 2 x^2), y' alike; points with
+     * r2 > dist_cutoff^2 are culled.  1: applied, and the intrinsics gradient carries all 13 entries.  0: a plain
+     * pinhole (the coefficients must be zero, TRIPS_DEV_NONZERO_DISTORTION otherwise; no cut-off radius). */
+    int distortion;
+    float dist_cutoff;                          /* RenderParams::dist_cutoff (Settings.h:61: 20) */
 } TripsRenderParams;
 
 /* Gradient outputs of BlendPointCloudBackward (src/lib/rendering/PointRenderer.cu:1423-1426).
@@ -111,7 +118,7 @@ typedef struct
     float* background;   /* [C] */
     float* points;       /* [N,4], w = 0 */
     double* pose_tangent; /* [n_images,6] */
-    float* intrinsics;   /* [n_cameras,13]; only the 5 pinhole coefficients receive gradients */
+    float* intrinsics;   /* [n_cameras,13]; the 8 distortion coefficients receive gradients when TripsRenderParams.distortion is set */
     float* confidence;   /* [n_tex] */
     float* point_size;   /* [N] ("g_layer") */
 } TripsGrads;

@@ -39,7 +39,8 @@ class OrParams(C.Structure):
     _fields_ = [("num_layers", C.c_int), ("k_keep", C.c_int), ("train", C.c_int), ("drop_out_points_by_radius", C.c_int),
                 ("drop_out_radius_threshold", C.c_float), ("viewer_only", C.c_int), ("stability_cutoff_value", C.c_float),
                 ("bg_uses_Tn", C.c_int), ("use_layer_point_size", C.c_int), ("render_points_in_all_lower_resolutions", C.c_int),
-                ("combine_lists", C.c_int), ("saturated_alpha_accumulation", C.c_int)]
+                ("combine_lists", C.c_int), ("saturated_alpha_accumulation", C.c_int), ("distortion", C.c_int),
+                ("dist_cutoff", C.c_float)]
 
 
 def lib():
@@ -87,10 +88,12 @@ def _ptr(a):
 
 def make_params(num_layers, k_keep, train, drop_out_points_by_radius=False, drop_out_radius_threshold=0.6,
                 viewer_only=False, stability_cutoff_value=10000.0, bg_uses_Tn=False, use_layer_point_size=True,
-                render_points_in_all_lower_resolutions=True, combine_lists=False, saturated_alpha_accumulation=False) -> OrParams:
+                render_points_in_all_lower_resolutions=True, combine_lists=False, saturated_alpha_accumulation=False,
+                distortion=False, dist_cutoff=20.0) -> OrParams:
     return OrParams(num_layers, k_keep, int(train), int(drop_out_points_by_radius), drop_out_radius_threshold,
                     int(viewer_only), stability_cutoff_value, int(bg_uses_Tn), int(use_layer_point_size),
-                    int(render_points_in_all_lower_resolutions), int(combine_lists), int(saturated_alpha_accumulation))
+                    int(render_points_in_all_lower_resolutions), int(combine_lists), int(saturated_alpha_accumulation),
+                    int(distortion), float(dist_cutoff))
 
 
 def make_view(w, h, pose8, intr13, crop_transform=(1, 1, 0, 0, 0), crop_rotation=(1, 0, 0, 1)) -> OrView:
@@ -191,7 +194,7 @@ class Frame:
         out = dict(texture=np.zeros((s.channels, s.n_tex), np.float64), confidence=np.zeros(s.n_tex, np.float64),
                    position=np.zeros((s.n, 4), np.float64), point_size=np.zeros(s.n, np.float64),
                    background=np.zeros(s.channels, np.float64), pose=np.zeros(6, np.float64),
-                   intrinsics=np.zeros(5, np.float64))
+                   intrinsics=np.zeros(13, np.float64))
         lib().or_backward(self._h, C.byref(s.struct), C.byref(self.view), C.byref(self.params), _ptr(g),
                           _ptr(out["texture"]), _ptr(out["confidence"]), _ptr(out["position"]), _ptr(out["point_size"]),
                           _ptr(out["background"]), _ptr(out["pose"]), _ptr(out["intrinsics"]))

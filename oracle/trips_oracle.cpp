@@ -82,9 +82,49 @@ struct Cam
     float r00, r01, r10, r11;        // crop rotation
     float cenx, ceny;                // (w/2, h/2) with integer division, RenderForward.cu:303
     int w, h;
+    float k1, k2, k3, k4, k5, k6, p1, p2;  // distortion coefficients
+    bool dist = false;                     // apply them (and the cut-off radius)
+    float cut2 = 0.f;                      // dist_cutoff^2
 };
 
-Cam make_cam(const OrView* v)
+// saiga's distortNormalizedPoint restated (see OrParams.distortion): rational radial factor + tangential terms.
+// J (optional): d(xd, yd) / d(x, y) row-major; Jk (optional): d(xd, yd) / d(k1 k2 k3 k4 k5 k6 p1 p2), two rows of 8.
+inline void distort(const Cam& c, float x, float y, float& xd, float& yd, float* J, float* Jk)
+{
+    const float x2 = x * x, y2 = y * y;
+    const float r2 = x2 + y2, xy2 = 2.f * x * y;
+    const float r4 = r2 * r2, r6 = r4 * r2;
+    const float A  = ((1.f + c.k1 * r2) + c.k2 * r4) + c.k3 * r6;
+    const float B  = ((1.f + c.k4 * r2) + c.k5 * r4) + c.k6 * r6;
+    const float iB = 1.f / B;
+    const float radial = A * iB;
+    const float tx = c.p1 * xy2 + c.p2 * (r2 + 2.f * x2);
+    const float ty = c.p1 * (r2 + 2.f * y2) + c.p2 * xy2;
+    xd = x * radial + tx;
+    yd = y * radial + ty;
+    if (J)
+    {
+        const float dA = (c.k1 + 2.f * c.k2 * r2) + 3.f * c.k3 * r4;
+        const float dB = (c.k4 + 2.f * c.k5 * r2) + 3.f * c.k6 * r4;
+        const float dr = (dA * B - A * dB) * iB * iB;  // d radial / d r2
+        J[0] = radial + x * dr * (2.f * x) + (2.f * c.p1 * y + 6.f * c.p2 * x);
+        J[1] = x * dr * (2.f * y) + (2.f * c.p1 * x + 2.f * c.p2 * y);
+        J[2] = y * dr * (2.f * x) + (2.f * c.p1 * x + 2.f * c.p2 * y);
+        J[3] = radial + y * dr * (2.f * y) + (6.f * c.p1 * y + 2.f * c.p2 * x);
+    }
+    if (Jk)
+    {
+        const float AiB2 = A * iB * iB;
+        Jk[0] = x * r2 * iB, Jk[1] = x * r4 * iB, Jk[2] = x * r6 * iB;
+        Jk[3] = -x * AiB2 * r2, Jk[4] = -x * AiB2 * r4, Jk[5] = -x * AiB2 * r6;
+        Jk[6] = xy2, Jk[7] = r2 + 2.f * x2;
+        Jk[8] = y * r2 * iB, Jk[9] = y * r4 * iB, Jk[10] = y * r6 * iB;
+        Jk[11] = -y * AiB2 * r2, Jk[12] = -y * AiB2 * r4, Jk[13] = -y * AiB2 * r6;
+        Jk[14] = r2 + 2.f * y2, Jk[15] = xy2;
+    }
+}
+
+Cam make_cam(const OrView* v, const OrParams* pr = nullptr)
 {
     Cam c;
     c.V   = make_pose(v->pose);
@@ -106,6 +146,10 @@ Cam make_cam(const OrView* v)
     c.h   = v->h;
     c.cenx = (float)(v->w / 2);
     c.ceny = (float)(v->h / 2);
+    c.k1 = v->intrinsics[5], c.k2 = v->intrinsics[6], c.k3 = v->intrinsics[7], c.k4 = v->intrinsics[8];
+    c.k5 = v->intrinsics[9], c.k6 = v->intrinsics[10], c.p1 = v->intrinsics[11], c.p2 = v->intrinsics[12];
+    c.dist = pr && pr->distortion;
+    c.cut2 = pr ? pr->dist_cutoff * pr->dist_cutoff : 0.f;
     return c;
 }
 
@@ -119,6 +163,14 @@ inline void project(const Cam& c, const float* p, float& u, float& v, float& z)
     float iz = 1.f / pv[2];
     float nx = pv[0] * iz;
     float ny = pv[1] * iz;
+    if (c.dist)
+    {
+        // outside the cut-off radius the routine returns (100000, 100000) and the caller sets z = 0
+        if (nx * nx + ny * ny > c.cut2) z = 0.f;
+        float xd, yd;
+        distort(c, nx, ny, xd, yd, nullptr, nullptr);
+        nx = xd, ny = yd;
+    }
     // K.normalizedToImage
     float ix = (c.fx * nx + c.s * ny) + c.cx;
     float iy = c.fy * ny + c.cy;
@@ -226,7 +278,7 @@ float or_expf(float x) { return tm_expf(x); }
 float or_logf(float x) { return tm_logf(x); }
 void or_project(const OrView* view, const float* p3, float* u, float* v, float* z)
 {
-    Cam c = make_cam(view);
+    Cam c = make_cam(view);  // (no parameters: zero distortion)
     project(c, p3, *u, *v, *z);
 }
 
@@ -260,7 +312,7 @@ OrFrame* or_forward(const OrScene* sc, const OrView* view, const OrParams* pr)
         f->base[L] = b;
         f->P       = b;
     }
-    const Cam cam = make_cam(view);
+    const Cam cam = make_cam(view, pr);
     f->depth.assign(N, -1.f);
     f->nlayers.assign(N, 0);
     f->first.assign(N, 0);
@@ -553,16 +605,16 @@ void or_backward(const OrFrame* f, const OrScene* sc, const OrView* view, const 
                  double* g_background, double* g_pose, double* g_intrinsics)
 {
     const int C = f->C, L = f->L, K = f->K;
-    const Cam cam   = make_cam(view);
+    const Cam cam   = make_cam(view, pr);
     const float fxc = cam.fx * cam.cfx;
     std::vector<double> bg_acc(C, 0.0);
     double pose_acc[6] = {0, 0, 0, 0, 0, 0};
-    double k_acc[5]    = {0, 0, 0, 0, 0};
+    double k_acc[13]   = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};  // fx fy cx cy s, then the 8 distortion coefficients
 #pragma omp parallel
     {
         std::vector<double> bg_local(C, 0.0);
         double pose_local[6] = {0, 0, 0, 0, 0, 0};
-        double k_local[5]    = {0, 0, 0, 0, 0};
+        double k_local[13]   = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
 #pragma omp for schedule(dynamic, 1024)
         for (int64_t p = 0; p < f->P; ++p)
         {
@@ -695,7 +747,7 @@ void or_backward(const OrFrame* f, const OrScene* sc, const OrView* view, const 
                 float gbs   = conf * lf * ga;
                 float grad0 = J[q][0] * gbs, grad1 = J[q][1] * gbs;  // dR_dp = J_uv^T * e_q * gbs
 
-                // ProjectPointPinholeBackward (PointRendererHelper.h:434-494), zero distortion
+                // ProjectPointPinholeBackward (PointRendererHelper.h:434-494)
                 const float* pos = sc->position + (size_t)pid * 4;
                 float pv[3];
                 transform_point(cam.V, pos, pv);
@@ -711,6 +763,19 @@ void or_backward(const OrFrame* f, const OrScene* sc, const OrView* view, const 
                 float gk1 = cam.cs * gr0 + cam.cfy * gr1;
                 float gn0 = cam.fx * gk0;                // J_p_K1^T = [[fx,0],[s,fy]]
                 float gn1 = cam.s * gk0 + cam.fy * gk1;
+                if (cam.dist)
+                {
+                    // distortNormalizedPoint between DivideByZ and K (PointRendererHelper.h:468-470): the pinhole
+                    // coefficients see the distorted coordinates, the chain continues through J_p_dis^T, and the
+                    // eight coefficients receive J_dis_dis^T (PointRendererHelper.h:485-491)
+                    float xd, yd, Jd[4], Jk[16];
+                    distort(cam, nx, ny, xd, yd, Jd, Jk);
+                    for (int k = 0; k < 8; ++k) k_local[5 + k] += (double)(Jk[k] * gn0 + Jk[8 + k] * gn1);
+                    const float g0 = Jd[0] * gn0 + Jd[2] * gn1;
+                    const float g1 = Jd[1] * gn0 + Jd[3] * gn1;
+                    gn0 = g0, gn1 = g1;
+                    nx = xd, ny = yd;  // for the pinhole coefficients below
+                }
                 // DivideByZ^T
                 float gv0 = iz * gn0;
                 float gv1 = iz * gn1;
@@ -756,7 +821,7 @@ void or_backward(const OrFrame* f, const OrScene* sc, const OrView* view, const 
         {
             for (int c = 0; c < C; ++c) bg_acc[c] += bg_local[c];
             for (int k = 0; k < 6; ++k) pose_acc[k] += pose_local[k];
-            for (int k = 0; k < 5; ++k) k_acc[k] += k_local[k];
+            for (int k = 0; k < 13; ++k) k_acc[k] += k_local[k];
         }
     }
     if (g_background)
@@ -764,7 +829,7 @@ void or_backward(const OrFrame* f, const OrScene* sc, const OrView* view, const 
     if (g_pose)
         for (int k = 0; k < 6; ++k) g_pose[k] += pose_acc[k];
     if (g_intrinsics)
-        for (int k = 0; k < 5; ++k) g_intrinsics[k] += k_acc[k];
+        for (int k = 0; k < 13; ++k) g_intrinsics[k] += k_acc[k];
 }
 
 // ---- A5: Adam (adam_step, MyAdam.cu:41-88) ----
@@ -800,7 +865,7 @@ void or_adam(int64_t n, float* w, const float* g, float* m, float* v, int64_t* s
 // with a libm softplus, out[5] = points where tm_softplus and the libm softplus differ in any bit.
 void or_layer_divergence(const OrFrame* f, const OrScene* sc, const OrView* view, const OrParams* pr, int64_t* out)
 {
-    const Cam cam   = make_cam(view);
+    const Cam cam   = make_cam(view, pr);
     const float fxc = cam.fx * cam.cfx;
     const int L     = pr->num_layers;
     int64_t vis = 0, big = 0, dceil = 0, dfloor = 0, dlayers = 0, dsoft = 0;

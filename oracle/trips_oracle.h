@@ -34,7 +34,7 @@ typedef struct
 {
     int w, h;
     double pose[8];         /* world->view: quaternion x,y,z,w then translation x,y,z, one pad */
-    float intrinsics[13];   /* fx fy cx cy s + 8 distortion coefficients (must be zero) */
+    float intrinsics[13];   /* fx fy cx cy s + 8 distortion coefficients k1..k6 p1 p2 (applied when OrParams.distortion) */
     float crop_transform[5]; /* fx fy cx cy s */
     float crop_rotation[4]; /* row-major 2x2 */
 } OrView;
@@ -56,6 +56,13 @@ typedef struct
     int combine_lists;                          /* 1: a pixel also draws from the lists of the coarser layers above it */
     int saturated_alpha_accumulation;           /* forward: second pipeline only (RenderForward.cu:3524-3548; compiled out
                                                    of the first, :908-935); backward: always (RenderBackward.cu:227-259) */
+    /* Lens distortion of ProjectPointPinholeWoNormal (PointRendererHelper.h:232-253).  distortNormalizedPoint lives in
+     * the saiga library (External/saiga, not part of the reference tree): restated here as the 8-coefficient rational
+     * model with tangential terms that saiga's Distortion struct documents (OpenCV's k1 k2 p1 p2 k3 k4 k5 k6 model),
+     * coefficient order k1 k2 k3 k4 k5 k6 p1 p2, points with x^2 + y^2 > dist_cutoff^2 culled (the reference tests
+     * for the 100000 the routine returns there, PointRendererHelper.h:246-249).  UNPINNED like the rest. */
+    int distortion;    /* 0: coefficients must be zero and dist_cutoff is not applied */
+    float dist_cutoff; /* RenderParams::dist_cutoff, Settings.h:61 (20) */
 } OrParams;
 
 typedef struct OrFrame OrFrame; /* all intermediates of one rendered view */
@@ -84,7 +91,8 @@ void or_get_records(const OrFrame* f, int32_t* nrec /*[P]*/, int32_t* rec_pid /*
 void or_backward(const OrFrame* f, const OrScene* scene, const OrView* view, const OrParams* params,
                  const float* grad_pyramid, double* g_texture /*[C,n_tex]*/, double* g_confidence /*[n_tex]*/,
                  double* g_position /*[N,4], w untouched*/, double* g_point_size /*[N]*/,
-                 double* g_background /*[C]*/, double* g_pose /*[6] or NULL*/, double* g_intrinsics /*[5] or NULL*/);
+                 double* g_background /*[C]*/, double* g_pose /*[6] or NULL*/,
+                 double* g_intrinsics /*[13] or NULL: fx fy cx cy s, then the 8 distortion coefficients*/);
 
 /* Reference Adam (MyAdam.cu:41-88) over n elements; steps is int64 per element. */
 void or_adam(int64_t n, float* w, const float* g, float* m, float* v, int64_t* steps, float lr, float beta1,

@@ -41,7 +41,9 @@ def compute():
                     f"offsets_{b}": offsets, f"frags_{b}": frags, f"nrec_{b}": nrec, f"rec_pid_{b}": pid,
                     f"rec_alpha_{b}": alpha, f"pyramid_{b}": f.pyramid_flat()})
         for k, v in grads.items():
-            out[f"grad_{k}_{b}"] = v
+            # the fixture holds the five pinhole coefficients' gradients (the scene has no lens distortion, for which the
+            # oracle returns eight more entries)
+            out[f"grad_{k}_{b}"] = v[:5] if k == "intrinsics" else v
     return out
 
 

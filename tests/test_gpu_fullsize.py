@@ -148,6 +148,6 @@ def test_full_size_parity(name, oracle_lib, cuda_lib):
     gintr = ns.intrinsics.intrinsics.grad.cpu().numpy()
     for b, v in enumerate(views):
         assert rel_err(gpose[v], ref["pose"][b]) <= TOL_GRAD, "pose gradient"
-        assert rel_err(gintr[v, :5], ref["intrinsics"][b]) <= TOL_GRAD, "intrinsics gradient"
+        assert rel_err(gintr[v, :5], ref["intrinsics"][b][:5]) <= TOL_GRAD, "intrinsics gradient"
     report["gradients"] = grads
     parity_report(name, report)

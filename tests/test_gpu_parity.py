@@ -77,6 +77,15 @@ def _variants():
                                       dict(strict, drop_out_points_by_radius=True, drop_out_radius_threshold=2.0), None)
     v["second_combine_three_views_long_lists"] = (scenes.tiny(seed=49, n_points=20000, width=64, height=48, n_views=3),
                                                   dict(combine_lists=True), None)
+    # lens distortion: all eight coefficients non-zero and different per view, a cut-off radius that culls the image corners
+    s = scenes.tiny(seed=51, n_points=6000, n_views=3, num_layers=5, size_range=(5e-3, 0.5))
+    s.intrinsics[:, 5:] = np.array([-0.12, 0.05, -0.01, 0.03, -0.02, 0.004, 2e-3, -3e-3], np.float32)
+    s.intrinsics[1, 5:] *= -0.5
+    s.intrinsics[2, 5:] *= 2.0
+    v["lens_distortion"] = (s, dict(distortion=True, dist_cutoff=0.55), None)
+    s = scenes.tiny(seed=52, n_points=4000, channels=8)
+    s.intrinsics[:, 5:] = np.array([0.2, -0.05, 0.0, 0.0, 0.0, 0.0, -4e-3, 1e-3], np.float32)
+    v["lens_distortion_second_pipeline_C8"] = (s, dict(distortion=True, render_points_in_all_lower_resolutions=False), None)
     # seeded random corners of the parameter space: K = 1 / 4, L = 2 / 5 / 6 / 7, odd image sizes, texture index, drop-out
     rr = np.random.default_rng(2024)
     for i in range(8):
@@ -184,8 +193,12 @@ def test_forward_backward_parity(name, oracle_lib, cuda_lib):
     gintr = ns.intrinsics.intrinsics.grad.cpu().numpy()
     for b in range(len(frames)):
         assert rel_err(gpose[b], ref["pose"][b]) <= TOL_GRAD, "pose gradient"
-        assert rel_err(gintr[b, :5], ref["intrinsics"][b]) <= TOL_GRAD, "intrinsics gradient"
-        assert np.all(gintr[b, 5:] == 0)
+        assert rel_err(gintr[b, :5], ref["intrinsics"][b][:5]) <= TOL_GRAD, "intrinsics gradient"
+        if kw.get("distortion"):
+            assert np.all(ref["intrinsics"][b][5:] != 0)
+            assert rel_err(gintr[b, 5:], ref["intrinsics"][b][5:]) <= TOL_GRAD, "distortion coefficient gradient"
+        else:
+            assert np.all(gintr[b, 5:] == 0)
 
 
 def test_forward_inference_matches_training_output(oracle_lib, cuda_lib):

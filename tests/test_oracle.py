@@ -400,6 +400,90 @@ def test_backward_against_finite_differences(oracle_lib):
     assert np.median(errs) < 5e-2, errs
 
 
+# ---- lens distortion (the 8-coefficient model of saiga's distortNormalizedPoint, restated) ----
+def _one_point(x, y, z, intr_extra, fx=100.0, w=64, h=48, **kw):
+    pos = np.array([[x, y, z, 0.0]], np.float32)
+    sa = oracle.SceneArrays(pos, np.array([-6.0], np.float32), np.ones((4, 1), np.float32), np.array([0.5], np.float32),
+                            np.full(4, 0.25, np.float32))
+    k = intr(fx, w, h)
+    k[5:] = intr_extra
+    f = oracle.forward(sa, oracle.make_view(w, h, IDENT, k), oracle.make_params(1, 16, True, **kw))
+    return f
+
+
+def test_distortion_known_answers(oracle_lib):
+    fx, z = 100.0, 2.0
+    x, y = 0.2, -0.1  # normalised coordinates (x / z, y / z) = (0.1, -0.05)
+    nx, ny = 0.1, -0.05
+    r2 = nx * nx + ny * ny
+    # coefficients are ignored unless the distortion flag is set
+    f = _one_point(x, y, z, [0.5, 0, 0, 0, 0, 0, 0, 0])
+    assert abs(f.points()[2][0, 0] - (32 + fx * nx)) < 1e-4
+    # k1 only: radial factor 1 + k1 r^2
+    f = _one_point(x, y, z, [0.5, 0, 0, 0, 0, 0, 0, 0], distortion=True)
+    u, v = f.points()[2][0, :2]
+    assert abs(u - (32 + fx * nx * (1 + 0.5 * r2))) < 1e-4 and abs(v - (24 + fx * ny * (1 + 0.5 * r2))) < 1e-4
+    # the rational form: (1 + k1 r2 + k2 r4 + k3 r6) / (1 + k4 r2 + k5 r4 + k6 r6)
+    ks = [0.3, -0.2, 0.1, 0.05, -0.03, 0.02]
+    f = _one_point(x, y, z, ks + [0, 0], distortion=True)
+    rad = (1 + ks[0] * r2 + ks[1] * r2 ** 2 + ks[2] * r2 ** 3) / (1 + ks[3] * r2 + ks[4] * r2 ** 2 + ks[5] * r2 ** 3)
+    u, v = f.points()[2][0, :2]
+    assert abs(u - (32 + fx * nx * rad)) < 1e-4 and abs(v - (24 + fx * ny * rad)) < 1e-4
+    # tangential terms: x' = x + 2 p1 x y + p2 (r2 + 2 x^2), y' = y + p1 (r2 + 2 y^2) + 2 p2 x y
+    p1, p2 = 0.01, -0.02
+    f = _one_point(x, y, z, [0, 0, 0, 0, 0, 0, p1, p2], distortion=True)
+    u, v = f.points()[2][0, :2]
+    assert abs(u - (32 + fx * (nx + 2 * p1 * nx * ny + p2 * (r2 + 2 * nx * nx)))) < 1e-4
+    assert abs(v - (24 + fx * (ny + p1 * (r2 + 2 * ny * ny) + 2 * p2 * nx * ny))) < 1e-4
+    # outside the cut-off radius the point is culled, inside it is drawn
+    assert _one_point(x, y, z, [0] * 8, distortion=True, dist_cutoff=0.1).V == 0  # r = 0.1118 > 0.1
+    assert _one_point(x, y, z, [0] * 8, distortion=True, dist_cutoff=0.12).V == 1
+
+
+def test_distortion_backward_against_finite_differences(oracle_lib):
+    """Gradients with respect to the eight distortion coefficients, the pinhole coefficients and the positions through a
+    distorted projection (one layer, consistent background weight, as in the test above)."""
+    s = scenes.tiny(n_points=300, width=32, height=24, num_layers=1, n_views=1, seed=6, fx=40.0, size_range=(0.01, 0.05))
+    s.confidence[:] = np.clip(s.confidence * 0.6 + 0.1, 0, 1)
+    coeff = np.array([-0.12, 0.05, -0.01, 0.03, -0.02, 0.004, 2e-3, -3e-3], np.float32)
+    g = np.random.default_rng(3).normal(size=s.channels * 32 * 24).astype(np.float32)
+
+    def run(intr13, position=None):
+        sa = oracle.SceneArrays.from_scene(s) if position is None else oracle.SceneArrays(position, s.point_size, s.texture, s.confidence, s.background)
+        v = oracle.make_view(s.width, s.height, s.poses[0], intr13)
+        return oracle.forward(sa, v, oracle.make_params(1, 16, True, bg_uses_Tn=True, distortion=True))
+
+    k0 = s.intrinsics[0].copy()
+    k0[5:] = coeff
+    f0 = run(k0)
+    grads = f0.backward(g)
+    assert grads["intrinsics"].shape == (13,) and np.all(grads["intrinsics"][5:] != 0)
+    # the loss is piecewise smooth in every camera coefficient (a sum over all points): central differences
+    steps = [1e-2, 1e-2, 1e-3, 1e-3, 1e-4] + [2e-3] * 6 + [2e-4] * 2
+    for k in range(13):
+        lo, hi = k0.copy(), k0.copy()
+        lo[k] -= steps[k]
+        hi[k] += steps[k]
+        fd = (_loss(run(hi), g) - _loss(run(lo), g)) / (2 * steps[k])
+        ref = grads["intrinsics"][k]
+        assert abs(fd - ref) <= 0.08 * max(abs(fd), abs(ref)) + 1e-3 * np.abs(grads["intrinsics"]).max(), (k, fd, ref)
+    # positions through J_p_dis
+    rng = np.random.default_rng(4)
+    vis = np.nonzero(f0.points()[0] > 0)[0]
+    errs = []
+    for i in rng.choice(vis, 8, replace=False):
+        for ax in range(2):
+            lo, hi = s.position.copy(), s.position.copy()
+            lo[i, ax] -= 2e-4
+            hi[i, ax] += 2e-4
+            fd = (_loss(run(k0, hi), g) - _loss(run(k0, lo), g)) / 4e-4
+            errs.append(abs(fd - grads["position"][i, ax]) / max(abs(fd), abs(grads["position"][i, ax]), 1e-2))
+    assert np.median(errs) < 5e-2, errs
+    # and the distortion changes the picture at all
+    k1 = s.intrinsics[0].copy()
+    assert not np.array_equal(run(k1).pyramid_flat(), f0.pyramid_flat())
+
+
 GOLDEN = __import__("os").path.join(__import__("os").path.dirname(__file__), "golden", "tiny_scene.npz")
 
 

@@ -52,7 +52,7 @@ class TripsRenderParams(C.Structure):
                 ("drop_out_radius_threshold", C.c_float), ("viewer_only", C.c_int), ("stability_cutoff_value", C.c_float),
                 ("bg_uses_Tn", C.c_int), ("confidence_is_raw", C.c_int), ("confidence_scale", C.c_float), ("texture_abs", C.c_int),
                 ("use_layer_point_size", C.c_int), ("render_points_in_all_lower_resolutions", C.c_int), ("combine_lists", C.c_int),
-                ("saturated_alpha_accumulation", C.c_int)]
+                ("saturated_alpha_accumulation", C.c_int), ("distortion", C.c_int), ("dist_cutoff", C.c_float)]
 
 
 class TripsGrads(C.Structure):

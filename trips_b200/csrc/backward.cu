@@ -471,13 +471,18 @@ cudaError_t launch_blend_backward(const ScenePtrs& sc, const CamConst* cams, con
 // zero distortion), the softplus derivative for the size, and adds the entry's gradients to its point
 // (one set of atomics per visible point and view instead of one per fragment).  Pose and intrinsics gradients
 // are summed per view in double (RenderBackward.cu:453-466,587-611).
-template <int C, bool CAM_GRADS>
+// DIST: lens distortion between the division by z and the pinhole matrix (TripsRenderParams.distortion): the
+// view-space position then comes from the entry's world position (the stored projection cannot be undistorted in
+// closed form), the chain goes through J_p_dis^T and the eight coefficients receive J_dis_dis^T
+// (PointRendererHelper.h:468-491).  A separate instantiation: the plain pinhole carries none of it.
+template <int C, bool CAM_GRADS, bool DIST>
 __global__ __launch_bounds__(256) void entry_grad_finish_kernel(FwdBuffers fb, BwdBuffers bb, const CamConst* __restrict__ cams, int B)
 {
     constexpr int GS = egrad_stride(C);
     constexpr int PS = egrad_stride(C);  // per-point row: xyz + size | descriptor row
+    constexpr int NA = CAM_GRADS ? (DIST ? 19 : 11) : 1;  // 6 pose + 5 pinhole (+ 8 distortion) sums per view
     __shared__ CamConst cam;
-    __shared__ double s_acc[8][11];
+    __shared__ double s_acc[8][NA];
     const int b = blockIdx.y;
     if (threadIdx.x < sizeof(CamConst) / 4) ((int*)&cam)[threadIdx.x] = ((const int*)&cams[b])[threadIdx.x];
     __syncthreads();
@@ -485,9 +490,9 @@ __global__ __launch_bounds__(256) void entry_grad_finish_kernel(FwdBuffers fb, B
     const unsigned long long first = fb.entry_base[b], n = fb.entry_base[b + 1] - first;
     const float4* head   = fb.ent_head + first * 2;
     const float* egrad   = bb.egrad + first * GS;
-    double acc[CAM_GRADS ? 11 : 1];
+    double acc[NA];
 #pragma unroll
-    for (int k = 0; k < (CAM_GRADS ? 11 : 1); ++k) acc[k] = 0.0;
+    for (int k = 0; k < NA; ++k) acc[k] = 0.0;
     for (unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
          i += (unsigned long long)gridDim.x * blockDim.x)
     {
@@ -502,8 +507,14 @@ __global__ __launch_bounds__(256) void entry_grad_finish_kernel(FwdBuffers fb, B
         // pinhole matrix gives the normalised coordinates, the stored depth scales them.  This spares the read of the
         // entry's world position (a third of the kernel's DRAM traffic); the round trip costs a few 1e-7 relative,
         // far inside the gradient tolerance.
-        const float vz = e1.y;
+        float vz = e1.y;
         float vx, vy;
+        if constexpr (DIST)
+        {
+            const float4 wp = *reinterpret_cast<const float4*>(fb.ent_tail + (first + i) * tail_stride(C));  // world xyz | texture index
+            transform_point(cam, wp.x, wp.y, wp.z, vx, vy, vz);
+        }
+        else
         {
             const float du = e0.x - cam.cenx, dv = e0.y - cam.ceny;
             const float idet = 1.f / (cam.r00 * cam.r11 - cam.r01 * cam.r10);
@@ -523,8 +534,23 @@ __global__ __launch_bounds__(256) void entry_grad_finish_kernel(FwdBuffers fb, B
             const float gr1 = cam.r01 * s4.x + cam.r11 * s4.y;
             const float gk0 = cam.cfx * gr0;
             const float gk1 = cam.cs * gr0 + cam.cfy * gr1;
-            const float gn0 = cam.fx * gk0;
-            const float gn1 = cam.s * gk0 + cam.fy * gk1;
+            float gn0 = cam.fx * gk0;
+            float gn1 = cam.s * gk0 + cam.fy * gk1;
+            float kx = vx * iz, ky = vy * iz;  // the normalised coordinates the pinhole matrix sees
+            if constexpr (DIST)
+            {
+                float xd, yd, Jd[4], Jk[16];
+                distort_point(cam, kx, ky, xd, yd, Jd, CAM_GRADS ? Jk : nullptr);
+                if constexpr (CAM_GRADS)
+                {
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) acc[11 + k] += (double)(Jk[k] * gn0 + Jk[8 + k] * gn1);
+                }
+                const float g0 = Jd[0] * gn0 + Jd[2] * gn1;
+                const float g1 = Jd[1] * gn0 + Jd[3] * gn1;
+                gn0 = g0, gn1 = g1;
+                kx = xd, ky = yd;
+            }
             const float gv0 = iz * gn0;
             const float gv1 = iz * gn1;
             const float gv2 = (-vx * iz * iz) * gn0 + (-vy * iz * iz) * gn1;
@@ -535,7 +561,7 @@ __global__ __launch_bounds__(256) void entry_grad_finish_kernel(FwdBuffers fb, B
             atomicAdd(reinterpret_cast<float4*>(bb.g_point + row * PS), make_float4(gp0, gp1, gp2, gl));
             if constexpr (CAM_GRADS)
             {
-                const float nx = vx * iz, ny = vy * iz;
+                const float nx = kx, ny = ky;
                 acc[0] += (double)gv0;
                 acc[1] += (double)gv1;
                 acc[2] += (double)gv2;
@@ -568,13 +594,13 @@ __global__ __launch_bounds__(256) void entry_grad_finish_kernel(FwdBuffers fb, B
     {
         const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 #pragma unroll
-        for (int k = 0; k < 11; ++k)
+        for (int k = 0; k < NA; ++k)
         {
             const double v = warp_sum_d(acc[k]);
             if (lane == 0) s_acc[warp][k] = v;
         }
         __syncthreads();
-        if (threadIdx.x < 11)
+        if (threadIdx.x < NA)
         {
             double v = 0.0;
             for (int w = 0; w < 8; ++w) v += s_acc[w][threadIdx.x];
@@ -582,8 +608,10 @@ __global__ __launch_bounds__(256) void entry_grad_finish_kernel(FwdBuffers fb, B
             {
                 if (threadIdx.x < 6)
                     atomicAdd(bb.g_pose + (size_t)b * 6 + threadIdx.x, v);
-                else
+                else if (threadIdx.x < 11)
                     atomicAdd(bb.g_k + (size_t)b * 5 + (threadIdx.x - 6), v);
+                else
+                    atomicAdd(bb.g_dis + (size_t)b * 8 + (threadIdx.x - 11), v);
             }
         }
     }
@@ -660,7 +688,7 @@ __global__ __launch_bounds__(256) void unpack_point_kernel(const float* __restri
 }
 
 __global__ void unpack_small_kernel(int C, int B, const CamConst* __restrict__ cams, const double* g_bg, const double* g_pose,
-                                    const double* g_k, float* out_bg, double* out_pose, float* out_intr)
+                                    const double* g_k, const double* g_dis, float* out_bg, double* out_pose, float* out_intr)
 {
     // launched with one thread: B and C are tiny, and several views may share an image / camera index
     if (out_bg)
@@ -670,7 +698,10 @@ __global__ void unpack_small_kernel(int C, int B, const CamConst* __restrict__ c
         if (out_pose)
             for (int k = 0; k < 6; ++k) out_pose[(size_t)cams[b].image_index * 6 + k] += g_pose[b * 6 + k];
         if (out_intr)
+        {
             for (int k = 0; k < 5; ++k) out_intr[(size_t)cams[b].camera_index * 13 + k] += (float)g_k[b * 5 + k];
+            for (int k = 0; k < 8; ++k) out_intr[(size_t)cams[b].camera_index * 13 + 5 + k] += (float)g_dis[b * 8 + k];  // zero without distortion
+        }
     }
 }
 
@@ -684,10 +715,14 @@ cudaError_t launch_unpack_grads(const ScenePtrs& sc, const CamConst* cams, int B
         dim3 grid(bx, B);
 #define TRIPS_FIN_CASE(CC)                                                                                      \
     case CC:                                                                                                    \
-        if (cam_grads)                                                                                          \
-            entry_grad_finish_kernel<CC, true><<<grid, 256, 0, st>>>(fb, bb, cams, B);                          \
+        if (cam_grads && pr.distortion)                                                                         \
+            entry_grad_finish_kernel<CC, true, true><<<grid, 256, 0, st>>>(fb, bb, cams, B);                    \
+        else if (cam_grads)                                                                                     \
+            entry_grad_finish_kernel<CC, true, false><<<grid, 256, 0, st>>>(fb, bb, cams, B);                   \
+        else if (pr.distortion)                                                                                 \
+            entry_grad_finish_kernel<CC, false, true><<<grid, 256, 0, st>>>(fb, bb, cams, B);                   \
         else                                                                                                    \
-            entry_grad_finish_kernel<CC, false><<<grid, 256, 0, st>>>(fb, bb, cams, B);                         \
+            entry_grad_finish_kernel<CC, false, false><<<grid, 256, 0, st>>>(fb, bb, cams, B);                  \
         break;
         if (sc.N > 0)
         {
@@ -738,7 +773,7 @@ cudaError_t launch_unpack_grads(const ScenePtrs& sc, const CamConst* cams, int B
         }
 #undef TRIPS_UNPACK_CASE
     }
-    unpack_small_kernel<<<1, 1, 0, st>>>(sc.C, B, cams, bb.g_bg, bb.g_pose, bb.g_k, out.background, out.pose_tangent,
+    unpack_small_kernel<<<1, 1, 0, st>>>(sc.C, B, cams, bb.g_bg, bb.g_pose, bb.g_k, bb.g_dis, out.background, out.pose_tangent,
                                          out.intrinsics);
     return cudaGetLastError();
 }

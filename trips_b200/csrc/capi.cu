@@ -459,7 +459,7 @@ static int forward_views(TripsContext* ctx, const TripsScene* scene, const Trips
     CU_CHECK(ctx, cudaMemcpyAsync(ctx->views.p, views, sizeof(TripsView) * B, cudaMemcpyHostToDevice, st));
     STAGE(ctx, TRIPS_STAGE_SETUP, 1, st,
           launch_setup_cams((const TripsView*)ctx->views.p, B, scene->poses, scene->n_images, scene->intrinsics,
-                            scene->n_cameras, (CamConst*)ctx->cams.p, fb.stats, st));
+                            scene->n_cameras, params->distortion, params->dist_cutoff, (CamConst*)ctx->cams.p, fb.stats, st));
     const CamConst* cams = (const CamConst*)ctx->cams.p;
     // crowded: the last call that reported back saw more than kHotKey visible points in one (view, bin, tile) group
     STAGE(ctx, TRIPS_STAGE_BIN_POINTS, bin_count_launches((int)N, B), st,
@@ -623,7 +623,7 @@ int trips_backward(TripsContext* ctx, const TripsScene* scene, const float* cons
     CU_CHECK(ctx, ensure(ctx->egrad, sizeof(float) * GS * ctx->entry_cap + 16));  // one row per entry the arrays can hold
     CU_CHECK(ctx, ensure(ctx->g_point, sizeof(float) * GS * N + 16));
     CU_CHECK(ctx, ensure(ctx->g_conf_pt, sizeof(float) * N + 16));
-    const size_t small_bytes = sizeof(double) * (TRIPS_MAX_CHANNELS + (size_t)B * 11);
+    const size_t small_bytes = sizeof(double) * (TRIPS_MAX_CHANNELS + (size_t)B * 19);  // background | per view: 6 pose, 5 pinhole, 8 distortion
     CU_CHECK(ctx, ensure(ctx->g_small, small_bytes));
     BwdBuffers bb;
     bb.egrad        = (float*)ctx->egrad.p;
@@ -632,6 +632,7 @@ int trips_backward(TripsContext* ctx, const TripsScene* scene, const float* cons
     bb.g_bg         = (double*)ctx->g_small.p;
     bb.g_pose       = bb.g_bg + TRIPS_MAX_CHANNELS;
     bb.g_k          = bb.g_pose + (size_t)B * 6;
+    bb.g_dis        = bb.g_k + (size_t)B * 5;
     ScenePtrs sp  = scene_ptrs(scene);
     FwdBuffers fb = fwd_buffers(ctx);
     // all accumulators start from zero (timed with the gradient bookkeeping of the unpack stage)

@@ -49,6 +49,9 @@ struct CamConst
     float r00, r01, r10, r11;
     float cenx, ceny;
     int image_index, camera_index;
+    float k1, k2, k3, k4, k5, k6, p1, p2;  // lens distortion (TripsRenderParams.distortion)
+    float cut2;                            // dist_cutoff^2
+    int dist;                              // apply the distortion and the cut-off radius
 };
 
 struct LayerPtrs
@@ -133,6 +136,7 @@ struct BwdBuffers
     double* g_bg;         // [C]
     double* g_pose;       // [B,6]
     double* g_k;          // [B,5]
+    double* g_dis;        // [B,8] distortion coefficients
 };
 
 // The reference has two forward pipelines (PointRenderer.cu:730-731): the second (CountTiled, CollectTiled2[Pointsize],
@@ -167,7 +171,45 @@ __device__ __forceinline__ void transform_point(const CamConst& V, float px, flo
     oz       = ((pz + V.qw * uz) + cz) + V.tz;
 }
 
-// ProjectPointPinholeWoNormal with zero distortion + crop transform + crop rotation
+// saiga's distortNormalizedPoint restated: the 8-coefficient rational model with tangential terms (the operation order
+// is the CPU oracle's).  J (optional): d(xd, yd) / d(x, y) row-major; Jk (optional): d(xd, yd) / d(k1..k6, p1, p2), two
+// rows of 8.
+__device__ __forceinline__ void distort_point(const CamConst& c, float x, float y, float& xd, float& yd, float* J, float* Jk)
+{
+    const float x2 = x * x, y2 = y * y;
+    const float r2 = x2 + y2, xy2 = 2.f * x * y;
+    const float r4 = r2 * r2, r6 = r4 * r2;
+    const float A  = ((1.f + c.k1 * r2) + c.k2 * r4) + c.k3 * r6;
+    const float B  = ((1.f + c.k4 * r2) + c.k5 * r4) + c.k6 * r6;
+    const float iB = 1.f / B;
+    const float radial = A * iB;
+    const float tx = c.p1 * xy2 + c.p2 * (r2 + 2.f * x2);
+    const float ty = c.p1 * (r2 + 2.f * y2) + c.p2 * xy2;
+    xd = x * radial + tx;
+    yd = y * radial + ty;
+    if (J)
+    {
+        const float dA = (c.k1 + 2.f * c.k2 * r2) + 3.f * c.k3 * r4;
+        const float dB = (c.k4 + 2.f * c.k5 * r2) + 3.f * c.k6 * r4;
+        const float dr = (dA * B - A * dB) * iB * iB;  // d radial / d r2
+        J[0] = radial + x * dr * (2.f * x) + (2.f * c.p1 * y + 6.f * c.p2 * x);
+        J[1] = x * dr * (2.f * y) + (2.f * c.p1 * x + 2.f * c.p2 * y);
+        J[2] = y * dr * (2.f * x) + (2.f * c.p1 * x + 2.f * c.p2 * y);
+        J[3] = radial + y * dr * (2.f * y) + (6.f * c.p1 * y + 2.f * c.p2 * x);
+    }
+    if (Jk)
+    {
+        const float AiB2 = A * iB * iB;
+        Jk[0] = x * r2 * iB, Jk[1] = x * r4 * iB, Jk[2] = x * r6 * iB;
+        Jk[3] = -x * AiB2 * r2, Jk[4] = -x * AiB2 * r4, Jk[5] = -x * AiB2 * r6;
+        Jk[6] = xy2, Jk[7] = r2 + 2.f * x2;
+        Jk[8] = y * r2 * iB, Jk[9] = y * r4 * iB, Jk[10] = y * r6 * iB;
+        Jk[11] = -y * AiB2 * r2, Jk[12] = -y * AiB2 * r4, Jk[13] = -y * AiB2 * r6;
+        Jk[14] = r2 + 2.f * y2, Jk[15] = xy2;
+    }
+}
+
+// ProjectPointPinholeWoNormal + crop transform + crop rotation
 // (PointRendererHelper.h:232-253, RenderForward.cu:302-303,69-76).
 __device__ __forceinline__ void project_point(const CamConst& c, float px, float py, float pz, float& u, float& v, float& z)
 {
@@ -177,6 +219,15 @@ __device__ __forceinline__ void project_point(const CamConst& c, float px, float
     float iz = 1.f / vz;
     float nx = vx * iz;
     float ny = vy * iz;
+    if (c.dist)  // uniform per view
+    {
+        // outside the cut-off radius distortNormalizedPoint returns (100000, 100000) and the caller sets z = 0
+        // (PointRendererHelper.h:246-249)
+        if (nx * nx + ny * ny > c.cut2) z = 0.f;
+        float xd, yd;
+        distort_point(c, nx, ny, xd, yd, nullptr, nullptr);
+        nx = xd, ny = yd;
+    }
     float ix = (c.fx * nx + c.s * ny) + c.cx;
     float iy = c.fy * ny + c.cy;
     float jx = (c.cfx * ix + c.cs * iy) + c.ccx;
@@ -263,7 +314,7 @@ __device__ __forceinline__ void tile_pixel(const Geom& g, int tile, int lane, in
 
 // ---- launchers (forward.cu / backward.cu / adam.cu) ----
 cudaError_t launch_setup_cams(const TripsView* d_views, int B, const double* poses, int n_images, const float* intrinsics,
-                              int n_cameras, CamConst* cams, DevStats* stats, cudaStream_t st);
+                              int n_cameras, int distortion, float dist_cutoff, CamConst* cams, DevStats* stats, cudaStream_t st);
 cudaError_t launch_bin_count(const ScenePtrs& sc, const CamConst* cams, const Geom& g, const TripsRenderParams& pr, int B,
                              const FwdBuffers& fb, unsigned long long entry_cap, bool hot, int sm_count, cudaStream_t st);
 cudaError_t launch_bin_scatter(const ScenePtrs& sc, const CamConst* cams, const Geom& g, const TripsRenderParams& pr, int B,

@@ -14,8 +14,8 @@ namespace trips
 // per-view camera constants
 // ------------------------------------------------------------------------------------------------------------
 __global__ void setup_cams_kernel(const TripsView* __restrict__ views, int B, const double* __restrict__ poses, int n_images,
-                                  const float* __restrict__ intrinsics, int n_cameras, CamConst* __restrict__ cams,
-                                  DevStats* stats)
+                                  const float* __restrict__ intrinsics, int n_cameras, int distortion, float dist_cutoff,
+                                  CamConst* __restrict__ cams, DevStats* stats)
 {
     int b = blockIdx.x * blockDim.x + threadIdx.x;
     if (b >= B) return;
@@ -52,7 +52,10 @@ __global__ void setup_cams_kernel(const TripsView* __restrict__ views, int B, co
     c.s  = k[4];
     bool dist = false;
     for (int i = 5; i < 13; ++i) dist |= (k[i] != 0.f);
-    if (dist) atomicOr(&stats->status, TRIPS_DEV_NONZERO_DISTORTION);
+    if (dist && !distortion) atomicOr(&stats->status, TRIPS_DEV_NONZERO_DISTORTION);  // a plain pinhole was asked for: ignored
+    c.k1 = k[5], c.k2 = k[6], c.k3 = k[7], c.k4 = k[8], c.k5 = k[9], c.k6 = k[10], c.p1 = k[11], c.p2 = k[12];
+    c.cut2 = dist_cutoff * dist_cutoff;
+    c.dist = distortion ? 1 : 0;
     c.cfx  = v.crop_transform[0];
     c.cfy  = v.crop_transform[1];
     c.ccx  = v.crop_transform[2];
@@ -70,9 +73,9 @@ __global__ void setup_cams_kernel(const TripsView* __restrict__ views, int B, co
 }
 
 cudaError_t launch_setup_cams(const TripsView* d_views, int B, const double* poses, int n_images, const float* intrinsics,
-                              int n_cameras, CamConst* cams, DevStats* stats, cudaStream_t st)
+                              int n_cameras, int distortion, float dist_cutoff, CamConst* cams, DevStats* stats, cudaStream_t st)
 {
-    setup_cams_kernel<<<(B + 63) / 64, 64, 0, st>>>(d_views, B, poses, n_images, intrinsics, n_cameras, cams, stats);
+    setup_cams_kernel<<<(B + 63) / 64, 64, 0, st>>>(d_views, B, poses, n_images, intrinsics, n_cameras, distortion, dist_cutoff, cams, stats);
     return cudaGetLastError();
 }
 

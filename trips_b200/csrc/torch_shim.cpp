@@ -89,6 +89,12 @@ void NeuralRenderInfo::set_pipeline_flags(bool use_layer_point_size, bool render
     params.saturated_alpha_accumulation           = saturated_alpha_accumulation ? 1 : 0;
 }
 
+void NeuralRenderInfo::set_distortion(bool distortion, double dist_cutoff)
+{
+    params.distortion  = distortion ? 1 : 0;
+    params.dist_cutoff = (float)dist_cutoff;
+}
+
 int64_t NeuralRenderInfo::last_status()
 {
     return cache->handle ? (int64_t)trips_last_status(cache->handle, c10::cuda::getCurrentCUDAStream().stream()) : 0;
@@ -495,6 +501,7 @@ TORCH_LIBRARY(trips_b200, m)
         .def("set_params", &NeuralRenderInfo::set_params)
         .def("set_texture_preparation", &NeuralRenderInfo::set_texture_preparation)
         .def("set_pipeline_flags", &NeuralRenderInfo::set_pipeline_flags)
+        .def("set_distortion", &NeuralRenderInfo::set_distortion)
         .def("last_status", &NeuralRenderInfo::last_status);
     m.class_<PointRenderModuleHolder>("PointRenderModule")
         .def(torch::init<int64_t>())

@@ -43,7 +43,7 @@ struct NeuralRenderInfo : torch::CustomClassHolder
     // scene (NeuralScene: point_cloud_cuda, texture, poses, intrinsics)
     Tensor texture, background_color, t_position, poses_se3, tangent_poses, intrinsics, confidence_value_of_point, t_point_size, t_index;
     std::vector<TripsView> images;  // ReducedImageInfo, SceneData.h:40-61
-    TripsRenderParams params{8, 16, 0, 0, 0.f, 0, 0.f, 0, 0, 10.f, 0, 1, 1, 0, 0};  // the reference's defaults (Settings.h)
+    TripsRenderParams params{8, 16, 0, 0, 0.f, 0, 0.f, 0, 0, 10.f, 0, 1, 1, 0, 0, 0, 20.f};  // the reference's defaults (Settings.h)
     double dropout     = 0.0;
     int64_t num_layers = 8;
     bool train         = false;
@@ -62,6 +62,8 @@ struct NeuralRenderInfo : torch::CustomClassHolder
     // the flags that select the reference's second forward pipeline (RenderParams, Settings.h; PointRenderer.cu:730-731)
     void set_pipeline_flags(bool use_layer_point_size, bool render_points_in_all_lower_resolutions, bool combine_lists,
                             bool saturated_alpha_accumulation);
+    // lens distortion: apply the 8 coefficients of the intrinsics rows and the cut-off radius (RenderParams::dist_cutoff)
+    void set_distortion(bool distortion, double dist_cutoff);
     int64_t last_status();
 };
 

@@ -59,6 +59,9 @@ class RenderParams:
     confidence_is_raw: bool = False
     confidence_scale: float = 10.0
     texture_abs: bool = False
+    # lens distortion: apply the 8 coefficients of the intrinsics rows and the cut-off radius (RenderParams::dist_cutoff)
+    distortion: bool = False
+    dist_cutoff: float = 20.0
 
 
 @dataclass
@@ -154,7 +157,7 @@ class PointRendererCache:
                                       p.drop_out_radius_threshold, int(p.viewer_only), p.stability_cutoff_value,
                                       int(p.bg_uses_Tn), int(p.confidence_is_raw), float(p.confidence_scale), int(p.texture_abs),
                                       int(p.use_layer_point_size), int(p.render_points_in_all_lower_resolutions), int(p.combine_lists),
-                                      int(p.saturated_alpha_accumulation))
+                                      int(p.saturated_alpha_accumulation), int(p.distortion), float(p.dist_cutoff))
 
     # -- forward / backward -----------------------------------------------------------------------------------------
     def forward(self, info: NeuralRenderInfo, texture, background_color, points, intrinsics, confidence, point_size,
