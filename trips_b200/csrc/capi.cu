@@ -473,7 +473,7 @@ static int forward_views(TripsContext* ctx, const TripsScene* scene, const Trips
         fb           = fwd_buffers(ctx);
     }
     STAGE(ctx, TRIPS_STAGE_BIN_POINTS, bin_scatter_launches((int)N, B), st, launch_bin_scatter(sp, cams, g, *params, B, fb, ctx->crowded, ctx->sm_count, st));
-    if (N > 0) STAGE(ctx, TRIPS_STAGE_COUNT, 1, st, launch_count(sp, g, B, fb, strict_layers(*params), ctx->sm_count, st));
+    if (N > 0) STAGE(ctx, TRIPS_STAGE_COUNT, 1, st, launch_count(sp, g, B, fb, strict_layers(*params), wait_for_sizes ? (unsigned long long)h_stats->visible : ctx->need_entries, ctx->sm_count, st));
     {
         FwdBuffers fscan = fb;
         if (wait_for_sizes) fscan.frag_cap = ~0ull;  // sizing pass: the list buffer is grown below, nothing can overflow yet

@@ -330,7 +330,9 @@ cudaError_t launch_point_rank(const float4* position, int N, unsigned* scratch, 
                               int sm_count, cudaStream_t st);
 cudaError_t launch_scan(const Geom& g, int B, int k_keep, const FwdBuffers& fb, int nchunks, cudaStream_t st);
 // strict: an entry's layers start at the layer below log2(size) instead of layer 0 (strict_layers above)
-cudaError_t launch_count(const ScenePtrs& sc, const Geom& g, int B, const FwdBuffers& fb, bool strict, int sm_count, cudaStream_t st);
+// entries_hint: the number of entries of the call as far as the host knows it (selects the size of the work tickets)
+cudaError_t launch_count(const ScenePtrs& sc, const Geom& g, int B, const FwdBuffers& fb, bool strict, unsigned long long entries_hint, int sm_count,
+                         cudaStream_t st);
 cudaError_t launch_collect(const ScenePtrs& sc, const Geom& g, int B, const FwdBuffers& fb, bool strict, int sm_count, cudaStream_t st);
 // top-K + blend by the rules of the reference's second forward pipeline (one thread per pixel)
 cudaError_t launch_second_blend(const ScenePtrs& sc, const Geom& g, const TripsRenderParams& pr, int B, const FwdBuffers& fb,

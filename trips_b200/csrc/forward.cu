@@ -959,6 +959,10 @@ cudaError_t launch_scan(const Geom& g, int B, int k_keep, const FwdBuffers& fb, 
 // a whole point, and travels with the fragment.
 // ------------------------------------------------------------------------------------------------------------
 constexpr int kWinChunkCount   = 4096;  // entries per block ticket, counting pass
+constexpr int kWinSparse       = 512;   // entries of a bin up to which the window of shared-memory counters is bypassed
+constexpr int kWinChunkCountFew = 1024;  // the same when the call has too few entries for kWinTicketsPerBlock tickets of 4096 per resident block:
+constexpr int kWinTicketsPerBlock = 6;   // measured count pass, tickets of 4096 / 1024: config 4 (2 views, 16 M entries) 0.58 / 0.25 ms, config 2
+                                         // (4 M) 0.093 / 0.09 ms; config 3 (27 M) 0.31 / 0.52 ms, config 5 (39 M) 0.40 / 0.53 ms
 constexpr int kWinChunkCollect = 1024;  // and collecting pass: the lists a chunk writes to must stay in L2 until complete (measured with tile-ordered entries: 256 1.80 ms, 512 1.46 ms, 1024 1.35 ms, 2048 1.47 ms)
 constexpr int kWinThreads    = 256;
 constexpr int kWinBlocksPerSM = 8;  // grid size of the window kernels, in blocks per SM
@@ -1127,8 +1131,53 @@ __device__ __forceinline__ uint64_t evict_last_policy()
     return policy;
 }
 
+// A bin with few entries inside a ticket (sky, far ground: a ticket can span hundreds of such bins) is not worth clearing
+// and flushing a window of shared-memory counters with three block barriers: its footprints go straight to the pixels'
+// global counters.  (On a 2560x1440 view of 20 M points with half of the bins nearly empty, the blocks that drew the
+// sparse tickets ran 12 times longer than the others.)  Not inlined: the dense path keeps its registers.
 template <bool COLLECT, bool STRICT>
-__global__ __launch_bounds__(kWinThreads, kWinMinBlocks) void window_kernel(const __grid_constant__ Geom g, FwdBuffers fb, int B)
+__device__ __noinline__ void sparse_bin_footprints(const Geom& g, const float4* __restrict__ head, uint32_t lo, uint32_t hi, uint8_t* queue,
+                                                   uint32_t* pixel_ctr, uint4* frags, uint64_t keep)
+{
+    for_each_footprint<COLLECT, STRICT>(head, lo, hi, queue, g.L, [&](const float4& e0, const float4& e1, float x, float y, int layer, uint32_t ei) {
+        const int px = __float2int_rd(x), py = __float2int_rd(y);
+        const int Wl = g.W[layer];
+        uint32_t* c  = pixel_ctr + g.base[layer] + py * Wl + px;
+        if constexpr (!COLLECT)
+        {
+            atomicAdd(c, 1u);
+            atomicAdd(c + 1, 1u);
+            atomicAdd(c + Wl, 1u);
+            atomicAdd(c + Wl + 1, 1u);
+        }
+        else
+        {
+            const float conf   = e0.w;
+            const uint32_t pid = __float_as_uint(e1.x), zb = __float_as_uint(e1.y);
+            const float lf  = layer_factor(e0.z, layer, g.L, nullptr);
+            const float dx0 = fabsf(x - (float)px), dx1 = fabsf(x - (float)(px + 1));
+            const float dy0 = fabsf(y - (float)py), dy1 = fabsf(y - (float)(py + 1));
+            auto alpha = [&](float dx, float dy) {
+                float bl = (1.f - dx) * (1.f - dy);
+                if (dx > 1.f || dy > 1.f) bl = 0.f;
+                float a = bl * conf;
+                a *= lf;
+                return __float_as_uint(a);
+            };
+            const uint32_t s00 = atomicAdd(c, 1u);
+            const uint32_t s10 = atomicAdd(c + 1, 1u);
+            const uint32_t s01 = atomicAdd(c + Wl, 1u);
+            const uint32_t s11 = atomicAdd(c + Wl + 1, 1u);
+            store_frag(frags + s00, make_uint4(pid, zb, alpha(dx0, dy0), ei), keep);
+            store_frag(frags + s10, make_uint4(pid, zb, alpha(dx1, dy0), ei), keep);
+            store_frag(frags + s01, make_uint4(pid, zb, alpha(dx0, dy1), ei), keep);
+            store_frag(frags + s11, make_uint4(pid, zb, alpha(dx1, dy1), ei), keep);
+        }
+    });
+}
+
+template <bool COLLECT, bool STRICT>
+__global__ __launch_bounds__(kWinThreads, kWinMinBlocks) void window_kernel(const __grid_constant__ Geom g, FwdBuffers fb, int B, int chunk)
 {
     __shared__ uint32_t s_cnt[kWinMax];
     __shared__ uint32_t s_base[COLLECT ? kWinMax : 1];
@@ -1147,13 +1196,18 @@ __global__ __launch_bounds__(kWinThreads, kWinMinBlocks) void window_kernel(cons
     const uint32_t* bfirst = fb.bin_cursor + (size_t)b * g.n_bins;
     uint32_t c0, c1;
     int bin;
-    while (next_chunk(fb, g, b, n_entry, s_tmp, COLLECT ? kWinChunkCollect : kWinChunkCount, c0, c1, bin))
+    while (next_chunk(fb, g, b, n_entry, s_tmp, chunk, c0, c1, bin))
     {
         for (; bin < g.n_bins && bfirst[bin] < c1; ++bin)
         {
             const uint32_t bin_end = (bin + 1 < g.n_bins) ? bfirst[bin + 1] : n_entry;
             const uint32_t lo = max(c0, bfirst[bin]), hi = min(c1, bin_end);
             if (lo >= hi) continue;  // uniform: all threads read the same values
+            if (bin_end - bfirst[bin] <= (uint32_t)kWinSparse)  // the whole bin is sparse (a short piece of a dense bin still pays off in the window)
+            {
+                sparse_bin_footprints<COLLECT, STRICT>(g, head, lo, hi, s_queue[threadIdx.x >> 5], pixel_ctr, frags, keep);
+                continue;
+            }
             const Window w = make_window(g, bin);
             const int n_win = win_off(g.L);
             for (int i = threadIdx.x; i < n_win; i += kWinThreads) s_cnt[i] = 0;
@@ -1224,14 +1278,18 @@ __global__ __launch_bounds__(kWinThreads, kWinMinBlocks) void window_kernel(cons
     }
 }
 
-cudaError_t launch_count(const ScenePtrs& sc, const Geom& g, int B, const FwdBuffers& fb, bool strict, int sm_count, cudaStream_t st)
+cudaError_t launch_count(const ScenePtrs& sc, const Geom& g, int B, const FwdBuffers& fb, bool strict, unsigned long long entries_hint, int sm_count,
+                         cudaStream_t st)
 {
     cudaError_t e = cudaMemsetAsync(fb.ticket, 0, sizeof(unsigned) * B, st);
     if (e != cudaSuccess) return e;
+    // entries_hint: the number of entries of the call as far as the host knows it (the previous call's, or this call's own count)
+    const bool few  = entries_hint / kWinChunkCount < (unsigned long long)kWinTicketsPerBlock * sm_count * kWinMinBlocks;
+    const int chunk = few ? kWinChunkCountFew : kWinChunkCount;
     if (strict)
-        window_kernel<false, true><<<sm_count * kWinBlocksPerSM, kWinThreads, 0, st>>>(g, fb, B);
+        window_kernel<false, true><<<sm_count * kWinBlocksPerSM, kWinThreads, 0, st>>>(g, fb, B, chunk);
     else
-        window_kernel<false, false><<<sm_count * kWinBlocksPerSM, kWinThreads, 0, st>>>(g, fb, B);
+        window_kernel<false, false><<<sm_count * kWinBlocksPerSM, kWinThreads, 0, st>>>(g, fb, B, chunk);
     return cudaGetLastError();
 }
 
@@ -1240,9 +1298,9 @@ cudaError_t launch_collect(const ScenePtrs& sc, const Geom& g, int B, const FwdB
     cudaError_t e = cudaMemsetAsync(fb.ticket, 0, sizeof(unsigned) * B, st);
     if (e != cudaSuccess) return e;
     if (strict)
-        window_kernel<true, true><<<sm_count * kWinBlocksPerSM, kWinThreads, 0, st>>>(g, fb, B);
+        window_kernel<true, true><<<sm_count * kWinBlocksPerSM, kWinThreads, 0, st>>>(g, fb, B, kWinChunkCollect);
     else
-        window_kernel<true, false><<<sm_count * kWinBlocksPerSM, kWinThreads, 0, st>>>(g, fb, B);
+        window_kernel<true, false><<<sm_count * kWinBlocksPerSM, kWinThreads, 0, st>>>(g, fb, B, kWinChunkCollect);
     return cudaGetLastError();
 }
 
