@@ -33,6 +33,7 @@ def test_status_strings_and_argument_errors_without_a_gpu(cuda_lib):
     assert cuda_lib.trips_context_create(None, 0) == _lib.ERR_INVALID_ARG
     assert cuda_lib.trips_forward(None, None, None, 0, None, None, None) == _lib.ERR_INVALID_ARG
     assert cuda_lib.trips_adam_step_static(None, 0, None) == _lib.ERR_INVALID_ARG
+    assert cuda_lib.trips_fused_reduce_adam_multicast(None, None, None, None, None, 0, 0, 0, None, None, None, None) == _lib.ERR_INVALID_ARG
     assert cuda_lib.trips_stage_name(1) == b"bin_points"
     import torch
     if not torch.cuda.is_available():
