@@ -43,7 +43,7 @@ def parse_args():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--render-only", action="store_true",
                     help="step = inference render (train = 0) of the rank's views, no backward, no Adam: the render-only batch of "
-                         "BASELINE config 5 is `--workload c5 --render-only --views-per-gpu 64/N`")
+                         "workload 5 (64 random views) is `--workload c5 --render-only --views-per-gpu 64/N`")
     ap.add_argument("--no-strong", action="store_true", help="N>1: skip the strong-scaling pass (8 views split over the ranks)")
     ap.add_argument("--cpu-views", type=int, default=12, help="views of the workload the CPU baseline renders")
     ap.add_argument("--op", default="step", choices=["step", "resize_points", "texture_prepare"],
@@ -500,7 +500,7 @@ def run_ours(args, rank, world, local_rank):
         e2e["host_link"] = {"h2d_gb_per_s_per_gpu": h2d / (ms_e_step * 1e6), "h2d_gb_per_s_all_gpus": world * h2d / (ms_e_step * 1e6),
                             "ms_over_device_step": ms_e_step - ms_step}
 
-    # ---- N > 1: the split BASELINE config 3 names (a global batch of 8 views, 8 / N per rank), strong scaling ----
+    # ---- N > 1: the same global batch of 8 views split over the ranks (8 / N per rank): strong scaling ----
     strong = None
     if world > 1 and not args.render_only and not args.no_strong and args.workload == "c3" and 8 % world == 0 and B >= 8 // world:
         sb = 8 // world
