@@ -173,8 +173,8 @@ def stage_bytes(stage, N, P, C, B, F, Kf, V=0):
 # call, from a quarter of the points with all 8 views (binning_adam_kernels_1.5Mpts_8views_ncu_sections.md).
 # Traffic grows in proportion to the unit count.  Units: F fragments, Kf kept fragments, NB points x views, V entries
 # (visible points over all views), N points.
-DRAM_BYTES_PER_UNIT = {"count": [(5.2, "F")], "collect": [(19.7, "F")], "sort_blend": [(35.5, "F")], "blend_backward": [(41.4, "Kf")],
-                       "bin_points": [(43.1, "NB")], "unpack_grads": [(23.5 + 126.4, "V"), (196.8, "N")], "adam": [(337.3, "N")]}
+DRAM_BYTES_PER_UNIT = {"count": [(5.2, "F")], "collect": [(20.2, "F")], "sort_blend": [(35.4, "F")], "blend_backward": [(41.6, "Kf")],
+                       "bin_points": [(43.1, "NB")], "unpack_grads": [(23.4 + 126.5, "V"), (196.9, "N")], "adam": [(337.3, "N")]}
 
 
 def stage_traffic(stage, N, B, F, Kf, V=0):
