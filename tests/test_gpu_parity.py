@@ -201,12 +201,17 @@ def test_forward_backward_parity(name, oracle_lib, cuda_lib):
             assert np.all(gintr[b, 5:] == 0)
 
 
-def test_forward_inference_matches_training_output(oracle_lib, cuda_lib):
-    """train = false renders the same pyramid and keeps no records (RenderForward.cu:865-880 vs 957-979)."""
+@pytest.mark.parametrize("flags", [{}, dict(render_points_in_all_lower_resolutions=False, combine_lists=True, saturated_alpha_accumulation=True),
+                                   dict(distortion=True, dist_cutoff=0.5)], ids=["first_pipeline", "second_pipeline", "lens_distortion"])
+def test_forward_inference_matches_training_output(oracle_lib, cuda_lib, flags):
+    """train = false renders the same pyramid and keeps no records (RenderForward.cu:865-880 vs 957-979); with 20 views the
+    inference call also runs through more than one sub-batch of views."""
     import torch
-    s = scenes.tiny(seed=31)
-    _, _, frames = oracle_frames(s, train=False)
-    ns, info, blend = gpu_render(s, train=False)
+    s = scenes.tiny(seed=31, n_views=20, n_points=3000)
+    if flags.get("distortion"):
+        s.intrinsics[:, 5:] = np.array([-0.1, 0.03, 0.0, 0.02, 0.0, 0.0, 1e-3, -2e-3], np.float32)
+    _, _, frames = oracle_frames(s, train=False, **flags)
+    ns, info, blend = gpu_render(s, train=False, **flags)
     with torch.no_grad():
         outs = blend(info)
     for b, f in enumerate(frames):
