@@ -25,6 +25,7 @@ def test_shim_registers_class_and_operator(shim):
     assert hasattr(torch.ops.trips_b200, "blend_point_cloud") and hasattr(torch.ops.trips_b200, "adam_step")
     info.set_texture_preparation(True, 10.0, True)
     info.set_pipeline_flags(True, False, True, False)
+    info.set_distortion(True, 20.0)
     assert torch.classes.trips_b200.PointRenderModule(4) is not None
     opt = torch.classes.trips_b200.MyAdam()
     with pytest.raises(RuntimeError):
