@@ -37,13 +37,17 @@ def test_shim_registers_class_and_operator(shim):
 # (use_layer_point_size, render_points_in_all_lower_resolutions, combine_lists, saturated_alpha_accumulation): the
 # reference's defaults, and a combination that selects its second forward pipeline
 @pytest.mark.gpu
-@pytest.mark.parametrize("flags", [(True, True, False, False), (True, False, True, True)], ids=["first_pipeline", "second_pipeline"])
+# the fifth entry: lens distortion
+@pytest.mark.parametrize("flags", [(True, True, False, False, False), (True, False, True, True, False), (True, True, False, False, True)],
+                         ids=["first_pipeline", "second_pipeline", "lens_distortion"])
 def test_shim_matches_python_mirror(shim, cuda_lib, flags):
     torch = shim
     from trips_b200 import scenes
     from trips_b200.modules import NeuralScene, images_for
     from trips_b200.renderer import BlendPointCloud, NeuralRenderInfo, PointRendererCache, RenderParams
     s = scenes.tiny(n_points=5000, seed=9, width=96, height=64, num_layers=4, n_views=2)
+    if flags[4]:
+        s.intrinsics[:, 5:] = np.array([-0.1, 0.04, 0.0, 0.02, 0.0, 0.0, 2e-3, -1e-3], np.float32)
     dev = torch.device("cuda")
 
     def leaves(ns):
@@ -54,7 +58,8 @@ def test_shim_matches_python_mirror(shim, cuda_lib, flags):
     # Python mirror
     ns = NeuralScene.from_synthetic(s, device=dev)
     params = RenderParams(num_texture_channels=s.channels, k_keep=s.k_keep, use_layer_point_size=flags[0],
-                          render_points_in_all_lower_resolutions=flags[1], combine_lists=flags[2], saturated_alpha_accumulation=flags[3])
+                          render_points_in_all_lower_resolutions=flags[1], combine_lists=flags[2], saturated_alpha_accumulation=flags[3],
+                          distortion=flags[4], dist_cutoff=0.6)
     info = NeuralRenderInfo(scene=ns, images=images_for(s, [0, 1]), params=params, num_layers=s.num_layers, train=True,
                             cache=PointRendererCache(dev))
     outs = BlendPointCloud(info)
@@ -75,7 +80,8 @@ def test_shim_matches_python_mirror(shim, cuda_lib, flags):
         cinfo.add_image(im.w, im.h, im.image_index, im.camera_index, im.camera_model_type, [float(x) for x in im.crop_transform],
                         [float(x) for x in im.crop_rotation])
     cinfo.set_params(s.num_layers, s.k_keep, True, False, 0.0, False, 0.0, False, 0.0)
-    cinfo.set_pipeline_flags(*flags)
+    cinfo.set_pipeline_flags(*flags[:4])
+    cinfo.set_distortion(flags[4], 0.6)
     couts = torch.ops.trips_b200.blend_point_cloud(cinfo)  # BlendPointCloud(NeuralRenderInfo*), RenderInfo.cpp:27
     assert cinfo.last_status() == 0
     assert len(couts) == len(ref_out)
